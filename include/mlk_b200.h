@@ -1,0 +1,167 @@
+/*
+ * C ABI of the B200 native-layout kernel library (libmlk_b200.so).
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, launches hand-written
+ * sm_100a kernels on that stream and returns a status code.  No entry point allocates device
+ * memory, synchronises the host or throws.  Each one replaces one operator of the reference
+ * extension module `muxi_layout_kernels_ext` (reference file:line given per function);
+ * "dim letters" follow the reference: m = weight rows (output features), n = tokens, k = reduction,
+ * C[n,m] = alpha * B[n,k] * A[m,k]^T (+ bias[m]).
+ *
+ * dtype codes: 0 = bf16, 1 = fp16, 2 = e4m3 weights with bf16 activations ("soft FP8").
+ */
+#ifndef MLK_B200_H_
+#define MLK_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* mlk_stream_t; /* == cudaStream_t */
+
+enum {
+    MLK_OK = 0,
+    MLK_ERR_INVALID_ARG = 1, /* a precondition the reference enforces with TORCH_CHECK is violated */
+    MLK_ERR_UNSUPPORTED = 2, /* valid request no kernel of this build implements */
+    MLK_ERR_CUDA = 3,        /* a CUDA runtime call failed */
+    MLK_ERR_IO = 4           /* dispatch table file could not be opened */
+};
+
+enum { MLK_BF16 = 0, MLK_FP16 = 1, MLK_E4M3 = 2 };
+
+/* Dispatch tables, one per packaged CSV file (reference: csrc/arg_selector.cu:80,157,232,303,375,454,531). */
+enum {
+    MLK_TABLE_GEMM_ABC = 0,           /* layout_gemm_dispatch_arg.csv            */
+    MLK_TABLE_GEMM_CONTINUOUS_C = 1,  /* continuous_gemm_dispatch_arg.csv        */
+    MLK_TABLE_GEMM_LAYOUT_A = 2,      /* layoutA_gemm_dispatch_arg.csv           */
+    MLK_TABLE_GEMM_LAYOUT_A_FP8 = 3,  /* layoutA_Soft_Fp8_gemm_dispatch_arg.csv  */
+    MLK_TABLE_GEMV_FP16 = 4,          /* layout_gemv_dispatch_arg.csv            */
+    MLK_TABLE_GEMV_BF16 = 5,          /* layout_gemv_bf16_dispatch_arg.csv       */
+    MLK_TABLE_GEMV_FP8 = 6            /* layout_gemv_soft_fp8_dispatch_arg.csv   */
+};
+
+/* ---- library ------------------------------------------------------------------------------- */
+
+const char* mlk_status_string(int status);
+/* Message of the last failing call on the calling thread ("" if none). */
+const char* mlk_last_error(void);
+/* Build identification: "sm_100a" plus the ABI version. */
+const char* mlk_build_info(void);
+
+/* ---- dispatch tables (reference: csrc/arg_selector.cu:14-87, class per table) ------------------ */
+
+/* Reads a CSV table (header line + integer rows).  A file that cannot be opened yields MLK_ERR_IO and
+ * leaves the table empty, i.e. every lookup falls back to the shape-based default. */
+int mlk_table_load(int table, const char* csv_path);
+/* Exact-key lookup; out4 = {kernelId,p1,p2,p3} for GEMM tables, {BLOCK_DIM_X,KernelId,p1,p2} for GeMV
+ * tables (n is ignored there).  *hit is 1 when the key was present, 0 when the default was returned. */
+int mlk_table_lookup(int table, int m, int n, int k, int out4[4], int* hit);
+const char* mlk_table_file_name(int table);
+
+/* ---- prepack ops ---------------------------------------------------------------------------- */
+
+/* W[m,k] row-major -> layout A [m/16][k/8][16][8] (inverse != 0: back).  elem_bytes 2 (bf16/fp16) or 1 (e4m3).
+ * The reference builds this layout with torch view/permute (benchmark_and_test/gemm_benchmark.py:41-42). */
+int mlk_layoutA(const void* in, void* out, int64_t m, int64_t k, int elem_bytes, int inverse, mlk_stream_t s);
+/* B[n,k] row-major 16-bit -> layout B [k/32][n/16][4][16][8].  Reference: layoutB, csrc/layout_b.cu:65-99. */
+int mlk_layoutB(const void* B, void* B_out, int n, int k, mlk_stream_t s);
+/* Layout C [m/32][n/16][4][16][8] 16-bit -> C[n,m] row-major.  Reference: reLayoutC, csrc/re_layout_c.cu:63-95. */
+int mlk_reLayoutC(const void* C_in, void* C_out, int m, int n, mlk_stream_t s);
+/* Bytes [b0,b1,b2,b3] of every 32-bit word -> [b0,b2,b1,b3]; its own inverse.
+ * Reference: fp8_weight_repack, csrc/fp8_weight_repack.cu:44-67. */
+int mlk_fp8_weight_repack(const void* weight, void* out, int64_t nbytes, mlk_stream_t s);
+
+/* ---- GeMV: y[1,m] = alpha * A x (+ bias) ------------------------------------------------------- */
+
+/* Explicit tuning arguments.  Reference: gemv_layoutA_wapper, csrc/gemv_layout_a.cu:17-71.
+ *   kernelId 1: tensor-core streaming kernel, kernelParam1 = row groups per warp (1,2), kernelParam2 = split-K (1,2,4,8)
+ *   kernelId 2: CUDA-core FMA + shuffle kernel, same two parameters (bf16/fp16 only)
+ *   scale_matrix: e4m3 only, fp32 [ceil(m/128)][ceil(k/128)], may be NULL (= all ones)
+ *   fp8_order: 0 natural bytes, 1 bytes as written by mlk_fp8_weight_repack
+ *   beta is accepted and ignored, as in the reference kernels. */
+int mlk_gemv_layoutA_wapper(const void* A, const void* x, void* y, int m, int k, int dtype, float alpha, float beta,
+                            int blockDimX, int kernelId, int kernelParam1, int kernelParam2,
+                            const float* scale_matrix, const void* bias, int fp8_order, mlk_stream_t s);
+/* Table-driven.  Reference: gemv_layoutA, csrc/gemv_layout_a.cu:73-150. */
+int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dtype, float alpha, float beta,
+                     const float* scale_matrix, const void* bias, int fp8_order, mlk_stream_t s);
+
+/* ---- narrow GEMM: C[n,m] = alpha * B A^T (+ bias), n <= 256 ------------------------------------------- */
+
+/* kernelId 1: kernelParam1 = row groups per warp (1,2), kernelParam2 = row warps per CTA (1,2,4,8),
+ * kernelParam3 = split-K over a thread-block cluster (1,2,4,8). */
+
+/* A layout A, B row-major [n,k], C row-major [n,m].  Reference: gemm_layoutA_wapper, csrc/gemm_layout_A.cu:684-750. */
+int mlk_gemm_layoutA_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha,
+                            float beta, int kernelParam1, int kernelParam2, int kernelParam3, int kernelId,
+                            const void* bias, mlk_stream_t s);
+/* Reference: gemm_layoutA, csrc/gemm_layout_A.cu:752-787. */
+int mlk_gemm_layoutA(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha, float beta,
+                     const void* bias, mlk_stream_t s);
+/* e4m3 A with fp32 128x128 block scales (NULL = ones), bf16 B and C.
+ * Reference: gemm_layoutA_soft_fp8_wapper, csrc/gemm_layout_A_soft_fp8.cu:749. */
+int mlk_gemm_layoutA_soft_fp8_wapper(const void* A, const float* A_scale, const void* B, void* C, int m, int n, int k,
+                                     float alpha, float beta, int kernelParam1, int kernelParam2, int kernelParam3,
+                                     int kernelId, const void* bias, int fp8_order, mlk_stream_t s);
+/* Reference: gemm_layoutA_soft_fp8, csrc/gemm_layout_A_soft_fp8.cu:825. */
+int mlk_gemm_layoutA_soft_fp8(const void* A, const float* A_scale, const void* B, void* C, int m, int n, int k,
+                              float alpha, float beta, const void* bias, int fp8_order, mlk_stream_t s);
+/* A layout A, B layout B, C row-major.  Reference: gemm_layoutAB_ContinuousC_wapper,
+ * csrc/gemm_layout_ab_continuous_c.cu:982; table-driven form :1051. */
+int mlk_gemm_layoutAB_ContinuousC_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype,
+                                         float alpha, float beta, int kernelParam1, int kernelParam2,
+                                         int kernelParam3, int kernelId, const void* bias, mlk_stream_t s);
+int mlk_gemm_layoutAB_ContinuousC(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha,
+                                  float beta, const void* bias, mlk_stream_t s);
+/* A layout A, B layout B, C layout C.  Reference: gemm_layoutABC_wapper, csrc/gemm_layout_abc.cu:685;
+ * table-driven form :754. */
+int mlk_gemm_layoutABC_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha,
+                              float beta, int kernelParam1, int kernelParam2, int kernelParam3, int kernelId,
+                              const void* bias, mlk_stream_t s);
+int mlk_gemm_layoutABC(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha, float beta,
+                       const void* bias, mlk_stream_t s);
+
+/* ---- fused MoE ("plan C") ------------------------------------------------------------------------ */
+
+/* Router: softmax (score_fun 0) or sigmoid (1) of gating_output[T,E] (bf16/fp16, dtype code 0/1), optional
+ * per-expert selection bias, group-limited top-k with "lower id wins" ties; writes experts_ids int32 [T,topK]
+ * and the un-biased scores selected_experts_weights [T,topK] (same dtype as the logits).
+ * Any E <= 256 divisible by n_groups, any topK_groups <= n_groups, topK <= 32.
+ * Reference: fused_routing_gate, csrc/moe_kernels/fused_gating.cu:5-67 (kernels fused_topK.h:24,332). */
+int mlk_fused_routing_gate(const void* gating_output, int score_fun, int batch_size, int num_experts, int n_groups,
+                           int topK_groups, int32_t* experts_ids, void* selected_experts_weights, int topK,
+                           const void* load_balance_bias, int dtype, mlk_stream_t s);
+
+/* Token alignment: groups the flat slots i = token*topK + j by (mapped) expert, pads every expert's run to a
+ * multiple of microBatchSize with the caller's sentinel, and records one expert id per block.
+ *   sorted_token_ids  [T*topK + E*(mbs-1)]  pre-filled by the caller with T*topK
+ *   cumsum_buffer     [E+1]   on return: [e] = start_e + count_e for e < E, [E] = padded total
+ *   padded_num_experts[1]     number of blocks
+ *   experts_ids_out   [ceil(len/mbs)] expert of each block
+ *   experts_map       [experts_map_len] global -> local expert id or -1, may be NULL; an id outside the map
+ *                     is skipped like a -1 entry
+ * Reference: batched_routed_activation_indexed_to_expert_block_indexed, csrc/moe_kernels/fused_experts_compute.cu:6-48. */
+int mlk_moe_align(int batchSize, int expertCount, int topK, int microBatchSize, const int32_t* topk_ids,
+                  int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
+                  int32_t* experts_ids_out, const int32_t* experts_map, int experts_map_len, mlk_stream_t s);
+
+/* Expert compute: alignment, gather-GEMM1 with fused SiLU*up, GEMM2 with fused routing-weight scale and
+ * scatter-add into y.  w1 [E,2I,H] (gate rows then up rows) and w2 [E,H,I], each expert in layout A;
+ * x [T,H]; topk_ids/topk_weights [T,topK]; C is caller workspace of T*topK*2I elements; y [T,H] must be zero.
+ * dtype 0/1: 16-bit weights; dtype 2: e4m3 weights with optional fp32 block scales w1_scale [E,2I/128,H/128],
+ * w2_scale [E,H/128,I/128] (NULL = ones).
+ * Reference: fused_experts_compute (both overloads), csrc/moe_kernels/fused_experts_compute.cu:50-188,190-296. */
+int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int batch_size, int expert_count,
+                              int topK, int hidden, int inter, const int32_t* topk_ids, const void* topk_weights,
+                              int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
+                              int32_t* experts_ids, void* C, void* y, const float* w1_scale, const float* w2_scale,
+                              int dtype, int fp8_order, int microBatchSize, const int32_t* experts_map,
+                              int experts_map_len, int tune_rg, int tune_sk1, int tune_sk2, mlk_stream_t s);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MLK_B200_H_ */

@@ -1,0 +1,253 @@
+// extern "C" entry points declared in include/mlk_b200.h: argument checks, table lookup, dispatch.
+#include "../../include/mlk_b200.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "dense.cuh"
+#include "moe.cuh"
+#include "selector.h"
+#include "status.h"
+
+namespace mlk {
+
+namespace {
+thread_local char g_err[512] = {0};
+}
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+const char* last_error() { return g_err; }
+void clear_error() { g_err[0] = 0; }
+
+int launch_layout_a(const void*, void*, long long, long long, int, int, cudaStream_t);
+int launch_layout_b(const void*, void*, int, int, cudaStream_t);
+int launch_relayout_c(const void*, void*, int, int, cudaStream_t);
+int launch_fp8_repack(const void*, void*, long long, cudaStream_t);
+
+namespace {
+
+int wt_of(int dtype) {
+    switch (dtype) {
+        case MLK_BF16: return kBF16;
+        case MLK_FP16: return kFP16;
+        case MLK_E4M3: return kE4M3;
+    }
+    return -1;
+}
+
+// The reference's GEMM entry points require m % 128 == 0 and k % 128 == 0 (csrc/gemm_layout_A.cu:774-776).
+int check_gemm_shape(int m, int n, int k) {
+    if (m <= 0 || n <= 0 || k <= 0) return fail(kInvalidArg, "gemm: m, n, k must be positive");
+    if (m % 128 != 0) return fail(kInvalidArg, "m must be a multiple of 128 (m=%d)", m);
+    if (k % 128 != 0) return fail(kInvalidArg, "k must be a multiple of 128 (k=%d)", k);
+    return kOk;
+}
+
+int gemm_common(int variant_x, int variant_c, const void* A, const float* scale, const void* B, void* C, int m, int n,
+                int k, int dtype, float alpha, int p1, int p2, int p3, int kernelId, const void* bias, int fp8_order,
+                cudaStream_t s) {
+    clear_error();
+    const int wt = wt_of(dtype);
+    if (wt < 0) return fail(kInvalidArg, "Unsupported data type code %d", dtype);
+    if (int st = check_gemm_shape(m, n, k)) return st;
+    if (kernelId != 1)
+        return fail(kUnsupported, "gemm: kernelId %d is not built (1 = tensor-core streaming kernel)", kernelId);
+    DenseParams p{};
+    p.A = A; p.X = B; p.C = C; p.bias = bias; p.scale = scale;
+    p.m = m; p.n = n; p.k = k; p.alpha = alpha;
+    p.x_layout = variant_x; p.c_layout = variant_c; p.fp8_order = fp8_order;
+    p.rg = p1; p.wm = p2; p.sk = p3; p.threads = 256;
+    return launch_dense_mma(wt, p, s);
+}
+
+int gemm_table(int table, int variant_x, int variant_c, const void* A, const float* scale, const void* B, void* C,
+               int m, int n, int k, int dtype, float alpha, const void* bias, int fp8_order, cudaStream_t s) {
+    clear_error();
+    if (int st = check_gemm_shape(m, n, k)) return st;
+    TuneArgs t = global_table(table).get(m, n, k, nullptr);
+    // A table row that this shape cannot run with (e.g. copied from another GPU's table) falls back to the default.
+    const bool ok = t.a == 1 && (t.b == 1 || t.b == 2) && (t.c == 1 || t.c == 2 || t.c == 4 || t.c == 8) &&
+                    (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b * t.c) == 0;
+    if (!ok) t = default_args(table, m, n, k);
+    return gemm_common(variant_x, variant_c, A, scale, B, C, m, n, k, dtype, alpha, t.b, t.c, t.d, t.a, bias,
+                       fp8_order, s);
+}
+
+}  // namespace
+}  // namespace mlk
+
+using namespace mlk;
+
+extern "C" {
+
+const char* mlk_status_string(int status) {
+    switch (status) {
+        case MLK_OK: return "ok";
+        case MLK_ERR_INVALID_ARG: return "invalid argument";
+        case MLK_ERR_UNSUPPORTED: return "unsupported";
+        case MLK_ERR_CUDA: return "CUDA error";
+        case MLK_ERR_IO: return "I/O error";
+    }
+    return "unknown status";
+}
+
+const char* mlk_last_error(void) { return last_error(); }
+
+const char* mlk_build_info(void) { return "mlk_b200 abi 1, sm_100a"; }
+
+int mlk_table_load(int table, const char* csv_path) {
+    clear_error();
+    if (table < 0 || table >= kNumTables) return fail(kInvalidArg, "table id %d out of range", table);
+    if (!csv_path) return fail(kInvalidArg, "null path");
+    if (global_table(table).load(csv_path) != 0) return fail(kIoError, "cannot open %s", csv_path);
+    return kOk;
+}
+
+int mlk_table_lookup(int table, int m, int n, int k, int out4[4], int* hit) {
+    clear_error();
+    if (table < 0 || table >= kNumTables) return fail(kInvalidArg, "table id %d out of range", table);
+    if (!out4) return fail(kInvalidArg, "null output");
+    bool h = false;
+    const TuneArgs t = global_table(table).get(m, n, k, &h);
+    out4[0] = t.a; out4[1] = t.b; out4[2] = t.c; out4[3] = t.d;
+    if (hit) *hit = h ? 1 : 0;
+    return kOk;
+}
+
+const char* mlk_table_file_name(int table) { return table_file_name(table); }
+
+int mlk_layoutA(const void* in, void* out, int64_t m, int64_t k, int elem_bytes, int inverse, mlk_stream_t s) {
+    clear_error();
+    return launch_layout_a(in, out, m, k, elem_bytes, inverse, (cudaStream_t)s);
+}
+int mlk_layoutB(const void* B, void* B_out, int n, int k, mlk_stream_t s) {
+    clear_error();
+    return launch_layout_b(B, B_out, n, k, (cudaStream_t)s);
+}
+int mlk_reLayoutC(const void* C_in, void* C_out, int m, int n, mlk_stream_t s) {
+    clear_error();
+    return launch_relayout_c(C_in, C_out, m, n, (cudaStream_t)s);
+}
+int mlk_fp8_weight_repack(const void* weight, void* out, int64_t nbytes, mlk_stream_t s) {
+    clear_error();
+    return launch_fp8_repack(weight, out, nbytes, (cudaStream_t)s);
+}
+
+int mlk_gemv_layoutA_wapper(const void* A, const void* x, void* y, int m, int k, int dtype, float alpha, float,
+                            int blockDimX, int kernelId, int kernelParam1, int kernelParam2,
+                            const float* scale_matrix, const void* bias, int fp8_order, mlk_stream_t s) {
+    clear_error();
+    const int wt = wt_of(dtype);
+    if (wt < 0) return fail(kInvalidArg, "Unsupported data type code %d", dtype);
+    if (m <= 0 || k <= 0) return fail(kInvalidArg, "gemv: m and k must be positive");
+    if (m % 16 != 0) return fail(kInvalidArg, "GEMV m %% 16(at least) must be 0");
+    if (k % 32 != 0) return fail(kInvalidArg, "GEMV k %% 32(at least) must be 0");
+    DenseParams p{};
+    p.A = A; p.X = x; p.C = y; p.bias = bias; p.scale = scale_matrix;
+    p.m = m; p.n = 1; p.k = k; p.alpha = alpha;
+    p.x_layout = 0; p.c_layout = 0; p.fp8_order = fp8_order;
+    p.rg = kernelParam1; p.wm = 1; p.sk = kernelParam2; p.threads = blockDimX;
+    if (kernelId == 1) return launch_dense_mma(wt, p, (cudaStream_t)s);
+    if (kernelId == 2) return launch_gemv_simt(wt, p, 0, (cudaStream_t)s);
+    return fail(kUnsupported, "gemv: kernelId %d is not built (1 = tensor-core, 2 = CUDA-core)", kernelId);
+}
+
+int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dtype, float alpha, float beta,
+                     const float* scale_matrix, const void* bias, int fp8_order, mlk_stream_t s) {
+    clear_error();
+    if (m <= 0 || k <= 0) return fail(kInvalidArg, "gemv: m and k must be positive");
+    if (m % 16 != 0) return fail(kInvalidArg, "GEMV m %% 16(at least) must be 0");
+    if (k % 32 != 0) return fail(kInvalidArg, "GEMV k %% 32(at least) must be 0");
+    const int table = dtype == MLK_E4M3 ? kTableGemvSoftFp8 : (dtype == MLK_FP16 ? kTableGemvFp16 : kTableGemvBf16);
+    TuneArgs t = global_table(table).get(m, 1, k, nullptr);
+    // Same safety net as the reference (csrc/gemv_layout_a.cu:132-143): a row that cannot run falls back.
+    const bool ok = (t.a == 64 || t.a == 128 || t.a == 256) && (t.b == 1 || (t.b == 2 && dtype != MLK_E4M3)) &&
+                    (t.c == 1 || t.c == 2) && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.c) == 0;
+    if (!ok) t = default_args(table, m, 1, k);
+    return mlk_gemv_layoutA_wapper(A, x, y, m, k, dtype, alpha, beta, t.a, t.b, t.c, t.d, scale_matrix, bias,
+                                   fp8_order, s);
+}
+
+int mlk_gemm_layoutA_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha, float,
+                            int p1, int p2, int p3, int kernelId, const void* bias, mlk_stream_t s) {
+    if (dtype == MLK_E4M3) { clear_error(); return fail(kInvalidArg, "gemm_layoutA: use the soft_fp8 entry point for e4m3 weights"); }
+    return gemm_common(0, 0, A, nullptr, B, C, m, n, k, dtype, alpha, p1, p2, p3, kernelId, bias, 0, (cudaStream_t)s);
+}
+int mlk_gemm_layoutA(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha, float,
+                     const void* bias, mlk_stream_t s) {
+    if (dtype == MLK_E4M3) { clear_error(); return fail(kInvalidArg, "gemm_layoutA: use the soft_fp8 entry point for e4m3 weights"); }
+    return gemm_table(kTableGemmLayoutA, 0, 0, A, nullptr, B, C, m, n, k, dtype, alpha, bias, 0, (cudaStream_t)s);
+}
+int mlk_gemm_layoutA_soft_fp8_wapper(const void* A, const float* A_scale, const void* B, void* C, int m, int n, int k,
+                                     float alpha, float, int p1, int p2, int p3, int kernelId, const void* bias,
+                                     int fp8_order, mlk_stream_t s) {
+    return gemm_common(0, 0, A, A_scale, B, C, m, n, k, MLK_E4M3, alpha, p1, p2, p3, kernelId, bias, fp8_order,
+                       (cudaStream_t)s);
+}
+int mlk_gemm_layoutA_soft_fp8(const void* A, const float* A_scale, const void* B, void* C, int m, int n, int k,
+                              float alpha, float, const void* bias, int fp8_order, mlk_stream_t s) {
+    return gemm_table(kTableGemmLayoutASoftFp8, 0, 0, A, A_scale, B, C, m, n, k, MLK_E4M3, alpha, bias, fp8_order,
+                      (cudaStream_t)s);
+}
+int mlk_gemm_layoutAB_ContinuousC_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype,
+                                         float alpha, float, int p1, int p2, int p3, int kernelId, const void* bias,
+                                         mlk_stream_t s) {
+    if (dtype == MLK_E4M3) { clear_error(); return fail(kInvalidArg, "gemm_layoutAB_ContinuousC: 16-bit weights only"); }
+    return gemm_common(1, 0, A, nullptr, B, C, m, n, k, dtype, alpha, p1, p2, p3, kernelId, bias, 0, (cudaStream_t)s);
+}
+int mlk_gemm_layoutAB_ContinuousC(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha,
+                                  float, const void* bias, mlk_stream_t s) {
+    if (dtype == MLK_E4M3) { clear_error(); return fail(kInvalidArg, "gemm_layoutAB_ContinuousC: 16-bit weights only"); }
+    return gemm_table(kTableGemmContinuousC, 1, 0, A, nullptr, B, C, m, n, k, dtype, alpha, bias, 0, (cudaStream_t)s);
+}
+int mlk_gemm_layoutABC_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha,
+                              float, int p1, int p2, int p3, int kernelId, const void* bias, mlk_stream_t s) {
+    if (dtype == MLK_E4M3) { clear_error(); return fail(kInvalidArg, "gemm_layoutABC: 16-bit weights only"); }
+    return gemm_common(1, 1, A, nullptr, B, C, m, n, k, dtype, alpha, p1, p2, p3, kernelId, bias, 0, (cudaStream_t)s);
+}
+int mlk_gemm_layoutABC(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha, float,
+                       const void* bias, mlk_stream_t s) {
+    if (dtype == MLK_E4M3) { clear_error(); return fail(kInvalidArg, "gemm_layoutABC: 16-bit weights only"); }
+    return gemm_table(kTableGemmABC, 1, 1, A, nullptr, B, C, m, n, k, dtype, alpha, bias, 0, (cudaStream_t)s);
+}
+
+int mlk_fused_routing_gate(const void* gating_output, int score_fun, int batch_size, int num_experts, int n_groups,
+                           int topK_groups, int32_t* experts_ids, void* selected_experts_weights, int topK,
+                           const void* load_balance_bias, int dtype, mlk_stream_t s) {
+    clear_error();
+    return launch_router(gating_output, score_fun, batch_size, num_experts, n_groups, topK_groups, experts_ids,
+                         selected_experts_weights, topK, load_balance_bias, dtype, (cudaStream_t)s);
+}
+
+int mlk_moe_align(int batchSize, int expertCount, int topK, int microBatchSize, const int32_t* topk_ids,
+                  int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
+                  int32_t* experts_ids_out, const int32_t* experts_map, int experts_map_len, mlk_stream_t s) {
+    clear_error();
+    return launch_moe_align(batchSize, expertCount, topK, microBatchSize, topk_ids, sorted_token_ids, cumsum_buffer,
+                            padded_num_experts, experts_ids_out, experts_map, experts_map_len, (cudaStream_t)s);
+}
+
+int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int batch_size, int expert_count,
+                              int topK, int hidden, int inter, const int32_t* topk_ids, const void* topk_weights,
+                              int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
+                              int32_t* experts_ids, void* C, void* y, const float* w1_scale, const float* w2_scale,
+                              int dtype, int fp8_order, int microBatchSize, const int32_t* experts_map,
+                              int experts_map_len, int tune_rg, int tune_sk1, int tune_sk2, mlk_stream_t s) {
+    clear_error();
+    MoeParams p{};
+    p.w1 = w1; p.w2 = w2; p.x = x; p.T = batch_size; p.E = expert_count; p.topk = topK; p.H = hidden; p.I = inter;
+    p.topk_ids = topk_ids; p.topk_weights = topk_weights; p.sorted_token_ids = sorted_token_ids;
+    p.cumsum = cumsum_buffer; p.padded_num_experts = padded_num_experts; p.experts_ids = experts_ids;
+    p.C = C; p.y = y; p.w1_scale = w1_scale; p.w2_scale = w2_scale; p.dtype = dtype; p.fp8_order = fp8_order;
+    p.mbs = microBatchSize; p.experts_map = experts_map; p.experts_map_len = experts_map_len; p.rg = tune_rg; p.sk1 = tune_sk1; p.sk2 = tune_sk2;
+    return launch_fused_experts(p, (cudaStream_t)s);
+}
+
+}  // extern "C"

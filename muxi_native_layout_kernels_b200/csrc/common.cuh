@@ -1,0 +1,156 @@
+// Device-side building blocks shared by every kernel of the library (sm_100a only).
+//
+// Conventions used throughout:
+//   * "layout A" is the prepacked weight order [m/16][k/8][16 rows][8 elems]; a 16-row group's
+//     whole K extent is one contiguous run (reference: benchmark_and_test/gemm_benchmark.py:41-42).
+//   * Warp-level tensor-core tiles are mma.sync m16n8k16 with fp32 accumulators.  Lane l is
+//     (g = l >> 2, t = l & 3).  Weights are the 16-row operand, tokens the 8-column operand.
+//   * The contraction index inside one 32-element K chunk is permuted identically for both
+//     operands (lane t owns k-octet 4c+t), so one 16-byte load per lane feeds two MMAs and
+//     neither operand needs a shuffle.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "status.h"
+
+namespace mlk {
+
+
+// ---------------------------------------------------------------------------------------------
+// Global / shared memory access
+// ---------------------------------------------------------------------------------------------
+
+// 16-byte streaming load of weight bytes: read-only path, not kept in L1 (each weight byte is
+// used exactly once per launch).
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+    uint4 r;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "r"(addr));
+    return r;
+}
+
+// 16-byte asynchronous global->shared copy.  src_bytes == 0 writes zeros (used for K tails).
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src),
+                 "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-core tile: D(16x8,f32) += A(16x16) * B(16x8)
+// ---------------------------------------------------------------------------------------------
+template <int WT>
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    if constexpr (WT == kFP16) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+            "{%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+            "{%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Soft-FP8: two e4m3 bytes -> one packed bf16x2 register, exact.
+//
+// The reference decodes by placing the 7 exponent/mantissa bits at bits 26..20 of an fp32
+// pattern and multiplying by 2^120 (csrc/utils.cuh:232-251).  The same idea in packed 16-bit
+// form: put s at bit 15 and eeeemmm at bits 10..4 of each half (a bf16 whose exponent field is
+// 0000eeee), then one packed multiply by 2^120 re-biases the exponent (7 -> 127) and normalises
+// e4m3 subnormals.  The result is the exact bf16 value of the e4m3 number.
+//
+// `sel` picks which two bytes of the 32-bit word go to the (low, high) half; that is the only
+// place where the byte order produced by fp8_weight_repack differs from natural order.
+// ---------------------------------------------------------------------------------------------
+constexpr uint32_t kSelNat01 = 0x4140;  // natural order: bytes 0,1
+constexpr uint32_t kSelNat23 = 0x4342;  // natural order: bytes 2,3
+constexpr uint32_t kSelRep01 = 0x4240;  // "1324" repacked word [b0,b2,b1,b3]: elements 0,1
+constexpr uint32_t kSelRep23 = 0x4341;  // repacked: elements 2,3
+
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t w, uint32_t sel) {
+    uint32_t v = __byte_perm(w, 0u, sel);        // [b_lo, 0, b_hi, 0]
+    uint32_t x = (v << 4) + 0x78007800u;         // carries the sign from bit 11 up to bit 15
+    x &= 0x87F087F0u;                            // s0000eeeemmm0000 per half
+    uint32_t r;
+    asm("mul.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(0x7B807B80u));  // * 2^120, exact
+    return r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// 16-bit <-> fp32 helpers
+// ---------------------------------------------------------------------------------------------
+template <int WT>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    if constexpr (WT == kFP16) {
+        __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&h);
+    } else {
+        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+}
+
+template <int WT>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+    if constexpr (WT == kFP16) {
+        return __half22float2(*reinterpret_cast<__half2*>(&w));
+    } else {
+        // bf16 -> fp32 is a 16-bit shift
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+    }
+}
+
+template <int WT>
+__device__ __forceinline__ float load_scalar16(const void* base, int64_t idx) {
+    if constexpr (WT == kFP16) {
+        return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+    } else {
+        return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+    }
+}
+
+template <int WT>
+__device__ __forceinline__ float round16(float v) {
+    if constexpr (WT == kFP16) {
+        return __half2float(__float2half_rn(v));
+    } else {
+        return __bfloat162float(__float2bfloat16_rn(v));
+    }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+
+}  // namespace mlk

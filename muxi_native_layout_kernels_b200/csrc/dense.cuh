@@ -1,0 +1,31 @@
+// Host-visible description of one dense launch (GeMV and the three narrow-GEMM variants).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mlk {
+
+struct DenseParams {
+    const void* A;        // weights, layout A [m/16][k/8][16][8]
+    const void* X;        // activations: row-major [n,k] or layout B [k/32][n/16][4][16][8]
+    void* C;              // output: row-major [n,m] or layout C [m/32][n/16][4][16][8]
+    const void* bias;     // [m] in the activation dtype, or null
+    const float* scale;   // e4m3 only: [ceil(m/128)][ceil(k/128)] fp32 block scales, or null
+    int m, n, k;
+    float alpha;
+    int x_layout;         // 0 row-major, 1 layout B
+    int c_layout;         // 0 row-major, 1 layout C
+    int fp8_order;        // 0 natural byte order, 1 order written by fp8_weight_repack
+    // tuning
+    int rg;               // row groups per warp (1 or 2)          -- "APerWarp"
+    int wm;               // row warps per CTA (1,2,4,8)
+    int sk;               // cluster split-K (1,2,4,8)
+    int threads;          // CTA size (64,128,256)
+};
+
+// wt: kBF16 / kFP16 / kE4M3.  Returns an mlk status code.
+int launch_dense_mma(int wt, const DenseParams& p, cudaStream_t stream);
+int launch_gemv_simt(int wt, const DenseParams& p, int rows_per_warp_log2, cudaStream_t stream);
+
+}  // namespace mlk

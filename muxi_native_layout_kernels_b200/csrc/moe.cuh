@@ -1,0 +1,48 @@
+// Host-side launch interface of the fused-MoE kernels (router, token alignment, expert compute).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mlk {
+
+int launch_router(const void* gating_output, int score_fun, int T, int E, int n_groups, int topk_groups,
+                  int32_t* experts_ids, void* weights, int topk, const void* bias, int dtype, cudaStream_t s);
+
+// worklist == nullptr: alignment only (the stand-alone reference op).  Otherwise the kernel also writes
+// the expert-compute work list (see MoeWorkHeader) for blocks of `block_slots` slots.
+int launch_moe_align(int T, int E, int topk, int mbs, const int32_t* topk_ids, int32_t* sorted_token_ids,
+                     int32_t* cumsum, int32_t* padded_num_experts, int32_t* experts_ids_out,
+                     const int32_t* experts_map, int experts_map_len, cudaStream_t s, void* worklist = nullptr,
+                     int block_slots = 0);
+
+// Work list written by the alignment kernel into the spare half of the caller's workspace C:
+//   int32 header[4] = {n_items, 0, 0, 0}; then n_items x int4 {expert, first position in sorted_token_ids, slots, 0}
+struct MoeWorkHeader {
+    int n_items, pad0, pad1, pad2;
+};
+
+struct MoeParams {
+    const void* w1;   // [E, 2I, H] layout A per expert (gate rows, then up rows)
+    const void* w2;   // [E, H, I]  layout A per expert
+    const void* x;    // [T, H]
+    int T, E, topk, H, I;
+    const int32_t* topk_ids;      // [T, topk]
+    const void* topk_weights;     // [T, topk] activation dtype
+    int32_t* sorted_token_ids;    // [T*topk + E*(mbs-1)], pre-filled with T*topk
+    int32_t* cumsum;              // [E+1]
+    int32_t* padded_num_experts;  // [1]
+    int32_t* experts_ids;         // [ceil(len/mbs)]
+    void* C;                      // workspace, T*topk*2I activation elements
+    void* y;                      // [T, H], zero on entry
+    const float* w1_scale;        // e4m3: [E, 2I/128, H/128] or null
+    const float* w2_scale;        // e4m3: [E, H/128, I/128] or null
+    int dtype, fp8_order, mbs;
+    const int32_t* experts_map;
+    int experts_map_len;
+    int rg, sk1, sk2;             // tuning (0 = choose by shape)
+};
+
+int launch_fused_experts(const MoeParams& p, cudaStream_t s);
+
+}  // namespace mlk

@@ -1,0 +1,328 @@
+// Fused-MoE expert compute ("plan C"): alignment -> gather-GEMM1 with fused SiLU*up -> GEMM2 with fused
+// routing-weight scale, un-permute and accumulation into y.  Three launches, no host synchronisation.
+//
+// Replaces fused_experts_compute and its helpers (csrc/moe_kernels/fused_experts_compute.cu:50-296,
+// fused_experts_compute.h:50-163; kernels group_gemm_first.h:355, silu_and_mul.h:62, group_gemm_second.h:356
+// and their soft-fp8 twins).  Differences by design:
+//   * a work item is (expert, up to 64 of its slots), not a fixed 16-slot block, so for T <= 64 every
+//     selected expert's weights are streamed exactly once per layer call;
+//   * gate and up rows of W1 are paired inside one warp, so SiLU(gate)*up is applied to the fp32 sums and
+//     only the [slots, I] activation (not [slots, 2I]) goes through memory -- one launch and two 16-bit
+//     roundings fewer than the reference;
+//   * split-K partial sums are reduced in fp32 through (distributed) shared memory instead of 16-bit atomics.
+//   The only atomics left are the per-token accumulation of the top-k expert outputs into y, as in the
+//   reference (group_gemm_second.h:333-346).
+#include <algorithm>
+
+#include "moe.cuh"
+#include "status.h"
+#include "stream_core.cuh"
+
+namespace mlk {
+
+namespace {
+
+constexpr int kSmemLimit = 200 * 1024;
+
+struct MoeGemmParams {
+    const uint8_t* w;            // expert weights, layout A per expert
+    long long w_expert_bytes;
+    const float* scale;          // e4m3 block scales or null
+    long long scale_expert;      // floats per expert
+    const uint8_t* xsrc;         // GEMM1: x [T,H];  GEMM2: act [slots, I]
+    int x_row_div;               // GEMM1: topk (token = slot / topk);  GEMM2: 1
+    long long x_row_bytes;
+    void* out;                   // GEMM1: act [slots, I];  GEMM2: y [T,H]
+    const int32_t* sorted;
+    const int4* worklist;
+    const void* topk_weights;
+    int topk;
+    int rows;                    // weight rows handled per expert: GEMM1: I (gate rows; up rows are +I); GEMM2: H
+    int k;
+    int wm, stages, fp8_order;
+};
+
+// MODE 1: RG == 2, row group 0 = gate rows, row group 1 = the matching up rows.
+// MODE 2: plain rows, epilogue scales by the routing weight and accumulates into y.
+template <int WT, int NT, int RG, bool SCALE, int MODE>
+__global__ void __launch_bounds__(256) moe_gemm_kernel(const MoeGemmParams p) {
+    using S = CoreShape<NT, RG>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ CoreShared sh;
+    __shared__ int slot_of[kTokBlock];
+
+    const int n_items = p.worklist[0].x;
+    if ((int)blockIdx.z >= n_items) return;   // uniform over the cluster (clusters span y only)
+    const int4 item = p.worklist[1 + blockIdx.z];
+    const int expert = item.x, pos0 = item.y, nt = item.z;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int warps = blockDim.x >> 5;
+    const int WM = p.wm, WK = warps / WM;
+    const int wm = warp % WM, wk = warp / WM;
+    const int SK = gridDim.y, cr = blockIdx.y;
+    const int total_chunks = p.k >> 5;
+    constexpr int gran = SCALE ? 4 : 1;
+    const int parts = SK * WK;
+
+    if (tid < WK) k_partition(total_chunks, gran, parts, cr * WK + tid, sh.c0[tid], sh.c1[tid]);
+    if (tid < nt) {
+        const int slot = p.sorted[pos0 + tid];
+        slot_of[tid] = slot;
+        sh.xrow[tid] = (unsigned long long)p.xsrc + (unsigned long long)(slot / p.x_row_div) * p.x_row_bytes;
+    }
+    __syncthreads();
+
+    CoreArgs a;
+    const int c0 = sh.c0[wk];
+    a.nchunks = sh.c1[wk] - c0;
+    a.steps = (max_part_chunks(total_chunks, gran, parts) + S::CH - 1) / S::CH;
+    a.nt = nt;
+    a.wk = wk;
+    a.WK = WK;
+    a.stages = p.stages;
+    a.xs_base = smem_u32(smem);
+    a.xrows = nt;
+    a.stage_bytes = WK * nt * S::PITCH;
+    a.cstride = 64;
+    a.qstride = 16;
+    a.sel01 = p.fp8_order ? kSelRep01 : kSelNat01;
+    a.sel23 = p.fp8_order ? kSelRep23 : kSelNat23;
+    constexpr int esz = (WT == kE4M3) ? 1 : 2;
+    const int ldscale = (p.k + 127) >> 7;
+    const uint8_t* wbase = p.w + (long long)expert * p.w_expert_bytes;
+    const float* sbase = SCALE ? p.scale + (long long)expert * p.scale_expert : nullptr;
+    // CTA tile: MODE 1 -> WM gate groups + the WM matching up groups; MODE 2 -> RG*WM groups
+    const int tile_groups = (MODE == 1) ? WM : RG * WM;
+#pragma unroll
+    for (int r = 0; r < RG; ++r) {
+        int rgidx;
+        if (MODE == 1)
+            rgidx = blockIdx.x * WM + wm + r * (p.rows >> 4);
+        else
+            rgidx = blockIdx.x * tile_groups + wm * RG + r;
+        a.a_lane[r] = wbase + (size_t)rgidx * 16 * p.k * esz + (size_t)c0 * chunk_bytes<WT>() + t * (128 * esz) + g * 16;
+        a.scale[r] = SCALE ? sbase + (size_t)((rgidx * 16) >> 7) * ldscale + (c0 >> 2) : nullptr;
+    }
+
+    float acc[RG][NT][4];
+    stream_mma<WT, NT, RG, SCALE>(acc, a, sh);
+
+    float* part = reinterpret_cast<float*>(smem);
+    const int rows_cta = 16 * RG * WM;
+    const int PR = rows_cta + 4;
+    int lrow0[RG];
+#pragma unroll
+    for (int r = 0; r < RG; ++r) lrow0[r] = (MODE == 1) ? (r * WM + wm) * 16 : (wm * RG + r) * 16;
+    store_partials<WT, NT, RG>(part, acc, wk, PR, lrow0);
+
+    if constexpr (MODE == 1) {
+        // act[slot, col] = silu(gate) * up, one rounding
+        const int col0 = blockIdx.x * WM * 16;
+        reduce_and_emit<2>(part, WK, S::NTP, PR, nt, 2 * WM, 16 * WM, SK, [&](int tk, int ro, float (&v)[2][8]) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float gt = v[0][i];
+                o[i] = (gt / (1.f + __expf(-gt))) * v[1][i];
+            }
+            uint4 w;
+            w.x = pack2<WT == kFP16 ? kFP16 : kBF16>(o[0], o[1]);
+            w.y = pack2<WT == kFP16 ? kFP16 : kBF16>(o[2], o[3]);
+            w.z = pack2<WT == kFP16 ? kFP16 : kBF16>(o[4], o[5]);
+            w.w = pack2<WT == kFP16 ? kFP16 : kBF16>(o[6], o[7]);
+            uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + ((size_t)slot_of[tk] * p.rows + col0 + ro * 8) * 2;
+            *reinterpret_cast<uint4*>(dst) = w;
+        });
+    } else {
+        const int row0 = blockIdx.x * rows_cta;
+        const int H = p.rows;
+        reduce_and_emit<1>(part, WK, S::NTP, PR, nt, rows_cta >> 3, 0, SK, [&](int tk, int ro, float (&v)[1][8]) {
+            const int slot = slot_of[tk];
+            const float wgt = load_scalar16<WT == kFP16 ? kFP16 : kBF16>(p.topk_weights, slot);
+            const size_t off = (size_t)(slot / p.topk) * H + row0 + ro * 8;
+            if constexpr (WT == kFP16) {
+                __half2* y = reinterpret_cast<__half2*>(reinterpret_cast<__half*>(p.out) + off);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) atomicAdd(y + i, __floats2half2_rn(wgt * v[0][2 * i], wgt * v[0][2 * i + 1]));
+            } else {
+                __nv_bfloat162* y = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    atomicAdd(y + i, __floats2bfloat162_rn(wgt * v[0][2 * i], wgt * v[0][2 * i + 1]));
+            }
+        });
+    }
+}
+
+template <int WT, int NT, int RG, bool SCALE, int MODE>
+int launch_moe_inst(const MoeGemmParams& p0, int tiles, int sk, int max_items, cudaStream_t stream) {
+    using S = CoreShape<NT, RG>;
+    MoeGemmParams p = p0;
+    const int warps = 8;
+    const int WK = warps / p.wm;
+    const int rows_cta = 16 * RG * p.wm;
+    const size_t stage = (size_t)WK * S::NTP * S::PITCH;
+    const size_t part = (size_t)WK * S::NTP * (rows_cta + 4) * sizeof(float);
+    int stages = 3;
+    if (std::max(stage * 3, part) > (size_t)kSmemLimit) stages = 2;
+    const size_t smem = std::max(stage * stages, part);
+    if (smem > (size_t)kSmemLimit) return fail(kUnsupported, "moe: tile needs %zu bytes of shared memory", smem);
+    p.stages = stages;
+
+    auto kern = moe_gemm_kernel<WT, NT, RG, SCALE, MODE>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+        if (e != cudaSuccess) return fail(kCudaError, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        attr_set[dev & 63] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles, sk, max_items);
+    cfg.blockDim = dim3(warps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = sk;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (sk > 1) ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    if (e != cudaSuccess) return fail(kCudaError, "moe gemm launch: %s", cudaGetErrorString(e));
+    return kOk;
+}
+
+template <int WT, bool SCALE, int MODE>
+int launch_moe_nt(const MoeGemmParams& p, int nt_tiles, int rg, int tiles, int sk, int max_items, cudaStream_t s) {
+#define MLK_CASE(NT_, RG_) \
+    if (nt_tiles == NT_ && rg == RG_) return launch_moe_inst<WT, NT_, RG_, SCALE, MODE>(p, tiles, sk, max_items, s);
+    if constexpr (MODE == 1) {
+        MLK_CASE(1, 2) MLK_CASE(2, 2) MLK_CASE(4, 2) MLK_CASE(8, 2)
+    } else {
+        MLK_CASE(1, 1) MLK_CASE(2, 1) MLK_CASE(4, 1) MLK_CASE(8, 1)
+        MLK_CASE(1, 2) MLK_CASE(2, 2) MLK_CASE(4, 2) MLK_CASE(8, 2)
+    }
+#undef MLK_CASE
+    return fail(kInvalidArg, "moe: unsupported tile (tokens tiles %d, row groups %d)", nt_tiles, rg);
+}
+
+template <int MODE>
+int launch_moe_gemm(int wt, bool scale, const MoeGemmParams& p, int nt_tiles, int rg, int tiles, int sk,
+                    int max_items, cudaStream_t s) {
+    switch (wt) {
+        case kBF16: return launch_moe_nt<kBF16, false, MODE>(p, nt_tiles, rg, tiles, sk, max_items, s);
+        case kFP16: return launch_moe_nt<kFP16, false, MODE>(p, nt_tiles, rg, tiles, sk, max_items, s);
+        case kE4M3:
+            return scale ? launch_moe_nt<kE4M3, true, MODE>(p, nt_tiles, rg, tiles, sk, max_items, s)
+                         : launch_moe_nt<kE4M3, false, MODE>(p, nt_tiles, rg, tiles, sk, max_items, s);
+    }
+    return fail(kUnsupported, "moe: unknown weight type %d", wt);
+}
+
+int pick_sk(int ctas, int chunks, int wk) {
+    int sk = 1;
+    while (sk < 8 && ctas * sk < 2 * 148 && chunks / (wk * sk * 2) >= 4) sk *= 2;
+    return sk;
+}
+
+}  // namespace
+
+int launch_fused_experts(const MoeParams& m, cudaStream_t s) {
+    if (!m.w1 || !m.w2 || !m.x || !m.topk_ids || !m.topk_weights || !m.sorted_token_ids || !m.cumsum ||
+        !m.padded_num_experts || !m.experts_ids || !m.C || !m.y)
+        return fail(kInvalidArg, "fused_experts_compute: null pointer");
+    if (m.T < 0 || m.E <= 0 || m.topk <= 0 || m.H <= 0 || m.I <= 0)
+        return fail(kInvalidArg, "fused_experts_compute: bad sizes");
+    if (m.T == 0) return kOk;
+    if (m.dtype < 0 || m.dtype > 2) return fail(kInvalidArg, "fused_experts_compute: Unsupported data type");
+    if (m.H % 32 != 0 || m.I % 32 != 0)
+        return fail(kInvalidArg, "fused_experts_compute: hidden and intermediate sizes must be multiples of 32 (H=%d I=%d)", m.H, m.I);
+    const bool scale = m.dtype == 2 && m.w1_scale && m.w2_scale;
+    if (m.dtype == 2 && (!!m.w1_scale != !!m.w2_scale))
+        return fail(kInvalidArg, "fused_experts_compute: give both block scales or neither");
+    if (scale && (m.H % 128 != 0 || m.I % 128 != 0))
+        return fail(kInvalidArg, "fused_experts_compute: 128x128 block scales need H and I to be multiples of 128");
+    const int mbs = m.mbs > 0 ? m.mbs : 16;
+    const int wt = m.dtype;
+    const int esz = (wt == kE4M3) ? 1 : 2;
+
+    // slots per work item: the token tile the GEMM kernels are instantiated for
+    const int nt_tiles = m.T <= 8 ? 1 : (m.T <= 16 ? 2 : (m.T <= 32 ? 4 : 8));
+    const int block_slots = nt_tiles * 8;
+    const long long slots = (long long)m.T * m.topk;
+    const int max_items = (int)std::min<long long>(slots, (long long)std::min<long long>(m.E, slots) + slots / block_slots);
+
+    // work list lives in the half of C that the fused activation does not need
+    uint8_t* cbytes = reinterpret_cast<uint8_t*>(m.C);
+    size_t wl_off = (size_t)slots * m.I * 2;
+    wl_off = (wl_off + 15) & ~(size_t)15;
+    const size_t c_bytes = (size_t)slots * 2 * m.I * 2;
+    if (wl_off + 16 * (size_t)(max_items + 1) > c_bytes)
+        return fail(kInvalidArg, "fused_experts_compute: workspace C too small for the work list");
+    void* worklist = cbytes + wl_off;
+
+    if (int st = launch_moe_align(m.T, m.E, m.topk, mbs, m.topk_ids, m.sorted_token_ids, m.cumsum,
+                                  m.padded_num_experts, m.experts_ids, m.experts_map, m.experts_map_len, s, worklist,
+                                  block_slots))
+        return st;
+
+    // ---- GEMM1: act[slot, 0..I) = silu(x W1_gate^T) * (x W1_up^T)
+    MoeGemmParams g1{};
+    g1.w = reinterpret_cast<const uint8_t*>(m.w1);
+    g1.w_expert_bytes = (long long)2 * m.I * m.H * esz;
+    g1.scale = scale ? m.w1_scale : nullptr;
+    g1.scale_expert = (long long)((2 * m.I + 127) / 128) * ((m.H + 127) / 128);
+    g1.xsrc = reinterpret_cast<const uint8_t*>(m.x);
+    g1.x_row_div = m.topk;
+    g1.x_row_bytes = (long long)m.H * 2;
+    g1.out = m.C;
+    g1.sorted = m.sorted_token_ids;
+    g1.worklist = reinterpret_cast<const int4*>(worklist);
+    g1.topk_weights = m.topk_weights;
+    g1.topk = m.topk;
+    g1.rows = m.I;
+    g1.k = m.H;
+    g1.fp8_order = m.fp8_order;
+    int wm1 = (nt_tiles >= 8) ? 4 : (nt_tiles >= 2 ? 2 : 1);
+    while (wm1 > 1 && (m.I / 16) % wm1 != 0) wm1 >>= 1;
+    if ((m.I / 16) % wm1 != 0) return fail(kInvalidArg, "fused_experts_compute: I must be a multiple of 16");
+    g1.wm = wm1;
+    const int tiles1 = (m.I / 16) / wm1;
+    int sk1 = m.sk1 > 0 ? m.sk1 : pick_sk(tiles1 * std::min(m.E, (int)slots), m.H / 32, 8 / wm1);
+    if (sk1 != 1 && sk1 != 2 && sk1 != 4 && sk1 != 8) return fail(kInvalidArg, "fused_experts_compute: split-K must be 1, 2, 4 or 8");
+    if (int st = launch_moe_gemm<1>(wt, scale, g1, nt_tiles, 2, tiles1, sk1, max_items, s)) return st;
+
+    // ---- GEMM2: y[token] += w[slot] * (act[slot] W2^T)
+    MoeGemmParams g2{};
+    g2.w = reinterpret_cast<const uint8_t*>(m.w2);
+    g2.w_expert_bytes = (long long)m.H * m.I * esz;
+    g2.scale = scale ? m.w2_scale : nullptr;
+    g2.scale_expert = (long long)((m.H + 127) / 128) * ((m.I + 127) / 128);
+    g2.xsrc = reinterpret_cast<const uint8_t*>(m.C);
+    g2.x_row_div = 1;
+    g2.x_row_bytes = (long long)m.I * 2;
+    g2.out = m.y;
+    g2.sorted = m.sorted_token_ids;
+    g2.worklist = reinterpret_cast<const int4*>(worklist);
+    g2.topk_weights = m.topk_weights;
+    g2.topk = m.topk;
+    g2.rows = m.H;
+    g2.k = m.I;
+    g2.fp8_order = m.fp8_order;
+    int rg2 = (m.rg == 1 || m.rg == 2) ? m.rg : ((nt_tiles >= 2 && m.H % 32 == 0) ? 2 : 1);
+    int wm2 = (nt_tiles >= 8) ? 4 : (nt_tiles >= 2 ? 2 : 1);
+    while (wm2 > 1 && (m.H / 16) % (rg2 * wm2) != 0) wm2 >>= 1;
+    if ((m.H / 16) % (rg2 * wm2) != 0) rg2 = 1;
+    g2.wm = wm2;
+    const int tiles2 = (m.H / 16) / (rg2 * wm2);
+    int sk2 = m.sk2 > 0 ? m.sk2 : pick_sk(tiles2 * std::min(m.E, (int)slots), m.I / 32, 8 / wm2);
+    if (sk2 != 1 && sk2 != 2 && sk2 != 4 && sk2 != 8) return fail(kInvalidArg, "fused_experts_compute: split-K must be 1, 2, 4 or 8");
+    return launch_moe_gemm<2>(wt, scale, g2, nt_tiles, rg2, tiles2, sk2, max_items, s);
+}
+
+}  // namespace mlk

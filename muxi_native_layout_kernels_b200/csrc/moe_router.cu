@@ -1,0 +1,184 @@
+// MoE router: score function + optional selection bias + group-limited top-k, one warp per token.
+//
+// Semantics follow the reference's torch formulation (muxi_layout_kernels/utils.py:160-216) with the
+// tie rule of its device kernel (csrc/moe_kernels/fused_topK.h:255-262, "lower id wins"):
+//   score = softmax(logits) or sigmoid(logits), fp32 math, rounded to the logits' 16-bit type
+//   sel   = score + bias (rounded) if a bias is given, else score
+//   group score = max of sel in the group, or the rounded sum of its two largest sel with a bias
+//   keep the topk_groups best groups (ties: lower group id); sel of every other group becomes 0
+//   pick topk largest sel (ties: lower expert id); returned weights are the un-biased scores
+//   output order: ascending expert id for softmax, selection order for sigmoid (fused_topK.h:294-306, :575-586)
+// Unlike the reference launcher (fused_gating.h:22: only 8 groups / 4 kept / top-8), any E <= 256 that the
+// group count divides is accepted.
+#include "common.cuh"
+#include "moe.cuh"
+#include "status.h"
+
+namespace mlk {
+
+namespace {
+
+constexpr int kVPT = 8;   // experts per lane, strided: e = lane + 32*i
+
+__device__ __forceinline__ void argmax_pair(float& v, int& e) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, v, o);
+        const int oe = __shfl_xor_sync(0xFFFFFFFFu, e, o);
+        if (ov > v || (ov == v && oe < e)) { v = ov; e = oe; }
+    }
+}
+
+template <int WT>
+__global__ void __launch_bounds__(128) router_kernel(const void* __restrict__ logits, int score_fun, int T, int E,
+                                                     int G, int KG, int32_t* __restrict__ ids, void* __restrict__ wts,
+                                                     int topk, const void* __restrict__ bias) {
+    extern __shared__ float sm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (row >= T) return;
+    float* ssel = sm + warp * (E + 2 * G);
+    float* sg = ssel + E;
+    int* gmask = reinterpret_cast<int*>(sg + G);
+    const float NEG = -INFINITY;
+
+    float x[kVPT], score[kVPT], sel[kVPT];
+#pragma unroll
+    for (int i = 0; i < kVPT; ++i) {
+        const int e = lane + 32 * i;
+        x[i] = (e < E) ? load_scalar16<WT>(logits, (int64_t)row * E + e) : NEG;
+    }
+    if (score_fun == 0) {
+        float mx = x[0];
+#pragma unroll
+        for (int i = 1; i < kVPT; ++i) mx = fmaxf(mx, x[i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < kVPT; ++i) {
+            const int e = lane + 32 * i;
+            score[i] = (e < E) ? expf(x[i] - mx) : 0.f;
+            sum += score[i];
+        }
+        sum = warp_sum(sum);
+#pragma unroll
+        for (int i = 0; i < kVPT; ++i) score[i] = round16<WT>(__fdiv_rn(score[i], sum));
+    } else {
+#pragma unroll
+        for (int i = 0; i < kVPT; ++i) score[i] = round16<WT>(__fdiv_rn(1.f, 1.f + expf(-x[i])));
+    }
+#pragma unroll
+    for (int i = 0; i < kVPT; ++i) {
+        const int e = lane + 32 * i;
+        if (e < E) {
+            sel[i] = (bias != nullptr) ? round16<WT>(score[i] + load_scalar16<WT>(bias, e)) : score[i];
+        } else {
+            sel[i] = NEG;
+        }
+    }
+
+    if (G > 1) {
+        const int gs = E / G;
+#pragma unroll
+        for (int i = 0; i < kVPT; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E) ssel[e] = sel[i];
+        }
+        __syncwarp();
+        for (int gi = lane; gi < G; gi += 32) {
+            float m1 = NEG, m2 = NEG;
+            for (int j = 0; j < gs; ++j) {
+                const float v = ssel[gi * gs + j];
+                if (v > m1) { m2 = m1; m1 = v; } else if (v > m2) { m2 = v; }
+            }
+            sg[gi] = (bias != nullptr && gs > 1) ? round16<WT>(m1 + m2) : m1;
+            gmask[gi] = 0;
+        }
+        __syncwarp();
+        for (int r = 0; r < KG; ++r) {
+            float bv = NEG;
+            int bg = 0x7FFFFFFF;
+            for (int gi = lane; gi < G; gi += 32) {
+                if (gmask[gi]) continue;
+                const float v = sg[gi];
+                if (v > bv || bg == 0x7FFFFFFF) { bv = v; bg = gi; }
+            }
+            argmax_pair(bv, bg);
+            __syncwarp();
+            if (lane == 0 && bg < G) gmask[bg] = 1;
+            __syncwarp();
+        }
+#pragma unroll
+        for (int i = 0; i < kVPT; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E && !gmask[e / gs]) sel[i] = 0.f;
+        }
+    }
+
+    int my_id = 0x7FFFFFFF;
+    float my_w = 0.f;
+    for (int r = 0; r < topk; ++r) {
+        float bv = NEG;
+        int be = 0x7FFFFFFF;
+#pragma unroll
+        for (int i = 0; i < kVPT; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E && (sel[i] > bv || be == 0x7FFFFFFF)) { bv = sel[i]; be = e; }
+        }
+        argmax_pair(bv, be);
+        const int owner = be & 31, oi = be >> 5;
+        float sc = 0.f;
+#pragma unroll
+        for (int i = 0; i < kVPT; ++i) {
+            if (i == oi) {
+                sc = score[i];
+                if (lane == owner) sel[i] = NEG;
+            }
+        }
+        sc = __shfl_sync(0xFFFFFFFFu, sc, owner);
+        if (lane == r) { my_id = be; my_w = sc; }
+    }
+    int pos = lane;
+    if (score_fun == 0) {
+        pos = 0;
+        for (int j = 0; j < topk; ++j) {
+            const int idj = __shfl_sync(0xFFFFFFFFu, my_id, j);
+            pos += (idj < my_id) ? 1 : 0;
+        }
+    }
+    if (lane < topk) {
+        ids[(int64_t)row * topk + pos] = my_id;
+        if constexpr (WT == kFP16)
+            reinterpret_cast<__half*>(wts)[(int64_t)row * topk + pos] = __float2half_rn(my_w);
+        else
+            reinterpret_cast<__nv_bfloat16*>(wts)[(int64_t)row * topk + pos] = __float2bfloat16_rn(my_w);
+    }
+}
+
+}  // namespace
+
+int launch_router(const void* gating_output, int score_fun, int T, int E, int n_groups, int topk_groups,
+                  int32_t* experts_ids, void* weights, int topk, const void* bias, int dtype, cudaStream_t s) {
+    if (!gating_output || !experts_ids || !weights) return fail(kInvalidArg, "fused_routing_gate: null pointer");
+    if (T < 0) return fail(kInvalidArg, "fused_routing_gate: negative batch size");
+    if (T == 0) return kOk;
+    if (score_fun != 0 && score_fun != 1) return fail(kInvalidArg, "fused_routing_gate: score_fun must be 0 (softmax) or 1 (sigmoid)");
+    if (E <= 0 || E > 32 * kVPT) return fail(kUnsupported, "fused_routing_gate: 1 <= num_experts <= 256 (got %d)", E);
+    if (n_groups <= 0 || E % n_groups != 0) return fail(kInvalidArg, "fused_routing_gate: n_groups=%d must divide num_experts=%d", n_groups, E);
+    if (topk_groups <= 0 || topk_groups > n_groups) return fail(kInvalidArg, "fused_routing_gate: topK_groups=%d out of range", topk_groups);
+    if (topk <= 0 || topk > 32 || topk > E) return fail(kInvalidArg, "fused_routing_gate: topK=%d out of range (1..min(32,E))", topk);
+    if (dtype != 0 && dtype != 1) return fail(kInvalidArg, "fused_routing_gate: gating_output must be bf16 or fp16");
+    const int warps = 4;
+    const int grid = (T + warps - 1) / warps;
+    const size_t smem = (size_t)warps * (E + 2 * n_groups) * sizeof(float);
+    if (dtype == 1)
+        router_kernel<kFP16><<<grid, warps * 32, smem, s>>>(gating_output, score_fun, T, E, n_groups, topk_groups,
+                                                            experts_ids, weights, topk, bias);
+    else
+        router_kernel<kBF16><<<grid, warps * 32, smem, s>>>(gating_output, score_fun, T, E, n_groups, topk_groups,
+                                                            experts_ids, weights, topk, bias);
+    return check_launch("fused_routing_gate");
+}
+
+}  // namespace mlk

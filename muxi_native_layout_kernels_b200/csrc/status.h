@@ -1,0 +1,32 @@
+// Status codes and the thread-local error message behind mlk_last_error().
+#pragma once
+
+#include <cuda_runtime.h>
+
+namespace mlk {
+
+// Weight/activation type tags (also the dtype codes of the C ABI); used as template arguments.
+constexpr int kBF16 = 0;  // bf16 weights, bf16 activations
+constexpr int kFP16 = 1;  // fp16 weights, fp16 activations
+constexpr int kE4M3 = 2;  // e4m3 weights decoded to bf16 in registers, bf16 activations
+
+enum Status : int {
+    kOk = 0,
+    kInvalidArg = 1,    // a precondition of the reference API is violated (shape, divisibility, null)
+    kUnsupported = 2,   // valid request that no kernel of this build implements
+    kCudaError = 3,     // a CUDA runtime call failed (message holds cudaGetErrorString)
+    kIoError = 4,       // dispatch table file could not be read / parsed
+};
+
+// printf-style; returns `code` so call sites can `return fail(kInvalidArg, "...", ...)`.
+int fail(int code, const char* fmt, ...);
+const char* last_error();
+void clear_error();
+
+inline int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(kCudaError, "%s: %s", what, cudaGetErrorString(e));
+    return kOk;
+}
+
+}  // namespace mlk

@@ -1,0 +1,103 @@
+"""Fused MoE layer, "plan C": router -> renormalise -> expert compute, with no host synchronisation.
+
+Same signature and semantics as the reference's ``muxi_layout_kernels.muxi_moe_planC.fused_moe``
+(muxi_layout_kernels/muxi_moe_planC.py:6-149); the reference's MetaX tile arguments are accepted and, apart from
+``APerWarp``, ignored.  Differences a caller can rely on:
+  * the router accepts any group configuration with ``num_experts % num_expert_group == 0`` (the reference
+    kernel only 8 groups / 4 kept / top-8);
+  * ``w1_scale``/``w2_scale`` may be ``None`` with ``soft_fp8=True`` (unit scales);
+  * the launch sequence is 4 kernels (router, alignment, GEMM1+SiLU, GEMM2+combine) instead of 6.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from . import ext
+
+
+def fused_moe(
+    hidden_states: torch.Tensor,  # [batch_size, hidden_size]
+    w1: torch.Tensor,             # [E, 2I, H], every expert in layout A (gate rows first, then up rows)
+    w2: torch.Tensor,             # [E, H, I],  every expert in layout A
+    gating_output: torch.Tensor,  # [batch_size, num_experts] router logits
+    topk: int,
+    renormalize: bool,
+    use_grouped_topk: bool = False,
+    num_expert_group: Optional[int] = None,
+    topk_group: Optional[int] = None,
+    w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+    block_shape: Optional[List[int]] = None,
+    gating_bias: Optional[torch.Tensor] = None,
+    score_func: str = "softmax",
+    soft_fp8: bool = False,
+    APerWarp: int = 2,
+    splitK: int = 3,
+    tile_m_2: int = 128,
+    tile_n_2: int = 16,
+    tile_k_2: int = 128,
+    block_dim_x_gemm: int = 256,
+    experts_map: Optional[torch.Tensor] = None,
+    fp8_repacked: bool = False,
+) -> torch.Tensor:
+    assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
+    if num_expert_group is None:
+        num_expert_group = 1
+    if topk_group is None:
+        topk_group = 1
+    if not use_grouped_topk and num_expert_group != 1:
+        raise ValueError("When use_grouped_topk is False, num_expert_group must be 1.")
+
+    shape = hidden_states.size()
+    B, H = hidden_states.shape
+    num_experts = gating_output.shape[1]
+    dev = hidden_states.device
+
+    if score_func == "softmax":
+        score_fun = 0
+    elif score_func == "sigmoid":
+        score_fun = 1
+    else:
+        raise ValueError("Unsupported scoring function")
+
+    # 1. router
+    topk_ids = torch.empty(B, topk, dtype=torch.int32, device=dev)
+    topk_weights = torch.empty(B, topk, dtype=hidden_states.dtype, device=dev)
+    ext.fused_routing_gate(gating_output, score_fun, B, H, num_expert_group, topk_group, topk_ids, topk_weights,
+                           topk, gating_bias)
+    if renormalize:
+        # in the activation dtype, like the reference (muxi_moe_planC.py:69-70)
+        topk_weights = topk_weights / topk_weights.sum(dim=-1, keepdim=True)
+
+    # 2. experts
+    e1, m1, k1 = w1.shape
+    e2, m2, k2 = w2.shape
+    assert e1 == e2
+    assert k1 == m2
+    micro_batchsize = 16
+    max_num_tokens_padded = topk * B + num_experts * (micro_batchsize - 1)
+    sorted_token_ids = torch.full((max_num_tokens_padded,), B * topk, dtype=torch.int32, device=dev)
+    cumsum_buffer = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    padded_num_experts = torch.empty(1, dtype=torch.int32, device=dev)
+    experts_ids = torch.empty((max_num_tokens_padded + micro_batchsize - 1) // micro_batchsize, dtype=torch.int32,
+                              device=dev)
+    # workspace: the fused GEMM1 epilogue writes [B*topk, I] activations into the first half; the second half
+    # holds the expert work list.  Nothing in it has to be zero.
+    C = torch.empty(topk * m1 * B, dtype=hidden_states.dtype, device=dev)
+    y = torch.zeros_like(hidden_states)
+
+    if experts_map is not None and experts_map.dtype != torch.int:
+        experts_map = experts_map.to(torch.int)
+    if soft_fp8:
+        ext.fused_experts_compute(w1, w2, hidden_states, B, e1, topk, topk_ids, topk_weights, sorted_token_ids,
+                                  cumsum_buffer, padded_num_experts, experts_ids, C, y, w1_scale, w2_scale,
+                                  block_shape if block_shape is not None else [128, 128], soft_fp8,
+                                  experts_map=experts_map, fp8_repacked=fp8_repacked)
+    else:
+        ext.fused_experts_compute(w1, w2, hidden_states, B, e1, topk, topk_ids, topk_weights, sorted_token_ids,
+                                  cumsum_buffer, padded_num_experts, experts_ids, C, y, APerWarp=APerWarp,
+                                  splitK=splitK, tile_m_2=tile_m_2, tile_n_2=tile_n_2, tile_k_2=tile_k_2,
+                                  block_dim_x_gemm=block_dim_x_gemm, experts_map=experts_map)
+    return y.view(shape)

@@ -1,0 +1,22 @@
+"""pytest configuration: the `gpu` marker and import paths.
+
+`python -m pytest tests -m "not gpu"` runs on a CPU-only machine (oracle vs golden vectors, host logic, C-ABI
+symbol checks); `-m gpu` holds the parity tests proper, which call the CUDA kernels through the C ABI.
+"""
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
+
+
+@pytest.fixture(scope="session")
+def golden_dir():
+    return ROOT / "tests" / "golden"

@@ -1,0 +1,133 @@
+"""CPU-side checks of the C-ABI library and the host logic above it (no kernel is launched here)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared_symbols():
+    text = (ROOT / "include" / "mlk_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mlk_[A-Za-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from muxi_native_layout_kernels_b200 import _lib
+    names = _declared_symbols()
+    assert len(names) >= 20
+    raw = ctypes.CDLL(str(_lib.LIB_PATH))
+    for n in names:
+        assert hasattr(raw, n), f"{n} is declared in include/mlk_b200.h but not exported"
+    # and the ctypes prototypes cover the header exactly
+    assert sorted(_lib.PROTOTYPES) == names
+
+
+def test_status_strings_and_build_info():
+    from muxi_native_layout_kernels_b200._lib import lib
+    assert lib.mlk_status_string(0) == b"ok"
+    assert lib.mlk_status_string(1) == b"invalid argument"
+    assert b"sm_100a" in lib.mlk_build_info()
+
+
+def test_table_load_lookup_and_miss_default(tmp_path, capfd):
+    from muxi_native_layout_kernels_b200._lib import lib
+    p = tmp_path / "t.csv"
+    p.write_text("m,n,k,kernelId,kernelParam1,kernelParam2,kernelParam3\n"
+                 "4096,16,4096,1,2,4,2\n"
+                 "bad,line\n"
+                 "4096,16,4096,1,1,2,8\n"          # later duplicate wins (reference: arg_selector.cu:49)
+                 "128,32,256,1,2,1,1\n")
+    assert lib.mlk_table_load(2, str(p).encode()) == 0
+    out = (ctypes.c_int * 4)()
+    hit = ctypes.c_int(-1)
+    assert lib.mlk_table_lookup(2, 4096, 16, 4096, out, ctypes.byref(hit)) == 0
+    assert list(out) == [1, 1, 2, 8] and hit.value == 1
+    assert "Invalid line" in capfd.readouterr().err
+    # miss: warns once, returns a runnable default, then remembers it
+    assert lib.mlk_table_lookup(2, 8192, 8, 1024, out, ctypes.byref(hit)) == 0
+    first = list(out)
+    assert hit.value == 0 and first[0] == 1 and first[1] in (1, 2) and first[2] in (1, 2, 4, 8) and first[3] in (1, 2, 4, 8)
+    assert "No matching arguments" in capfd.readouterr().err
+    assert lib.mlk_table_lookup(2, 8192, 8, 1024, out, ctypes.byref(hit)) == 0
+    assert list(out) == first and hit.value == 1
+    assert capfd.readouterr().err == ""
+    # GeMV tables are keyed by (m, k) with six columns
+    q = tmp_path / "v.csv"
+    q.write_text("m,k,BLOCK_DIM_X,KernelId,KernelParam1,KernelParam2\n4096,4096,128,2,1,4\n")
+    assert lib.mlk_table_load(5, str(q).encode()) == 0
+    assert lib.mlk_table_lookup(5, 4096, 999, 4096, out, ctypes.byref(hit)) == 0
+    assert list(out) == [128, 2, 1, 4] and hit.value == 1
+    # missing file: I/O status, lookups still answer with defaults
+    assert lib.mlk_table_load(5, b"/nonexistent/file.csv") == 4
+    assert lib.mlk_table_lookup(5, 4096, 1, 4096, out, ctypes.byref(hit)) == 0 and hit.value == 0
+    assert lib.mlk_table_lookup(9, 1, 1, 1, out, ctypes.byref(hit)) == 1
+    from muxi_native_layout_kernels_b200 import _lib
+    _lib.load_tables()   # restore the packaged tables for the other tests
+
+
+def test_packaged_tables_exist_with_reference_headers():
+    from muxi_native_layout_kernels_b200._lib import PKG_DIR, lib
+    gemm_hdr = "m,n,k,kernelId,kernelParam1,kernelParam2,kernelParam3"
+    gemv_hdr = "m,k,BLOCK_DIM_X,KernelId,KernelParam1,KernelParam2"
+    for t in range(7):
+        f = PKG_DIR / lib.mlk_table_file_name(t).decode()
+        assert f.exists(), f
+        assert f.read_text().splitlines()[0].strip() == (gemv_hdr if t >= 4 else gemm_hdr)
+
+
+def test_argument_errors_surface_as_runtime_error_without_a_gpu():
+    import muxi_native_layout_kernels_b200 as mlk
+    A = torch.zeros(8, 16, 16, 8, dtype=torch.bfloat16)
+    B = torch.zeros(1, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="A must be a CUDA tensor"):
+        mlk.gemv_layoutA(A, B)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        mlk.layoutB(torch.zeros(16, 32, dtype=torch.bfloat16))
+    with pytest.raises(NotImplementedError):
+        mlk.gemmEx(A, B)
+    with pytest.raises(NotImplementedError):
+        mlk.muxi_hgemm(A, B)
+
+
+def test_c_abi_rejects_bad_shapes_before_touching_the_device():
+    from muxi_native_layout_kernels_b200._lib import lib
+    one = ctypes.c_void_p(16)   # never dereferenced: the shape check comes first
+    assert lib.mlk_gemm_layoutA(one, one, one, 100, 16, 128, 0, 1.0, 0.0, None, None) == 1
+    assert b"multiple of 128" in lib.mlk_last_error()
+    assert lib.mlk_gemv_layoutA_wapper(one, one, one, 40, 64, 0, 1.0, 0.0, 256, 1, 1, 1, None, None, 0, None) == 1
+    assert lib.mlk_gemv_layoutA_wapper(one, one, one, 64, 64, 0, 1.0, 0.0, 256, 7, 1, 1, None, None, 0, None) == 2
+    assert lib.mlk_gemm_layoutA_wapper(one, one, one, 128, 16, 128, 0, 1.0, 0.0, 3, 1, 1, 1, None, None) == 1
+    assert lib.mlk_layoutB(one, one, 10, 32, None) == 1
+    assert lib.mlk_fp8_weight_repack(one, one, 6, None) == 1
+    assert lib.mlk_fused_routing_gate(one, 0, 4, 300, 1, 1, one, one, 2, None, 0, None) == 2
+    assert lib.mlk_fused_routing_gate(one, 0, 4, 64, 3, 1, one, one, 2, None, 0, None) == 1
+
+
+def test_drop_in_alias_package_exposes_reference_names():
+    import muxi_layout_kernels
+    from muxi_layout_kernels.muxi_moe_planC import fused_moe as planC  # noqa: F401
+    from muxi_layout_kernels.utils import fused_moe, scale_tensor, scale_whole_tensor  # noqa: F401
+    for name in ("layoutB", "reLayoutC", "gemm_layoutABC", "gemm_layoutA_linear", "gemm_layoutA",
+                 "gemm_layoutA_soft_fp8", "gemm_layoutAB_ContinuousC", "gemv_layoutA", "gemm_layoutABC_wapper",
+                 "gemm_layoutA_wapper", "gemm_layoutA_soft_fp8_wapper", "gemm_layoutAB_ContinuousC_wapper",
+                 "gemv_layoutA_wapper", "fp8_weight_repack", "fused_routing_gate",
+                 "batched_routed_activation_indexed_to_expert_block_indexed", "fused_experts_compute",
+                 "gemmEx", "muxi_hgemm", "routing_gate", "experts_compute"):
+        assert hasattr(muxi_layout_kernels, name), name
+
+
+def test_package_utils_match_reference_helpers(golden_dir):
+    """The package's own torch helpers (public API of the reference package) against the golden vectors."""
+    from muxi_native_layout_kernels_b200 import utils
+    g = torch.load(golden_dir / "dequant.pt")
+    assert torch.equal(utils.scale_tensor(g["w8"].view(torch.float8_e4m3fn).to(torch.bfloat16), g["scale"]), g["out"])
+    assert torch.equal(utils.scale_whole_tensor(g["we"].view(torch.float8_e4m3fn), g["se"]), g["oute"])
+    torch.set_num_threads(1)
+    m = torch.load(golden_dir / "moe_softmax_top2.pt")
+    y = utils.fused_moe(m["x"], m["w1"], m["w2"], m["logits"], m["topk"], m["groups"], m["topk_group"],
+                        global_num_experts=m["logits"].shape[1], renormalize=m["renormalize"])
+    assert torch.equal(y, m["y"])
