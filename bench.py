@@ -1,0 +1,308 @@
+"""Benchmark of the weight-streaming hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (config.workload = "narrow_gemm_bf16_llama8b"): one step is one pass over the narrow-GEMM grid
+tokens in {1,2,4,8,16,32,64} x (N,K) in {(4096,4096),(14336,4096),(4096,14336)}, bf16, native-layout weights,
+row-major activations (gemm_layoutA) -- 21 kernel launches.  Cases are ordered so that the same weight matrix is
+never used twice in a row: 235-268 MB of other weights stream between two uses, more than the 126 MB L2, so every
+launch reads its weights from HBM.  metric = algorithmic bytes of the step / device time of the step.
+At N > 1 every weight matrix is sharded over its output rows (rank g owns rows [g*N/G, (g+1)*N/G)), activations are
+replicated, no collective runs in the data path; total work is fixed, hence "scaling": "strong".
+
+value      device-resident inputs; the step is captured once in a CUDA graph and replayed K times (launch overhead
+           of the Python host does not enter), timed with CUDA events, max over ranks.
+e2e        the same step through the public Python API with HOST inputs: every case copies its activations from
+           pinned host memory, runs, and copies its result back; weights stay resident (they are model state,
+           prepacked once offline).
+roofline   HBM; achieved = algorithmic bytes per launch / average launch duration over the timed region.
+cpu_baseline / --impl reference: the reference's torch formulation of the same math on the host cores
+           ((X.float() @ W.float().T).to(bf16), the expected-value path of its benchmarks), all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+TOKENS = [1, 2, 4, 8, 16, 32, 64]
+SHAPES = [(4096, 4096), (14336, 4096), (4096, 14336)]
+NOMINAL_HBM_GBS = 8000.0
+
+
+def algorithmic_bytes(n_tok: int, N: int, K: int, wbytes: int = 2) -> int:
+    """The reference's own traffic formula (benchmark_and_test/gemv_benchmark.py:111): weights + activations in + out."""
+    return N * K * wbytes + 2 * (n_tok * K + n_tok * N)
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+                for n_, v in zip(names, r[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n_)
+            except Exception:
+                continue
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def case_order():
+    return [(n, N, K) for n in TOKENS for (N, K) in SHAPES]
+
+
+# ------------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's torch math on the host cores
+# ------------------------------------------------------------------------------------------------------
+
+def cpu_pass(weights, acts):
+    from oracle import dense as odense
+    out = None
+    for (n, N, K) in case_order():
+        out = odense.gemm_ref(acts[(n, K)], weights[(N, K)])
+    return out
+
+
+def cpu_inputs():
+    g = torch.Generator().manual_seed(1)
+    weights = {s: (torch.randn(s[0], s[1], generator=g) * 0.02).to(torch.bfloat16) for s in SHAPES}
+    acts = {(n, K): torch.randn(n, K, generator=g).to(torch.bfloat16) for n in TOKENS for K in (4096, 14336)}
+    return weights, acts
+
+
+def time_cpu(passes: int, warm: int = 1):
+    torch.set_num_threads(os.cpu_count() or 1)
+    weights, acts = cpu_inputs()
+    for _ in range(warm):
+        cpu_pass(weights, acts)
+    t0 = time.perf_counter()
+    for _ in range(passes):
+        cpu_pass(weights, acts)
+    dt = (time.perf_counter() - t0) / passes
+    total = sum(algorithmic_bytes(n, N, K) for (n, N, K) in case_order())
+    return total / dt / 1e9, dt
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    gbs, dt = time_cpu(max(1, args.steps), warm=min(1, args.warmup))
+    line = {
+        "impl": "reference", "metric": "narrow_gemm_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "narrow_gemm_bf16_llama8b", "tokens": TOKENS, "shapes": SHAPES, "variant": "torch fp32 matmul on host"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+                         "sample": f"{max(1, args.steps)} full passes over the 21-case grid (whole workload, all host threads)"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------------
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    import muxi_native_layout_kernels_b200 as mlk
+
+    rank, world, local = dist_env()
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device for --impl ours"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # inputs: seeded on the CPU, identical on every rank; each rank keeps its row shard of every weight matrix
+    g = torch.Generator().manual_seed(1)
+    weights, host_acts = {}, {}
+    for (N, K) in SHAPES:
+        W = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+        rows = N // world
+        assert rows % 128 == 0, "row shard must stay a multiple of 128"
+        weights[(N, K)] = mlk.layoutA(W[rank * rows:(rank + 1) * rows].contiguous().to(dev))
+    for n in TOKENS:
+        for K in (4096, 14336):
+            host_acts[(n, K)] = torch.randn(n, K, generator=g).to(torch.bfloat16).pin_memory()
+    dev_acts = {k: v.to(dev) for k, v in host_acts.items()}
+    host_out = {(n, N): torch.empty(n, N // world, dtype=torch.bfloat16).pin_memory() for n in TOKENS for (N, _) in SHAPES}
+    order = case_order()
+    step_bytes_total = sum(algorithmic_bytes(n, N, K) for (n, N, K) in order)
+
+    def step_device():
+        out = None
+        for (n, N, K) in order:
+            out = mlk.gemm_layoutA(weights[(N, K)], dev_acts[(n, K)])
+        return out
+
+    def step_e2e():
+        for (n, N, K) in order:
+            x = host_acts[(n, K)].to(dev, non_blocking=True)
+            c = mlk.gemm_layoutA(weights[(N, K)], x)
+            host_out[(n, N)].copy_(c, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step_device()
+    torch.cuda.synchronize()
+
+    # capture one step, replay it K times
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step_device()
+        with torch.cuda.graph(graph, stream=side):
+            step_device()
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+
+    # end-to-end through the public API with host buffers
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+
+    if rank == 0:
+        ms_step = ms / args.steps
+        value = step_bytes_total / (ms_step * 1e-3) / 1e9
+        e2e_value = step_bytes_total / (ms_e2e / args.steps * 1e-3) / 1e9
+        peak, peak_kind = measured_peak()
+        per_rank_bytes = sum(algorithmic_bytes(n, N // world, K) for (n, N, K) in order)
+        achieved = per_rank_bytes / (ms_step * 1e-3) / 1e9
+        line = {
+            "metric": "narrow_gemm_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "narrow_gemm_bf16_llama8b", "tokens": TOKENS, "shapes": SHAPES, "variant": "gemm_layoutA",
+                       "launches_per_step": len(order), "sharding": f"rows/{world}",
+                       "l2": "consecutive launches use different weight matrices; >= 235 MB stream between two uses of one matrix (L2 is 126 MB)",
+                       "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "GB/s",
+                    "h2d_bytes_per_step": sum(n * K * 2 for (n, N, K) in order),
+                    "d2h_bytes_per_step": sum(n * (N // world) * 2 for (n, N, K) in order)},
+            "gpu_launches": len(order) * args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": f"of {peak_kind}", "kernel": "dense_mma_kernel"},
+        }
+        if world == 1 and not args.no_cpu:
+            gbs, dt = time_cpu(passes=args.cpu_passes)
+            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+                                    "sample": f"{args.cpu_passes} full passes over the 21-case grid, torch fp32 matmul, all host threads"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--cpu-passes", type=int, default=5)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -147,18 +147,24 @@ int mlk_moe_align(int batchSize, int expertCount, int topK, int microBatchSize, 
                   int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
                   int32_t* experts_ids_out, const int32_t* experts_map, int experts_map_len, mlk_stream_t s);
 
-/* Expert compute: alignment, gather-GEMM1 with fused SiLU*up, GEMM2 with fused routing-weight scale and
- * scatter-add into y.  w1 [E,2I,H] (gate rows then up rows) and w2 [E,H,I], each expert in layout A;
- * x [T,H]; topk_ids/topk_weights [T,topK]; C is caller workspace of T*topK*2I elements; y [T,H] must be zero.
+/* Expert compute: alignment, gather-GEMM1 with fused SiLU*up, GEMM2 with fused routing-weight scale, then the
+ * un-permute and sum over each token's topK experts.  w1 [E,2I,H] (gate rows then up rows) and w2 [E,H,I], each
+ * expert in layout A; x [T,H]; topk_ids/topk_weights [T,topK]; C is caller workspace of T*topK*2I elements;
+ * y [T,H] must be zero.
  * dtype 0/1: 16-bit weights; dtype 2: e4m3 weights with optional fp32 block scales w1_scale [E,2I/128,H/128],
  * w2_scale [E,H/128,I/128] (NULL = ones).
+ * combine_scratch: optional T*topK*H floats.  With it the weighted expert outputs are kept in fp32 and summed per
+ * token in a fixed order with one final rounding (bit-reproducible).  With NULL they are accumulated into y with
+ * 16-bit atomics, as the reference does (csrc/moe_kernels/group_gemm_second.h:333-346): one rounding per addend
+ * and an unspecified order.
  * Reference: fused_experts_compute (both overloads), csrc/moe_kernels/fused_experts_compute.cu:50-188,190-296. */
 int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int batch_size, int expert_count,
                               int topK, int hidden, int inter, const int32_t* topk_ids, const void* topk_weights,
                               int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
                               int32_t* experts_ids, void* C, void* y, const float* w1_scale, const float* w2_scale,
                               int dtype, int fp8_order, int microBatchSize, const int32_t* experts_map,
-                              int experts_map_len, int tune_rg, int tune_sk1, int tune_sk2, mlk_stream_t s);
+                              int experts_map_len, float* combine_scratch, int64_t combine_scratch_bytes,
+                              int tune_rg, int tune_sk1, int tune_sk2, mlk_stream_t s);
 
 #ifdef __cplusplus
 }

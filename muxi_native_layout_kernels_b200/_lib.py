@@ -48,7 +48,7 @@ PROTOTYPES = {
     "mlk_moe_align": (c_int, [c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_vp]),
     "mlk_fused_experts_compute": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp,
                                           c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp,
-                                          c_int, c_int, c_int, c_int, c_vp]),
+                                          c_int, c_vp, c_i64, c_int, c_int, c_int, c_vp]),
 }
 
 

@@ -239,14 +239,16 @@ int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int
                               int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
                               int32_t* experts_ids, void* C, void* y, const float* w1_scale, const float* w2_scale,
                               int dtype, int fp8_order, int microBatchSize, const int32_t* experts_map,
-                              int experts_map_len, int tune_rg, int tune_sk1, int tune_sk2, mlk_stream_t s) {
+                              int experts_map_len, float* combine_scratch, int64_t combine_scratch_bytes,
+                              int tune_rg, int tune_sk1, int tune_sk2, mlk_stream_t s) {
     clear_error();
     MoeParams p{};
     p.w1 = w1; p.w2 = w2; p.x = x; p.T = batch_size; p.E = expert_count; p.topk = topK; p.H = hidden; p.I = inter;
     p.topk_ids = topk_ids; p.topk_weights = topk_weights; p.sorted_token_ids = sorted_token_ids;
     p.cumsum = cumsum_buffer; p.padded_num_experts = padded_num_experts; p.experts_ids = experts_ids;
     p.C = C; p.y = y; p.w1_scale = w1_scale; p.w2_scale = w2_scale; p.dtype = dtype; p.fp8_order = fp8_order;
-    p.mbs = microBatchSize; p.experts_map = experts_map; p.experts_map_len = experts_map_len; p.rg = tune_rg; p.sk1 = tune_sk1; p.sk2 = tune_sk2;
+    p.mbs = microBatchSize; p.experts_map = experts_map; p.experts_map_len = experts_map_len;
+    p.scratch = combine_scratch; p.scratch_bytes = combine_scratch_bytes; p.rg = tune_rg; p.sk1 = tune_sk1; p.sk2 = tune_sk2;
     return launch_fused_experts(p, (cudaStream_t)s);
 }
 

@@ -129,15 +129,22 @@ __global__ void __launch_bounds__(256) dense_mma_kernel(const DenseKernelParams 
 template <int WT, int NT, int RG, bool SCALE>
 int launch_mma_inst(const DenseParams& p, cudaStream_t stream) {
     using S = CoreShape<NT, RG>;
-    const int warps = p.threads / 32;
-    const int WK = warps / p.wm;
+    // A token tile that is wide relative to the CTA's K split may not fit in shared memory; drop K-split warps
+    // (never below the requested row warps) until it does.  Results do not depend on the K split.
+    int threads = p.threads;
     const int rows_cta = 16 * RG * p.wm;
     const int ntmax = std::min(p.n, S::NTP);
-    const size_t stage = (size_t)WK * ntmax * S::PITCH;
-    const size_t part = (size_t)WK * S::NTP * (rows_cta + 4) * sizeof(float);
+    size_t smem = 0;
     int stages = 3;
-    if (std::max(stage * 3, part) > (size_t)kSmemLimit) stages = 2;
-    const size_t smem = std::max(stage * stages, part);
+    for (;;) {
+        const int WK = (threads / 32) / p.wm;
+        const size_t stage = (size_t)WK * ntmax * S::PITCH;
+        const size_t part = (size_t)WK * S::NTP * (rows_cta + 4) * sizeof(float);
+        stages = (std::max(stage * 3, part) > (size_t)kSmemLimit) ? 2 : 3;
+        smem = std::max(stage * stages, part);
+        if (smem <= (size_t)kSmemLimit || threads / 64 < p.wm || threads <= 32) break;
+        threads /= 2;
+    }
     if (smem > (size_t)kSmemLimit)
         return fail(kUnsupported, "dense: tile needs %zu bytes of shared memory (rg=%d wm=%d threads=%d n=%d)",
                     smem, RG, p.wm, p.threads, p.n);
@@ -154,7 +161,7 @@ int launch_mma_inst(const DenseParams& p, cudaStream_t stream) {
     DenseKernelParams kp{p, stages};
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.m / rows_cta, p.sk, (p.n + kTokBlock - 1) / kTokBlock);
-    cfg.blockDim = dim3(p.threads);
+    cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

@@ -40,6 +40,8 @@ struct MoeParams {
     int dtype, fp8_order, mbs;
     const int32_t* experts_map;
     int experts_map_len;
+    float* scratch;               // optional [T*topk, H] fp32 for the deterministic combine
+    long long scratch_bytes;
     int rg, sk1, sk2;             // tuning (0 = choose by shape)
 };
 

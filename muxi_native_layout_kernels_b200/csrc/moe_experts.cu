@@ -40,6 +40,7 @@ struct MoeGemmParams {
     int rows;                    // weight rows handled per expert: GEMM1: I (gate rows; up rows are +I); GEMM2: H
     int k;
     int wm, stages, fp8_order;
+    float* scratch;              // GEMM2: [slots, H] fp32 weighted outputs (deterministic combine) or null (atomics)
 };
 
 // MODE 1: RG == 2, row group 0 = gate rows, row group 1 = the matching up rows.
@@ -141,6 +142,12 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const MoeGemmParams p) {
         reduce_and_emit<1>(part, WK, S::NTP, PR, nt, rows_cta >> 3, 0, SK, [&](int tk, int ro, float (&v)[1][8]) {
             const int slot = slot_of[tk];
             const float wgt = load_scalar16<WT == kFP16 ? kFP16 : kBF16>(p.topk_weights, slot);
+            if (p.scratch != nullptr) {
+                float4* dst = reinterpret_cast<float4*>(p.scratch + (size_t)slot * H + row0 + ro * 8);
+                dst[0] = make_float4(wgt * v[0][0], wgt * v[0][1], wgt * v[0][2], wgt * v[0][3]);
+                dst[1] = make_float4(wgt * v[0][4], wgt * v[0][5], wgt * v[0][6], wgt * v[0][7]);
+                return;
+            }
             const size_t off = (size_t)(slot / p.topk) * H + row0 + ro * 8;
             if constexpr (WT == kFP16) {
                 __half2* y = reinterpret_cast<__half2*>(reinterpret_cast<__half*>(p.out) + off);
@@ -153,6 +160,37 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const MoeGemmParams p) {
                     atomicAdd(y + i, __floats2bfloat162_rn(wgt * v[0][2 * i], wgt * v[0][2 * i + 1]));
             }
         });
+    }
+}
+
+// Un-permute + sum: y[t, :] = round16( sum_j scratch[t*topk + j, :] ) over the slots whose expert lives on this
+// rank, in ascending j.  One thread per (token, 8 columns).
+template <int WT>
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ scratch,
+                                                         const int32_t* __restrict__ topk_ids,
+                                                         const int32_t* __restrict__ experts_map, int map_len, int E,
+                                                         int T, int topk, int H, void* __restrict__ y) {
+    const int octs = H >> 3;
+    const long long total = (long long)T * octs;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / octs), o = (int)(i - (long long)t * octs);
+        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < topk; ++j) {
+            int e = topk_ids[t * topk + j];
+            if (experts_map != nullptr) e = (e >= 0 && e < map_len) ? experts_map[e] : -1;
+            if (e < 0 || e >= E) continue;
+            const float4* src = reinterpret_cast<const float4*>(scratch + ((size_t)t * topk + j) * H + o * 8);
+            const float4 u = src[0], w = src[1];
+            a[0] += u.x; a[1] += u.y; a[2] += u.z; a[3] += u.w;
+            a[4] += w.x; a[5] += w.y; a[6] += w.z; a[7] += w.w;
+        }
+        uint4 out;
+        out.x = pack2<WT>(a[0], a[1]);
+        out.y = pack2<WT>(a[2], a[3]);
+        out.z = pack2<WT>(a[4], a[5]);
+        out.w = pack2<WT>(a[6], a[7]);
+        reinterpret_cast<uint4*>(y)[i] = out;
     }
 }
 
@@ -322,7 +360,23 @@ int launch_fused_experts(const MoeParams& m, cudaStream_t s) {
     const int tiles2 = (m.H / 16) / (rg2 * wm2);
     int sk2 = m.sk2 > 0 ? m.sk2 : pick_sk(tiles2 * std::min(m.E, (int)slots), m.I / 32, 8 / wm2);
     if (sk2 != 1 && sk2 != 2 && sk2 != 4 && sk2 != 8) return fail(kInvalidArg, "fused_experts_compute: split-K must be 1, 2, 4 or 8");
-    return launch_moe_gemm<2>(wt, scale, g2, nt_tiles, rg2, tiles2, sk2, max_items, s);
+    const bool det = m.scratch != nullptr;
+    if (det && m.scratch_bytes < (long long)slots * m.H * 4)
+        return fail(kInvalidArg, "fused_experts_compute: combine scratch holds %lld bytes, needs %lld", m.scratch_bytes,
+                    (long long)slots * m.H * 4);
+    if (det && m.H % 8 != 0) return fail(kInvalidArg, "fused_experts_compute: H must be a multiple of 8");
+    g2.scratch = det ? m.scratch : nullptr;
+    if (int st = launch_moe_gemm<2>(wt, scale, g2, nt_tiles, rg2, tiles2, sk2, max_items, s)) return st;
+    if (!det) return kOk;
+    const long long total = (long long)m.T * (m.H / 8);
+    const int grid = (int)std::min<long long>((total + 255) / 256, 148LL * 8);
+    if (wt == kFP16)
+        moe_combine_kernel<kFP16><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
+                                                      m.topk, m.H, m.y);
+    else
+        moe_combine_kernel<kBF16><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
+                                                      m.topk, m.H, m.y);
+    return check_launch("moe_combine");
 }
 
 }  // namespace mlk

@@ -412,12 +412,15 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
         experts_map=None``  (block_shape must be [128,128] and soft_fp8 True; scales may be None = unit scales)
     The tile arguments of the first form describe the reference's MetaX kernels; here only ``APerWarp`` (row groups
     per warp of the second GEMM: 1 or 2, other values = automatic) is used, split-K is chosen from the shape.
-    Extra keyword ``fp8_repacked`` marks e4m3 weights that went through ``fp8_weight_repack``.
+    Extra keywords: ``fp8_repacked`` marks e4m3 weights that went through ``fp8_weight_repack``;
+    ``deterministic`` (default True) sums each token's expert outputs in fp32 in a fixed order with one rounding,
+    False uses 16-bit atomic adds into ``y`` as the reference does.
     """
     w1, w2, x = experts_weights_matrix1, experts_weights_matrix2, activations
     fp8_form = (len(args) > 0 and not isinstance(args[0], int)) or any(
         k_ in kwargs for k_ in ("w1_scale", "w2_scale", "block_shape", "soft_fp8"))
     fp8_repacked = bool(kwargs.pop("fp8_repacked", False))
+    deterministic = bool(kwargs.pop("deterministic", True))
     if fp8_form:
         names = ["w1_scale", "w2_scale", "block_shape", "soft_fp8", "microBatchSize", "experts_map"]
         vals = {"soft_fp8": False, "microBatchSize": 16, "experts_map": None}
@@ -477,12 +480,15 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
         code = _act_code(x)
         rg = vals["APerWarp"] if vals["APerWarp"] in (1, 2) else 0
     mp, ml = _map_args(vals["experts_map"])
+    # fp32 [slots, H] buffer for the fixed-order combine (torch's caching allocator makes this a pointer bump)
+    scratch = torch.empty((batch_size * topK, k1), dtype=torch.float32, device=x.device) if deterministic else None
     check(lib.mlk_fused_experts_compute(w1.data_ptr(), w2.data_ptr(), x.data_ptr(), batch_size, E, topK, k1, k2,
                                         topk_ids.data_ptr(), actived_experts_weights.data_ptr(),
                                         sorted_token_ids.data_ptr(), cumsum_buffer.data_ptr(),
                                         padded_num_experts.data_ptr(), experts_ids.data_ptr(), C.data_ptr(),
                                         y.data_ptr(), _ptr(w1s), _ptr(w2s), code, int(fp8_repacked),
-                                        int(vals["microBatchSize"]), mp, ml, rg, 0, 0, _stream(x)))
+                                        int(vals["microBatchSize"]), mp, ml, _ptr(scratch),
+                                        0 if scratch is None else scratch.numel() * 4, rg, 0, 0, _stream(x)))
 
 
 # ---------------------------------------------------------------------------------------------------

@@ -6,7 +6,9 @@ Same signature and semantics as the reference's ``muxi_layout_kernels.muxi_moe_p
   * the router accepts any group configuration with ``num_experts % num_expert_group == 0`` (the reference
     kernel only 8 groups / 4 kept / top-8);
   * ``w1_scale``/``w2_scale`` may be ``None`` with ``soft_fp8=True`` (unit scales);
-  * the launch sequence is 4 kernels (router, alignment, GEMM1+SiLU, GEMM2+combine) instead of 6.
+  * each token's expert outputs are summed in fp32 in a fixed order and rounded once (``deterministic=True``,
+    the default); ``deterministic=False`` accumulates into ``y`` with 16-bit atomics like the reference;
+  * the launch sequence is 5 kernels (router, alignment, GEMM1+SiLU, GEMM2, combine) instead of 6.
 """
 from __future__ import annotations
 
@@ -41,6 +43,7 @@ def fused_moe(
     block_dim_x_gemm: int = 256,
     experts_map: Optional[torch.Tensor] = None,
     fp8_repacked: bool = False,
+    deterministic: bool = True,
 ) -> torch.Tensor:
     assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
     if num_expert_group is None:
@@ -94,10 +97,11 @@ def fused_moe(
         ext.fused_experts_compute(w1, w2, hidden_states, B, e1, topk, topk_ids, topk_weights, sorted_token_ids,
                                   cumsum_buffer, padded_num_experts, experts_ids, C, y, w1_scale, w2_scale,
                                   block_shape if block_shape is not None else [128, 128], soft_fp8,
-                                  experts_map=experts_map, fp8_repacked=fp8_repacked)
+                                  experts_map=experts_map, fp8_repacked=fp8_repacked, deterministic=deterministic)
     else:
         ext.fused_experts_compute(w1, w2, hidden_states, B, e1, topk, topk_ids, topk_weights, sorted_token_ids,
                                   cumsum_buffer, padded_num_experts, experts_ids, C, y, APerWarp=APerWarp,
                                   splitK=splitK, tile_m_2=tile_m_2, tile_n_2=tile_n_2, tile_k_2=tile_k_2,
-                                  block_dim_x_gemm=block_dim_x_gemm, experts_map=experts_map)
+                                  block_dim_x_gemm=block_dim_x_gemm, experts_map=experts_map,
+                                  deterministic=deterministic)
     return y.view(shape)

@@ -1,0 +1,269 @@
+"""GeMV / narrow GEMM / soft-FP8 on the GPU (through the C ABI) against the CPU oracle.
+
+Tolerance: |got - want| <= 1e-2 + 1e-2 * |want| on the 16-bit outputs (fp32 accumulation on both sides), the
+combined form of the "max-abs / max-rel <= 1e-2" bar: a bf16 value of magnitude 4..8 has a unit in the last place
+of 0.031, so a pure absolute bound cannot hold for correct results, and a pure relative one blows up near zero.
+"""
+import itertools
+
+import pytest
+import torch
+
+import muxi_native_layout_kernels_b200 as mlk
+from oracle import dense as odense
+from oracle import layouts as olay
+from tests.gpu_util import DT, assert_close, rand_e4m3, randn, require_gpu
+
+pytestmark = pytest.mark.gpu
+
+
+def _weights(m, k, seed, dtype, dev, scale=0.02):
+    W = randn((m, k), seed, scale, dtype)
+    return W, mlk.layoutA(W.to(dev))
+
+
+# ----------------------------------------------------------------------------------------------------
+# e4m3 decode: every byte value, both byte orders, exact
+# ----------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("repacked", [False, True])
+def test_e4m3_decode_is_exact_for_all_256_bytes(repacked):
+    dev = require_gpu()
+    table = torch.from_numpy(olay.e4m3_decode_table())
+    raw = (torch.arange(128 * 128, dtype=torch.int64) * 37 % 256).to(torch.uint8).reshape(128, 128)
+    assert raw.unique().numel() == 256
+    w8 = raw.view(torch.float8_e4m3fn).to(dev)
+    A = mlk.layoutA(w8)
+    if repacked:
+        A = mlk.fp8_weight_repack(A)
+    want = table[raw.long()]                      # [m, k] fp32, NaN bytes -> +-480
+    for half in range(2):                         # 64 one-hot tokens per call
+        X = torch.zeros(64, 128, dtype=torch.bfloat16)
+        X[torch.arange(64), half * 64 + torch.arange(64)] = 1.0
+        for (rg, wm, sk) in [(1, 1, 1), (2, 4, 2)]:
+            C = mlk.gemm_layoutA_soft_fp8_wapper(A, None, X.to(dev), 128, 64, 128, kernelParam1=rg, kernelParam2=wm,
+                                                 kernelParam3=sk, fp8_repacked=repacked)
+            got = C.float().cpu()                 # [token j, row] = W[row, half*64 + j]
+            assert torch.equal(got, want[:, half * 64:(half + 1) * 64].t().contiguous())
+
+
+# ----------------------------------------------------------------------------------------------------
+# GeMV
+# ----------------------------------------------------------------------------------------------------
+
+GEMV_SHAPES = [(16, 32), (64, 160), (128, 1024), (272, 352), (512, 4096)]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+@pytest.mark.parametrize("kernel_id", [1, 2])
+def test_gemv_all_launch_parameters(dt, kernel_id):
+    dev = require_gpu()
+    for (m, k) in GEMV_SHAPES:
+        W, A = _weights(m, k, 10 + m, DT[dt], dev, 0.05)
+        x = randn((1, k), 11 + k, 1.0, DT[dt])
+        want = odense.gemm_ref(x, W)
+        for threads, rg, sk in itertools.product([64, 128, 256], [1, 2], [1, 2, 4, 8]):
+            if m % (16 * rg):
+                continue
+            y = mlk.gemv_layoutA_wapper(A, x.to(dev), m, k, blockDimX=threads, kernelId=kernel_id, kernelParam1=rg,
+                                        kernelParam2=sk)
+            assert y.shape == (1, m) and y.dtype == DT[dt]
+            assert_close(y, want, f"gemv {dt} id={kernel_id} m={m} k={k} threads={threads} rg={rg} sk={sk}")
+
+
+def test_gemv_alpha_bias_and_table_path():
+    dev = require_gpu()
+    m, k = 256, 512
+    for dt in ("bf16", "fp16"):
+        W, A = _weights(m, k, 20, DT[dt], dev, 0.05)
+        x = randn((1, k), 21, 1.0, DT[dt])
+        bias = randn((1, m), 22, 1.0, DT[dt])
+        y = mlk.gemv_layoutA(A, x.to(dev), alpha=0.5, beta=3.0, bias=bias.to(dev))   # beta is ignored
+        assert_close(y, odense.gemm_ref(x, W, alpha=0.5, bias=bias), f"gemv table {dt}")
+        for kid in (1, 2):
+            y = mlk.gemv_layoutA_wapper(A, x.to(dev), m, k, alpha=2.0, kernelId=kid, bias=bias.to(dev))
+            assert_close(y, odense.gemm_ref(x, W, alpha=2.0, bias=bias), f"gemv wapper {dt} {kid}")
+
+
+@pytest.mark.parametrize("repacked", [False, True])
+def test_gemv_soft_fp8(repacked):
+    dev = require_gpu()
+    for (m, k) in [(128, 128), (256, 1024), (384, 4096)]:
+        W8 = rand_e4m3((m, k), 30 + m)
+        A = mlk.layoutA(W8.to(dev))
+        if repacked:
+            A = mlk.fp8_weight_repack(A)
+        x = randn((1, k), 31, 1.0, torch.bfloat16)
+        want = odense.gemm_ref(x, W8.to(torch.bfloat16))
+        for threads, rg, sk in itertools.product([128, 256], [1, 2], [1, 2, 8]):
+            y = mlk.gemv_layoutA_wapper(A, x.to(dev), m, k, blockDimX=threads, kernelParam1=rg, kernelParam2=sk,
+                                        fp8_repacked=repacked)
+            assert_close(y, want, f"gemv fp8 m={m} k={k} threads={threads} rg={rg} sk={sk}")
+        # block scales: compared with fp32 weight * fp32 scale (what the kernel applies, to the fp32 block sums)
+        scale = (torch.rand((m + 127) // 128, (k + 127) // 128, generator=torch.Generator().manual_seed(32)) * 2).float()
+        y = mlk.gemv_layoutA(A, x.to(dev), scale_matrix=scale.to(dev), fp8_repacked=repacked)
+        want_s = (x.float() @ odense.dequant_exact_scale(W8, scale).t()).to(torch.bfloat16)
+        assert_close(y, want_s, f"gemv fp8 scaled m={m} k={k}")
+        # and within tolerance of the reference's own dequantise-then-GEMM recipe (weights rounded to bf16 first)
+        want_r = odense.gemm_ref(x, odense.dequant_block_scaled(W8, scale))
+        assert_close(y, want_r, f"gemv fp8 scaled vs reference recipe m={m} k={k}", scale_atol=True)
+
+
+def test_gemv_kernel2_rejects_what_it_cannot_do():
+    dev = require_gpu()
+    W8 = rand_e4m3((128, 128), 40)
+    A = mlk.layoutA(W8.to(dev))
+    x = randn((1, 128), 41).to(dev)
+    with pytest.raises(RuntimeError, match="no e4m3 variant"):
+        mlk.gemv_layoutA_wapper(A, x, 128, 128, kernelId=2)
+    with pytest.raises(RuntimeError, match="kernelId"):
+        mlk.gemv_layoutA_wapper(A, x, 128, 128, kernelId=5)
+    with pytest.raises(RuntimeError, match="same k"):
+        mlk.gemv_layoutA(A, randn((1, 256), 42).to(dev))
+
+
+# ----------------------------------------------------------------------------------------------------
+# narrow GEMM, three layout variants
+# ----------------------------------------------------------------------------------------------------
+
+GEMM_CONFIGS = [(1, 1, 1), (1, 1, 8), (2, 1, 2), (1, 2, 1), (2, 2, 4), (1, 4, 2), (2, 4, 1), (1, 8, 1), (2, 8, 2)]
+TOKENS = [1, 2, 3, 8, 9, 16, 17, 32, 33, 64, 65, 128, 200, 256]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+def test_gemm_layoutA_tokens_and_configs(dt):
+    dev = require_gpu()
+    for (m, k) in [(256, 128), (512, 640), (384, 2048)]:
+        W, A = _weights(m, k, 50 + m, DT[dt], dev, 0.05)
+        for n in TOKENS:
+            X = randn((n, k), 51 + n, 1.0, DT[dt])
+            want = odense.gemm_ref(X, W)
+            for (rg, wm, sk) in GEMM_CONFIGS:
+                if m % (16 * rg * wm):
+                    continue
+                C = mlk.gemm_layoutA_wapper(A, X.to(dev), m, n, k, kernelParam1=rg, kernelParam2=wm, kernelParam3=sk)
+                assert C.shape == (n, m)
+                assert_close(C, want, f"gemm_layoutA {dt} m={m} k={k} n={n} rg={rg} wm={wm} sk={sk}")
+            assert_close(mlk.gemm_layoutA(A, X.to(dev)), want, f"gemm_layoutA table {dt} m={m} k={k} n={n}")
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+def test_gemm_layoutB_variants(dt):
+    dev = require_gpu()
+    for (m, k) in [(256, 256), (512, 1024)]:
+        W, A = _weights(m, k, 60 + m, DT[dt], dev, 0.05)
+        bias = randn((1, m), 61, 1.0, DT[dt])
+        for n in [16, 32, 48, 64, 128, 256]:
+            X = randn((n, k), 62 + n, 1.0, DT[dt])
+            XB = mlk.layoutB(X.to(dev))
+            want = odense.gemm_ref(X, W, alpha=1.5, bias=bias)
+            for (rg, wm, sk) in [(1, 1, 1), (2, 2, 2), (2, 4, 4), (1, 8, 1)]:
+                C = mlk.gemm_layoutAB_ContinuousC_wapper(A, XB, m, n, k, alpha=1.5, kernelParam1=rg, kernelParam2=wm,
+                                                         kernelParam3=sk, bias=bias.to(dev))
+                assert_close(C, want, f"ContinuousC {dt} m={m} k={k} n={n} {(rg, wm, sk)}")
+                C5 = mlk.gemm_layoutABC_wapper(A, XB, m, n, k, alpha=1.5, kernelParam1=rg, kernelParam2=wm,
+                                               kernelParam3=sk, bias=bias.to(dev))
+                assert C5.shape == (m // 32, n // 16, 4, 16, 8)
+                assert_close(mlk.reLayoutC(C5), want, f"ABC {dt} m={m} k={k} n={n} {(rg, wm, sk)}")
+                # the reference's own un-permute recipe (benchmark_and_test/gemm_benchmark.py:74-76)
+                assert torch.equal(C5.permute(1, 3, 0, 2, 4).reshape(n, m), mlk.reLayoutC(C5))
+            assert_close(mlk.gemm_layoutAB_ContinuousC(A, XB, alpha=1.5, bias=bias.to(dev)), want, "ContinuousC table")
+            assert_close(mlk.reLayoutC(mlk.gemm_layoutABC(A, XB, alpha=1.5, bias=bias.to(dev))), want, "ABC table")
+
+
+@pytest.mark.parametrize("repacked", [False, True])
+def test_gemm_soft_fp8(repacked):
+    dev = require_gpu()
+    for (m, k) in [(256, 256), (512, 1024)]:
+        W8 = rand_e4m3((m, k), 70 + m)
+        A = mlk.layoutA(W8.to(dev))
+        if repacked:
+            A = mlk.fp8_weight_repack(A)
+        scale = (torch.rand(m // 128, k // 128, generator=torch.Generator().manual_seed(71)) * 2).float()
+        for n in [1, 5, 8, 16, 24, 32, 64, 100]:
+            X = randn((n, k), 72 + n, 1.0, torch.bfloat16)
+            want = odense.gemm_ref(X, W8.to(torch.bfloat16))
+            want_s = (X.float() @ odense.dequant_exact_scale(W8, scale).t()).to(torch.bfloat16)
+            for (rg, wm, sk) in [(1, 1, 1), (2, 1, 2), (2, 2, 1), (1, 4, 2), (2, 8, 1)]:
+                C = mlk.gemm_layoutA_soft_fp8_wapper(A, None, X.to(dev), m, n, k, kernelParam1=rg, kernelParam2=wm,
+                                                     kernelParam3=sk, fp8_repacked=repacked)
+                assert_close(C, want, f"fp8 gemm m={m} k={k} n={n} {(rg, wm, sk)}")
+                Cs = mlk.gemm_layoutA_soft_fp8_wapper(A, scale.to(dev), X.to(dev), m, n, k, kernelParam1=rg,
+                                                      kernelParam2=wm, kernelParam3=sk, fp8_repacked=repacked)
+                assert_close(Cs, want_s, f"fp8 scaled gemm m={m} k={k} n={n} {(rg, wm, sk)}")
+            assert_close(mlk.gemm_layoutA_soft_fp8(A, scale.to(dev), X.to(dev), fp8_repacked=repacked), want_s, "fp8 table")
+            if not repacked:
+                assert_close(mlk.gemm_layoutA_linear(A, X.to(dev), scale_matrix=scale.to(dev)), want_s, "linear fp8")
+
+
+def test_gemm_errors_and_determinism():
+    dev = require_gpu()
+    W, A = _weights(256, 256, 80, torch.bfloat16, dev)
+    X = randn((16, 256), 81).to(dev)
+    with pytest.raises(RuntimeError, match="multiple of 128"):
+        mlk.gemm_layoutA(mlk.layoutA(randn((144, 256), 82).to(dev)), X)
+    with pytest.raises(RuntimeError, match="same k"):
+        mlk.gemm_layoutA(A, randn((16, 128), 83).to(dev))
+    with pytest.raises(RuntimeError, match="kernelId"):
+        mlk.gemm_layoutA_wapper(A, X, 256, 16, 256, kernelId=2)
+    with pytest.raises(RuntimeError, match="row tile"):
+        A128 = mlk.layoutA(randn((128, 256), 84).to(dev))
+        mlk.gemm_layoutA_wapper(A128, X, 128, 16, 256, kernelParam1=2, kernelParam2=8, kernelParam3=1)
+    with pytest.raises(RuntimeError, match="same data type"):
+        mlk.gemm_layoutA(A, X.to(torch.float16))
+    # split-K partial sums are reduced in a fixed order: bit-identical from run to run
+    ref = mlk.gemm_layoutA_wapper(A, X, 256, 16, 256, kernelParam1=1, kernelParam2=1, kernelParam3=8)
+    for _ in range(5):
+        assert torch.equal(ref, mlk.gemm_layoutA_wapper(A, X, 256, 16, 256, kernelParam1=1, kernelParam2=1, kernelParam3=8))
+
+
+# ----------------------------------------------------------------------------------------------------
+# the benchmark configurations at full size
+# ----------------------------------------------------------------------------------------------------
+
+def test_config_gemv_4096_bf16():
+    """bf16 GeMV, N=K=4096, W ~ N(0, 0.02^2), x ~ N(0,1), seed 0; oracle = fp32 matmul on the CPU, cast to bf16."""
+    dev = require_gpu()
+    W = randn((4096, 4096), 0, 0.02)
+    x = randn((1, 4096), 1000, 1.0)
+    A = mlk.layoutA(W.to(dev))
+    want = odense.gemm_ref(x, W)
+    assert_close(mlk.gemv_layoutA(A, x.to(dev)), want, "C1 table path")
+    for kid, rg, sk in [(1, 1, 1), (1, 2, 4), (2, 1, 2), (2, 2, 8)]:
+        y = mlk.gemv_layoutA_wapper(A, x.to(dev), 4096, 4096, kernelId=kid, kernelParam1=rg, kernelParam2=sk)
+        rep = assert_close(y, want, f"C1 id={kid} rg={rg} sk={sk}")
+    print("C1", rep)
+
+
+@pytest.mark.parametrize("N,K", [(4096, 4096), (14336, 4096), (4096, 14336)])
+def test_config_narrow_gemm_llama8b(N, K):
+    dev = require_gpu()
+    for dt in ("bf16", "fp16"):
+        W = randn((N, K), 1, 0.02, DT[dt])
+        A = mlk.layoutA(W.to(dev))
+        Wf = W.float()
+        for n in [1, 2, 4, 8, 16, 32, 64]:
+            X = randn((n, K), 1000 + n, 1.0, DT[dt])
+            want = (X.float() @ Wf.t()).to(DT[dt])
+            assert_close(mlk.gemm_layoutA(A, X.to(dev)), want, f"C2 layoutA {dt} {(N, K)} n={n}")
+            Xp = torch.zeros(max(16, (n + 15) // 16 * 16), K, dtype=DT[dt])
+            Xp[:n] = X                             # the layout-B variants need n % 16 == 0: zero-pad, then slice
+            XB = mlk.layoutB(Xp.to(dev))
+            assert_close(mlk.gemm_layoutAB_ContinuousC(A, XB)[:n], want, f"C2 ContinuousC {dt} {(N, K)} n={n}")
+            assert_close(mlk.reLayoutC(mlk.gemm_layoutABC(A, XB))[:n], want, f"C2 ABC {dt} {(N, K)} n={n}")
+
+
+@pytest.mark.parametrize("N,K", [(28672, 8192), (8192, 28672), (8192, 8192)])
+def test_config_soft_fp8_llama70b(N, K):
+    dev = require_gpu()
+    W8 = rand_e4m3((N, K), 2)
+    A = mlk.layoutA(W8.to(dev))
+    Wf = W8.float()
+    x = randn((1, K), 2000, 1.0)
+    assert_close(mlk.gemv_layoutA(A, x.to(dev)), (x.float() @ Wf.t()).to(torch.bfloat16), f"C3 gemv {(N, K)}")
+    A_rep = mlk.fp8_weight_repack(A)
+    for n in [1, 8, 32]:
+        X = randn((n, K), 2000 + n, 1.0)
+        want = (X.float() @ Wf.t()).to(torch.bfloat16)
+        assert_close(mlk.gemm_layoutA_soft_fp8(A, None, X.to(dev)), want, f"C3 gemm {(N, K)} n={n}")
+        assert_close(mlk.gemm_layoutA_soft_fp8(A_rep, None, X.to(dev), fp8_repacked=True), want, f"C3 repacked n={n}")
