@@ -50,6 +50,18 @@ const char* mlk_last_error(void);
 /* Build identification: "sm_100a" plus the ABI version. */
 const char* mlk_build_info(void);
 
+/* Library-wide options.
+ *   MLK_OPT_PDL (default 1): kernels are launched with programmatic stream serialization, so a kernel may become
+ *     resident while its predecessor in the stream drains; every kernel waits (griddepcontrol.wait) before it reads
+ *     anything an earlier kernel may have written and before it writes anything.
+ *   MLK_OPT_STATIC_WEIGHTS (default 0): promise that weight tensors (A, w1, w2, block scales) are not written by any
+ *     kernel of the calling stream while these ops are in flight (weights prepacked once, the serving situation).
+ *     The dense kernels then start streaming weights before that wait.  Leave it 0 if a kernel that produces
+ *     weights (e.g. mlk_layoutA) can immediately precede a GEMM on the same stream. */
+enum { MLK_OPT_PDL = 0, MLK_OPT_STATIC_WEIGHTS = 1 };
+int mlk_set_option(int option_id, int value);
+int mlk_get_option(int option_id);
+
 /* ---- dispatch tables (reference: csrc/arg_selector.cu:14-87, class per table) ------------------ */
 
 /* Reads a CSV table (header line + integer rows).  A file that cannot be opened yields MLK_ERR_IO and

@@ -19,6 +19,8 @@ PROTOTYPES = {
     "mlk_status_string": (c_cp, [c_int]),
     "mlk_last_error": (c_cp, []),
     "mlk_build_info": (c_cp, []),
+    "mlk_set_option": (c_int, [c_int, c_int]),
+    "mlk_get_option": (c_int, [c_int]),
     "mlk_table_load": (c_int, [c_int, c_cp]),
     "mlk_table_lookup": (c_int, [c_int, c_int, c_int, c_int, C.POINTER(c_int), C.POINTER(c_int)]),
     "mlk_table_file_name": (c_cp, [c_int]),
@@ -60,7 +62,7 @@ def _load() -> C.CDLL:
     path = os.environ.get("MLK_B200_LIB", str(LIB_PATH))
     if not os.path.exists(path):
         raise ImportError(
-            f"{path} is missing: build it with `python -m muxi_native_layout_kernels_b200.build` "
+            f"{path} is missing: build it with `python muxi_native_layout_kernels_b200/build.py` "
             "(needs nvcc; there is no non-CUDA fallback)"
         )
     lib = C.CDLL(path)

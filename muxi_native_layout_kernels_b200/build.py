@@ -1,6 +1,7 @@
 """Builds libmlk_b200.so (the C-ABI library of hand-written sm_100a kernels) next to this file.
 
-Usage: ``python -m muxi_native_layout_kernels_b200.build [--force] [--verbose]``.
+Usage: ``python muxi_native_layout_kernels_b200/build.py [--force] [--verbose]`` (run it as a script: importing the
+package would try to load the library that is about to be built).
 Plays the role of the reference's ``setup.py`` (setup.py:56-103: one extension, 21 sources), but the
 result is a plain shared library with an ``extern "C"`` surface and no dependency on torch headers.
 nvcc cross-compiles without a GPU, so this also runs on a CPU-only machine.

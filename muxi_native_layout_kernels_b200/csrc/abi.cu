@@ -26,6 +26,14 @@ int fail(int code, const char* fmt, ...) {
 const char* last_error() { return g_err; }
 void clear_error() { g_err[0] = 0; }
 
+namespace {
+int g_options[kNumOptions] = {1, 0};
+}
+int option(int which) { return (which >= 0 && which < kNumOptions) ? g_options[which] : 0; }
+void set_option(int which, int value) {
+    if (which >= 0 && which < kNumOptions) g_options[which] = value;
+}
+
 int launch_layout_a(const void*, void*, long long, long long, int, int, cudaStream_t);
 int launch_layout_b(const void*, void*, int, int, cudaStream_t);
 int launch_relayout_c(const void*, void*, int, int, cudaStream_t);
@@ -101,6 +109,14 @@ const char* mlk_status_string(int status) {
 const char* mlk_last_error(void) { return last_error(); }
 
 const char* mlk_build_info(void) { return "mlk_b200 abi 1, sm_100a"; }
+
+int mlk_set_option(int option_id, int value) {
+    clear_error();
+    if (option_id < 0 || option_id >= kNumOptions) return fail(kInvalidArg, "unknown option %d", option_id);
+    set_option(option_id, value);
+    return kOk;
+}
+int mlk_get_option(int option_id) { return option(option_id); }
 
 int mlk_table_load(int table, const char* csv_path) {
     clear_error();

@@ -24,6 +24,7 @@ constexpr int kSmemLimit = 200 * 1024;
 struct DenseKernelParams {
     DenseParams p;
     int stages;
+    int static_weights;
 };
 
 // Output store shared by both families: 8 consecutive weight rows of one token, 16 bytes.
@@ -59,6 +60,7 @@ __device__ __forceinline__ void emit_dense(const DenseParams& p, int token, int 
 template <int WT, int NT, int RG, bool SCALE>
 __global__ void __launch_bounds__(256) dense_mma_kernel(const DenseKernelParams kp) {
     using S = CoreShape<NT, RG>;
+    constexpr bool XDIRECT = (NT == 1);
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ CoreShared sh;
     const DenseParams& p = kp.p;
@@ -77,6 +79,33 @@ __global__ void __launch_bounds__(256) dense_mma_kernel(const DenseKernelParams 
     constexpr int gran = SCALE ? 4 : 1;
     const int parts = SK * WK;
 
+    // this warp's K slice and weight addresses need nothing but kernel arguments
+    CoreArgs a;
+    int c0, c1;
+    k_partition(total_chunks, gran, parts, cr * WK + wk, c0, c1);
+    a.nchunks = c1 - c0;
+    constexpr int esz = (WT == kE4M3) ? 1 : 2;
+    const int ldscale = (p.k + 127) >> 7;
+#pragma unroll
+    for (int r = 0; r < RG; ++r) {
+        const int rgidx = blockIdx.x * (RG * WM) + wm * RG + r;
+        a.a_lane[r] = reinterpret_cast<const uint8_t*>(p.A) + (size_t)rgidx * 16 * p.k * esz +
+                      (size_t)c0 * chunk_bytes<WT>() + t * (128 * esz) + g * 16;
+        a.scale[r] = SCALE ? p.scale + (size_t)((rgidx * 16) >> 7) * ldscale + (c0 >> 2) : nullptr;
+    }
+    AFrag<WT> ring[S::CH][RG];
+    if (kp.static_weights) {
+        // weights are never written by a kernel of this stream: start streaming them before the kernels this
+        // launch depends on have finished, and let the next launch do the same
+        ring_init<WT, NT, RG>(ring, a);
+        pdl_launch_dependents();
+        pdl_wait();
+    } else {
+        pdl_wait();
+        pdl_launch_dependents();
+        ring_init<WT, NT, RG>(ring, a);
+    }
+
     if (tid < WK) k_partition(total_chunks, gran, parts, cr * WK + tid, sh.c0[tid], sh.c1[tid]);
     if (tid < nt) {
         const int row = tok0 + tid;
@@ -87,9 +116,6 @@ __global__ void __launch_bounds__(256) dense_mma_kernel(const DenseKernelParams 
     }
     __syncthreads();
 
-    CoreArgs a;
-    const int c0 = sh.c0[wk];
-    a.nchunks = sh.c1[wk] - c0;
     a.steps = (max_part_chunks(total_chunks, gran, parts) + S::CH - 1) / S::CH;
     a.nt = nt;
     a.wk = wk;
@@ -102,18 +128,9 @@ __global__ void __launch_bounds__(256) dense_mma_kernel(const DenseKernelParams 
     a.qstride = (p.x_layout == 0) ? 16 : 256;
     a.sel01 = p.fp8_order ? kSelRep01 : kSelNat01;
     a.sel23 = p.fp8_order ? kSelRep23 : kSelNat23;
-    constexpr int esz = (WT == kE4M3) ? 1 : 2;
-    const int ldscale = (p.k + 127) >> 7;
-#pragma unroll
-    for (int r = 0; r < RG; ++r) {
-        const int rgidx = blockIdx.x * (RG * WM) + wm * RG + r;
-        a.a_lane[r] = reinterpret_cast<const uint8_t*>(p.A) + (size_t)rgidx * 16 * p.k * esz +
-                      (size_t)c0 * chunk_bytes<WT>() + t * (128 * esz) + g * 16;
-        a.scale[r] = SCALE ? p.scale + (size_t)((rgidx * 16) >> 7) * ldscale + (c0 >> 2) : nullptr;
-    }
 
     float acc[RG][NT][4];
-    stream_mma<WT, NT, RG, SCALE>(acc, a, sh);
+    stream_mma<WT, NT, RG, SCALE, XDIRECT>(acc, ring, a, sh);
 
     float* part = reinterpret_cast<float*>(smem);
     const int PR = rows_cta + 4;
@@ -138,7 +155,7 @@ int launch_mma_inst(const DenseParams& p, cudaStream_t stream) {
     int stages = 3;
     for (;;) {
         const int WK = (threads / 32) / p.wm;
-        const size_t stage = (size_t)WK * ntmax * S::PITCH;
+        const size_t stage = (NT == 1) ? 0 : (size_t)WK * ntmax * S::PITCH;   // one token tile: no staging
         const size_t part = (size_t)WK * S::NTP * (rows_cta + 4) * sizeof(float);
         stages = (std::max(stage * 3, part) > (size_t)kSmemLimit) ? 2 : 3;
         smem = std::max(stage * stages, part);
@@ -158,19 +175,15 @@ int launch_mma_inst(const DenseParams& p, cudaStream_t stream) {
         if (e != cudaSuccess) return fail(kCudaError, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
         attr_set[dev & 63] = true;
     }
-    DenseKernelParams kp{p, stages};
+    DenseKernelParams kp{p, stages, option(kOptStaticWeights)};
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.m / rows_cta, p.sk, (p.n + kTokBlock - 1) / kTokBlock);
     cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = p.sk;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
     cfg.attrs = attr;
-    cfg.numAttrs = (p.sk > 1) ? 1 : 0;
+    cfg.numAttrs = launch_attrs(attr, p.sk);
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, kp);
     if (e != cudaSuccess) return fail(kCudaError, "dense_mma launch: %s", cudaGetErrorString(e));
     return kOk;
@@ -193,7 +206,7 @@ int launch_mma_wt(const DenseParams& p, cudaStream_t stream) {
 // 8 fp32 FMAs.  One xor-16 shuffle folds the two octet halves, shared memory folds the K slices.
 // ---------------------------------------------------------------------------------------------
 template <int WT, int RG>
-__global__ void __launch_bounds__(256) gemv_simt_kernel(const DenseParams p) {
+__global__ void __launch_bounds__(256) gemv_simt_kernel(const DenseParams p, const int static_weights) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int D = 8;   // 16-byte weight loads in flight per row group
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -218,11 +231,19 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const DenseParams p) {
     for (int r = 0; r < RG; ++r) acc[r] = 0.f;
 
     uint4 ring[D][RG];
+    if (!static_weights) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
 #pragma unroll
     for (int d = 0; d < D; ++d)
 #pragma unroll
         for (int r = 0; r < RG; ++r)
             ring[d][r] = (d < nunits) ? ldg_stream16(ap[r] + (size_t)d * 512) : make_uint4(0, 0, 0, 0);
+    if (static_weights) {   // see dense_mma_kernel
+        pdl_launch_dependents();
+        pdl_wait();
+    }
 
     for (int ub = 0; ub < nunits; ub += D) {
 #pragma unroll
@@ -268,14 +289,10 @@ int launch_simt_inst(const DenseParams& p, cudaStream_t stream) {
     cfg.blockDim = dim3(p.threads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = p.sk;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
     cfg.attrs = attr;
-    cfg.numAttrs = (p.sk > 1) ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_simt_kernel<WT, RG>, p);
+    cfg.numAttrs = launch_attrs(attr, p.sk);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_simt_kernel<WT, RG>, p, option(kOptStaticWeights));
     if (e != cudaSuccess) return fail(kCudaError, "gemv_simt launch: %s", cudaGetErrorString(e));
     return kOk;
 }

@@ -52,6 +52,10 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const MoeGemmParams p) {
     __shared__ CoreShared sh;
     __shared__ int slot_of[kTokBlock];
 
+    // the work list comes from the alignment kernel earlier in the stream
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr bool XDIRECT = (NT == 1);
     const int n_items = p.worklist[0].x;
     if ((int)blockIdx.z >= n_items) return;   // uniform over the cluster (clusters span y only)
     const int4 item = p.worklist[1 + blockIdx.z];
@@ -67,29 +71,10 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const MoeGemmParams p) {
     constexpr int gran = SCALE ? 4 : 1;
     const int parts = SK * WK;
 
-    if (tid < WK) k_partition(total_chunks, gran, parts, cr * WK + tid, sh.c0[tid], sh.c1[tid]);
-    if (tid < nt) {
-        const int slot = p.sorted[pos0 + tid];
-        slot_of[tid] = slot;
-        sh.xrow[tid] = (unsigned long long)p.xsrc + (unsigned long long)(slot / p.x_row_div) * p.x_row_bytes;
-    }
-    __syncthreads();
-
     CoreArgs a;
-    const int c0 = sh.c0[wk];
-    a.nchunks = sh.c1[wk] - c0;
-    a.steps = (max_part_chunks(total_chunks, gran, parts) + S::CH - 1) / S::CH;
-    a.nt = nt;
-    a.wk = wk;
-    a.WK = WK;
-    a.stages = p.stages;
-    a.xs_base = smem_u32(smem);
-    a.xrows = nt;
-    a.stage_bytes = WK * nt * S::PITCH;
-    a.cstride = 64;
-    a.qstride = 16;
-    a.sel01 = p.fp8_order ? kSelRep01 : kSelNat01;
-    a.sel23 = p.fp8_order ? kSelRep23 : kSelNat23;
+    int c0, c1;
+    k_partition(total_chunks, gran, parts, cr * WK + wk, c0, c1);
+    a.nchunks = c1 - c0;
     constexpr int esz = (WT == kE4M3) ? 1 : 2;
     const int ldscale = (p.k + 127) >> 7;
     const uint8_t* wbase = p.w + (long long)expert * p.w_expert_bytes;
@@ -106,9 +91,32 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const MoeGemmParams p) {
         a.a_lane[r] = wbase + (size_t)rgidx * 16 * p.k * esz + (size_t)c0 * chunk_bytes<WT>() + t * (128 * esz) + g * 16;
         a.scale[r] = SCALE ? sbase + (size_t)((rgidx * 16) >> 7) * ldscale + (c0 >> 2) : nullptr;
     }
+    AFrag<WT> ring[S::CH][RG];
+    ring_init<WT, NT, RG>(ring, a);
+
+    if (tid < WK) k_partition(total_chunks, gran, parts, cr * WK + tid, sh.c0[tid], sh.c1[tid]);
+    if (tid < nt) {
+        const int slot = p.sorted[pos0 + tid];
+        slot_of[tid] = slot;
+        sh.xrow[tid] = (unsigned long long)p.xsrc + (unsigned long long)(slot / p.x_row_div) * p.x_row_bytes;
+    }
+    __syncthreads();
+
+    a.steps = (max_part_chunks(total_chunks, gran, parts) + S::CH - 1) / S::CH;
+    a.nt = nt;
+    a.wk = wk;
+    a.WK = WK;
+    a.stages = p.stages;
+    a.xs_base = smem_u32(smem);
+    a.xrows = nt;
+    a.stage_bytes = WK * nt * S::PITCH;
+    a.cstride = 64;
+    a.qstride = 16;
+    a.sel01 = p.fp8_order ? kSelRep01 : kSelNat01;
+    a.sel23 = p.fp8_order ? kSelRep23 : kSelNat23;
 
     float acc[RG][NT][4];
-    stream_mma<WT, NT, RG, SCALE>(acc, a, sh);
+    stream_mma<WT, NT, RG, SCALE, XDIRECT>(acc, ring, a, sh);
 
     float* part = reinterpret_cast<float*>(smem);
     const int rows_cta = 16 * RG * WM;
@@ -201,7 +209,7 @@ int launch_moe_inst(const MoeGemmParams& p0, int tiles, int sk, int max_items, c
     const int warps = 8;
     const int WK = warps / p.wm;
     const int rows_cta = 16 * RG * p.wm;
-    const size_t stage = (size_t)WK * S::NTP * S::PITCH;
+    const size_t stage = (NT == 1) ? 0 : (size_t)WK * S::NTP * S::PITCH;
     const size_t part = (size_t)WK * S::NTP * (rows_cta + 4) * sizeof(float);
     int stages = 3;
     if (std::max(stage * 3, part) > (size_t)kSmemLimit) stages = 2;
@@ -223,13 +231,9 @@ int launch_moe_inst(const MoeGemmParams& p0, int tiles, int sk, int max_items, c
     cfg.blockDim = dim3(warps * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = sk;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
     cfg.attrs = attr;
-    cfg.numAttrs = (sk > 1) ? 1 : 0;
+    cfg.numAttrs = launch_attrs(attr, sk);
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
     if (e != cudaSuccess) return fail(kCudaError, "moe gemm launch: %s", cudaGetErrorString(e));
     return kOk;

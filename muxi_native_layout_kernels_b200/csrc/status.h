@@ -23,6 +23,33 @@ int fail(int code, const char* fmt, ...);
 const char* last_error();
 void clear_error();
 
+// Library-wide options (mlk_set_option).
+enum Option : int {
+    kOptPdl = 0,            // launch kernels with programmatic stream serialization (default 1)
+    kOptStaticWeights = 1,  // weight tensors are never written by kernels of the calling stream (default 0)
+    kNumOptions = 2,
+};
+int option(int which);
+void set_option(int which, int value);
+
+// Fills the launch attributes common to the streaming kernels: cluster split-K and programmatic dependent launch.
+inline int launch_attrs(cudaLaunchAttribute* attr, int cluster_y) {
+    int n = 0;
+    if (cluster_y > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = cluster_y;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (option(kOptPdl)) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    return n;
+}
+
 inline int check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(kCudaError, "%s: %s", what, cudaGetErrorString(e));

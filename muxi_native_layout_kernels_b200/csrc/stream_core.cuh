@@ -97,6 +97,30 @@ __device__ __forceinline__ void load_afrag(AFrag<WT>& f, const uint8_t* p, bool 
     }
 }
 
+// Programmatic dependent launch: lets the next kernel of the stream become resident while this one drains.
+// wait() returns once every kernel this launch depends on has completed and its writes are visible; nothing
+// produced by an earlier kernel may be read, and nothing may be written, before it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Issues the first CH chunks of this lane's weight stream (the prefetch ring).
+template <int WT, int NT, int RG>
+__device__ __forceinline__ void ring_init(AFrag<WT> (&ring)[CoreShape<NT, RG>::CH][RG], const CoreArgs& a) {
+    constexpr int CH = CoreShape<NT, RG>::CH;
+    constexpr int CB = chunk_bytes<WT>();
+#pragma unroll
+    for (int cc = 0; cc < CH; ++cc)
+#pragma unroll
+        for (int r = 0; r < RG; ++r)
+            load_afrag<WT>(ring[cc][r], a.a_lane[r] + (long long)cc * CB, cc < a.nchunks);
+}
+
+__device__ __forceinline__ uint4 ldg_cached16(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+
 // The main loop.  acc[r][j] is the 16x8 fp32 tile of row group r and token tile j.
 //
 // Lane (g,t) addressing inside a 32-k chunk c:
@@ -104,13 +128,17 @@ __device__ __forceinline__ void load_afrag(AFrag<WT>& f, const uint8_t* p, bool 
 //   e4m3 weights:   rows 2g and 2g+1 of k-octet 4c+t (one 16-byte load); the MMA row index
 //                   rho maps to weight row 2*rho (rho < 8) or 2*(rho-8)+1, undone when the
 //                   accumulators are written out.
-//   tokens:         row 8j+g, k-octet 4c+t (one 16-byte shared-memory load)
-template <int WT, int NT, int RG, bool SCALE>
-__device__ __forceinline__ void stream_mma(float (&acc)[RG][NT][4], const CoreArgs& a,
-                                           const CoreShared& sh) {
+//   tokens:         row 8j+g, k-octet 4c+t (one 16-byte load)
+// XDIRECT (NT == 1 only): the token fragments come straight from global memory through L1 with their own
+// register ring -- no shared-memory stages and no CTA barrier in the loop, every warp streams on its own.
+// Otherwise the token tile is staged through shared memory (cp.async, 2-3 stages) and shared by the row warps.
+template <int WT, int NT, int RG, bool SCALE, bool XDIRECT>
+__device__ __forceinline__ void stream_mma(float (&acc)[RG][NT][4], AFrag<WT> (&ring)[CoreShape<NT, RG>::CH][RG],
+                                           const CoreArgs& a, const CoreShared& sh) {
     using S = CoreShape<NT, RG>;
     constexpr int CH = S::CH;
     constexpr int CB = chunk_bytes<WT>();
+    static_assert(!XDIRECT || NT == 1, "direct token loads are for a single token tile");
     const int lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
 
@@ -134,43 +162,56 @@ __device__ __forceinline__ void stream_mma(float (&acc)[RG][NT][4], const CoreAr
         }
     }
 
-    // token-tile prologue
-    for (int st = 0; st < a.stages - 1; ++st) {
-        if (st < a.steps) fill_stage<NT, RG>(a, sh, st, st);
-        cp_async_commit();
-    }
-
-    // weight prefetch ring: CH chunks per row group
-    AFrag<WT> ring[CH][RG];
+    uint4 xring[XDIRECT ? CH : 1];
+    const uint8_t* xlane = nullptr;
+    if constexpr (XDIRECT) {
+        const bool has_row = g < a.nt;
+        xlane = has_row ? reinterpret_cast<const uint8_t*>(sh.xrow[g]) + (long long)sh.c0[a.wk] * a.cstride + t * a.qstride
+                        : nullptr;
 #pragma unroll
-    for (int cc = 0; cc < CH; ++cc)
-#pragma unroll
-        for (int r = 0; r < RG; ++r)
-            load_afrag<WT>(ring[cc][r], a.a_lane[r] + (long long)cc * CB, cc < a.nchunks);
-
-    const uint32_t lane_x = ((uint32_t)t ^ ((uint32_t)(g & 1) << 2)) << 4;
-
-    for (int s = 0; s < a.steps; ++s) {
-        if (a.stages == 3) cp_async_wait<1>(); else cp_async_wait<0>();
-        __syncthreads();
-        {
-            const int sf = s + a.stages - 1;
-            if (sf < a.steps) fill_stage<NT, RG>(a, sh, sf, sf % a.stages);
+        for (int cc = 0; cc < CH; ++cc)
+            xring[cc] = (has_row && cc < a.nchunks) ? ldg_cached16(xlane + (long long)cc * a.cstride) : make_uint4(0, 0, 0, 0);
+    } else {
+        // token-tile prologue
+        for (int st = 0; st < a.stages - 1; ++st) {
+            if (st < a.steps) fill_stage<NT, RG>(a, sh, st, st);
             cp_async_commit();
         }
-        const uint32_t xs =
-            a.xs_base + (s % a.stages) * a.stage_bytes + a.wk * a.xrows * S::PITCH + g * S::PITCH;
+    }
+
+    const uint32_t lane_x = ((uint32_t)t ^ ((uint32_t)(g & 1) << 2)) << 4;
+    const int steps = XDIRECT ? (a.nchunks + CH - 1) / CH : a.steps;
+
+    for (int s = 0; s < steps; ++s) {
+        uint32_t xs = 0;
+        if constexpr (!XDIRECT) {
+            if (a.stages == 3) cp_async_wait<1>(); else cp_async_wait<0>();
+            __syncthreads();
+            {
+                const int sf = s + a.stages - 1;
+                if (sf < a.steps) fill_stage<NT, RG>(a, sh, sf, sf % a.stages);
+                cp_async_commit();
+            }
+            xs = a.xs_base + (s % a.stages) * a.stage_bytes + a.wk * a.xrows * S::PITCH + g * S::PITCH;
+        }
 
 #pragma unroll
         for (int cc = 0; cc < CH; ++cc) {
             // token fragments of this chunk
             uint4 xb[NT];
+            if constexpr (XDIRECT) {
+                xb[0] = xring[cc];
+                const int cn = (s + 1) * CH + cc;
+                xring[cc] = (xlane != nullptr && cn < a.nchunks) ? ldg_cached16(xlane + (long long)cn * a.cstride)
+                                                               : make_uint4(0, 0, 0, 0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                if (8 * j + g < a.nt) {
-                    xb[j] = lds16(xs + j * 8 * S::PITCH + (((uint32_t)cc << 6) ^ lane_x));
-                } else {
-                    xb[j] = make_uint4(0, 0, 0, 0);
+                for (int j = 0; j < NT; ++j) {
+                    if (8 * j + g < a.nt) {
+                        xb[j] = lds16(xs + j * 8 * S::PITCH + (((uint32_t)cc << 6) ^ lane_x));
+                    } else {
+                        xb[j] = make_uint4(0, 0, 0, 0);
+                    }
                 }
             }
             if constexpr (SCALE) {
@@ -227,7 +268,7 @@ __device__ __forceinline__ void stream_mma(float (&acc)[RG][NT][4], const CoreAr
             }
         }
     }
-    cp_async_wait<0>();
+    if constexpr (!XDIRECT) cp_async_wait<0>();
     __syncthreads();   // every warp is done with the token stages: shared memory can be reused
 }
 

@@ -17,6 +17,7 @@ import torch
 from ._lib import MlkError, check, lib
 
 __all__ = [
+    "set_static_weights", "set_pdl",
     "layoutA", "layoutA_inverse", "layoutB", "reLayoutC", "fp8_weight_repack",
     "gemv_layoutA", "gemv_layoutA_wapper",
     "gemm_layoutA", "gemm_layoutA_wapper", "gemm_layoutA_soft_fp8", "gemm_layoutA_soft_fp8_wapper",
@@ -28,6 +29,18 @@ __all__ = [
 ]
 
 _FP8_DTYPES = tuple(getattr(torch, n) for n in ("float8_e4m3fn", "uint8", "int8") if hasattr(torch, n))
+
+
+def set_static_weights(enabled: bool) -> None:
+    """Promise that weight tensors are not written by kernels of the calling stream while ops of this library are
+    in flight (weights prepacked once, then only read).  The dense kernels then begin streaming weights while the
+    preceding kernel is still draining.  Off by default."""
+    check(lib.mlk_set_option(1, int(bool(enabled))))
+
+
+def set_pdl(enabled: bool) -> None:
+    """Programmatic dependent launch for all kernels of this library (on by default)."""
+    check(lib.mlk_set_option(0, int(bool(enabled))))
 
 
 def _chk(cond: bool, msg: str) -> None:

@@ -162,7 +162,10 @@ def main(argv=None):
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
     ap.add_argument("--out", default=str(PKG_DIR), help="directory of the table files")
     ap.add_argument("--redo", action="store_true", help="re-scan keys that are already in the table")
+    ap.add_argument("--no-static-weights", action="store_true",
+                    help="time without the static-weights promise (see ext.set_static_weights)")
     a = ap.parse_args(argv)
+    mlk.set_static_weights(not a.no_static_weights)
     fname, kind = TABLES[a.table]
     gemv = kind.startswith("gemv")
     dtype = torch.float16 if (a.dtype == "fp16" or kind == "gemv_fp16") and kind != "gemv_bf16" else torch.bfloat16

@@ -217,6 +217,36 @@ def test_gemm_errors_and_determinism():
         assert torch.equal(ref, mlk.gemm_layoutA_wapper(A, X, 256, 16, 256, kernelParam1=1, kernelParam2=1, kernelParam3=8))
 
 
+def test_static_weights_and_pdl_modes_give_identical_results():
+    """Launch options change when loads are issued, never what is computed: bit-identical outputs."""
+    dev = require_gpu()
+    W, A = _weights(1024, 2048, 90, torch.bfloat16, dev)
+    torch.cuda.synchronize()           # the weights are complete before any launch under the static promise
+    outs = {}
+    try:
+        for pdl, static in [(True, False), (True, True), (False, False)]:
+            mlk.set_pdl(pdl)
+            mlk.set_static_weights(static)
+            res = []
+            x = randn((1, 2048), 91).to(dev)
+            for it in range(20):       # a dependent chain: each output feeds the next activation
+                y = mlk.gemv_layoutA_wapper(A, x, 1024, 2048, kernelId=1 + it % 2, kernelParam1=1 + it % 2, kernelParam2=2)
+                C = mlk.gemm_layoutA_wapper(A, torch.cat([x, x * 0.5]).contiguous(), 1024, 2, 2048, kernelParam1=1,
+                                            kernelParam2=2, kernelParam3=2)
+                C16 = mlk.gemm_layoutA_wapper(A, x.expand(16, 2048).contiguous(), 1024, 16, 2048, kernelParam1=2,
+                                              kernelParam2=2, kernelParam3=1)
+                res += [y, C, C16]
+                x = torch.cat([y, y], dim=1).contiguous()
+            torch.cuda.synchronize()
+            outs[(pdl, static)] = [r.cpu() for r in res]
+    finally:
+        mlk.set_pdl(True)
+        mlk.set_static_weights(False)
+    base = outs[(False, False)]
+    for k_, v in outs.items():
+        assert all(torch.equal(a, b) for a, b in zip(v, base)), k_
+
+
 # ----------------------------------------------------------------------------------------------------
 # the benchmark configurations at full size
 # ----------------------------------------------------------------------------------------------------
