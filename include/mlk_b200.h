@@ -102,16 +102,31 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
 
 /* ---- narrow GEMM: C[n,m] = alpha * B A^T (+ bias), n <= 256 ------------------------------------------- */
 
-/* kernelId 1: kernelParam1 = row groups per warp (1,2), kernelParam2 = row warps per CTA (1,2,4,8),
- * kernelParam3 = split-K over a thread-block cluster (1,2,4,8). */
+/* kernelId 1 (warp-level tensor-core streaming kernel, any n <= 256): kernelParam1 = row groups per warp (1,2),
+ *   kernelParam2 = row warps per CTA (1,2,4,8), kernelParam3 = split-K over a thread-block cluster (1,2,4,8).
+ * kernelId 2 (tcgen05 / tensor-memory tile kernel, 16-bit weights, row-major B, n <= 64): kernelParam1 = split-K CTAs
+ *   per 128-row tile (>= 1), kernelParam2 = TMA pipeline stages (2,4,6,8), kernelParam3 unused.  Split-K > 1 needs the
+ *   caller-provided scratch below; without it the kernel runs with split-K 1. */
+
+/* Scratch lent to one call (device pointers).  workspace: tiles * splitK * Npad * 128 floats, any content
+ * (tiles = m/128, Npad = 16, 32 or 64).  counters: >= m/128 ints that are zero on entry; every kernel leaves them
+ * zero again, so one buffer per stream can be reused by successive calls.  status: one int, sticky error word of the
+ * bounded waits inside the kernel (0 = ok), may be NULL. */
+typedef struct mlk_aux {
+    void* workspace;
+    int64_t workspace_bytes;
+    int32_t* counters;
+    int32_t n_counters;
+    int32_t* status;
+} mlk_aux;
 
 /* A layout A, B row-major [n,k], C row-major [n,m].  Reference: gemm_layoutA_wapper, csrc/gemm_layout_A.cu:684-750. */
 int mlk_gemm_layoutA_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha,
                             float beta, int kernelParam1, int kernelParam2, int kernelParam3, int kernelId,
-                            const void* bias, mlk_stream_t s);
+                            const void* bias, const mlk_aux* aux, mlk_stream_t s);
 /* Reference: gemm_layoutA, csrc/gemm_layout_A.cu:752-787. */
 int mlk_gemm_layoutA(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha, float beta,
-                     const void* bias, mlk_stream_t s);
+                     const void* bias, const mlk_aux* aux, mlk_stream_t s);
 /* e4m3 A with fp32 128x128 block scales (NULL = ones), bf16 B and C.
  * Reference: gemm_layoutA_soft_fp8_wapper, csrc/gemm_layout_A_soft_fp8.cu:749. */
 int mlk_gemm_layoutA_soft_fp8_wapper(const void* A, const float* A_scale, const void* B, void* C, int m, int n, int k,

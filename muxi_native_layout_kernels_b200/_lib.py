@@ -32,8 +32,8 @@ PROTOTYPES = {
                                         c_int, c_vp, c_vp, c_int, c_vp]),
     "mlk_gemv_layoutA": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_vp, c_int, c_vp]),
     "mlk_gemm_layoutA_wapper": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_int, c_int,
-                                        c_int, c_int, c_vp, c_vp]),
-    "mlk_gemm_layoutA": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_vp]),
+                                        c_int, c_int, c_vp, c_vp, c_vp]),
+    "mlk_gemm_layoutA": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_vp, c_vp]),
     "mlk_gemm_layoutA_soft_fp8_wapper": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_f32, c_f32, c_int,
                                                  c_int, c_int, c_int, c_vp, c_int, c_vp]),
     "mlk_gemm_layoutA_soft_fp8": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_int,
@@ -52,6 +52,12 @@ PROTOTYPES = {
                                           c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp,
                                           c_int, c_vp, c_i64, c_int, c_int, c_int, c_vp]),
 }
+
+
+class MlkAux(C.Structure):
+    """struct mlk_aux of include/mlk_b200.h."""
+    _fields_ = [("workspace", c_vp), ("workspace_bytes", c_i64), ("counters", c_vp), ("n_counters", C.c_int32),
+                ("status", c_vp)]
 
 
 class MlkError(RuntimeError):

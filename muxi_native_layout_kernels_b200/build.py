@@ -25,6 +25,7 @@ LIB_PATH = PKG_DIR / "libmlk_b200.so"
 SOURCES = [
     "abi.cu",
     "dense.cu",
+    "dense_umma.cu",
     "prepack.cu",
     "moe_router.cu",
     "moe_align.cu",

@@ -60,32 +60,45 @@ int check_gemm_shape(int m, int n, int k) {
 
 int gemm_common(int variant_x, int variant_c, const void* A, const float* scale, const void* B, void* C, int m, int n,
                 int k, int dtype, float alpha, int p1, int p2, int p3, int kernelId, const void* bias, int fp8_order,
-                cudaStream_t s) {
+                cudaStream_t s, const mlk_aux* aux = nullptr) {
     clear_error();
     const int wt = wt_of(dtype);
     if (wt < 0) return fail(kInvalidArg, "Unsupported data type code %d", dtype);
     if (int st = check_gemm_shape(m, n, k)) return st;
-    if (kernelId != 1)
-        return fail(kUnsupported, "gemm: kernelId %d is not built (1 = tensor-core streaming kernel)", kernelId);
     DenseParams p{};
     p.A = A; p.X = B; p.C = C; p.bias = bias; p.scale = scale;
     p.m = m; p.n = n; p.k = k; p.alpha = alpha;
     p.x_layout = variant_x; p.c_layout = variant_c; p.fp8_order = fp8_order;
+    if (kernelId == 2) {
+        DenseAux da{};
+        if (aux) {
+            da.workspace = aux->workspace; da.workspace_bytes = aux->workspace_bytes; da.counters = aux->counters;
+            da.n_counters = aux->n_counters; da.status = aux->status;
+        }
+        int sk = p1;
+        if (!aux || !aux->workspace || !aux->counters) sk = 1;
+        return launch_dense_umma(wt, p, sk, p2, aux ? &da : nullptr, s);
+    }
+    if (kernelId != 1)
+        return fail(kUnsupported, "gemm: kernelId %d is not built (1 = warp-level streaming kernel, 2 = tcgen05 tile kernel)", kernelId);
     p.rg = p1; p.wm = p2; p.sk = p3; p.threads = 256;
     return launch_dense_mma(wt, p, s);
 }
 
 int gemm_table(int table, int variant_x, int variant_c, const void* A, const float* scale, const void* B, void* C,
-               int m, int n, int k, int dtype, float alpha, const void* bias, int fp8_order, cudaStream_t s) {
+               int m, int n, int k, int dtype, float alpha, const void* bias, int fp8_order, cudaStream_t s,
+               const mlk_aux* aux = nullptr) {
     clear_error();
     if (int st = check_gemm_shape(m, n, k)) return st;
     TuneArgs t = global_table(table).get(m, n, k, nullptr);
     // A table row that this shape cannot run with (e.g. copied from another GPU's table) falls back to the default.
-    const bool ok = t.a == 1 && (t.b == 1 || t.b == 2) && (t.c == 1 || t.c == 2 || t.c == 4 || t.c == 8) &&
-                    (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b * t.c) == 0;
-    if (!ok) t = default_args(table, m, n, k);
+    const bool ok1 = t.a == 1 && (t.b == 1 || t.b == 2) && (t.c == 1 || t.c == 2 || t.c == 4 || t.c == 8) &&
+                     (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b * t.c) == 0;
+    const bool ok2 = t.a == 2 && variant_x == 0 && dtype != MLK_E4M3 && n <= 64 && t.b >= 1 &&
+                     (t.c == 2 || t.c == 4 || t.c == 6 || t.c == 8);
+    if (!ok1 && !ok2) t = default_args(table, m, n, k);
     return gemm_common(variant_x, variant_c, A, scale, B, C, m, n, k, dtype, alpha, t.b, t.c, t.d, t.a, bias,
-                       fp8_order, s);
+                       fp8_order, s, aux);
 }
 
 }  // namespace
@@ -192,14 +205,14 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
 }
 
 int mlk_gemm_layoutA_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha, float,
-                            int p1, int p2, int p3, int kernelId, const void* bias, mlk_stream_t s) {
+                            int p1, int p2, int p3, int kernelId, const void* bias, const mlk_aux* aux, mlk_stream_t s) {
     if (dtype == MLK_E4M3) { clear_error(); return fail(kInvalidArg, "gemm_layoutA: use the soft_fp8 entry point for e4m3 weights"); }
-    return gemm_common(0, 0, A, nullptr, B, C, m, n, k, dtype, alpha, p1, p2, p3, kernelId, bias, 0, (cudaStream_t)s);
+    return gemm_common(0, 0, A, nullptr, B, C, m, n, k, dtype, alpha, p1, p2, p3, kernelId, bias, 0, (cudaStream_t)s, aux);
 }
 int mlk_gemm_layoutA(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha, float,
-                     const void* bias, mlk_stream_t s) {
+                     const void* bias, const mlk_aux* aux, mlk_stream_t s) {
     if (dtype == MLK_E4M3) { clear_error(); return fail(kInvalidArg, "gemm_layoutA: use the soft_fp8 entry point for e4m3 weights"); }
-    return gemm_table(kTableGemmLayoutA, 0, 0, A, nullptr, B, C, m, n, k, dtype, alpha, bias, 0, (cudaStream_t)s);
+    return gemm_table(kTableGemmLayoutA, 0, 0, A, nullptr, B, C, m, n, k, dtype, alpha, bias, 0, (cudaStream_t)s, aux);
 }
 int mlk_gemm_layoutA_soft_fp8_wapper(const void* A, const float* A_scale, const void* B, void* C, int m, int n, int k,
                                      float alpha, float, int p1, int p2, int p3, int kernelId, const void* bias,

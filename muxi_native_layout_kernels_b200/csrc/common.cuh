@@ -147,6 +147,12 @@ __device__ __forceinline__ float round16(float v) {
     }
 }
 
+// Programmatic dependent launch: lets the next kernel of the stream become resident while this one drains.
+// wait() returns once every kernel this launch depends on has completed and its writes are visible; nothing
+// produced by an earlier kernel may be read, and nothing may be written, before it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);

@@ -24,8 +24,18 @@ struct DenseParams {
     int threads;          // CTA size (64,128,256)
 };
 
+// Caller-provided scratch for kernels that split K over independent CTAs (all pointers device memory).
+struct DenseAux {
+    void* workspace;             // fp32 partial tiles, any content
+    long long workspace_bytes;
+    int* counters;               // zero on entry; every kernel leaves them zero again
+    int n_counters;
+    int* status;                 // sticky error word, 0 = ok; may be null
+};
+
 // wt: kBF16 / kFP16 / kE4M3.  Returns an mlk status code.
 int launch_dense_mma(int wt, const DenseParams& p, cudaStream_t stream);
+int launch_dense_umma(int wt, const DenseParams& p, int sk, int stages, const DenseAux* aux, cudaStream_t stream);
 int launch_gemv_simt(int wt, const DenseParams& p, int rows_per_warp_log2, cudaStream_t stream);
 
 }  // namespace mlk

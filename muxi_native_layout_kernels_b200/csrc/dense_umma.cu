@@ -1,0 +1,427 @@
+// Narrow GEMM for 16..64 tokens on the 5th-generation tensor cores: C[n,m] = alpha * X[n,k] * A[m,k]^T (+ bias).
+//
+// "Swap-AB" tile: the 128 weight rows are the UMMA M dimension, the (padded) tokens the N dimension, the fp32
+// accumulator [128 x N] lives in tensor memory.  Why the native weight layout fits without any shuffle: one
+// layout-A block [16 rows][8 k] is 256 contiguous bytes = two K-major, no-swizzle UMMA core matrices (8 rows x 16
+// bytes each).  A 3-D TMA tensor map over global memory (256-byte block, row group, k-octet) with box
+// (block, 8 row groups, 8 k-octets) lands a 128 x 64 weight tile in shared memory as [k-octet][row group][256 B],
+// which one shared-memory descriptor addresses with uniform strides: 8-row step 128 B, k-octet step 2048 B.
+// Activations are row-major; a 2-D tensor map with the 128-byte swizzle delivers the [N x 64] tile in the
+// canonical K-major SW128 layout (rows beyond n are zero-filled by the TMA unit).
+//
+// Structure per CTA (128 threads): lane 0 of warp 0 issues TMA loads into a ring of stages, lane 0 of warp 1
+// issues tcgen05.mma (4 per stage, K = 16 each) and releases stages with tcgen05.commit, then all four warps read
+// the accumulator with tcgen05.ld and write the output.  K is split over gridDim.y CTAs; partial tiles go to an
+// fp32 workspace and the CTA that arrives last at a per-tile counter adds them in a fixed order (no spinning,
+// bit-reproducible).  Every mbarrier wait is bounded: on expiry the kernel records a code in *status, stops, waits
+// (bounded) for its own TMA copies, frees its tensor memory and returns.
+//
+// Role in the reference: the CTA-tile kernel GemmMmaJustLayoutAKernel2 (csrc/gemm_layout_A.cu:296) -- weights and
+// tokens staged through shared memory, tile_m in {64,128}, tile_k 128 -- selected by kernelId 2 in the tables.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "dense.cuh"
+#include "status.h"
+
+namespace mlk {
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kBlockK = 64;                       // k elements per stage
+constexpr int kABytes = kTileM * kBlockK * 2;     // 16 KB
+constexpr uint32_t kSpinLimit = 1u << 20;         // try_wait attempts before giving up (about a second at worst)
+
+struct UmmaParams {
+    void* C;
+    const void* bias;
+    float alpha;
+    int m, n, k;
+    int c_layout;
+    int kblocks;       // k / 64
+    float* ws;         // [tiles][sk][NP][128] fp32 partial tiles (sk > 1)
+    int* counters;     // [tiles], zero between launches
+    int* status;       // sticky error word (0 = ok), may be null
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets in 16-byte units,
+// version 1, layout type in bits 61..63 (0 = no swizzle, 2 = 128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)layout << 61;
+    return d;
+}
+
+template <int WT, int NP>
+constexpr uint32_t instr_desc() {
+    // D = f32 (1 << 4); A, B formats at bits 7 / 10 (0 = f16, 1 = bf16); both K-major; N >> 3 at 17; M >> 4 at 24
+    constexpr uint32_t fmt = (WT == kFP16) ? 0u : 1u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(NP >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+}
+
+// ---- kernel ---------------------------------------------------------------------------------------------
+
+template <int WT, int NP, int STAGES>
+__global__ void __launch_bounds__(128) dense_umma_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                         const __grid_constant__ CUtensorMap map_x, const UmmaParams p,
+                                                         const int static_weights) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr int kBBytes = NP * 128;
+    constexpr uint32_t kTmemCols = NP < 32 ? 32 : NP;
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int last_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = blockIdx.x, split = blockIdx.y, SK = gridDim.y;
+    // 1024-byte aligned operand ring: all A stages, then all B stages
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_base = base, b_base = base + STAGES * kABytes;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    const uint32_t accum_bar = bar0 + 8u * (2 * STAGES);
+
+    // this CTA's k blocks
+    const int kb0 = (int)((long long)p.kblocks * split / SK);
+    const int kb1 = (int)((long long)p.kblocks * (split + 1) / SK);
+    const int nkb = kb1 - kb0;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+
+    bool ok = true;
+    int issued = 0;
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer ----
+        // Weights may stream before the preceding kernel has finished only under the static-weights promise;
+        // activations never do.
+        if (!static_weights) pdl_wait();
+        pdl_launch_dependents();
+        bool waited = !static_weights;
+        for (int i = 0; i < nkb && ok; ++i) {
+            const int s = i % STAGES;
+            if (i >= STAGES) ok = mbar_wait(empty_bar(s), ((i / STAGES) - 1) & 1);
+            if (!ok) break;
+            mbar_expect_tx(full_bar(s), kABytes + kBBytes);
+            tma_load_3d(a_base + s * kABytes, &map_a, full_bar(s), 0, tile * (kTileM / 16), (kb0 + i) * (kBlockK / 8));
+            if (!waited) { pdl_wait(); waited = true; }
+            tma_load_2d(b_base + s * kBBytes, &map_x, full_bar(s), (kb0 + i) * kBlockK, 0);
+            ++issued;
+        }
+        if (!waited) pdl_wait();
+        if (!ok && p.status) atomicExch(p.status, 1);
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        constexpr uint32_t idesc = instr_desc<WT, NP>();
+        for (int i = 0; i < nkb && ok; ++i) {
+            const int s = i % STAGES;
+            ok = mbar_wait(full_bar(s), (i / STAGES) & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int kk = 0; kk < kBlockK / 16; ++kk) {
+                // A: no swizzle, 8-row step 128 B, k-octet step 2048 B; one MMA consumes two k-octets
+                const uint64_t da = smem_desc(a_base + s * kABytes + kk * 4096, 2048, 128, 0);
+                // B: 128-byte swizzle, 8-token step 1024 B; one MMA consumes 32 bytes of each 128-byte row
+                const uint64_t db = smem_desc(b_base + s * kBBytes + kk * 32, 16, 1024, 2);
+                umma_f16(tmem, da, db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(empty_bar(s));     // arrives when the MMAs above have finished reading the stage
+        }
+        if (ok) umma_commit(accum_bar);    // arrives when the whole accumulation is complete
+        if (!ok && p.status) atomicExch(p.status, 2);
+    }
+    __syncwarp();
+
+    // ---- epilogue: every warp owns 32 accumulator rows (TMEM lanes 32*warp ..) ----
+    bool acc_ok = true;
+    if (nkb > 0) {
+        if (lane == 0) acc_ok = mbar_wait(accum_bar, 0);
+        acc_ok = __shfl_sync(0xFFFFFFFFu, acc_ok ? 1 : 0, 0) != 0;
+        if (!acc_ok && lane == 0 && p.status) atomicExch(p.status, 3);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    float v[NP];
+    if (acc_ok && nkb > 0) {
+#pragma unroll
+        for (int c = 0; c < NP; c += 16) {
+            uint32_t r[16];
+            tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[c + i] = __uint_as_float(r[i]);
+        }
+    } else {
+#pragma unroll
+        for (int c = 0; c < NP; ++c) v[c] = 0.f;
+    }
+
+    const int lrow = warp * 32 + lane;
+    const int row = tile * kTileM + lrow;
+    bool do_store = acc_ok;
+    if (SK > 1) {
+        // partial tile -> workspace; the CTA that finds the counter at SK-1 adds all partials in split order
+        float* wsp = p.ws + ((size_t)(tile * SK + split) * NP) * kTileM + lrow;
+#pragma unroll
+        for (int c = 0; c < NP; ++c) __stcg(wsp + (size_t)c * kTileM, v[c]);
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) last_flag = (atomicAdd(p.counters + tile, 1) == SK - 1) ? 1 : 0;
+        __syncthreads();
+        do_store = do_store && last_flag;
+        if (last_flag) {
+            __threadfence();
+#pragma unroll
+            for (int c = 0; c < NP; ++c) v[c] = 0.f;
+            for (int sp = 0; sp < SK; ++sp) {
+                const float* q = p.ws + ((size_t)(tile * SK + sp) * NP) * kTileM + lrow;
+#pragma unroll
+                for (int c = 0; c < NP; ++c) v[c] += __ldcg(q + (size_t)c * kTileM);
+            }
+            if (tid == 0) p.counters[tile] = 0;   // ready for the next launch
+        }
+    }
+    if (do_store) {
+        const float b = (p.bias != nullptr) ? load_scalar16<WT>(p.bias, row) : 0.f;
+#pragma unroll
+        for (int c = 0; c < NP; ++c) {
+            if (c < p.n) {
+                const float o = fmaf(p.alpha, v[c], b);
+                size_t idx;
+                if (p.c_layout == 0) {
+                    idx = (size_t)c * p.m + row;
+                } else {
+                    const int NB = p.n >> 4;
+                    idx = ((((size_t)(row >> 5) * NB + (c >> 4)) * 4 + ((row >> 3) & 3)) * 16 + (c & 15)) * 8 + (row & 7);
+                }
+                if constexpr (WT == kFP16)
+                    reinterpret_cast<__half*>(p.C)[idx] = __float2half_rn(o);
+                else
+                    reinterpret_cast<__nv_bfloat16*>(p.C)[idx] = __float2bfloat16_rn(o);
+            }
+        }
+    }
+
+    // ---- teardown ----
+    // If the pipeline stopped early, wait (bounded) until every TMA copy this CTA issued has landed, so that no
+    // copy is in flight into shared memory when the CTA exits.
+    if (warp == 0 && lane == 0 && !(acc_ok && ok)) {
+        for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(full_bar(i % STAGES), (i / STAGES) & 1);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- host ------------------------------------------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(ptr);
+    });
+    return fn;
+}
+
+bool make_map_a(CUtensorMap* map, const void* A, int m, int k, int wt) {
+    const cuuint64_t dims[3] = {128, (cuuint64_t)(m / 16), (cuuint64_t)(k / 8)};
+    const cuuint64_t strides[2] = {(cuuint64_t)16 * k * 2, 256};
+    const cuuint32_t box[3] = {128, kTileM / 16, kBlockK / 8};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return encode_fn()(map, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                       const_cast<void*>(A), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_map_x(CUtensorMap* map, const void* X, int n, int k, int wt, int np) {
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)n};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {kBlockK, (cuuint32_t)np};
+    const cuuint32_t estr[2] = {1, 1};
+    return encode_fn()(map, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                       const_cast<void*>(X), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int WT, int NP, int STAGES>
+int launch_inst(const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& up, int tiles, int sk, cudaStream_t s) {
+    auto kern = dense_umma_kernel<WT, NP, STAGES>;
+    const size_t smem = (size_t)STAGES * (kABytes + NP * 128) + 1024;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(kCudaError, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        attr_set[dev & 63] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles, sk, 1);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    cfg.attrs = attr;
+    cfg.numAttrs = launch_attrs(attr, 1);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mx, up, option(kOptStaticWeights));
+    if (e != cudaSuccess) return fail(kCudaError, "dense_umma launch: %s", cudaGetErrorString(e));
+    return kOk;
+}
+
+template <int WT, int NP>
+int launch_stages(int stages, const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& up, int tiles, int sk,
+                  cudaStream_t s) {
+    switch (stages) {
+        case 2: return launch_inst<WT, NP, 2>(ma, mx, up, tiles, sk, s);
+        case 4: return launch_inst<WT, NP, 4>(ma, mx, up, tiles, sk, s);
+        case 6: return launch_inst<WT, NP, 6>(ma, mx, up, tiles, sk, s);
+        case 8: return launch_inst<WT, NP, 8>(ma, mx, up, tiles, sk, s);
+    }
+    return fail(kInvalidArg, "dense (tcgen05): stages must be one of 2, 4, 6, 8 (got %d)", stages);
+}
+
+template <int WT>
+int launch_np(int np, int stages, const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& up, int tiles, int sk,
+              cudaStream_t s) {
+    switch (np) {
+        case 16: return launch_stages<WT, 16>(stages, ma, mx, up, tiles, sk, s);
+        case 32: return launch_stages<WT, 32>(stages, ma, mx, up, tiles, sk, s);
+        case 64: return launch_stages<WT, 64>(stages, ma, mx, up, tiles, sk, s);
+    }
+    return fail(kInvalidArg, "dense (tcgen05): bad token tile %d", np);
+}
+
+}  // namespace
+
+// sk: split-K CTAs per 128-row tile (any value >= 1 that the workspace can hold); stages: 2, 4, 6 or 8.
+int launch_dense_umma(int wt, const DenseParams& p, int sk, int stages, const DenseAux* aux, cudaStream_t stream) {
+    if (wt != kBF16 && wt != kFP16) return fail(kUnsupported, "dense (tcgen05): 16-bit weights only");
+    if (!p.A || !p.X || !p.C) return fail(kInvalidArg, "dense: null pointer");
+    if (p.x_layout != 0) return fail(kUnsupported, "dense (tcgen05): activations must be row-major");
+    if (p.m % kTileM != 0 || p.k % kBlockK != 0) return fail(kInvalidArg, "dense (tcgen05): need m %% 128 == 0 and k %% 64 == 0");
+    if (p.n < 1 || p.n > 64) return fail(kUnsupported, "dense (tcgen05): 1..64 tokens per launch (got %d)", p.n);
+    if (p.c_layout == 1 && p.n % 16 != 0) return fail(kInvalidArg, "dense: layout C needs n %% 16 == 0");
+    if (((uintptr_t)p.A & 15) || ((uintptr_t)p.X & 15)) return fail(kInvalidArg, "dense (tcgen05): operands must be 16-byte aligned");
+    if (encode_fn() == nullptr) return fail(kUnsupported, "dense (tcgen05): cuTensorMapEncodeTiled is not available");
+    const int np = p.n <= 16 ? 16 : (p.n <= 32 ? 32 : 64);
+    const int tiles = p.m / kTileM;
+    const int kblocks = p.k / kBlockK;
+    if (sk < 1) sk = 1;
+    if (sk > kblocks) sk = kblocks;
+    if (sk > 1) {
+        if (!aux || !aux->workspace || !aux->counters)
+            return fail(kInvalidArg, "dense (tcgen05): split-K needs a workspace and counters");
+        const long long need = (long long)tiles * sk * np * kTileM * 4;
+        if (aux->workspace_bytes < need) return fail(kInvalidArg, "dense (tcgen05): workspace holds %lld bytes, needs %lld", (long long)aux->workspace_bytes, need);
+        if (aux->n_counters < tiles) return fail(kInvalidArg, "dense (tcgen05): %d counters, needs %d", aux->n_counters, tiles);
+    }
+    CUtensorMap ma, mx;
+    if (!make_map_a(&ma, p.A, p.m, p.k, wt)) return fail(kUnsupported, "dense (tcgen05): weight tensor map rejected");
+    if (!make_map_x(&mx, p.X, p.n, p.k, wt, np)) return fail(kUnsupported, "dense (tcgen05): activation tensor map rejected");
+    UmmaParams up{};
+    up.C = p.C; up.bias = p.bias; up.alpha = p.alpha; up.m = p.m; up.n = p.n; up.k = p.k; up.c_layout = p.c_layout;
+    up.kblocks = kblocks;
+    up.ws = aux ? reinterpret_cast<float*>(aux->workspace) : nullptr;
+    up.counters = aux ? aux->counters : nullptr;
+    up.status = aux ? aux->status : nullptr;
+    if (wt == kFP16) return launch_np<kFP16>(np, stages, ma, mx, up, tiles, sk, stream);
+    return launch_np<kBF16>(np, stages, ma, mx, up, tiles, sk, stream);
+}
+
+}  // namespace mlk

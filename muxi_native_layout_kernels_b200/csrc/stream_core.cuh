@@ -97,12 +97,6 @@ __device__ __forceinline__ void load_afrag(AFrag<WT>& f, const uint8_t* p, bool 
     }
 }
 
-// Programmatic dependent launch: lets the next kernel of the stream become resident while this one drains.
-// wait() returns once every kernel this launch depends on has completed and its writes are visible; nothing
-// produced by an earlier kernel may be read, and nothing may be written, before it.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
 // Issues the first CH chunks of this lane's weight stream (the prefetch ring).
 template <int WT, int NT, int RG>
 __device__ __forceinline__ void ring_init(AFrag<WT> (&ring)[CoreShape<NT, RG>::CH][RG], const CoreArgs& a) {

@@ -14,10 +14,12 @@ from typing import List, Optional
 
 import torch
 
-from ._lib import MlkError, check, lib
+import ctypes
+
+from ._lib import MlkAux, MlkError, check, lib
 
 __all__ = [
-    "set_static_weights", "set_pdl",
+    "set_static_weights", "set_pdl", "kernel_status",
     "layoutA", "layoutA_inverse", "layoutB", "reLayoutC", "fp8_weight_repack",
     "gemv_layoutA", "gemv_layoutA_wapper",
     "gemm_layoutA", "gemm_layoutA_wapper", "gemm_layoutA_soft_fp8", "gemm_layoutA_soft_fp8_wapper",
@@ -240,6 +242,38 @@ def _gemm_checks(A, B, b_layout: bool):
     return m, n, A_k
 
 
+_SYNC_BUFFERS = {}   # (device index, stream handle) -> (counters, status)
+_MAX_SPLIT_K = 16
+
+
+def _aux(B: torch.Tensor, m: int, n: int):
+    """Scratch for kernels that split K over independent CTAs: a per-call fp32 workspace from torch's caching
+    allocator (stream-ordered, so concurrent streams never share it) and, per (device, stream), a persistent block of
+    counters that every kernel leaves zeroed plus the sticky status word of the kernels' bounded waits."""
+    if n > 64:
+        return None, None
+    key = (B.device.index, _stream(B))
+    tiles = m // 128
+    bufs = _SYNC_BUFFERS.get(key)
+    if bufs is None or bufs[0].numel() < tiles:
+        bufs = (torch.zeros(max(4096, tiles), dtype=torch.int32, device=B.device),
+                torch.zeros(1, dtype=torch.int32, device=B.device))
+        _SYNC_BUFFERS[key] = bufs
+    npad = 16 if n <= 16 else (32 if n <= 32 else 64)
+    ws = torch.empty(tiles * _MAX_SPLIT_K * npad * 128, dtype=torch.float32, device=B.device)
+    aux = MlkAux(ws.data_ptr(), ws.numel() * 4, bufs[0].data_ptr(), bufs[0].numel(), bufs[1].data_ptr())
+    return aux, ws
+
+
+def kernel_status(device=None) -> int:
+    """Sticky status word of the bounded waits inside the tcgen05 kernels for the current stream of `device`
+    (0 = no wait ever expired).  Synchronises the stream."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), torch.cuda.current_stream(dev).cuda_stream)
+    bufs = _SYNC_BUFFERS.get(key)
+    return 0 if bufs is None else int(bufs[1].item())
+
+
 def _alloc_c(B, m, n, c_layout: bool):
     if c_layout:
         return torch.empty((m // 32, n // 16, 4, 16, 8), dtype=B.dtype, device=B.device)
@@ -252,8 +286,9 @@ def gemm_layoutA(A, B, alpha: float = 1, beta: float = 0, bias=None):
     code = _dense_code(A, B)
     _chk(code != 2, "Unsupported data type")
     C = _alloc_c(B, m, n, False)
+    aux, _keep = _aux(B, m, n)
     check(lib.mlk_gemm_layoutA(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, code, alpha, beta,
-                               _bias_ptr(bias, B, m), _stream(B)))
+                               _bias_ptr(bias, B, m), None if aux is None else ctypes.byref(aux), _stream(B)))
     return C
 
 
@@ -265,9 +300,11 @@ def gemm_layoutA_wapper(A, B, m: int, n: int, k: int, alpha: float = 1, beta: fl
     code = _dense_code(A, B)
     _chk(code != 2, "Unsupported data type")
     C = _alloc_c(B, m, n, False)
+    aux, _keep = _aux(B, m, n) if kernelId == 2 else (None, None)
+    _chk(kernelId != 2 or kernelParam1 <= _MAX_SPLIT_K, f"split-K of the tcgen05 kernel is limited to {_MAX_SPLIT_K}")
     check(lib.mlk_gemm_layoutA_wapper(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, code, alpha, beta,
                                       kernelParam1, kernelParam2, kernelParam3, kernelId, _bias_ptr(bias, B, m),
-                                      _stream(B)))
+                                      None if aux is None else ctypes.byref(aux), _stream(B)))
     return C
 
 

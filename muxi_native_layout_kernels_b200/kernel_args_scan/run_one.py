@@ -4,7 +4,7 @@ under a profiler, or to try launch arguments by hand.
     python -m muxi_native_layout_kernels_b200.kernel_args_scan.run_one --op gemm_layoutA --shape 14336x4096 \
            --tokens 8 [--dtype bf16|fp16|fp8] [--args 1,2,4] [--iters 5] [--copies 3]
 
---args: kernelParam1,kernelParam2,kernelParam3 (GEMM) or blockDimX,kernelId,kernelParam1,kernelParam2 (gemv);
+--args: kernelParam1,kernelParam2,kernelParam3[,kernelId] (GEMM) or blockDimX,kernelId,kernelParam1,kernelParam2 (gemv);
 without it the packaged dispatch table decides.  --copies weight copies are cycled so that consecutive launches
 read different HBM lines.
 """
@@ -55,7 +55,8 @@ def main(argv=None):
         fn = getattr(mlk, a.op + ("_wapper" if args else ""))
         xin = XB if XB is not None else X
         if args:
-            return fn(A, xin, m, n, k, kernelParam1=args[0], kernelParam2=args[1], kernelParam3=args[2])
+            return fn(A, xin, m, n, k, kernelParam1=args[0], kernelParam2=args[1], kernelParam3=args[2],
+                      kernelId=args[3] if len(args) > 3 else 1)
         return fn(A, xin)
 
     want = (X.float() @ W.float().t()).to(adt)

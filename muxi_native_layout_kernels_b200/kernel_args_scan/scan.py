@@ -125,13 +125,19 @@ def scan_one(kind, m, n, k, dtype, log):
     else:
         cands = [(1, rg, wm, sk) for rg, wm, sk in itertools.product([1, 2], [1, 2, 4, 8], [1, 2, 4, 8])
                  if m % (16 * rg * wm) == 0]
+        if kind == "a" and n <= 64:
+            # tcgen05 tile kernel: split-K chosen so that tiles * split-K lands near a multiple of the SM count
+            tiles = m // 128
+            sks = sorted({1, 2, 3, 4, 6, 8, 12, 16} | {max(1, min(16, round(148 * w / tiles))) for w in (1, 2, 3)})
+            cands += [(2, sk, st, 0) for sk in sks for st in (4, 8) if sk <= k // 64]
     best, best_t = None, float("inf")
     for c in cands:
         if kind.startswith("gemv"):
             t_, kid, rg, sk = c
             call = lambda A: mlk.gemv_layoutA_wapper(A, X, m, k, blockDimX=t_, kernelId=kid, kernelParam1=rg, kernelParam2=sk)
         elif kind == "a":
-            call = lambda A: mlk.gemm_layoutA_wapper(A, X, m, n, k, kernelParam1=c[1], kernelParam2=c[2], kernelParam3=c[3])
+            call = lambda A: mlk.gemm_layoutA_wapper(A, X, m, n, k, kernelParam1=c[1], kernelParam2=c[2], kernelParam3=c[3],
+                                                     kernelId=c[0])
         elif kind == "a_fp8":
             call = lambda A: mlk.gemm_layoutA_soft_fp8_wapper(A, None, X, m, n, k, kernelParam1=c[1], kernelParam2=c[2], kernelParam3=c[3])
         elif kind == "conc":
