@@ -104,12 +104,13 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
 
 /* kernelId 1 (warp-level tensor-core streaming kernel, any n <= 256): kernelParam1 = row groups per warp (1,2),
  *   kernelParam2 = row warps per CTA (1,2,4,8), kernelParam3 = split-K over a thread-block cluster (1,2,4,8).
- * kernelId 2 (tcgen05 / tensor-memory tile kernel, 16-bit weights, row-major B, n <= 64): kernelParam1 = split-K CTAs
- *   per 128-row tile (>= 1), kernelParam2 = TMA pipeline stages (2,4,6,8), kernelParam3 unused.  Split-K > 1 needs the
- *   caller-provided scratch below; without it the kernel runs with split-K 1. */
+ * kernelId 2 (tcgen05 / tensor-memory tile kernel, 16-bit weights, row-major B, n <= 64): persistent CTAs that split
+ *   the (128-row tile, 64-wide k block) work units evenly; kernelParam1 = CTAs per SM the grid is sized for (1..4),
+ *   kernelParam2 = TMA pipeline stages (2,4,6,8), kernelParam3 unused.  Splitting tiles between CTAs needs the
+ *   caller-provided scratch below; without it the kernel runs one CTA per tile. */
 
-/* Scratch lent to one call (device pointers).  workspace: tiles * splitK * Npad * 128 floats, any content
- * (tiles = m/128, Npad = 16, 32 or 64).  counters: >= m/128 ints that are zero on entry; every kernel leaves them
+/* Scratch lent to one call (device pointers).  workspace: mlk_gemm_workspace_bytes(m, n, k) bytes, any content.
+ * counters: >= m/128 ints that are zero on entry; every kernel leaves them
  * zero again, so one buffer per stream can be reused by successive calls.  status: one int, sticky error word of the
  * bounded waits inside the kernel (0 = ok), may be NULL. */
 typedef struct mlk_aux {
@@ -119,6 +120,10 @@ typedef struct mlk_aux {
     int32_t n_counters;
     int32_t* status;
 } mlk_aux;
+
+/* Workspace size (bytes) that covers every kernelId-2 launch of this shape on the current device; 0 if the shape
+ * cannot use that kernel. */
+int64_t mlk_gemm_workspace_bytes(int m, int n, int k);
 
 /* A layout A, B row-major [n,k], C row-major [n,m].  Reference: gemm_layoutA_wapper, csrc/gemm_layout_A.cu:684-750. */
 int mlk_gemm_layoutA_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha,

@@ -75,9 +75,7 @@ int gemm_common(int variant_x, int variant_c, const void* A, const float* scale,
             da.workspace = aux->workspace; da.workspace_bytes = aux->workspace_bytes; da.counters = aux->counters;
             da.n_counters = aux->n_counters; da.status = aux->status;
         }
-        int sk = p1;
-        if (!aux || !aux->workspace || !aux->counters) sk = 1;
-        return launch_dense_umma(wt, p, sk, p2, aux ? &da : nullptr, s);
+        return launch_dense_umma(wt, p, p1, p2, aux ? &da : nullptr, s);
     }
     if (kernelId != 1)
         return fail(kUnsupported, "gemm: kernelId %d is not built (1 = warp-level streaming kernel, 2 = tcgen05 tile kernel)", kernelId);
@@ -94,7 +92,7 @@ int gemm_table(int table, int variant_x, int variant_c, const void* A, const flo
     // A table row that this shape cannot run with (e.g. copied from another GPU's table) falls back to the default.
     const bool ok1 = t.a == 1 && (t.b == 1 || t.b == 2) && (t.c == 1 || t.c == 2 || t.c == 4 || t.c == 8) &&
                      (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b * t.c) == 0;
-    const bool ok2 = t.a == 2 && variant_x == 0 && dtype != MLK_E4M3 && n <= 64 && t.b >= 1 &&
+    const bool ok2 = t.a == 2 && variant_x == 0 && dtype != MLK_E4M3 && n <= 64 && t.b >= 1 && t.b <= 4 &&
                      (t.c == 2 || t.c == 4 || t.c == 6 || t.c == 8);
     if (!ok1 && !ok2) t = default_args(table, m, n, k);
     return gemm_common(variant_x, variant_c, A, scale, B, C, m, n, k, dtype, alpha, t.b, t.c, t.d, t.a, bias,
@@ -130,6 +128,19 @@ int mlk_set_option(int option_id, int value) {
     return kOk;
 }
 int mlk_get_option(int option_id) { return option(option_id); }
+
+int64_t mlk_gemm_workspace_bytes(int m, int n, int k) {
+    if (m <= 0 || n <= 0 || k <= 0 || m % 128 != 0 || k % 64 != 0 || n > 64) return 0;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 0;
+    long long best = 0;
+    for (int c = 1; c <= 4; ++c) {
+        const long long b = umma_workspace_bytes(m, n, k, sms, c);
+        best = b > best ? b : best;
+    }
+    return best;
+}
 
 int mlk_table_load(int table, const char* csv_path) {
     clear_error();

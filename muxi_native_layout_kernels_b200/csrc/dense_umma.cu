@@ -44,7 +44,8 @@ struct UmmaParams {
     int m, n, k;
     int c_layout;
     int kblocks;       // k / 64
-    float* ws;         // [tiles][sk][NP][128] fp32 partial tiles (sk > 1)
+    float* ws;         // [tiles][max_parts][NP][128] fp32 partial tiles
+    int max_parts;     // workspace slots per tile
     int* counters;     // [tiles], zero between launches
     int* status;       // sticky error word (0 = ok), may be null
 };
@@ -125,39 +126,61 @@ constexpr uint32_t instr_desc() {
 }
 
 // ---- kernel ---------------------------------------------------------------------------------------------
+//
+// Work decomposition ("stream-K"): the unit of work is (128-row tile, 64-wide k block); units are numbered
+// tile-major and split into gridDim.x contiguous, equally long ranges, one per CTA, so every SM streams the same
+// number of weight bytes whatever the shape.  A CTA's range decomposes into segments (one tile each).  A segment
+// that covers all k blocks of its tile is written straight to C; otherwise the fp32 partial tile goes to the
+// workspace slot (tile, j), j = CTA index minus the first CTA that touches the tile, and the CTA that arrives last
+// at the tile's counter adds the slots in ascending j and writes C.
+//
+// Warp roles (192 threads): warp 0 lane 0 = TMA producer, warp 1 = tensor-memory owner and (lane 0) MMA issuer,
+// warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4)...).  Two accumulators in tensor memory alternate
+// between segments so the MMAs of the next segment overlap the epilogue of the previous one.
+
+__device__ __forceinline__ int cta_of_unit(long long u, long long U, int G) {
+    // the g with floor(U*g/G) <= u < floor(U*(g+1)/G)
+    return (int)(((u + 1) * G - 1) / U);
+}
 
 template <int WT, int NP, int STAGES>
-__global__ void __launch_bounds__(128) dense_umma_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__ CUtensorMap map_a,
                                                          const __grid_constant__ CUtensorMap map_x, const UmmaParams p,
                                                          const int static_weights) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int kBBytes = NP * 128;
-    constexpr uint32_t kTmemCols = NP < 32 ? 32 : NP;
-    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    constexpr uint32_t kTmemCols = 2 * NP < 32 ? 32 : 2 * NP;
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
     __shared__ uint32_t tmem_slot;
     __shared__ int last_flag;
+    __shared__ volatile int ep_go;
+    __shared__ volatile int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile = blockIdx.x, split = blockIdx.y, SK = gridDim.y;
+    const int G = gridDim.x, g = blockIdx.x;
+    const int KB = p.kblocks;
+    const long long U = (long long)(p.m / kTileM) * KB;
+    const long long u0 = U * g / G, u1 = U * (g + 1) / G;
+
     // 1024-byte aligned operand ring: all A stages, then all B stages
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t a_base = base, b_base = base + STAGES * kABytes;
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
-    const uint32_t accum_bar = bar0 + 8u * (2 * STAGES);
-
-    // this CTA's k blocks
-    const int kb0 = (int)((long long)p.kblocks * split / SK);
-    const int kb1 = (int)((long long)p.kblocks * (split + 1) / SK);
-    const int nkb = kb1 - kb0;
+    auto acc_full = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+    auto acc_empty = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), 4);
+        }
+        abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -171,124 +194,156 @@ __global__ void __launch_bounds__(128) dense_umma_kernel(const __grid_constant__
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_slot;
 
-    bool ok = true;
     int issued = 0;
     if (warp == 0 && lane == 0) {
-        // ---- TMA producer ----
+        // ---- TMA producer: one stage per unit, running ahead of the MMAs by up to STAGES units ----
         // Weights may stream before the preceding kernel has finished only under the static-weights promise;
         // activations never do.
         if (!static_weights) pdl_wait();
         pdl_launch_dependents();
         bool waited = !static_weights;
-        for (int i = 0; i < nkb && ok; ++i) {
+        int i = 0;
+        for (long long u = u0; u < u1; ++u, ++i) {
             const int s = i % STAGES;
-            if (i >= STAGES) ok = mbar_wait(empty_bar(s), ((i / STAGES) - 1) & 1);
-            if (!ok) break;
+            if (i >= STAGES && !mbar_wait(empty_bar(s), ((i / STAGES) - 1) & 1)) {
+                abort_flag = 1;
+                if (p.status) atomicExch(p.status, 1);
+            }
+            if (abort_flag) break;
+            const int tile = (int)(u / KB), kb = (int)(u - (long long)tile * KB);
             mbar_expect_tx(full_bar(s), kABytes + kBBytes);
-            tma_load_3d(a_base + s * kABytes, &map_a, full_bar(s), 0, tile * (kTileM / 16), (kb0 + i) * (kBlockK / 8));
+            tma_load_3d(a_base + s * kABytes, &map_a, full_bar(s), 0, tile * (kTileM / 16), kb * (kBlockK / 8));
             if (!waited) { pdl_wait(); waited = true; }
-            tma_load_2d(b_base + s * kBBytes, &map_x, full_bar(s), (kb0 + i) * kBlockK, 0);
+            tma_load_2d(b_base + s * kBBytes, &map_x, full_bar(s), kb * kBlockK, 0);
             ++issued;
         }
         if (!waited) pdl_wait();
-        if (!ok && p.status) atomicExch(p.status, 1);
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
         constexpr uint32_t idesc = instr_desc<WT, NP>();
-        for (int i = 0; i < nkb && ok; ++i) {
-            const int s = i % STAGES;
-            ok = mbar_wait(full_bar(s), (i / STAGES) & 1);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int kk = 0; kk < kBlockK / 16; ++kk) {
-                // A: no swizzle, 8-row step 128 B, k-octet step 2048 B; one MMA consumes two k-octets
-                const uint64_t da = smem_desc(a_base + s * kABytes + kk * 4096, 2048, 128, 0);
-                // B: 128-byte swizzle, 8-token step 1024 B; one MMA consumes 32 bytes of each 128-byte row
-                const uint64_t db = smem_desc(b_base + s * kBBytes + kk * 32, 16, 1024, 2);
-                umma_f16(tmem, da, db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        int i = 0, seg = 0;
+        for (long long u = u0; u < u1 && !abort_flag; ++seg) {
+            const int tile = (int)(u / KB), kb_begin = (int)(u - (long long)tile * KB);
+            const int kb_end = (int)min((long long)KB, kb_begin + (u1 - u));
+            const int b = seg & 1;
+            if (seg >= 2 && !mbar_wait(acc_empty(b), ((seg >> 1) - 1) & 1)) {
+                abort_flag = 1;
+                if (p.status) atomicExch(p.status, 4);
+                break;
             }
-            umma_commit(empty_bar(s));     // arrives when the MMAs above have finished reading the stage
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int kb = kb_begin; kb < kb_end; ++kb, ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(full_bar(s), (i / STAGES) & 1)) {
+                    abort_flag = 1;
+                    if (p.status) atomicExch(p.status, 2);
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int kk = 0; kk < kBlockK / 16; ++kk) {
+                    // A: no swizzle, 8-row step 128 B, k-octet step 2048 B; one MMA consumes two k-octets
+                    const uint64_t da = smem_desc(a_base + s * kABytes + kk * 4096, 2048, 128, 0);
+                    // B: 128-byte swizzle, 8-token step 1024 B; one MMA consumes 32 bytes of each 128-byte row
+                    const uint64_t db = smem_desc(b_base + s * kBBytes + kk * 32, 16, 1024, 2);
+                    umma_f16(tmem + b * NP, da, db, idesc, (kb > kb_begin || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(empty_bar(s));     // arrives when the MMAs above have finished reading the stage
+            }
+            if (abort_flag) break;
+            umma_commit(acc_full(b));          // arrives when this segment's accumulation is complete
+            u += kb_end - kb_begin;
         }
-        if (ok) umma_commit(accum_bar);    // arrives when the whole accumulation is complete
-        if (!ok && p.status) atomicExch(p.status, 2);
+    } else if (warp >= 2) {
+        // ---- epilogue warps ----
+        const int quad = warp & 3;
+        const int lrow = quad * 32 + lane;
+        const int etid = tid - 64;
+        int seg = 0;
+        for (long long u = u0; u < u1; ++seg) {
+            const int tile = (int)(u / KB), kb_begin = (int)(u - (long long)tile * KB);
+            const int kb_end = (int)min((long long)KB, kb_begin + (u1 - u));
+            const int b = seg & 1;
+            if (lane == 0 && !mbar_wait(acc_full(b), (seg >> 1) & 1)) {
+                abort_flag = 1;
+                if (p.status) atomicExch(p.status, 3);
+            }
+            // The four epilogue warps must leave together (they share named barrier 1): one thread reads the
+            // abort flag and publishes the decision.
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (etid == 0) ep_go = abort_flag ? 0 : 1;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!ep_go) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float v[NP];
+#pragma unroll
+            for (int c = 0; c < NP; c += 16) {
+                uint32_t r[16];
+                tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + b * NP + c, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[c + i] = __uint_as_float(r[i]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(b)) : "memory");
+
+            bool do_store = true;
+            if (!(kb_begin == 0 && kb_end == KB)) {
+                // partial tile: park it in the workspace; the last arriver adds all parts in CTA order
+                const int g_first = cta_of_unit((long long)tile * KB, U, G);
+                const int g_last = cta_of_unit((long long)(tile + 1) * KB - 1, U, G);
+                const int parts = g_last - g_first + 1;
+                float* wsp = p.ws + ((size_t)(tile * p.max_parts + (g - g_first)) * NP) * kTileM + lrow;
+#pragma unroll
+                for (int c = 0; c < NP; ++c) __stcg(wsp + (size_t)c * kTileM, v[c]);
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (etid == 0) last_flag = (atomicAdd(p.counters + tile, 1) == parts - 1) ? 1 : 0;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                do_store = last_flag != 0;
+                if (do_store) {
+                    __threadfence();
+#pragma unroll
+                    for (int c = 0; c < NP; ++c) v[c] = 0.f;
+                    for (int j = 0; j < parts; ++j) {
+                        const float* q = p.ws + ((size_t)(tile * p.max_parts + j) * NP) * kTileM + lrow;
+#pragma unroll
+                        for (int c = 0; c < NP; ++c) v[c] += __ldcg(q + (size_t)c * kTileM);
+                    }
+                    if (etid == 0) p.counters[tile] = 0;   // ready for the next launch
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag may be rewritten by the next segment
+            }
+            if (do_store) {
+                const int row = tile * kTileM + lrow;
+                const float bia = (p.bias != nullptr) ? load_scalar16<WT>(p.bias, row) : 0.f;
+#pragma unroll
+                for (int c = 0; c < NP; ++c) {
+                    if (c < p.n) {
+                        const float o = fmaf(p.alpha, v[c], bia);
+                        size_t idx;
+                        if (p.c_layout == 0) {
+                            idx = (size_t)c * p.m + row;
+                        } else {
+                            const int NB = p.n >> 4;
+                            idx = ((((size_t)(row >> 5) * NB + (c >> 4)) * 4 + ((row >> 3) & 3)) * 16 + (c & 15)) * 8 + (row & 7);
+                        }
+                        if constexpr (WT == kFP16)
+                            reinterpret_cast<__half*>(p.C)[idx] = __float2half_rn(o);
+                        else
+                            reinterpret_cast<__nv_bfloat16*>(p.C)[idx] = __float2bfloat16_rn(o);
+                    }
+                }
+            }
+            u += kb_end - kb_begin;
+        }
     }
     __syncwarp();
-
-    // ---- epilogue: every warp owns 32 accumulator rows (TMEM lanes 32*warp ..) ----
-    bool acc_ok = true;
-    if (nkb > 0) {
-        if (lane == 0) acc_ok = mbar_wait(accum_bar, 0);
-        acc_ok = __shfl_sync(0xFFFFFFFFu, acc_ok ? 1 : 0, 0) != 0;
-        if (!acc_ok && lane == 0 && p.status) atomicExch(p.status, 3);
-    }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-
-    float v[NP];
-    if (acc_ok && nkb > 0) {
-#pragma unroll
-        for (int c = 0; c < NP; c += 16) {
-            uint32_t r[16];
-            tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, r);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int i = 0; i < 16; ++i) v[c + i] = __uint_as_float(r[i]);
-        }
-    } else {
-#pragma unroll
-        for (int c = 0; c < NP; ++c) v[c] = 0.f;
-    }
-
-    const int lrow = warp * 32 + lane;
-    const int row = tile * kTileM + lrow;
-    bool do_store = acc_ok;
-    if (SK > 1) {
-        // partial tile -> workspace; the CTA that finds the counter at SK-1 adds all partials in split order
-        float* wsp = p.ws + ((size_t)(tile * SK + split) * NP) * kTileM + lrow;
-#pragma unroll
-        for (int c = 0; c < NP; ++c) __stcg(wsp + (size_t)c * kTileM, v[c]);
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) last_flag = (atomicAdd(p.counters + tile, 1) == SK - 1) ? 1 : 0;
-        __syncthreads();
-        do_store = do_store && last_flag;
-        if (last_flag) {
-            __threadfence();
-#pragma unroll
-            for (int c = 0; c < NP; ++c) v[c] = 0.f;
-            for (int sp = 0; sp < SK; ++sp) {
-                const float* q = p.ws + ((size_t)(tile * SK + sp) * NP) * kTileM + lrow;
-#pragma unroll
-                for (int c = 0; c < NP; ++c) v[c] += __ldcg(q + (size_t)c * kTileM);
-            }
-            if (tid == 0) p.counters[tile] = 0;   // ready for the next launch
-        }
-    }
-    if (do_store) {
-        const float b = (p.bias != nullptr) ? load_scalar16<WT>(p.bias, row) : 0.f;
-#pragma unroll
-        for (int c = 0; c < NP; ++c) {
-            if (c < p.n) {
-                const float o = fmaf(p.alpha, v[c], b);
-                size_t idx;
-                if (p.c_layout == 0) {
-                    idx = (size_t)c * p.m + row;
-                } else {
-                    const int NB = p.n >> 4;
-                    idx = ((((size_t)(row >> 5) * NB + (c >> 4)) * 4 + ((row >> 3) & 3)) * 16 + (c & 15)) * 8 + (row & 7);
-                }
-                if constexpr (WT == kFP16)
-                    reinterpret_cast<__half*>(p.C)[idx] = __float2half_rn(o);
-                else
-                    reinterpret_cast<__nv_bfloat16*>(p.C)[idx] = __float2bfloat16_rn(o);
-            }
-        }
-    }
 
     // ---- teardown ----
     // If the pipeline stopped early, wait (bounded) until every TMA copy this CTA issued has landed, so that no
     // copy is in flight into shared memory when the CTA exits.
-    if (warp == 0 && lane == 0 && !(acc_ok && ok)) {
+    if (warp == 0 && lane == 0 && abort_flag) {
         for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(full_bar(i % STAGES), (i / STAGES) & 1);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -340,7 +395,7 @@ bool make_map_x(CUtensorMap* map, const void* X, int n, int k, int wt, int np) {
 }
 
 template <int WT, int NP, int STAGES>
-int launch_inst(const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& up, int tiles, int sk, cudaStream_t s) {
+int launch_inst(const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& up, int G, cudaStream_t s) {
     auto kern = dense_umma_kernel<WT, NP, STAGES>;
     const size_t smem = (size_t)STAGES * (kABytes + NP * 128) + 1024;
     static bool attr_set[64] = {};
@@ -352,8 +407,8 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& 
         attr_set[dev & 63] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles, sk, 1);
-    cfg.blockDim = dim3(128);
+    cfg.gridDim = dim3(G, 1, 1);
+    cfg.blockDim = dim3(192);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
@@ -365,32 +420,45 @@ int launch_inst(const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& 
 }
 
 template <int WT, int NP>
-int launch_stages(int stages, const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& up, int tiles, int sk,
+int launch_stages(int stages, const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& up, int G,
                   cudaStream_t s) {
     switch (stages) {
-        case 2: return launch_inst<WT, NP, 2>(ma, mx, up, tiles, sk, s);
-        case 4: return launch_inst<WT, NP, 4>(ma, mx, up, tiles, sk, s);
-        case 6: return launch_inst<WT, NP, 6>(ma, mx, up, tiles, sk, s);
-        case 8: return launch_inst<WT, NP, 8>(ma, mx, up, tiles, sk, s);
+        case 2: return launch_inst<WT, NP, 2>(ma, mx, up, G, s);
+        case 4: return launch_inst<WT, NP, 4>(ma, mx, up, G, s);
+        case 6: return launch_inst<WT, NP, 6>(ma, mx, up, G, s);
+        case 8: return launch_inst<WT, NP, 8>(ma, mx, up, G, s);
     }
     return fail(kInvalidArg, "dense (tcgen05): stages must be one of 2, 4, 6, 8 (got %d)", stages);
 }
 
 template <int WT>
-int launch_np(int np, int stages, const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& up, int tiles, int sk,
+int launch_np(int np, int stages, const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& up, int G,
               cudaStream_t s) {
     switch (np) {
-        case 16: return launch_stages<WT, 16>(stages, ma, mx, up, tiles, sk, s);
-        case 32: return launch_stages<WT, 32>(stages, ma, mx, up, tiles, sk, s);
-        case 64: return launch_stages<WT, 64>(stages, ma, mx, up, tiles, sk, s);
+        case 16: return launch_stages<WT, 16>(stages, ma, mx, up, G, s);
+        case 32: return launch_stages<WT, 32>(stages, ma, mx, up, G, s);
+        case 64: return launch_stages<WT, 64>(stages, ma, mx, up, G, s);
     }
     return fail(kInvalidArg, "dense (tcgen05): bad token tile %d", np);
 }
 
 }  // namespace
 
-// sk: split-K CTAs per 128-row tile (any value >= 1 that the workspace can hold); stages: 2, 4, 6 or 8.
-int launch_dense_umma(int wt, const DenseParams& p, int sk, int stages, const DenseAux* aux, cudaStream_t stream) {
+// Workspace slots per tile needed when tiles * kblocks work units are split over G CTAs.
+int umma_max_parts(int tiles, int kblocks, int G) {
+    const long long U = (long long)tiles * kblocks;
+    int mx = 1;
+    for (int t = 0; t < tiles; ++t) {
+        const int gf = (int)((((long long)t * kblocks + 1) * G - 1) / U);
+        const int gl = (int)((((long long)(t + 1) * kblocks) * G - 1) / U);
+        mx = gl - gf + 1 > mx ? gl - gf + 1 : mx;
+    }
+    return mx;
+}
+
+// ctas_per_sm: resident CTAs per SM the grid is sized for (grid = ctas_per_sm * SM count, capped by the number of
+// work units); stages: 2, 4, 6 or 8 (two CTAs per SM fit with at most 4).
+int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages, const DenseAux* aux, cudaStream_t stream) {
     if (wt != kBF16 && wt != kFP16) return fail(kUnsupported, "dense (tcgen05): 16-bit weights only");
     if (!p.A || !p.X || !p.C) return fail(kInvalidArg, "dense: null pointer");
     if (p.x_layout != 0) return fail(kUnsupported, "dense (tcgen05): activations must be row-major");
@@ -399,16 +467,25 @@ int launch_dense_umma(int wt, const DenseParams& p, int sk, int stages, const De
     if (p.c_layout == 1 && p.n % 16 != 0) return fail(kInvalidArg, "dense: layout C needs n %% 16 == 0");
     if (((uintptr_t)p.A & 15) || ((uintptr_t)p.X & 15)) return fail(kInvalidArg, "dense (tcgen05): operands must be 16-byte aligned");
     if (encode_fn() == nullptr) return fail(kUnsupported, "dense (tcgen05): cuTensorMapEncodeTiled is not available");
+    if (ctas_per_sm < 1 || ctas_per_sm > 4) return fail(kInvalidArg, "dense (tcgen05): CTAs per SM must be 1..4 (got %d)", ctas_per_sm);
     const int np = p.n <= 16 ? 16 : (p.n <= 32 ? 32 : 64);
     const int tiles = p.m / kTileM;
     const int kblocks = p.k / kBlockK;
-    if (sk < 1) sk = 1;
-    if (sk > kblocks) sk = kblocks;
-    if (sk > 1) {
-        if (!aux || !aux->workspace || !aux->counters)
-            return fail(kInvalidArg, "dense (tcgen05): split-K needs a workspace and counters");
-        const long long need = (long long)tiles * sk * np * kTileM * 4;
-        if (aux->workspace_bytes < need) return fail(kInvalidArg, "dense (tcgen05): workspace holds %lld bytes, needs %lld", (long long)aux->workspace_bytes, need);
+    static int sm_count[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (sm_count[dev & 63] == 0) cudaDeviceGetAttribute(&sm_count[dev & 63], cudaDevAttrMultiProcessorCount, dev);
+    long long G = (long long)sm_count[dev & 63] * ctas_per_sm;
+    const long long U = (long long)tiles * kblocks;
+    if (G > U) G = U;
+    // Without scratch only whole tiles can be handed out: one CTA per tile.
+    const bool have_aux = aux && aux->workspace && aux->counters;
+    if (!have_aux) G = tiles;
+    const int max_parts = umma_max_parts(tiles, kblocks, (int)G);
+    if (have_aux && max_parts > 1) {
+        const long long need = (long long)tiles * max_parts * np * kTileM * 4;
+        if (aux->workspace_bytes < need)
+            return fail(kInvalidArg, "dense (tcgen05): workspace holds %lld bytes, needs %lld", (long long)aux->workspace_bytes, need);
         if (aux->n_counters < tiles) return fail(kInvalidArg, "dense (tcgen05): %d counters, needs %d", aux->n_counters, tiles);
     }
     CUtensorMap ma, mx;
@@ -417,11 +494,21 @@ int launch_dense_umma(int wt, const DenseParams& p, int sk, int stages, const De
     UmmaParams up{};
     up.C = p.C; up.bias = p.bias; up.alpha = p.alpha; up.m = p.m; up.n = p.n; up.k = p.k; up.c_layout = p.c_layout;
     up.kblocks = kblocks;
-    up.ws = aux ? reinterpret_cast<float*>(aux->workspace) : nullptr;
-    up.counters = aux ? aux->counters : nullptr;
+    up.ws = have_aux ? reinterpret_cast<float*>(aux->workspace) : nullptr;
+    up.max_parts = max_parts;
+    up.counters = have_aux ? aux->counters : nullptr;
     up.status = aux ? aux->status : nullptr;
-    if (wt == kFP16) return launch_np<kFP16>(np, stages, ma, mx, up, tiles, sk, stream);
-    return launch_np<kBF16>(np, stages, ma, mx, up, tiles, sk, stream);
+    if (wt == kFP16) return launch_np<kFP16>(np, stages, ma, mx, up, (int)G, stream);
+    return launch_np<kBF16>(np, stages, ma, mx, up, (int)G, stream);
+}
+
+// Upper bound of the workspace launch_dense_umma can need for this shape on a device with `sms` SMs.
+long long umma_workspace_bytes(int m, int n, int k, int sms, int ctas_per_sm) {
+    const int np = n <= 16 ? 16 : (n <= 32 ? 32 : 64);
+    const int tiles = m / kTileM, kblocks = k / kBlockK;
+    long long G = (long long)sms * ctas_per_sm;
+    if (G > (long long)tiles * kblocks) G = (long long)tiles * kblocks;
+    return (long long)tiles * umma_max_parts(tiles, kblocks, (int)G) * np * kTileM * 4;
 }
 
 }  // namespace mlk

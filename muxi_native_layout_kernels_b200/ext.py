@@ -243,10 +243,10 @@ def _gemm_checks(A, B, b_layout: bool):
 
 
 _SYNC_BUFFERS = {}   # (device index, stream handle) -> (counters, status)
-_MAX_SPLIT_K = 16
+_WS_BYTES = {}       # (device index, m, n-tile, k) -> workspace bytes of the tcgen05 kernel
 
 
-def _aux(B: torch.Tensor, m: int, n: int):
+def _aux(B: torch.Tensor, m: int, n: int, k: int):
     """Scratch for kernels that split K over independent CTAs: a per-call fp32 workspace from torch's caching
     allocator (stream-ordered, so concurrent streams never share it) and, per (device, stream), a persistent block of
     counters that every kernel leaves zeroed plus the sticky status word of the kernels' bounded waits."""
@@ -260,7 +260,14 @@ def _aux(B: torch.Tensor, m: int, n: int):
                 torch.zeros(1, dtype=torch.int32, device=B.device))
         _SYNC_BUFFERS[key] = bufs
     npad = 16 if n <= 16 else (32 if n <= 32 else 64)
-    ws = torch.empty(tiles * _MAX_SPLIT_K * npad * 128, dtype=torch.float32, device=B.device)
+    wkey = (B.device.index, m, npad, k)
+    nbytes = _WS_BYTES.get(wkey)
+    if nbytes is None:
+        with torch.cuda.device(B.device):
+            nbytes = _WS_BYTES[wkey] = int(lib.mlk_gemm_workspace_bytes(m, n, k))
+    if nbytes == 0:
+        return None, None
+    ws = torch.empty(nbytes // 4, dtype=torch.float32, device=B.device)
     aux = MlkAux(ws.data_ptr(), ws.numel() * 4, bufs[0].data_ptr(), bufs[0].numel(), bufs[1].data_ptr())
     return aux, ws
 
@@ -286,7 +293,7 @@ def gemm_layoutA(A, B, alpha: float = 1, beta: float = 0, bias=None):
     code = _dense_code(A, B)
     _chk(code != 2, "Unsupported data type")
     C = _alloc_c(B, m, n, False)
-    aux, _keep = _aux(B, m, n)
+    aux, _keep = _aux(B, m, n, k)
     check(lib.mlk_gemm_layoutA(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, code, alpha, beta,
                                _bias_ptr(bias, B, m), None if aux is None else ctypes.byref(aux), _stream(B)))
     return C
@@ -300,8 +307,7 @@ def gemm_layoutA_wapper(A, B, m: int, n: int, k: int, alpha: float = 1, beta: fl
     code = _dense_code(A, B)
     _chk(code != 2, "Unsupported data type")
     C = _alloc_c(B, m, n, False)
-    aux, _keep = _aux(B, m, n) if kernelId == 2 else (None, None)
-    _chk(kernelId != 2 or kernelParam1 <= _MAX_SPLIT_K, f"split-K of the tcgen05 kernel is limited to {_MAX_SPLIT_K}")
+    aux, _keep = _aux(B, m, n, k) if kernelId == 2 else (None, None)
     check(lib.mlk_gemm_layoutA_wapper(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, code, alpha, beta,
                                       kernelParam1, kernelParam2, kernelParam3, kernelId, _bias_ptr(bias, B, m),
                                       None if aux is None else ctypes.byref(aux), _stream(B)))

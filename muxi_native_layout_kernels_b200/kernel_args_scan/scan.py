@@ -126,10 +126,8 @@ def scan_one(kind, m, n, k, dtype, log):
         cands = [(1, rg, wm, sk) for rg, wm, sk in itertools.product([1, 2], [1, 2, 4, 8], [1, 2, 4, 8])
                  if m % (16 * rg * wm) == 0]
         if kind == "a" and n <= 64:
-            # tcgen05 tile kernel: split-K chosen so that tiles * split-K lands near a multiple of the SM count
-            tiles = m // 128
-            sks = sorted({1, 2, 3, 4, 6, 8, 12, 16} | {max(1, min(16, round(148 * w / tiles))) for w in (1, 2, 3)})
-            cands += [(2, sk, st, 0) for sk in sks for st in (4, 8) if sk <= k // 64]
+            # tcgen05 tile kernel: CTAs per SM x pipeline stages (two CTAs share an SM only with <= 4 stages)
+            cands += [(2, 1, 4, 0), (2, 1, 6, 0), (2, 1, 8, 0), (2, 2, 2, 0), (2, 2, 4, 0), (2, 3, 2, 0)]
     best, best_t = None, float("inf")
     for c in cands:
         if kind.startswith("gemv"):

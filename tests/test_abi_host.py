@@ -96,11 +96,11 @@ def test_argument_errors_surface_as_runtime_error_without_a_gpu():
 def test_c_abi_rejects_bad_shapes_before_touching_the_device():
     from muxi_native_layout_kernels_b200._lib import lib
     one = ctypes.c_void_p(16)   # never dereferenced: the shape check comes first
-    assert lib.mlk_gemm_layoutA(one, one, one, 100, 16, 128, 0, 1.0, 0.0, None, None) == 1
+    assert lib.mlk_gemm_layoutA(one, one, one, 100, 16, 128, 0, 1.0, 0.0, None, None, None) == 1
     assert b"multiple of 128" in lib.mlk_last_error()
     assert lib.mlk_gemv_layoutA_wapper(one, one, one, 40, 64, 0, 1.0, 0.0, 256, 1, 1, 1, None, None, 0, None) == 1
     assert lib.mlk_gemv_layoutA_wapper(one, one, one, 64, 64, 0, 1.0, 0.0, 256, 7, 1, 1, None, None, 0, None) == 2
-    assert lib.mlk_gemm_layoutA_wapper(one, one, one, 128, 16, 128, 0, 1.0, 0.0, 3, 1, 1, 1, None, None) == 1
+    assert lib.mlk_gemm_layoutA_wapper(one, one, one, 128, 16, 128, 0, 1.0, 0.0, 3, 1, 1, 1, None, None, None) == 1
     assert lib.mlk_layoutB(one, one, 10, 32, None) == 1
     assert lib.mlk_fp8_weight_repack(one, one, 6, None) == 1
     assert lib.mlk_fused_routing_gate(one, 0, 4, 300, 1, 1, one, one, 2, None, 0, None) == 2
