@@ -102,8 +102,9 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
 
 /* ---- narrow GEMM: C[n,m] = alpha * B A^T (+ bias), n <= 256 ------------------------------------------- */
 
-/* kernelId 1 (warp-level tensor-core streaming kernel, any n <= 256): kernelParam1 = row groups per warp (1,2),
- *   kernelParam2 = row warps per CTA (1,2,4,8), kernelParam3 = split-K over a thread-block cluster (1,2,4,8).
+/* kernelId 1, 3, 4 (warp-level tensor-core streaming kernel with 256, 128, 64 threads per CTA, any n <= 256):
+ *   kernelParam1 = row groups per warp (1,2), kernelParam2 = row warps per CTA (1,2,4,8; the other warps split K),
+ *   kernelParam3 = split-K over a thread-block cluster (1,2,4,8).
  * kernelId 2 (tcgen05 / tensor-memory tile kernel, 16-bit weights, row-major B, n <= 64): persistent CTAs that split
  *   the (128-row tile, 64-wide k block) work units evenly; kernelParam1 = CTAs per SM the grid is sized for (1..4),
  *   kernelParam2 = TMA pipeline stages (2,4,6,8), kernelParam3 unused.  Splitting tiles between CTAs needs the

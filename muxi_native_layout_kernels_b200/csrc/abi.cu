@@ -77,9 +77,9 @@ int gemm_common(int variant_x, int variant_c, const void* A, const float* scale,
         }
         return launch_dense_umma(wt, p, p1, p2, aux ? &da : nullptr, s);
     }
-    if (kernelId != 1)
-        return fail(kUnsupported, "gemm: kernelId %d is not built (1 = warp-level streaming kernel, 2 = tcgen05 tile kernel)", kernelId);
-    p.rg = p1; p.wm = p2; p.sk = p3; p.threads = 256;
+    if (kernelId != 1 && kernelId != 3 && kernelId != 4)
+        return fail(kUnsupported, "gemm: kernelId %d is not built (1, 3, 4 = warp-level streaming kernel with 256, 128, 64 threads; 2 = tcgen05 tile kernel)", kernelId);
+    p.rg = p1; p.wm = p2; p.sk = p3; p.threads = kernelId == 1 ? 256 : (kernelId == 3 ? 128 : 64);
     return launch_dense_mma(wt, p, s);
 }
 
@@ -90,8 +90,9 @@ int gemm_table(int table, int variant_x, int variant_c, const void* A, const flo
     if (int st = check_gemm_shape(m, n, k)) return st;
     TuneArgs t = global_table(table).get(m, n, k, nullptr);
     // A table row that this shape cannot run with (e.g. copied from another GPU's table) falls back to the default.
-    const bool ok1 = t.a == 1 && (t.b == 1 || t.b == 2) && (t.c == 1 || t.c == 2 || t.c == 4 || t.c == 8) &&
-                     (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b * t.c) == 0;
+    const int twarps = t.a == 1 ? 8 : (t.a == 3 ? 4 : (t.a == 4 ? 2 : 0));
+    const bool ok1 = twarps > 0 && (t.b == 1 || t.b == 2) && (t.c == 1 || t.c == 2 || t.c == 4 || t.c == 8) &&
+                     t.c <= twarps && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b * t.c) == 0;
     const bool ok2 = t.a == 2 && variant_x == 0 && dtype != MLK_E4M3 && n <= 64 && t.b >= 1 && t.b <= 4 &&
                      (t.c == 2 || t.c == 4 || t.c == 6 || t.c == 8);
     if (!ok1 && !ok2) t = default_args(table, m, n, k);

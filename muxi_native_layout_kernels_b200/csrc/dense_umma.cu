@@ -3,9 +3,10 @@
 // "Swap-AB" tile: the 128 weight rows are the UMMA M dimension, the (padded) tokens the N dimension, the fp32
 // accumulator [128 x N] lives in tensor memory.  Why the native weight layout fits without any shuffle: one
 // layout-A block [16 rows][8 k] is 256 contiguous bytes = two K-major, no-swizzle UMMA core matrices (8 rows x 16
-// bytes each).  A 3-D TMA tensor map over global memory (256-byte block, row group, k-octet) with box
-// (block, 8 row groups, 8 k-octets) lands a 128 x 64 weight tile in shared memory as [k-octet][row group][256 B],
-// which one shared-memory descriptor addresses with uniform strides: 8-row step 128 B, k-octet step 2048 B.
+// bytes each).  A 4-D TMA tensor map over global memory (128-byte core matrix, k-octet, row group, half) lands a
+// 128 x 64 weight tile in shared memory as [half][row group][k-octet][128 B], which one shared-memory descriptor
+// addresses with uniform strides (8-row step 1024 B, k-octet step 128 B); accumulator rows are a fixed permutation
+// of the tile's weight rows, undone when the output is written.
 // Activations are row-major; a 2-D tensor map with the 128-byte swizzle delivers the [N x 64] tile in the
 // canonical K-major SW128 layout (rows beyond n are zero-filled by the TMA unit).
 //
@@ -79,6 +80,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
@@ -202,20 +209,23 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
         if (!static_weights) pdl_wait();
         pdl_launch_dependents();
         bool waited = !static_weights;
-        int i = 0;
-        for (long long u = u0; u < u1; ++u, ++i) {
+        // (tile, k block) advance by increment: a 64-bit division per stage in this single thread would cost more
+        // than the stage's memory time
+        int tile = (int)(u0 / KB), kb = (int)(u0 - (long long)tile * KB);
+        const int nunits = (int)(u1 - u0);
+        for (int i = 0; i < nunits; ++i) {
             const int s = i % STAGES;
             if (i >= STAGES && !mbar_wait(empty_bar(s), ((i / STAGES) - 1) & 1)) {
                 abort_flag = 1;
                 if (p.status) atomicExch(p.status, 1);
             }
             if (abort_flag) break;
-            const int tile = (int)(u / KB), kb = (int)(u - (long long)tile * KB);
             mbar_expect_tx(full_bar(s), kABytes + kBBytes);
-            tma_load_3d(a_base + s * kABytes, &map_a, full_bar(s), 0, tile * (kTileM / 16), kb * (kBlockK / 8));
+            tma_load_4d(a_base + s * kABytes, &map_a, full_bar(s), 0, kb * (kBlockK / 8), tile * (kTileM / 16), 0);
             if (!waited) { pdl_wait(); waited = true; }
             tma_load_2d(b_base + s * kBBytes, &map_x, full_bar(s), kb * kBlockK, 0);
             ++issued;
+            if (++kb == KB) { kb = 0; ++tile; }
         }
         if (!waited) pdl_wait();
     } else if (warp == 1 && lane == 0) {
@@ -242,8 +252,9 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int kk = 0; kk < kBlockK / 16; ++kk) {
-                    // A: no swizzle, 8-row step 128 B, k-octet step 2048 B; one MMA consumes two k-octets
-                    const uint64_t da = smem_desc(a_base + s * kABytes + kk * 4096, 2048, 128, 0);
+                    // A: no swizzle, [half][row group][k-octet][8 rows x 16 B]: 8-row step 1024 B, k-octet step 128 B;
+                    // one MMA consumes two k-octets
+                    const uint64_t da = smem_desc(a_base + s * kABytes + kk * 256, 128, 1024, 0);
                     // B: 128-byte swizzle, 8-token step 1024 B; one MMA consumes 32 bytes of each 128-byte row
                     const uint64_t db = smem_desc(b_base + s * kBBytes + kk * 32, 16, 1024, 2);
                     umma_f16(tmem + b * NP, da, db, idesc, (kb > kb_begin || kk > 0) ? 1u : 0u);
@@ -257,7 +268,9 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
     } else if (warp >= 2) {
         // ---- epilogue warps ----
         const int quad = warp & 3;
-        const int lrow = quad * 32 + lane;
+        const int lrow = quad * 32 + lane;          // accumulator row = TMEM lane
+        // accumulator row rho holds weight row 16*(rho%64 / 8) + 8*(rho / 64) + rho%8 of the tile (see make_map_a)
+        const int wrow = ((lrow & 63) >> 3) * 16 + (lrow >> 6) * 8 + (lrow & 7);
         const int etid = tid - 64;
         int seg = 0;
         for (long long u = u0; u < u1; ++seg) {
@@ -305,17 +318,28 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
                     __threadfence();
 #pragma unroll
                     for (int c = 0; c < NP; ++c) v[c] = 0.f;
-                    for (int j = 0; j < parts; ++j) {
-                        const float* q = p.ws + ((size_t)(tile * p.max_parts + j) * NP) * kTileM + lrow;
+                    // The adds keep ascending part order; the loads of UN parts are issued together so that
+                    // their L2 latencies overlap (UN * NP values in flight per thread).
+                    constexpr int UN = 64 / NP;
+                    const float* q0 = p.ws + ((size_t)(tile * p.max_parts) * NP) * kTileM + lrow;
+                    for (int j = 0; j < parts; j += UN) {
+                        float t[UN][NP];
 #pragma unroll
-                        for (int c = 0; c < NP; ++c) v[c] += __ldcg(q + (size_t)c * kTileM);
+                        for (int jj = 0; jj < UN; ++jj)
+#pragma unroll
+                            for (int c = 0; c < NP; ++c)
+                                t[jj][c] = (j + jj < parts) ? __ldcg(q0 + ((size_t)(j + jj) * NP + c) * kTileM) : 0.f;
+#pragma unroll
+                        for (int jj = 0; jj < UN; ++jj)
+#pragma unroll
+                            for (int c = 0; c < NP; ++c) v[c] += t[jj][c];
                     }
                     if (etid == 0) p.counters[tile] = 0;   // ready for the next launch
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag may be rewritten by the next segment
             }
             if (do_store) {
-                const int row = tile * kTileM + lrow;
+                const int row = tile * kTileM + wrow;
                 const float bia = (p.bias != nullptr) ? load_scalar16<WT>(p.bias, row) : 0.f;
 #pragma unroll
                 for (int c = 0; c < NP; ++c) {
@@ -372,12 +396,17 @@ EncodeFn encode_fn() {
     return fn;
 }
 
+// Weight tile map.  Global layout A is [row group][k-octet][half][8 rows][8 k]; the 4-D view (64 elements = one
+// 8-row core matrix, k-octet, row group, half) with box (64, 8, 8, 2) is traversed k-octet first, so each row
+// group's 2 KB run of a k block is fetched as consecutive requests, and lands in shared memory as
+// [half][row group][k-octet][128 B]: core matrix (accumulator 8-row group i = 8*half + row group, k-octet o) sits at
+// i*1024 + o*128, uniform strides for one M = 128 descriptor.
 bool make_map_a(CUtensorMap* map, const void* A, int m, int k, int wt) {
-    const cuuint64_t dims[3] = {128, (cuuint64_t)(m / 16), (cuuint64_t)(k / 8)};
-    const cuuint64_t strides[2] = {(cuuint64_t)16 * k * 2, 256};
-    const cuuint32_t box[3] = {128, kTileM / 16, kBlockK / 8};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    return encode_fn()(map, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+    const cuuint64_t dims[4] = {64, (cuuint64_t)(k / 8), (cuuint64_t)(m / 16), 2};
+    const cuuint64_t strides[3] = {256, (cuuint64_t)16 * k * 2, 128};
+    const cuuint32_t box[4] = {64, kBlockK / 8, kTileM / 16, 2};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return encode_fn()(map, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
                        const_cast<void*>(A), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;

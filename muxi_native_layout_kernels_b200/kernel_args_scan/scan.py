@@ -123,8 +123,9 @@ def scan_one(kind, m, n, k, dtype, log):
         cands = [(t, kid, rg, sk) for t, kid, rg, sk in itertools.product([64, 128, 256], [1, 2], [1, 2], [1, 2, 4, 8])
                  if not (fp8 and kid == 2) and m % (16 * rg) == 0]
     else:
-        cands = [(1, rg, wm, sk) for rg, wm, sk in itertools.product([1, 2], [1, 2, 4, 8], [1, 2, 4, 8])
-                 if m % (16 * rg * wm) == 0]
+        # kernelId 1 / 3 / 4: the warp-level kernel with 8 / 4 / 2 warps per CTA
+        cands = [(kid, rg, wm, sk) for kid, rg, wm, sk in itertools.product([1, 3, 4], [1, 2], [1, 2, 4, 8], [1, 2, 4])
+                 if m % (16 * rg * wm) == 0 and wm <= {1: 8, 3: 4, 4: 2}[kid]]
         if kind == "a" and n <= 64:
             # tcgen05 tile kernel: CTAs per SM x pipeline stages (two CTAs share an SM only with <= 4 stages)
             cands += [(2, 1, 4, 0), (2, 1, 6, 0), (2, 1, 8, 0), (2, 2, 2, 0), (2, 2, 4, 0), (2, 3, 2, 0)]
@@ -137,11 +138,14 @@ def scan_one(kind, m, n, k, dtype, log):
             call = lambda A: mlk.gemm_layoutA_wapper(A, X, m, n, k, kernelParam1=c[1], kernelParam2=c[2], kernelParam3=c[3],
                                                      kernelId=c[0])
         elif kind == "a_fp8":
-            call = lambda A: mlk.gemm_layoutA_soft_fp8_wapper(A, None, X, m, n, k, kernelParam1=c[1], kernelParam2=c[2], kernelParam3=c[3])
+            call = lambda A: mlk.gemm_layoutA_soft_fp8_wapper(A, None, X, m, n, k, kernelParam1=c[1], kernelParam2=c[2], kernelParam3=c[3],
+                                                              kernelId=c[0])
         elif kind == "conc":
-            call = lambda A: mlk.gemm_layoutAB_ContinuousC_wapper(A, XB, m, n, k, kernelParam1=c[1], kernelParam2=c[2], kernelParam3=c[3])
+            call = lambda A: mlk.gemm_layoutAB_ContinuousC_wapper(A, XB, m, n, k, kernelParam1=c[1], kernelParam2=c[2], kernelParam3=c[3],
+                                                                  kernelId=c[0])
         else:
-            call = lambda A: mlk.reLayoutC(mlk.gemm_layoutABC_wapper(A, XB, m, n, k, kernelParam1=c[1], kernelParam2=c[2], kernelParam3=c[3]))
+            call = lambda A: mlk.reLayoutC(mlk.gemm_layoutABC_wapper(A, XB, m, n, k, kernelParam1=c[1], kernelParam2=c[2], kernelParam3=c[3],
+                                                                     kernelId=c[0]))
         try:
             got = call(pool[0])
         except MlkError:
@@ -150,7 +154,7 @@ def scan_one(kind, m, n, k, dtype, log):
             log.writerow([m, n, k, *c, "WRONG"])
             continue
         if kind == "abc":                 # time the GEMM alone, not the un-permute used for the check
-            call = lambda A: mlk.gemm_layoutABC_wapper(A, XB, m, n, k, kernelParam1=c[1], kernelParam2=c[2], kernelParam3=c[3])
+            call = lambda A: mlk.gemm_layoutABC_wapper(A, XB, m, n, k, kernelParam1=c[1], kernelParam2=c[2], kernelParam3=c[3], kernelId=c[0])
         us = time_candidate(call, pool)
         log.writerow([m, n, k, *c, f"{us:.3f}"])
         if us < best_t:

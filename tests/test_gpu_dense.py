@@ -205,7 +205,7 @@ def test_gemm_errors_and_determinism():
     with pytest.raises(RuntimeError, match="same k"):
         mlk.gemm_layoutA(A, randn((16, 128), 83).to(dev))
     with pytest.raises(RuntimeError, match="kernelId"):
-        mlk.gemm_layoutA_wapper(A, X, 256, 16, 256, kernelId=3)
+        mlk.gemm_layoutA_wapper(A, X, 256, 16, 256, kernelId=7)
     with pytest.raises(RuntimeError, match="row tile"):
         A128 = mlk.layoutA(randn((128, 256), 84).to(dev))
         mlk.gemm_layoutA_wapper(A128, X, 128, 16, 256, kernelParam1=2, kernelParam2=8, kernelParam3=1)
