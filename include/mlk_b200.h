@@ -199,6 +199,17 @@ int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int
                               int experts_map_len, float* combine_scratch, int64_t combine_scratch_bytes,
                               int tune_rg, int tune_sk1, int tune_sk2, mlk_stream_t s);
 
+/* ---- expert-parallel token exchange (no counterpart in the reference, which is single-GPU) ------------------ */
+
+/* out[i,:] = x[idx[i],:] for n_rows rows of `hidden` 16-bit elements (hidden % 8 == 0); an index outside
+ * [0, x_rows) gives a zero row.  Builds the send buffer of the dispatch all-to-all. */
+int mlk_moe_gather_rows(const void* x, const int32_t* idx, void* out, int64_t n_rows, int hidden, int64_t x_rows,
+                        mlk_stream_t s);
+/* y[t,:] = round( sum_j float(rows[pos[t*topK + j],:]) ), j ascending, entries with pos outside [0, n_rows) skipped.
+ * Combine step: `rows` are the weighted expert outputs as they come back from the combine all-to-all. */
+int mlk_moe_unpermute_sum(const void* rows, const int32_t* pos, void* y, int64_t T, int topK, int hidden,
+                          int64_t n_rows, int dtype, mlk_stream_t s);
+
 #ifdef __cplusplus
 }
 #endif

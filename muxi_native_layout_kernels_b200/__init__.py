@@ -6,6 +6,6 @@ Importing fails if the CUDA library has not been built: there is no fallback pat
 """
 from .ext import *  # noqa: F401,F403
 from .ext import __all__ as _ext_all
-from . import ext, muxi_moe_planC, utils  # noqa: F401
+from . import ext, muxi_moe_planC, parallel, utils  # noqa: F401
 
-__all__ = list(_ext_all) + ["ext", "muxi_moe_planC", "utils"]
+__all__ = list(_ext_all) + ["ext", "muxi_moe_planC", "parallel", "utils"]

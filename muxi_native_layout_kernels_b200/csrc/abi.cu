@@ -275,6 +275,18 @@ int mlk_moe_align(int batchSize, int expertCount, int topK, int microBatchSize, 
                             padded_num_experts, experts_ids_out, experts_map, experts_map_len, (cudaStream_t)s);
 }
 
+int mlk_moe_gather_rows(const void* x, const int32_t* idx, void* out, int64_t n_rows, int hidden, int64_t x_rows,
+                        mlk_stream_t s) {
+    clear_error();
+    return launch_gather_rows(x, idx, out, n_rows, hidden, x_rows, (cudaStream_t)s);
+}
+
+int mlk_moe_unpermute_sum(const void* rows, const int32_t* pos, void* y, int64_t T, int topK, int hidden,
+                          int64_t n_rows, int dtype, mlk_stream_t s) {
+    clear_error();
+    return launch_unpermute_sum(rows, pos, y, T, topK, hidden, n_rows, dtype, (cudaStream_t)s);
+}
+
 int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int batch_size, int expert_count,
                               int topK, int hidden, int inter, const int32_t* topk_ids, const void* topk_weights,
                               int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,

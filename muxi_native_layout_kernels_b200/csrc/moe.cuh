@@ -47,4 +47,10 @@ struct MoeParams {
 
 int launch_fused_experts(const MoeParams& p, cudaStream_t s);
 
+// Expert-parallel exchange helpers (moe_exchange.cu).
+int launch_gather_rows(const void* x, const int32_t* idx, void* out, long long n_rows, int H, long long x_rows,
+                       cudaStream_t s);
+int launch_unpermute_sum(const void* rows, const int32_t* pos, void* y, long long T, int topk, int H, long long n_rows,
+                         int dtype, cudaStream_t s);
+
 }  // namespace mlk

@@ -1,0 +1,209 @@
+"""Sharding of the weight-streaming path over the GPUs of one node (one process per GPU, torch.distributed).
+
+The reference is single-GPU; its only hook is ``experts_map`` (csrc/moe_kernels/moe_align_tokens.h:46-49).  Two
+natural partitions exist and both are provided here:
+
+* dense layers: output features are independent, and layout A is row-group major, so rank g simply owns the weight
+  rows ``[g*m/G, (g+1)*m/G)``; activations are replicated and no collective is needed (``all_gather_columns`` is
+  there for callers that want the full ``y`` on every rank).
+* fused MoE, expert parallel: rank g owns experts ``[g*E/G, (g+1)*E/G)``.
+  - ``fused_moe_ep_replicated``: tokens replicated, every rank computes its experts' share through ``experts_map``
+    and the shares are all-reduced (what the reference's hook supports).
+  - ``fused_moe_ep``: tokens sharded; the router runs locally, every routed (token, slot) row travels to the rank
+    that owns its expert (all-to-all), is processed there as a one-expert token, travels back (all-to-all) and the
+    source rank adds each token's top-k rows in fp32 in a fixed order.
+
+The exchange plan (who sends how many rows to whom, and where returned rows belong) is plain integer tensor
+arithmetic and is kept separate from the device work (``plan_dispatch``) so that it runs -- and is tested -- on CPU
+tensors with the gloo backend as well.  All NCCL traffic lands in this GPU's own memory before any kernel reads it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+# ---------------------------------------------------------------------------------------------------------
+# dense layers
+# ---------------------------------------------------------------------------------------------------------
+
+def shard_rows(W: torch.Tensor, rank: int, world: int, multiple: int = 128) -> torch.Tensor:
+    """Rows ``[rank*m/world, (rank+1)*m/world)`` of ``W[m,k]`` (contiguous).  The shard height must stay a multiple
+    of ``multiple`` (128 for the GEMM entry points, 16 for GeMV)."""
+    m = W.shape[0]
+    if m % world != 0 or (m // world) % multiple != 0:
+        raise ValueError(f"{m} rows cannot be split over {world} ranks in multiples of {multiple}")
+    rows = m // world
+    return W[rank * rows:(rank + 1) * rows].contiguous()
+
+
+def all_gather_columns(y_local: torch.Tensor, group=None) -> torch.Tensor:
+    """``y_local[n, m/G]`` of every rank -> ``y[n, m]`` on every rank (optional; the sharded layer itself needs no
+    collective)."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return y_local
+    parts = [torch.empty_like(y_local) for _ in range(world)]
+    dist.all_gather(parts, y_local.contiguous(), group=group)
+    return torch.cat(parts, dim=-1)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# expert-parallel exchange plan (device independent)
+# ---------------------------------------------------------------------------------------------------------
+
+@dataclass
+class DispatchPlan:
+    send_slot: torch.Tensor      # int32 [n_send]: flat slot (token*topk + j) of every row sent, grouped by destination
+    send_token: torch.Tensor     # int32 [n_send]: source token of every row sent
+    send_expert: torch.Tensor    # int32 [n_send]: expert id local to the destination rank
+    send_counts: List[int]       # rows sent to each rank
+    slot_to_row: torch.Tensor    # int32 [T*topk]: position of slot in the send order (= in the returned rows)
+
+
+def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int) -> DispatchPlan:
+    """Groups the routed slots of this rank by destination rank (stable: ascending slot inside a destination)."""
+    T, topk = topk_ids.shape
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
+    order = torch.sort(dest, stable=True)[1]
+    counts = torch.bincount(dest, minlength=world)[:world]
+    slot_to_row = torch.empty_like(order)
+    slot_to_row[order] = torch.arange(order.numel(), device=order.device)
+    return DispatchPlan(
+        send_slot=order.to(torch.int32),
+        send_token=torch.div(order, topk, rounding_mode="floor").to(torch.int32),
+        send_expert=(flat[order] - dest[order] * experts_per_rank).to(torch.int32),
+        send_counts=[int(c) for c in counts.tolist()],      # host copy: all_to_all_single needs split sizes on the host
+        slot_to_row=slot_to_row.to(torch.int32),
+    )
+
+
+def exchange_counts(send_counts: List[int], device, group=None) -> List[int]:
+    world = dist.get_world_size(group)
+    s = torch.tensor(send_counts, dtype=torch.int64, device=device)
+    r = torch.empty(world, dtype=torch.int64, device=device)
+    dist.all_to_all_single(r, s, group=group)
+    return [int(v) for v in r.tolist()]
+
+
+def _a2a(send: torch.Tensor, send_counts: List[int], recv_counts: List[int], group=None) -> torch.Tensor:
+    recv = torch.empty((sum(recv_counts),) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+    dist.all_to_all_single(recv, send.contiguous(), output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
+    return recv
+
+
+def moe_exchange(
+    x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, experts_per_rank: int,
+    experts_fn: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
+    gather_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
+    combine_fn: Callable[[torch.Tensor, torch.Tensor, int, int], torch.Tensor],
+    group=None,
+) -> torch.Tensor:
+    """Dispatch -> local expert compute -> combine for this rank's tokens.
+
+    experts_fn(rows [R,H], local_expert [R] int32, weight [R]) -> weighted outputs [R,H] (same dtype as rows)
+    gather_fn(x [T,H], token_index [R] int32) -> rows [R,H]
+    combine_fn(rows [R,H], slot_to_row [T*topk] int32, T, topk) -> y [T,H]
+    """
+    world = dist.get_world_size(group)
+    T, topk = topk_ids.shape
+    plan = plan_dispatch(topk_ids, experts_per_rank, world)
+    recv_counts = exchange_counts(plan.send_counts, x.device, group)
+    rows = gather_fn(x, plan.send_token)
+    w_send = topk_weights.reshape(-1)[plan.send_slot.long()].contiguous()
+    rows_in = _a2a(rows, plan.send_counts, recv_counts, group)
+    e_in = _a2a(plan.send_expert, plan.send_counts, recv_counts, group)
+    w_in = _a2a(w_send, plan.send_counts, recv_counts, group)
+    out_rows = experts_fn(rows_in, e_in, w_in)
+    back = _a2a(out_rows, recv_counts, plan.send_counts, group)
+    return combine_fn(back, plan.slot_to_row, T, topk)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# GPU entry points
+# ---------------------------------------------------------------------------------------------------------
+
+def _gpu_gather(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    from ._lib import check, lib
+    out = torch.empty((idx.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    check(lib.mlk_moe_gather_rows(x.data_ptr(), idx.data_ptr(), out.data_ptr(), idx.numel(), x.shape[1], x.shape[0],
+                                  torch.cuda.current_stream(x.device).cuda_stream))
+    return out
+
+
+def _gpu_combine(rows: torch.Tensor, slot_to_row: torch.Tensor, T: int, topk: int) -> torch.Tensor:
+    from ._lib import check, lib
+    H = rows.shape[1]
+    y = torch.empty((T, H), dtype=rows.dtype, device=rows.device)
+    code = 1 if rows.dtype == torch.float16 else 0
+    check(lib.mlk_moe_unpermute_sum(rows.data_ptr() if rows.numel() else None, slot_to_row.data_ptr(), y.data_ptr(), T,
+                                    topk, H, rows.shape[0], code, torch.cuda.current_stream(rows.device).cuda_stream))
+    return y
+
+
+def fused_moe_ep(
+    hidden_states: torch.Tensor, w1_local: torch.Tensor, w2_local: torch.Tensor, gating_output: torch.Tensor,
+    topk: int, renormalize: bool, group=None, score_func: str = "softmax", num_expert_group: int = 1,
+    topk_group: int = 1, gating_bias: Optional[torch.Tensor] = None, w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None, soft_fp8: bool = False, fp8_repacked: bool = False,
+) -> torch.Tensor:
+    """Expert-parallel fused MoE for this rank's tokens ``hidden_states [T_local, H]``; ``w1_local [E/G, 2I, H]`` and
+    ``w2_local [E/G, H, I]`` hold this rank's experts in layout A; ``gating_output [T_local, E]`` covers all experts."""
+    from . import ext
+    T, H = hidden_states.shape
+    E = gating_output.shape[1]
+    world = dist.get_world_size(group)
+    e_local = w1_local.shape[0]
+    if e_local * world != E:
+        raise ValueError(f"{E} experts over {world} ranks need {E // max(world, 1)} local experts, got {e_local}")
+    dev = hidden_states.device
+    ids = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    wts = torch.empty(T, topk, dtype=hidden_states.dtype, device=dev)
+    ext.fused_routing_gate(gating_output, 0 if score_func == "softmax" else 1, T, H, num_expert_group, topk_group, ids,
+                           wts, topk, gating_bias)
+    if renormalize:
+        wts = wts / wts.sum(dim=-1, keepdim=True)
+
+    def experts_fn(rows, local_expert, weight):
+        R = rows.shape[0]
+        y = torch.zeros_like(rows)
+        if R == 0:
+            return y
+        m1 = w1_local.shape[1]
+        n_pad = R + e_local * 15
+        sorted_ids = torch.full((n_pad,), R, dtype=torch.int32, device=dev)
+        cumsum = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
+        nblk = torch.empty(1, dtype=torch.int32, device=dev)
+        blk = torch.empty((n_pad + 15) // 16, dtype=torch.int32, device=dev)
+        C = torch.empty(m1 * R, dtype=rows.dtype, device=dev)
+        args = (w1_local, w2_local, rows, R, e_local, 1, local_expert.view(R, 1).contiguous(),
+                weight.view(R, 1).contiguous(), sorted_ids, cumsum, nblk, blk, C, y)
+        if soft_fp8:
+            ext.fused_experts_compute(*args, w1_scale, w2_scale, [128, 128], True, fp8_repacked=fp8_repacked)
+        else:
+            ext.fused_experts_compute(*args)
+        return y
+
+    return moe_exchange(hidden_states, ids, wts, e_local, experts_fn, _gpu_gather, _gpu_combine, group)
+
+
+def fused_moe_ep_replicated(hidden_states, w1_local, w2_local, gating_output, topk, renormalize, group=None, **kw):
+    """Tokens replicated on every rank; each rank adds its experts' share (``experts_map``) and the shares are summed
+    with an all-reduce.  This is the expert-parallel mode the reference's ``experts_map`` hook was made for."""
+    from .muxi_moe_planC import fused_moe
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    E = gating_output.shape[1]
+    e_local = w1_local.shape[0]
+    emap = torch.full((E,), -1, dtype=torch.int32, device=hidden_states.device)
+    emap[rank * e_local:(rank + 1) * e_local] = torch.arange(e_local, dtype=torch.int32, device=hidden_states.device)
+    y = fused_moe(hidden_states, w1_local, w2_local, gating_output, topk, renormalize, experts_map=emap, **kw)
+    if world > 1:
+        y32 = y.float()
+        dist.all_reduce(y32, group=group)
+        y = y32.to(hidden_states.dtype)
+    return y

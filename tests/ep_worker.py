@@ -1,0 +1,65 @@
+"""Worker of tests/test_gpu_multi.py: launched by torch.distributed.run, one rank per GPU.  Compares the
+expert-parallel fused MoE (token-sharded all-to-all mode and replicated all-reduce mode) and the row-sharded dense
+layer with the single-GPU result computed on the same rank."""
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+import muxi_native_layout_kernels_b200 as mlk  # noqa: E402
+from muxi_native_layout_kernels_b200 import parallel  # noqa: E402
+from muxi_native_layout_kernels_b200.muxi_moe_planC import fused_moe  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    g = torch.Generator().manual_seed(77)
+    ok = True
+    for (E, topk, H, I, T, fp8) in [(16, 4, 256, 128, 24, False), (32, 8, 256, 128, 40, True)]:
+        x = torch.randn(world * T, H, generator=g).to(torch.bfloat16).to(dev)
+        logits = torch.randn(world * T, E, generator=g).to(torch.bfloat16).to(dev)
+        if fp8:
+            w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.25).to(torch.float8_e4m3fn).to(dev)
+            w2 = (torch.randn(E, H, I, generator=g) * 0.25).to(torch.float8_e4m3fn).to(dev)
+        else:
+            w1 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+            w2 = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+        w1a, w2a = mlk.layoutA(w1), mlk.layoutA(w2)
+        kw = dict(soft_fp8=True, block_shape=[128, 128]) if fp8 else {}
+        full = fused_moe(x, w1a, w2a, logits, topk, True, **kw).float()
+        el = E // world
+        w1l, w2l = w1a[rank * el:(rank + 1) * el].contiguous(), w2a[rank * el:(rank + 1) * el].contiguous()
+        xs, ls = x[rank * T:(rank + 1) * T].contiguous(), logits[rank * T:(rank + 1) * T].contiguous()
+        y_ep = parallel.fused_moe_ep(xs, w1l, w2l, ls, topk, True, soft_fp8=fp8).float()
+        want = full[rank * T:(rank + 1) * T]
+        scale = max(1.0, float(want.pow(2).mean().sqrt()))
+        d1 = (y_ep - want).abs()
+        ok1 = bool((d1 <= 1e-2 * scale + 1e-2 * want.abs()).all())
+        y_rep = parallel.fused_moe_ep_replicated(x, w1l, w2l, logits, topk, True, **kw).float()
+        d2 = (y_rep - full).abs()
+        ok2 = bool((d2 <= 1e-2 * scale + 1e-2 * full.abs()).all())
+        print(f"rank {rank} E={E} fp8={fp8}: ep max {float(d1.max()):.4g} ok={ok1}; replicated max {float(d2.max()):.4g} ok={ok2}", flush=True)
+        ok = ok and ok1 and ok2
+    # dense: row shard, then all-gather of the output columns
+    W = (torch.randn(1024, 512, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    X = torch.randn(8, 512, generator=g).to(torch.bfloat16).to(dev)
+    y_full = mlk.gemm_layoutA(mlk.layoutA(W), X)
+    y_loc = mlk.gemm_layoutA(mlk.layoutA(parallel.shard_rows(W, rank, world)), X)
+    ok3 = torch.equal(parallel.all_gather_columns(y_loc), y_full)
+    print(f"rank {rank} dense row shard ok={ok3}", flush=True)
+    ok = ok and ok3
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
