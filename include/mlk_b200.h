@@ -199,6 +199,20 @@ int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int
                               int experts_map_len, float* combine_scratch, int64_t combine_scratch_bytes,
                               int tune_rg, int tune_sk1, int tune_sk2, mlk_stream_t s);
 
+/* Expert compute for callers that must not allocate device memory (a plugin running under another runtime's memory
+ * pool, a serving loop whose allocator is off limits on the request path).  It has no
+ * counterpart in the reference.  Same arguments and results as mlk_fused_experts_compute with a combine scratch,
+ * except that the scratch is a device array built into the library: 8 MiB per GPU that loads the library, held
+ * until the process exits, which limits batch_size * topK * hidden to 2 Mi (2097152) floats -- larger calls fail
+ * with MLK_ERR_INVALID_ARG.  The first call on a device looks the array's address up; make that call before any
+ * stream capture.  All calls share the array: calls that overlap on the GPU (different streams) race on it. */
+int mlk_fused_experts_compute_static(const void* w1, const void* w2, const void* x, int batch_size, int expert_count,
+                                     int topK, int hidden, int inter, const int32_t* topk_ids, const void* topk_weights,
+                                     int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
+                                     int32_t* experts_ids, void* C, void* y, const float* w1_scale,
+                                     const float* w2_scale, int dtype, int fp8_order, int microBatchSize,
+                                     const int32_t* experts_map, int experts_map_len, mlk_stream_t s);
+
 /* ---- expert-parallel token exchange (no counterpart in the reference, which is single-GPU) ------------------ */
 
 /* out[i,:] = x[idx[i],:] for n_rows rows of `hidden` 16-bit elements (hidden % 8 == 0); an index outside

@@ -49,6 +49,9 @@ PROTOTYPES = {
     "mlk_fused_routing_gate": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_vp, c_int,
                                        c_vp]),
     "mlk_moe_align": (c_int, [c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_vp]),
+    "mlk_fused_experts_compute_static": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp,
+                                                 c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp,
+                                                 c_int, c_vp]),
     "mlk_moe_gather_rows": (c_int, [c_vp, c_vp, c_vp, c_i64, c_int, c_i64, c_vp]),
     "mlk_moe_unpermute_sum": (c_int, [c_vp, c_vp, c_vp, c_i64, c_int, c_int, c_i64, c_int, c_vp]),
     "mlk_fused_experts_compute": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp,

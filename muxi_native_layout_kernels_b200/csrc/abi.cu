@@ -305,4 +305,20 @@ int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int
     return launch_fused_experts(p, (cudaStream_t)s);
 }
 
+int mlk_fused_experts_compute_static(const void* w1, const void* w2, const void* x, int batch_size, int expert_count,
+                                     int topK, int hidden, int inter, const int32_t* topk_ids, const void* topk_weights,
+                                     int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
+                                     int32_t* experts_ids, void* C, void* y, const float* w1_scale,
+                                     const float* w2_scale, int dtype, int fp8_order, int microBatchSize,
+                                     const int32_t* experts_map, int experts_map_len, mlk_stream_t s) {
+    clear_error();
+    MoeParams p{};
+    p.w1 = w1; p.w2 = w2; p.x = x; p.T = batch_size; p.E = expert_count; p.topk = topK; p.H = hidden; p.I = inter;
+    p.topk_ids = topk_ids; p.topk_weights = topk_weights; p.sorted_token_ids = sorted_token_ids;
+    p.cumsum = cumsum_buffer; p.padded_num_experts = padded_num_experts; p.experts_ids = experts_ids;
+    p.C = C; p.y = y; p.w1_scale = w1_scale; p.w2_scale = w2_scale; p.dtype = dtype; p.fp8_order = fp8_order;
+    p.mbs = microBatchSize; p.experts_map = experts_map; p.experts_map_len = experts_map_len;
+    return launch_fused_experts_static(p, (cudaStream_t)s);
+}
+
 }  // extern "C"

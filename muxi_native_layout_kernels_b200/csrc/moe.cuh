@@ -46,6 +46,7 @@ struct MoeParams {
 };
 
 int launch_fused_experts(const MoeParams& p, cudaStream_t s);
+int launch_fused_experts_static(const MoeParams& p, cudaStream_t s);   // combine scratch in a built-in device array
 
 // Expert-parallel exchange helpers (moe_exchange.cu).
 int launch_gather_rows(const void* x, const int32_t* idx, void* out, long long n_rows, int H, long long x_rows,

@@ -383,4 +383,49 @@ int launch_fused_experts(const MoeParams& m, cudaStream_t s) {
     return check_launch("moe_combine");
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Expert compute for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc at all: a plugin that runs inside a memory pool it does not
+// own, or a serving loop whose memory budget was fixed at start-up and
+// whose allocator is off limits on the request path.  For them the fp32 buffer of the fixed-order combine (one row
+// of H floats per routed slot) lives in this file-scope device array instead of a caller-provided pointer.
+//
+//   * Size limit: T * topK * H <= kStaticCombineFloats (2 Mi floats = 8 MiB); larger problems are rejected.
+//   * Every GPU that loads the library carries these 8 MiB until the process exits.
+//   * In host code the array's name is only a stand-in; the device address is fetched once per device with
+//     cudaGetSymbolAddress while that device is current (first call on the device).  Make that first call before
+//     any stream capture.
+//   * All calls share the array and it keeps the previous call's contents.  Nothing in it has to start at zero:
+//     the second GEMM writes every row that the combine kernel later reads (rows of slots whose expert is not on
+//     this rank are never read).  Two calls that overlap on the GPU (different streams) race on it.
+constexpr long long kStaticCombineFloats = 2LL << 20;
+static __device__ __align__(256) float g_static_combine[kStaticCombineFloats];
+
+int launch_fused_experts_static(const MoeParams& p0, cudaStream_t s) {
+    const long long need = (long long)p0.T * p0.topk * p0.H;
+    if (p0.T < 0 || p0.topk <= 0 || p0.H <= 0) return fail(kInvalidArg, "fused_experts_compute_static: bad sizes");
+    if (need > kStaticCombineFloats)
+        return fail(kInvalidArg,
+                    "fused_experts_compute_static: batch_size * topK * hidden = %lld floats exceeds the built-in scratch of "
+                    "%lld floats; use mlk_fused_experts_compute with a caller-provided buffer",
+                    need, kStaticCombineFloats);
+    static float* dev_addr[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(kCudaError, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail(kUnsupported, "fused_experts_compute_static: device index %d out of range", dev);
+    if (dev_addr[dev] == nullptr) {
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_combine);
+        if (e != cudaSuccess || ptr == nullptr)
+            return fail(kCudaError, "cudaGetSymbolAddress(static combine scratch): %s", cudaGetErrorString(e));
+        dev_addr[dev] = ptr;
+    }
+    MoeParams p = p0;
+    p.scratch = dev_addr[dev];
+    p.scratch_bytes = kStaticCombineFloats * (long long)sizeof(float);
+    return launch_fused_experts(p, s);
+}
+
 }  // namespace mlk
