@@ -108,7 +108,9 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
  * kernelId 2 (tcgen05 / tensor-memory tile kernel, 16-bit weights, row-major B, n <= 64): persistent CTAs that split
  *   the (128-row tile, 64-wide k block) work units evenly; kernelParam1 = CTAs per SM the grid is sized for (1..4),
  *   kernelParam2 = TMA pipeline stages (2,4,6,8), kernelParam3 unused.  Splitting tiles between CTAs needs the
- *   caller-provided scratch below; without it the kernel runs one CTA per tile. */
+ *   caller-provided scratch below; without it the kernel runs one CTA per tile.
+ * kernelId 5, 6, 7 (CUDA-core FMA + shuffle kernel with 256, 128, 64 threads; 16-bit weights, row-major B and C,
+ *   n <= 4): kernelParam1 = row groups per warp (1,2), kernelParam2 unused, kernelParam3 = cluster split-K. */
 
 /* Scratch lent to one call (device pointers).  workspace: mlk_gemm_workspace_bytes(m, n, k) bytes, any content.
  * counters: >= m/128 ints that are zero on entry; every kernel leaves them

@@ -77,6 +77,13 @@ int gemm_common(int variant_x, int variant_c, const void* A, const float* scale,
         }
         return launch_dense_umma(wt, p, p1, p2, aux ? &da : nullptr, s);
     }
+    if (kernelId >= 5 && kernelId <= 7) {
+        // CUDA-core FMA kernel for 1..4 tokens; 5 / 6 / 7 = 256 / 128 / 64 threads; kernelParam1 = row groups per
+        // warp, kernelParam3 = cluster split-K
+        if (variant_x != 0 || variant_c != 0) return fail(kUnsupported, "gemm: the CUDA-core kernel needs row-major B and C");
+        p.rg = p1; p.wm = 1; p.sk = p3; p.threads = kernelId == 5 ? 256 : (kernelId == 6 ? 128 : 64);
+        return launch_gemv_simt(wt, p, 0, s);
+    }
     if (kernelId != 1 && kernelId != 3 && kernelId != 4)
         return fail(kUnsupported, "gemm: kernelId %d is not built (1, 3, 4 = warp-level streaming kernel with 256, 128, 64 threads; 2 = tcgen05 tile kernel)", kernelId);
     p.rg = p1; p.wm = p2; p.sk = p3; p.threads = kernelId == 1 ? 256 : (kernelId == 3 ? 128 : 64);
@@ -95,7 +102,9 @@ int gemm_table(int table, int variant_x, int variant_c, const void* A, const flo
                      t.c <= twarps && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b * t.c) == 0;
     const bool ok2 = t.a == 2 && variant_x == 0 && dtype != MLK_E4M3 && n <= 64 && t.b >= 1 && t.b <= 4 &&
                      (t.c == 2 || t.c == 4 || t.c == 6 || t.c == 8);
-    if (!ok1 && !ok2) t = default_args(table, m, n, k);
+    const bool ok5 = t.a >= 5 && t.a <= 7 && n <= 4 && variant_x == 0 && variant_c == 0 && dtype != MLK_E4M3 &&
+                     (t.b == 1 || t.b == 2) && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b) == 0;
+    if (!ok1 && !ok2 && !ok5) t = default_args(table, m, n, k);
     return gemm_common(variant_x, variant_c, A, scale, B, C, m, n, k, dtype, alpha, t.b, t.c, t.d, t.a, bias,
                        fp8_order, s, aux);
 }

@@ -205,7 +205,7 @@ int launch_mma_wt(const DenseParams& p, cudaStream_t stream) {
 // 16-byte weight load is matched by a 16-byte load of x (L1-resident, shared by half a warp) and
 // 8 fp32 FMAs.  One xor-16 shuffle folds the two octet halves, shared memory folds the K slices.
 // ---------------------------------------------------------------------------------------------
-template <int WT, int RG>
+template <int WT, int RG, int NTOK>
 __global__ void __launch_bounds__(256) gemv_simt_kernel(const DenseParams p, const int static_weights) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int D = 8;   // 16-byte weight loads in flight per row group
@@ -225,10 +225,13 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const DenseParams p, con
         ap[r] = reinterpret_cast<const uint8_t*>(p.A) + (size_t)(blockIdx.x * RG + r) * 16 * p.k * 2 +
                 (size_t)(u0 * 2 + half) * 256 + row * 16;
     const uint8_t* xp = reinterpret_cast<const uint8_t*>(p.X) + (size_t)(u0 * 2 + half) * 16;
+    const size_t xstride = (size_t)p.k * 2;   // bytes between token rows
 
-    float acc[RG];
+    float acc[RG][NTOK];
 #pragma unroll
-    for (int r = 0; r < RG; ++r) acc[r] = 0.f;
+    for (int r = 0; r < RG; ++r)
+#pragma unroll
+        for (int q = 0; q < NTOK; ++q) acc[r][q] = 0.f;
 
     uint4 ring[D][RG];
     if (!static_weights) {
@@ -249,41 +252,51 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const DenseParams p, con
 #pragma unroll
         for (int d = 0; d < D; ++d) {
             const int u = ub + d;
-            uint4 xv = make_uint4(0, 0, 0, 0);
-            if (u < nunits) xv = __ldg(reinterpret_cast<const uint4*>(xp + (size_t)u * 32));
-            const float2 x0 = unpack2<WT>(xv.x), x1 = unpack2<WT>(xv.y), x2 = unpack2<WT>(xv.z), x3 = unpack2<WT>(xv.w);
+            float2 xf[NTOK][4];
+#pragma unroll
+            for (int q = 0; q < NTOK; ++q) {
+                uint4 xv = make_uint4(0, 0, 0, 0);
+                if (u < nunits && q < p.n) xv = __ldg(reinterpret_cast<const uint4*>(xp + q * xstride + (size_t)u * 32));
+                xf[q][0] = unpack2<WT>(xv.x); xf[q][1] = unpack2<WT>(xv.y);
+                xf[q][2] = unpack2<WT>(xv.z); xf[q][3] = unpack2<WT>(xv.w);
+            }
 #pragma unroll
             for (int r = 0; r < RG; ++r) {
                 const uint4 w = ring[d][r];
                 const float2 w0 = unpack2<WT>(w.x), w1 = unpack2<WT>(w.y), w2 = unpack2<WT>(w.z), w3 = unpack2<WT>(w.w);
-                float s = acc[r];
-                s = fmaf(w0.x, x0.x, s); s = fmaf(w0.y, x0.y, s);
-                s = fmaf(w1.x, x1.x, s); s = fmaf(w1.y, x1.y, s);
-                s = fmaf(w2.x, x2.x, s); s = fmaf(w2.y, x2.y, s);
-                s = fmaf(w3.x, x3.x, s); s = fmaf(w3.y, x3.y, s);
-                acc[r] = s;
+#pragma unroll
+                for (int q = 0; q < NTOK; ++q) {
+                    float s = acc[r][q];
+                    s = fmaf(w0.x, xf[q][0].x, s); s = fmaf(w0.y, xf[q][0].y, s);
+                    s = fmaf(w1.x, xf[q][1].x, s); s = fmaf(w1.y, xf[q][1].y, s);
+                    s = fmaf(w2.x, xf[q][2].x, s); s = fmaf(w2.y, xf[q][2].y, s);
+                    s = fmaf(w3.x, xf[q][3].x, s); s = fmaf(w3.y, xf[q][3].y, s);
+                    acc[r][q] = s;
+                }
                 const int un = u + D;
                 ring[d][r] = (un < nunits) ? ldg_stream16(ap[r] + (size_t)un * 512) : make_uint4(0, 0, 0, 0);
             }
         }
     }
 
-    float* part = reinterpret_cast<float*>(smem);
+    float* part = reinterpret_cast<float*>(smem);   // [WK][NTOK][PR]
     const int PR = rows_cta + 4;
 #pragma unroll
-    for (int r = 0; r < RG; ++r) {
-        const float s = acc[r] + __shfl_xor_sync(0xFFFFFFFFu, acc[r], 16);
-        if (half == 0) part[warp * PR + r * 16 + row] = s;
-    }
+    for (int r = 0; r < RG; ++r)
+#pragma unroll
+        for (int q = 0; q < NTOK; ++q) {
+            const float s = acc[r][q] + __shfl_xor_sync(0xFFFFFFFFu, acc[r][q], 16);
+            if (half == 0) part[(warp * NTOK + q) * PR + r * 16 + row] = s;
+        }
     const int row0 = blockIdx.x * rows_cta;
-    reduce_and_emit<1>(part, WK, 1, PR, 1, rows_cta >> 3, 0, SK,
+    reduce_and_emit<1>(part, WK, NTOK, PR, p.n, rows_cta >> 3, 0, SK,
                        [&](int tk, int ro, float (&v)[1][8]) { emit_dense<WT>(p, tk, row0 + ro * 8, v[0]); });
 }
 
-template <int WT, int RG>
+template <int WT, int RG, int NTOK>
 int launch_simt_inst(const DenseParams& p, cudaStream_t stream) {
     const int warps = p.threads / 32;
-    const size_t smem = (size_t)warps * (16 * RG + 4) * sizeof(float);
+    const size_t smem = (size_t)warps * NTOK * (16 * RG + 4) * sizeof(float);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.m / (16 * RG), p.sk, 1);
     cfg.blockDim = dim3(p.threads);
@@ -292,7 +305,7 @@ int launch_simt_inst(const DenseParams& p, cudaStream_t stream) {
     cudaLaunchAttribute attr[2];
     cfg.attrs = attr;
     cfg.numAttrs = launch_attrs(attr, p.sk);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_simt_kernel<WT, RG>, p, option(kOptStaticWeights));
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_simt_kernel<WT, RG, NTOK>, p, option(kOptStaticWeights));
     if (e != cudaSuccess) return fail(kCudaError, "gemv_simt launch: %s", cudaGetErrorString(e));
     return kOk;
 }
@@ -337,13 +350,16 @@ int launch_dense_mma(int wt, const DenseParams& p, cudaStream_t stream) {
 
 int launch_gemv_simt(int wt, const DenseParams& p, int, cudaStream_t stream) {
     if (int s = check_common(p)) return s;
-    if (p.n != 1) return fail(kUnsupported, "gemv kernel 2 (CUDA-core) handles exactly one token; n=%d", p.n);
-    if (p.x_layout != 0) return fail(kInvalidArg, "gemv: x must be row-major");
+    if (p.n > 4) return fail(kUnsupported, "the CUDA-core kernel handles 1..4 tokens; n=%d", p.n);
+    if (p.x_layout != 0 || p.c_layout != 0) return fail(kInvalidArg, "the CUDA-core kernel needs row-major activations and output");
     if (wt == kE4M3) return fail(kUnsupported, "gemv kernel 2 (CUDA-core) has no e4m3 variant; use kernel 1");
     if (p.m % (16 * p.rg) != 0) return fail(kInvalidArg, "gemv: m=%d is not a multiple of %d", p.m, 16 * p.rg);
-#define MLK_CASE(WT_, RG_) \
-    if (wt == WT_ && p.rg == RG_) return launch_simt_inst<WT_, RG_>(p, stream);
-    MLK_CASE(kBF16, 1) MLK_CASE(kBF16, 2) MLK_CASE(kFP16, 1) MLK_CASE(kFP16, 2)
+    const int ntok = p.n <= 1 ? 1 : (p.n <= 2 ? 2 : 4);
+#define MLK_CASE(WT_, RG_, NT_) \
+    if (wt == WT_ && p.rg == RG_ && ntok == NT_) return launch_simt_inst<WT_, RG_, NT_>(p, stream);
+    MLK_CASE(kBF16, 1, 1) MLK_CASE(kBF16, 2, 1) MLK_CASE(kFP16, 1, 1) MLK_CASE(kFP16, 2, 1)
+    MLK_CASE(kBF16, 1, 2) MLK_CASE(kBF16, 2, 2) MLK_CASE(kFP16, 1, 2) MLK_CASE(kFP16, 2, 2)
+    MLK_CASE(kBF16, 1, 4) MLK_CASE(kBF16, 2, 4) MLK_CASE(kFP16, 1, 4) MLK_CASE(kFP16, 2, 4)
 #undef MLK_CASE
     return fail(kUnsupported, "gemv: unknown weight type %d", wt);
 }

@@ -126,6 +126,8 @@ def scan_one(kind, m, n, k, dtype, log):
         # kernelId 1 / 3 / 4: the warp-level kernel with 8 / 4 / 2 warps per CTA
         cands = [(kid, rg, wm, sk) for kid, rg, wm, sk in itertools.product([1, 3, 4], [1, 2], [1, 2, 4, 8], [1, 2, 4])
                  if m % (16 * rg * wm) == 0 and wm <= {1: 8, 3: 4, 4: 2}[kid]]
+        if kind == "a" and n <= 4:
+            cands += [(kid, rg, 0, sk) for kid, rg, sk in itertools.product([5, 6, 7], [1, 2], [1, 2, 4]) if m % (16 * rg) == 0]
         if kind == "a" and n <= 64:
             # tcgen05 tile kernel: CTAs per SM x pipeline stages (two CTAs share an SM only with <= 4 stages)
             cands += [(2, 1, 4, 0), (2, 1, 6, 0), (2, 1, 8, 0), (2, 2, 2, 0), (2, 2, 4, 0), (2, 3, 2, 0)]

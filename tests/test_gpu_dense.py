@@ -205,7 +205,7 @@ def test_gemm_errors_and_determinism():
     with pytest.raises(RuntimeError, match="same k"):
         mlk.gemm_layoutA(A, randn((16, 128), 83).to(dev))
     with pytest.raises(RuntimeError, match="kernelId"):
-        mlk.gemm_layoutA_wapper(A, X, 256, 16, 256, kernelId=7)
+        mlk.gemm_layoutA_wapper(A, X, 256, 16, 256, kernelId=9)
     with pytest.raises(RuntimeError, match="row tile"):
         A128 = mlk.layoutA(randn((128, 256), 84).to(dev))
         mlk.gemm_layoutA_wapper(A128, X, 128, 16, 256, kernelParam1=2, kernelParam2=8, kernelParam3=1)
@@ -242,6 +242,24 @@ def test_gemm_tcgen05_tile_kernel(dt):
     assert mlk.kernel_status() == 0, "a bounded wait inside the tcgen05 kernel expired"
     with pytest.raises(RuntimeError, match="stages"):
         mlk.gemm_layoutA_wapper(A, X, 1024, 40, 4096, kernelParam1=1, kernelParam2=3, kernelId=2)
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+def test_gemm_cuda_core_kernel_up_to_four_tokens(dt):
+    """kernelId 5/6/7: the CUDA-core FMA kernel behind the GEMM entry point for 1..4 tokens."""
+    dev = require_gpu()
+    for (m, k) in [(128, 128), (512, 640), (384, 2048)]:
+        W, A = _weights(m, k, 85 + m, DT[dt], dev, 0.05)
+        bias = randn((1, m), 86, 1.0, DT[dt])
+        for n in [1, 2, 3, 4]:
+            X = randn((n, k), 87 + n, 1.0, DT[dt])
+            want = odense.gemm_ref(X, W, alpha=0.75, bias=bias)
+            for kid, rg, sk in itertools.product([5, 6, 7], [1, 2], [1, 2, 8]):
+                C = mlk.gemm_layoutA_wapper(A, X.to(dev), m, n, k, alpha=0.75, kernelParam1=rg, kernelParam3=sk,
+                                            kernelId=kid, bias=bias.to(dev))
+                assert_close(C, want, f"cuda-core gemm {dt} m={m} k={k} n={n} kid={kid} rg={rg} sk={sk}")
+    with pytest.raises(RuntimeError, match="1..4 tokens"):
+        mlk.gemm_layoutA_wapper(A, randn((8, 2048), 88, 1.0, DT[dt]).to(dev), 384, 8, 2048, kernelId=5)
 
 
 def test_static_weights_and_pdl_modes_give_identical_results():
