@@ -282,6 +282,11 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": f"of {peak_kind}", "kernel": "dense_mma_kernel"},
         }
+        if world == 1 and not args.no_moe:
+            # second half of the metric: fused-MoE layer time (router + alignment + experts + combine), CUDA-graph
+            # replay over 8 different activation batches, see kernel_args_scan/moe_bench.py
+            from muxi_native_layout_kernels_b200.kernel_args_scan import moe_bench
+            line["moe_layer_us"] = moe_bench.run("both", None, 24, dev)
         if world == 1 and not args.no_cpu:
             gbs, dt = time_cpu(passes=args.cpu_passes)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
@@ -299,6 +304,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--cpu-passes", type=int, default=5)
+    ap.add_argument("--no-moe", action="store_true", help="skip the fused-MoE layer timings")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -169,9 +169,17 @@ int mlk_fused_routing_gate(const void* gating_output, int score_fun, int batch_s
                            int topK_groups, int32_t* experts_ids, void* selected_experts_weights, int topK,
                            const void* load_balance_bias, int dtype, mlk_stream_t s);
 
+/* Same, with the weights of every token divided by their sum when renormalize != 0 (the step the reference's Python
+ * orchestrator does with two torch ops, muxi_layout_kernels/muxi_moe_planC.py:69-70): fp32 sum rounded to the logits'
+ * dtype, fp32 quotient rounded to the logits' dtype. */
+int mlk_fused_routing_gate_renorm(const void* gating_output, int score_fun, int batch_size, int num_experts,
+                                  int n_groups, int topK_groups, int32_t* experts_ids, void* selected_experts_weights,
+                                  int topK, const void* load_balance_bias, int dtype, int renormalize, mlk_stream_t s);
+
 /* Token alignment: groups the flat slots i = token*topK + j by (mapped) expert, pads every expert's run to a
  * multiple of microBatchSize with the caller's sentinel, and records one expert id per block.
- *   sorted_token_ids  [T*topK + E*(mbs-1)]  pre-filled by the caller with T*topK
+ *   sorted_token_ids  [T*topK + E*(mbs-1)]  every position that holds no slot is set to the sentinel T*topK (the
+ *                     reference expects the caller to pre-fill it; doing so is harmless)
  *   cumsum_buffer     [E+1]   on return: [e] = start_e + count_e for e < E, [E] = padded total
  *   padded_num_experts[1]     number of blocks
  *   experts_ids_out   [ceil(len/mbs)] expert of each block
@@ -188,6 +196,9 @@ int mlk_moe_align(int batchSize, int expertCount, int topK, int microBatchSize, 
  * y [T,H] must be zero.
  * dtype 0/1: 16-bit weights; dtype 2: e4m3 weights with optional fp32 block scales w1_scale [E,2I/128,H/128],
  * w2_scale [E,H/128,I/128] (NULL = ones).
+ * tune: NULL, or six host ints {token tiles per work item (1,2,4,8 = 8..64 slots), row warps of GEMM1 (1,2,4),
+ * cluster split-K of GEMM1 (1,2,4,8), row groups per warp of GEMM2 (1,2), row warps of GEMM2 (1,2,4), cluster split-K of
+ * GEMM2}; a 0 lets the library choose that value from the shape.
  * combine_scratch: optional T*topK*H floats.  With it the weighted expert outputs are kept in fp32 and summed per
  * token in a fixed order with one final rounding (bit-reproducible).  With NULL they are accumulated into y with
  * 16-bit atomics, as the reference does (csrc/moe_kernels/group_gemm_second.h:333-346): one rounding per addend
@@ -199,7 +210,7 @@ int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int
                               int32_t* experts_ids, void* C, void* y, const float* w1_scale, const float* w2_scale,
                               int dtype, int fp8_order, int microBatchSize, const int32_t* experts_map,
                               int experts_map_len, float* combine_scratch, int64_t combine_scratch_bytes,
-                              int tune_rg, int tune_sk1, int tune_sk2, mlk_stream_t s);
+                              const int32_t* tune, mlk_stream_t s);
 
 /* Expert compute for callers that must not allocate device memory (a plugin running under another runtime's memory
  * pool, a serving loop whose allocator is off limits on the request path).  It has no

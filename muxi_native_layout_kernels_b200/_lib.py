@@ -48,6 +48,8 @@ PROTOTYPES = {
     "mlk_gemm_layoutABC": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_vp]),
     "mlk_fused_routing_gate": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_vp, c_int,
                                        c_vp]),
+    "mlk_fused_routing_gate_renorm": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_vp, c_int,
+                                              c_int, c_vp]),
     "mlk_moe_align": (c_int, [c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_vp]),
     "mlk_fused_experts_compute_static": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp,
                                                  c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp,
@@ -56,7 +58,7 @@ PROTOTYPES = {
     "mlk_moe_unpermute_sum": (c_int, [c_vp, c_vp, c_vp, c_i64, c_int, c_int, c_i64, c_int, c_vp]),
     "mlk_fused_experts_compute": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp,
                                           c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp,
-                                          c_int, c_vp, c_i64, c_int, c_int, c_int, c_vp]),
+                                          c_int, c_vp, c_i64, C.POINTER(C.c_int32), c_vp]),
 }
 
 

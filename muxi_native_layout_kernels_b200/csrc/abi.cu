@@ -276,6 +276,14 @@ int mlk_fused_routing_gate(const void* gating_output, int score_fun, int batch_s
                          selected_experts_weights, topK, load_balance_bias, dtype, (cudaStream_t)s);
 }
 
+int mlk_fused_routing_gate_renorm(const void* gating_output, int score_fun, int batch_size, int num_experts,
+                                  int n_groups, int topK_groups, int32_t* experts_ids, void* selected_experts_weights,
+                                  int topK, const void* load_balance_bias, int dtype, int renormalize, mlk_stream_t s) {
+    clear_error();
+    return launch_router(gating_output, score_fun, batch_size, num_experts, n_groups, topK_groups, experts_ids,
+                         selected_experts_weights, topK, load_balance_bias, dtype, (cudaStream_t)s, renormalize);
+}
+
 int mlk_moe_align(int batchSize, int expertCount, int topK, int microBatchSize, const int32_t* topk_ids,
                   int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
                   int32_t* experts_ids_out, const int32_t* experts_map, int experts_map_len, mlk_stream_t s) {
@@ -302,7 +310,7 @@ int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int
                               int32_t* experts_ids, void* C, void* y, const float* w1_scale, const float* w2_scale,
                               int dtype, int fp8_order, int microBatchSize, const int32_t* experts_map,
                               int experts_map_len, float* combine_scratch, int64_t combine_scratch_bytes,
-                              int tune_rg, int tune_sk1, int tune_sk2, mlk_stream_t s) {
+                              const int32_t* tune, mlk_stream_t s) {
     clear_error();
     MoeParams p{};
     p.w1 = w1; p.w2 = w2; p.x = x; p.T = batch_size; p.E = expert_count; p.topk = topK; p.H = hidden; p.I = inter;
@@ -310,7 +318,7 @@ int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int
     p.cumsum = cumsum_buffer; p.padded_num_experts = padded_num_experts; p.experts_ids = experts_ids;
     p.C = C; p.y = y; p.w1_scale = w1_scale; p.w2_scale = w2_scale; p.dtype = dtype; p.fp8_order = fp8_order;
     p.mbs = microBatchSize; p.experts_map = experts_map; p.experts_map_len = experts_map_len;
-    p.scratch = combine_scratch; p.scratch_bytes = combine_scratch_bytes; p.rg = tune_rg; p.sk1 = tune_sk1; p.sk2 = tune_sk2;
+    p.scratch = combine_scratch; p.scratch_bytes = combine_scratch_bytes; if (tune) { p.nt = tune[0]; p.wm1 = tune[1]; p.sk1 = tune[2]; p.rg = tune[3]; p.wm2 = tune[4]; p.sk2 = tune[5]; }
     return launch_fused_experts(p, (cudaStream_t)s);
 }
 

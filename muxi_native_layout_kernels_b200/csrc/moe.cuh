@@ -7,7 +7,8 @@
 namespace mlk {
 
 int launch_router(const void* gating_output, int score_fun, int T, int E, int n_groups, int topk_groups,
-                  int32_t* experts_ids, void* weights, int topk, const void* bias, int dtype, cudaStream_t s);
+                  int32_t* experts_ids, void* weights, int topk, const void* bias, int dtype, cudaStream_t s,
+                  int renormalize = 0);
 
 // worklist == nullptr: alignment only (the stand-alone reference op).  Otherwise the kernel also writes
 // the expert-compute work list (see MoeWorkHeader) for blocks of `block_slots` slots.
@@ -42,7 +43,7 @@ struct MoeParams {
     int experts_map_len;
     float* scratch;               // optional [T*topk, H] fp32 for the deterministic combine
     long long scratch_bytes;
-    int rg, sk1, sk2;             // tuning (0 = choose by shape)
+    int nt, wm1, sk1, rg, wm2, sk2;   // tuning (0 = choose by shape): token tiles, GEMM1 row warps / split-K, GEMM2 row groups / row warps / split-K
 };
 
 int launch_fused_experts(const MoeParams& p, cudaStream_t s);

@@ -6,7 +6,7 @@
 //   experts_ids_out[0..max_blocks) is zero-filled, then [b] = e for every block of expert e
 //   padded_num_experts[0] = number of blocks
 //   sorted_token_ids[start_e + r] = i for the r-th slot routed to e (order inside an expert is unspecified);
-//     positions not written keep the caller's sentinel
+//     every other position holds the sentinel T*topk (written here, so the caller need not pre-fill)
 //   cumsum_buffer: [e] = start_e + count_e for e < E, [E] = padded total -- the state the reference leaves
 //     behind after its second kernel has used the buffer as per-expert cursors
 //   experts_map: global id -> local id, -1 = not on this rank (slot is skipped)
@@ -21,7 +21,7 @@ namespace {
 constexpr int kMaxExperts = 1024;
 
 __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restrict__ topk_ids, int numel, int E,
-                                                        int mbs, int max_blocks, int32_t* __restrict__ sorted,
+                                                        int mbs, int max_blocks, int max_padded, int32_t* __restrict__ sorted,
                                                         int32_t* __restrict__ cumsum, int32_t* __restrict__ nblocks,
                                                         int32_t* __restrict__ block_expert,
                                                         const int32_t* __restrict__ experts_map, int n_global,
@@ -35,6 +35,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
 
     for (int e = tid; e < E; e += blockDim.x) cnt[e] = 0;
     for (int b = tid; b < max_blocks; b += blockDim.x) block_expert[b] = 0;
+    for (int i = tid; i < max_padded; i += blockDim.x) sorted[i] = numel;   // sentinel everywhere; slots overwrite it below
     __syncthreads();
 
     for (int i = tid; i < numel; i += blockDim.x) {
@@ -116,7 +117,7 @@ int launch_moe_align(int T, int E, int topk, int mbs, const int32_t* topk_ids, i
     const int max_blocks = (max_padded + mbs - 1) / mbs;
     if (experts_map != nullptr && experts_map_len <= 0) return fail(kInvalidArg, "moe_align: experts_map needs its length");
     const int n_global = experts_map_len;
-    moe_align_kernel<<<1, 1024, 0, s>>>(topk_ids, (int)numel, E, mbs, max_blocks, sorted_token_ids, cumsum,
+    moe_align_kernel<<<1, 1024, 0, s>>>(topk_ids, (int)numel, E, mbs, max_blocks, max_padded, sorted_token_ids, cumsum,
                                         padded_num_experts, experts_ids_out, experts_map, n_global,
                                         reinterpret_cast<int4*>(worklist), block_slots);
     return check_launch("moe_align");

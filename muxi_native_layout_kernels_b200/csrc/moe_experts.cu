@@ -294,9 +294,15 @@ int launch_fused_experts(const MoeParams& m, cudaStream_t s) {
     const int esz = (wt == kE4M3) ? 1 : 2;
 
     // slots per work item: the token tile the GEMM kernels are instantiated for
-    const int nt_tiles = m.T <= 8 ? 1 : (m.T <= 16 ? 2 : (m.T <= 32 ? 4 : 8));
-    const int block_slots = nt_tiles * 8;
+    // Sized from the expected load (the host cannot see the routing without a sync): twice the mean number of
+    // slots per expert, never more than the tokens (an expert gets a token at most once).  Experts that receive
+    // more than one block are split into several items and stream their weights once per item.
     const long long slots = (long long)m.T * m.topk;
+    const long long mean2 = (2 * slots + m.E - 1) / m.E;
+    const long long want = std::min<long long>(m.T, mean2);
+    int nt_tiles = want <= 8 ? 1 : (want <= 16 ? 2 : (want <= 32 ? 4 : 8));
+    if (m.nt == 1 || m.nt == 2 || m.nt == 4 || m.nt == 8) nt_tiles = m.nt;
+    const int block_slots = nt_tiles * 8;
     const int max_items = (int)std::min<long long>(slots, (long long)std::min<long long>(m.E, slots) + slots / block_slots);
 
     // work list lives in the half of C that the fused activation does not need
@@ -331,6 +337,7 @@ int launch_fused_experts(const MoeParams& m, cudaStream_t s) {
     g1.k = m.H;
     g1.fp8_order = m.fp8_order;
     int wm1 = (nt_tiles >= 8) ? 4 : (nt_tiles >= 2 ? 2 : 1);
+    if (m.wm1 == 1 || m.wm1 == 2 || m.wm1 == 4 || m.wm1 == 8) wm1 = m.wm1;
     while (wm1 > 1 && (m.I / 16) % wm1 != 0) wm1 >>= 1;
     if ((m.I / 16) % wm1 != 0) return fail(kInvalidArg, "fused_experts_compute: I must be a multiple of 16");
     g1.wm = wm1;
@@ -358,6 +365,7 @@ int launch_fused_experts(const MoeParams& m, cudaStream_t s) {
     g2.fp8_order = m.fp8_order;
     int rg2 = (m.rg == 1 || m.rg == 2) ? m.rg : ((nt_tiles >= 2 && m.H % 32 == 0) ? 2 : 1);
     int wm2 = (nt_tiles >= 8) ? 4 : (nt_tiles >= 2 ? 2 : 1);
+    if (m.wm2 == 1 || m.wm2 == 2 || m.wm2 == 4 || m.wm2 == 8) wm2 = m.wm2;
     while (wm2 > 1 && (m.H / 16) % (rg2 * wm2) != 0) wm2 >>= 1;
     if ((m.H / 16) % (rg2 * wm2) != 0) rg2 = 1;
     g2.wm = wm2;

@@ -32,7 +32,7 @@ __device__ __forceinline__ void argmax_pair(float& v, int& e) {
 template <int WT>
 __global__ void __launch_bounds__(128) router_kernel(const void* __restrict__ logits, int score_fun, int T, int E,
                                                      int G, int KG, int32_t* __restrict__ ids, void* __restrict__ wts,
-                                                     int topk, const void* __restrict__ bias) {
+                                                     int topk, const void* __restrict__ bias, int renormalize) {
     extern __shared__ float sm[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -139,6 +139,12 @@ __global__ void __launch_bounds__(128) router_kernel(const void* __restrict__ lo
         sc = __shfl_sync(0xFFFFFFFFu, sc, owner);
         if (lane == r) { my_id = be; my_w = sc; }
     }
+    if (renormalize) {
+        // w / sum(w) in the logits' dtype, as torch evaluates `w / w.sum(-1, keepdim=True)` on a 16-bit tensor:
+        // fp32 sum rounded to 16 bits, fp32 quotient rounded to 16 bits
+        const float s16 = round16<WT>(warp_sum(lane < topk ? my_w : 0.f));
+        my_w = round16<WT>(__fdiv_rn(my_w, s16));
+    }
     int pos = lane;
     if (score_fun == 0) {
         pos = 0;
@@ -159,7 +165,8 @@ __global__ void __launch_bounds__(128) router_kernel(const void* __restrict__ lo
 }  // namespace
 
 int launch_router(const void* gating_output, int score_fun, int T, int E, int n_groups, int topk_groups,
-                  int32_t* experts_ids, void* weights, int topk, const void* bias, int dtype, cudaStream_t s) {
+                  int32_t* experts_ids, void* weights, int topk, const void* bias, int dtype, cudaStream_t s,
+                  int renormalize) {
     if (!gating_output || !experts_ids || !weights) return fail(kInvalidArg, "fused_routing_gate: null pointer");
     if (T < 0) return fail(kInvalidArg, "fused_routing_gate: negative batch size");
     if (T == 0) return kOk;
@@ -174,10 +181,10 @@ int launch_router(const void* gating_output, int score_fun, int T, int E, int n_
     const size_t smem = (size_t)warps * (E + 2 * n_groups) * sizeof(float);
     if (dtype == 1)
         router_kernel<kFP16><<<grid, warps * 32, smem, s>>>(gating_output, score_fun, T, E, n_groups, topk_groups,
-                                                            experts_ids, weights, topk, bias);
+                                                            experts_ids, weights, topk, bias, renormalize);
     else
         router_kernel<kBF16><<<grid, warps * 32, smem, s>>>(gating_output, score_fun, T, E, n_groups, topk_groups,
-                                                            experts_ids, weights, topk, bias);
+                                                            experts_ids, weights, topk, bias, renormalize);
     return check_launch("fused_routing_gate");
 }
 

@@ -403,10 +403,11 @@ def gemm_layoutABC_wapper(A, B, m: int, n: int, k: int, alpha: float = 1, beta: 
 
 def fused_routing_gate(gating_output, score_fun: int, batch_size: int, hidden_size: int, n_groups: int,
                        topK_groups: int, experts_ids, selected_experts_weights, topK: int,
-                       load_balance_bias=None) -> None:
+                       load_balance_bias=None, *, renormalize: bool = False) -> None:
     """Router: softmax (0) / sigmoid (1) + optional bias + group-limited top-k; writes ``experts_ids`` (int32) and
     ``selected_experts_weights`` in place (csrc/moe_kernels/fused_gating.cu:5-67).  ``hidden_size`` is unused, as
-    in the reference."""
+    in the reference.  Extension: ``renormalize=True`` also divides every token's weights by their sum (in the logits'
+    dtype), which saves the two torch ops the reference orchestrator spends on it."""
     _cuda_contig(gating_output, "gating_output")
     _cuda_contig(experts_ids, "experts_ids")
     _cuda_contig(selected_experts_weights, "selected_experts_weights")
@@ -422,9 +423,10 @@ def fused_routing_gate(gating_output, score_fun: int, batch_size: int, hidden_si
         _cuda_contig(load_balance_bias, "load_balance_bias")
         _chk(load_balance_bias.dtype == gating_output.dtype and load_balance_bias.numel() == E,
              "load_balance_bias must be [E] in the gating dtype")
-    check(lib.mlk_fused_routing_gate(gating_output.data_ptr(), score_fun, batch_size, E, n_groups, topK_groups,
-                                     experts_ids.data_ptr(), selected_experts_weights.data_ptr(), topK,
-                                     _ptr(load_balance_bias), code, _stream(gating_output)))
+    check(lib.mlk_fused_routing_gate_renorm(gating_output.data_ptr(), score_fun, batch_size, E, n_groups, topK_groups,
+                                            experts_ids.data_ptr(), selected_experts_weights.data_ptr(), topK,
+                                            _ptr(load_balance_bias), code, int(bool(renormalize)),
+                                            _stream(gating_output)))
 
 
 def _map_args(experts_map):
@@ -470,13 +472,15 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
     per warp of the second GEMM: 1 or 2, other values = automatic) is used, split-K is chosen from the shape.
     Extra keywords: ``fp8_repacked`` marks e4m3 weights that went through ``fp8_weight_repack``;
     ``deterministic`` (default True) sums each token's expert outputs in fp32 in a fixed order with one rounding,
-    False uses 16-bit atomic adds into ``y`` as the reference does.
+    False uses 16-bit atomic adds into ``y`` as the reference does; ``tune`` = six launch integers (token tiles per
+    work item, GEMM1 row warps, GEMM1 split-K, GEMM2 row groups per warp, GEMM2 row warps, GEMM2 split-K; 0 = automatic).
     """
     w1, w2, x = experts_weights_matrix1, experts_weights_matrix2, activations
     fp8_form = (len(args) > 0 and not isinstance(args[0], int)) or any(
         k_ in kwargs for k_ in ("w1_scale", "w2_scale", "block_shape", "soft_fp8"))
     fp8_repacked = bool(kwargs.pop("fp8_repacked", False))
     deterministic = bool(kwargs.pop("deterministic", True))
+    tune = kwargs.pop("tune", None)
     if fp8_form:
         names = ["w1_scale", "w2_scale", "block_shape", "soft_fp8", "microBatchSize", "experts_map"]
         vals = {"soft_fp8": False, "microBatchSize": 16, "experts_map": None}
@@ -536,6 +540,11 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
         code = _act_code(x)
         rg = vals["APerWarp"] if vals["APerWarp"] in (1, 2) else 0
     mp, ml = _map_args(vals["experts_map"])
+    t6 = [0, 0, 0, rg, 0, 0]
+    if tune is not None:
+        _chk(len(tune) == 6, "tune must hold six integers")
+        t6 = [int(v) for v in tune]
+    tune_arr = (ctypes.c_int32 * 6)(*t6)
     # fp32 [slots, H] buffer for the fixed-order combine (torch's caching allocator makes this a pointer bump)
     scratch = torch.empty((batch_size * topK, k1), dtype=torch.float32, device=x.device) if deterministic else None
     check(lib.mlk_fused_experts_compute(w1.data_ptr(), w2.data_ptr(), x.data_ptr(), batch_size, E, topK, k1, k2,
@@ -544,7 +553,7 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
                                         padded_num_experts.data_ptr(), experts_ids.data_ptr(), C.data_ptr(),
                                         y.data_ptr(), _ptr(w1s), _ptr(w2s), code, int(fp8_repacked),
                                         int(vals["microBatchSize"]), mp, ml, _ptr(scratch),
-                                        0 if scratch is None else scratch.numel() * 4, rg, 0, 0, _stream(x)))
+                                        0 if scratch is None else scratch.numel() * 4, tune_arr, _stream(x)))
 
 
 # ---------------------------------------------------------------------------------------------------

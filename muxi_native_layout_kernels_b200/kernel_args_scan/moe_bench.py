@@ -1,0 +1,115 @@
+"""Times the fused MoE layer (router + alignment + expert compute + combine) on one GPU.
+
+    python -m muxi_native_layout_kernels_b200.kernel_args_scan.moe_bench [--config mixtral|fine|both] [--tokens 1,16]
+           [--iters 20] [--json]
+
+mixtral: E=8, top-2, H=4096, I=14336, bf16 weights ~ N(0, 0.02^2), seed 3.
+fine:    E=128, top-8, H=2048, I=768, e4m3 weights (N(0,1)*0.5 cast, repacked), seed 4.
+Role of the reference's benchmark_and_test/benchmark_muxi_moe.py.  Every iteration uses a different activation
+batch (8 batches are cycled), so different experts are hit; the layer is captured in a CUDA graph per batch and the
+replays are timed with CUDA events (us_graph), next to the eager Python call (us_eager, includes host overhead).
+Algorithmic bytes = distinct experts selected x 3*I*H*weight bytes + 4*T*H + 2*T*E.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+import muxi_native_layout_kernels_b200 as mlk
+from muxi_native_layout_kernels_b200.muxi_moe_planC import fused_moe
+
+CONFIGS = {
+    "mixtral": dict(E=8, topk=2, H=4096, I=14336, fp8=False, seed=3, tokens=[1, 16, 64, 256]),
+    "fine": dict(E=128, topk=8, H=2048, I=768, fp8=True, seed=4, tokens=[1, 32, 128, 512]),
+}
+NBATCH = 8
+
+
+def build(cfg, dev):
+    g = torch.Generator(device=dev).manual_seed(cfg["seed"])
+    E, H, I = cfg["E"], cfg["H"], cfg["I"]
+    if cfg["fp8"]:
+        w1 = (torch.randn(E, 2 * I, H, generator=g, device=dev) * 0.5).to(torch.float8_e4m3fn)
+        w2 = (torch.randn(E, H, I, generator=g, device=dev) * 0.5).to(torch.float8_e4m3fn)
+        w1 = mlk.fp8_weight_repack(mlk.layoutA(w1))
+        w2 = mlk.fp8_weight_repack(mlk.layoutA(w2))
+    else:
+        w1 = mlk.layoutA((torch.randn(E, 2 * I, H, generator=g, device=dev) * 0.02).to(torch.bfloat16))
+        w2 = mlk.layoutA((torch.randn(E, H, I, generator=g, device=dev) * 0.02).to(torch.bfloat16))
+    wg = (torch.randn(E, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    return w1, w2, wg, g
+
+
+def run_case(cfg, T, w1, w2, wg, g, dev, iters):
+    E, H, I, topk, fp8 = cfg["E"], cfg["H"], cfg["I"], cfg["topk"], cfg["fp8"]
+    xs = [torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16) for _ in range(NBATCH)]
+    logits = [(x.float() @ wg.float().t()).to(torch.bfloat16) for x in xs]
+    kw = dict(block_shape=[128, 128], soft_fp8=True, fp8_repacked=True) if fp8 else {}
+
+    def call(i):
+        return fused_moe(xs[i], w1, w2, logits[i], topk, True, **kw)
+
+    for i in range(NBATCH):
+        call(i)
+    torch.cuda.synchronize()
+    distinct = sum(int(torch.topk(torch.softmax(l.float(), -1), topk, dim=-1)[1].unique().numel()) for l in logits) / NBATCH
+    nbytes = distinct * 3 * I * H * (1 if fp8 else 2) + 4 * T * H + 2 * T * E
+    # eager
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for it in range(iters):
+        call(it % NBATCH)
+    e1.record()
+    torch.cuda.synchronize()
+    us_eager = e0.elapsed_time(e1) * 1e3 / iters
+    # graph: one graph holding all NBATCH layers back to back
+    graph = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(graph, stream=s):
+            for i in range(NBATCH):
+                call(i)
+    torch.cuda.current_stream().wait_stream(s)
+    graph.replay()
+    torch.cuda.synchronize()
+    reps = max(1, iters // NBATCH)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us_graph = e0.elapsed_time(e1) * 1e3 / (reps * NBATCH)
+    return {"T": T, "experts_hit": distinct, "us_graph": round(us_graph, 2), "us_eager": round(us_eager, 2),
+            "algorithmic_mb": round(nbytes / 1e6, 1), "gbs": round(nbytes / us_graph / 1e3, 1)}
+
+
+def run(config="both", tokens=None, iters=24, dev=None):
+    dev = dev or torch.device("cuda")
+    mlk.set_static_weights(True)
+    out = {}
+    for name in (["mixtral", "fine"] if config == "both" else [config]):
+        cfg = CONFIGS[name]
+        w1, w2, wg, g = build(cfg, dev)
+        out[name] = [run_case(cfg, T, w1, w2, wg, g, dev, iters) for T in (tokens or cfg["tokens"])]
+        del w1, w2
+        torch.cuda.empty_cache()
+    return out
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="both", choices=["mixtral", "fine", "both"])
+    ap.add_argument("--tokens", default=None)
+    ap.add_argument("--iters", type=int, default=24)
+    ap.add_argument("--json", action="store_true")
+    a = ap.parse_args()
+    res = run(a.config, [int(t) for t in a.tokens.split(",")] if a.tokens else None, a.iters)
+    if a.json:
+        print(json.dumps(res))
+    else:
+        for name, rows in res.items():
+            for r in rows:
+                print(name, r, flush=True)

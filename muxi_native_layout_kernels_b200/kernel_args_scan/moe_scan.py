@@ -1,0 +1,118 @@
+"""Scans the launch arguments of the fused-MoE expert kernels and writes moe_dispatch_arg.csv.
+
+    python -m muxi_native_layout_kernels_b200.kernel_args_scan.moe_scan [--config mixtral|fine|both] [--tokens ...]
+
+Role of the reference's kernel_args_scan/muxi_moe_args_scan.py.  For every token count a coordinate search is run:
+token tiles per work item x (GEMM1 row warps, split-K), then (GEMM2 row groups, row warps, split-K) with the best
+GEMM1 setting.  Each candidate is the whole layer captured in a CUDA graph over 8 different activation batches and
+timed with CUDA events; a candidate must agree with the automatic setting's output within 1e-2 (combined bound).
+"""
+from __future__ import annotations
+
+import argparse
+import csv
+import itertools
+
+import torch
+
+import muxi_native_layout_kernels_b200 as mlk
+from muxi_native_layout_kernels_b200._lib import MlkError
+from muxi_native_layout_kernels_b200.kernel_args_scan.moe_bench import CONFIGS, NBATCH, build
+from muxi_native_layout_kernels_b200.muxi_moe_planC import _MOE_TABLE_FILE, fused_moe
+
+HEADER = ["E", "topk", "H", "I", "fp8", "T", "nt", "wm1", "sk1", "rg2", "wm2", "sk2"]
+
+
+def time_layer(call, iters=3):
+    graph = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(graph, stream=s):
+            for i in range(NBATCH):
+                call(i)
+    torch.cuda.current_stream().wait_stream(s)
+    graph.replay()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) * 1e3 / NBATCH)
+    return best
+
+
+def scan_case(cfg, T, w1, w2, wg, g, dev):
+    E, H, I, topk, fp8 = cfg["E"], cfg["H"], cfg["I"], cfg["topk"], cfg["fp8"]
+    xs = [torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16) for _ in range(NBATCH)]
+    logits = [(x.float() @ wg.float().t()).to(torch.bfloat16) for x in xs]
+    kw = dict(block_shape=[128, 128], soft_fp8=True, fp8_repacked=True) if fp8 else {}
+    want = fused_moe(xs[0], w1, w2, logits[0], topk, True, tune=(0, 0, 0, 0, 0, 0), **kw).float()
+    tol = 1e-2 * max(1.0, float(want.pow(2).mean().sqrt()))
+
+    def try_args(args):
+        try:
+            got = fused_moe(xs[0], w1, w2, logits[0], topk, True, tune=args, **kw).float()
+        except MlkError:
+            return None
+        if not bool(((got - want).abs() <= tol + 1e-2 * want.abs()).all()):
+            return None
+        return time_layer(lambda i: fused_moe(xs[i], w1, w2, logits[i], topk, True, tune=args, **kw))
+
+    best_args, best_us = (0, 0, 0, 0, 0, 0), try_args((0, 0, 0, 0, 0, 0))
+    nts = [n for n in (1, 2, 4, 8) if n * 8 <= max(8, 2 * T)]
+    for nt in nts:
+        g1_best, g1_us = None, float("inf")
+        for wm1, sk1 in itertools.product([1, 2, 4], [1, 2]):
+            us = try_args((nt, wm1, sk1, 0, 0, 0))
+            if us is not None and us < g1_us:
+                g1_best, g1_us = (wm1, sk1), us
+        if g1_best is None:
+            continue
+        for rg2, wm2, sk2 in itertools.product([1, 2], [1, 2, 4], [1, 2, 4]):
+            args = (nt, g1_best[0], g1_best[1], rg2, wm2, sk2)
+            us = try_args(args)
+            if us is not None and us < best_us:
+                best_args, best_us = args, us
+    return best_args, best_us
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="both", choices=["mixtral", "fine", "both"])
+    ap.add_argument("--tokens", default=None)
+    ap.add_argument("--out", default=str(_MOE_TABLE_FILE))
+    a = ap.parse_args(argv)
+    dev = torch.device("cuda")
+    mlk.set_static_weights(True)
+    rows = {}
+    try:
+        with open(a.out) as f:
+            r = csv.reader(f)
+            next(r, None)
+            for row in r:
+                if len(row) == 12:
+                    rows[tuple(int(v) for v in row[:6])] = [int(v) for v in row[6:]]
+    except FileNotFoundError:
+        pass
+    for name in (["mixtral", "fine"] if a.config == "both" else [a.config]):
+        cfg = CONFIGS[name]
+        w1, w2, wg, g = build(cfg, dev)
+        for T in ([int(t) for t in a.tokens.split(",")] if a.tokens else cfg["tokens"]):
+            args, us = scan_case(cfg, T, w1, w2, wg, g, dev)
+            rows[(cfg["E"], cfg["topk"], cfg["H"], cfg["I"], int(cfg["fp8"]), T)] = list(args)
+            with open(a.out, "w", newline="") as f:
+                w = csv.writer(f)
+                w.writerow(HEADER)
+                for k in sorted(rows):
+                    w.writerow(list(k) + rows[k])
+            print(f"{name} T={T}: best {args} {us:.1f} us", flush=True)
+        del w1, w2
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()

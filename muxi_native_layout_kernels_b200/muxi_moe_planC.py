@@ -16,7 +16,46 @@ from typing import List, Optional
 
 import torch
 
+import csv
+from pathlib import Path
+
 from . import ext
+
+# Launch arguments of the expert-compute kernels, tuned offline by kernel_args_scan/moe_scan.py (the reference tunes
+# its MoE tile arguments with kernel_args_scan/muxi_moe_args_scan.py and bakes them into this function's defaults).
+# Key: (experts, topk, hidden, intermediate, fp8) -> [(tokens, (six ints))] sorted by tokens; the row with the
+# smallest tokens >= the batch is used.  A missing key means automatic choice inside the library.
+_MOE_TABLE_FILE = Path(__file__).resolve().parent / "moe_dispatch_arg.csv"
+_MOE_TABLE = None
+
+
+def _moe_table():
+    global _MOE_TABLE
+    if _MOE_TABLE is None:
+        table = {}
+        if _MOE_TABLE_FILE.exists():
+            with open(_MOE_TABLE_FILE) as f:
+                rows = csv.reader(f)
+                next(rows, None)
+                for r in rows:
+                    if len(r) != 12:
+                        continue
+                    v = [int(x) for x in r]
+                    table.setdefault(tuple(v[:5]), []).append((v[5], tuple(v[6:])))
+            for rows_ in table.values():
+                rows_.sort()
+        _MOE_TABLE = table
+    return _MOE_TABLE
+
+
+def lookup_moe_args(E: int, topk: int, H: int, I: int, fp8: bool, T: int):
+    rows = _moe_table().get((E, topk, H, I, int(fp8)))
+    if not rows:
+        return None
+    for t, args in rows:
+        if t >= T:
+            return args
+    return rows[-1][1]
 
 
 def fused_moe(
@@ -44,6 +83,7 @@ def fused_moe(
     experts_map: Optional[torch.Tensor] = None,
     fp8_repacked: bool = False,
     deterministic: bool = True,
+    tune=None,
 ) -> torch.Tensor:
     assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
     if num_expert_group is None:
@@ -68,11 +108,10 @@ def fused_moe(
     # 1. router
     topk_ids = torch.empty(B, topk, dtype=torch.int32, device=dev)
     topk_weights = torch.empty(B, topk, dtype=hidden_states.dtype, device=dev)
+    # renormalisation (reference: two torch ops, muxi_moe_planC.py:69-70) happens inside the router kernel, with the
+    # same roundings
     ext.fused_routing_gate(gating_output, score_fun, B, H, num_expert_group, topk_group, topk_ids, topk_weights,
-                           topk, gating_bias)
-    if renormalize:
-        # in the activation dtype, like the reference (muxi_moe_planC.py:69-70)
-        topk_weights = topk_weights / topk_weights.sum(dim=-1, keepdim=True)
+                           topk, gating_bias, renormalize=bool(renormalize))
 
     # 2. experts
     e1, m1, k1 = w1.shape
@@ -81,7 +120,8 @@ def fused_moe(
     assert k1 == m2
     micro_batchsize = 16
     max_num_tokens_padded = topk * B + num_experts * (micro_batchsize - 1)
-    sorted_token_ids = torch.full((max_num_tokens_padded,), B * topk, dtype=torch.int32, device=dev)
+    # the alignment kernel writes the sentinel itself: no fill kernel needed
+    sorted_token_ids = torch.empty((max_num_tokens_padded,), dtype=torch.int32, device=dev)
     cumsum_buffer = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
     padded_num_experts = torch.empty(1, dtype=torch.int32, device=dev)
     experts_ids = torch.empty((max_num_tokens_padded + micro_batchsize - 1) // micro_batchsize, dtype=torch.int32,
@@ -89,19 +129,23 @@ def fused_moe(
     # workspace: the fused GEMM1 epilogue writes [B*topk, I] activations into the first half; the second half
     # holds the expert work list.  Nothing in it has to be zero.
     C = torch.empty(topk * m1 * B, dtype=hidden_states.dtype, device=dev)
-    y = torch.zeros_like(hidden_states)
+    # the fixed-order combine writes every element of y; the atomic variant accumulates into zeros
+    y = torch.empty_like(hidden_states) if deterministic else torch.zeros_like(hidden_states)
 
+    if tune is None:
+        tune = lookup_moe_args(e1, topk, H, k2, soft_fp8, B)
     if experts_map is not None and experts_map.dtype != torch.int:
         experts_map = experts_map.to(torch.int)
     if soft_fp8:
         ext.fused_experts_compute(w1, w2, hidden_states, B, e1, topk, topk_ids, topk_weights, sorted_token_ids,
                                   cumsum_buffer, padded_num_experts, experts_ids, C, y, w1_scale, w2_scale,
                                   block_shape if block_shape is not None else [128, 128], soft_fp8,
-                                  experts_map=experts_map, fp8_repacked=fp8_repacked, deterministic=deterministic)
+                                  experts_map=experts_map, fp8_repacked=fp8_repacked, deterministic=deterministic,
+                                  tune=tune)
     else:
         ext.fused_experts_compute(w1, w2, hidden_states, B, e1, topk, topk_ids, topk_weights, sorted_token_ids,
                                   cumsum_buffer, padded_num_experts, experts_ids, C, y, APerWarp=APerWarp,
                                   splitK=splitK, tile_m_2=tile_m_2, tile_n_2=tile_n_2, tile_k_2=tile_k_2,
                                   block_dim_x_gemm=block_dim_x_gemm, experts_map=experts_map,
-                                  deterministic=deterministic)
+                                  deterministic=deterministic, tune=tune)
     return y.view(shape)

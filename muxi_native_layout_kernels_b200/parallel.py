@@ -164,9 +164,7 @@ def fused_moe_ep(
     ids = torch.empty(T, topk, dtype=torch.int32, device=dev)
     wts = torch.empty(T, topk, dtype=hidden_states.dtype, device=dev)
     ext.fused_routing_gate(gating_output, 0 if score_func == "softmax" else 1, T, H, num_expert_group, topk_group, ids,
-                           wts, topk, gating_bias)
-    if renormalize:
-        wts = wts / wts.sum(dim=-1, keepdim=True)
+                           wts, topk, gating_bias, renormalize=bool(renormalize))
 
     def experts_fn(rows, local_expert, weight):
         R = rows.shape[0]

@@ -43,7 +43,7 @@ def _call(static, x, w1, w2, ids, wts, E, topk, H, I):
         status = lib.mlk_fused_experts_compute_static(*common, stream)
     else:
         scratch = torch.empty(T * topk * H, dtype=torch.float32, device=dev)
-        status = lib.mlk_fused_experts_compute(*common, scratch.data_ptr(), scratch.numel() * 4, 0, 0, 0, stream)
+        status = lib.mlk_fused_experts_compute(*common, scratch.data_ptr(), scratch.numel() * 4, None, stream)
     torch.cuda.synchronize()
     return status, y
 
