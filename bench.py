@@ -39,6 +39,9 @@ if str(ROOT) not in sys.path:
 
 TOKENS = [1, 2, 4, 8, 16, 32, 64]
 SHAPES = [(4096, 4096), (14336, 4096), (4096, 14336)]
+# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, ncu captures of the three dense kernels on the
+# 14336 x 4096 weight: 123.4/117.5, 122.0/117.8, 123.1/119.8
+NCU_TRAFFIC_RATIO = 1.04
 NOMINAL_HBM_GBS = 8000.0
 
 
@@ -280,7 +283,11 @@ def run_ours(args):
                     "d2h_bytes_per_step": sum(n * (N // world) * 2 for (n, N, K) in order)},
             "gpu_launches": len(order) * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": f"of {peak_kind}", "kernel": "dense_mma_kernel"},
+                         "traffic": NCU_TRAFFIC_RATIO * per_rank_bytes / len(order),
+                         "traffic_source": "average bytes per launch = algorithmic bytes x 1.04, the dram read+write / "
+                                           "algorithmic ratio ncu measured on the three dense kernels (profiles/dense_kernels_14336x4096.md)",
+                         "peak_source": f"of {peak_kind}",
+                         "kernel": "dense_mma_kernel / dense_umma_kernel / gemv_simt_kernel (21 launches, averaged)"},
         }
         if world == 1 and not args.no_moe:
             # second half of the metric: fused-MoE layer time (router + alignment + experts + combine), CUDA-graph
