@@ -107,8 +107,11 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
  *   kernelParam3 = split-K over a thread-block cluster (1,2,4,8).
  * kernelId 2 (tcgen05 / tensor-memory tile kernel, 16-bit weights, row-major B, n <= 64): persistent CTAs that split
  *   the (128-row tile, 64-wide k block) work units evenly; kernelParam1 = CTAs per SM the grid is sized for (1..4),
- *   kernelParam2 = TMA pipeline stages (2,4,6,8), kernelParam3 unused.  Splitting tiles between CTAs needs the
- *   caller-provided scratch below; without it the kernel runs one CTA per tile.
+ *   kernelParam2 = TMA pipeline stages (2,3,4,5,6,8), kernelParam3 = 0 or 1.  Splitting tiles between CTAs needs
+ *   the caller-provided scratch below; without it the kernel runs one CTA per tile.
+ *   kernelParam3 = 2..8 selects the other decomposition of the same kernel: one thread-block cluster of that many
+ *   CTAs per 128-row tile, each CTA streaming an equal share of k, partial tiles added through distributed shared
+ *   memory (no scratch needed; kernelParam1 is ignored).
  * kernelId 5, 6, 7 (CUDA-core FMA + shuffle kernel with 256, 128, 64 threads; 16-bit weights, row-major B and C,
  *   n <= 4): kernelParam1 = row groups per warp (1,2), kernelParam2 unused, kernelParam3 = cluster split-K. */
 

@@ -75,7 +75,7 @@ int gemm_common(int variant_x, int variant_c, const void* A, const float* scale,
             da.workspace = aux->workspace; da.workspace_bytes = aux->workspace_bytes; da.counters = aux->counters;
             da.n_counters = aux->n_counters; da.status = aux->status;
         }
-        return launch_dense_umma(wt, p, p1, p2, aux ? &da : nullptr, s);
+        return launch_dense_umma(wt, p, p1, p2, p3, aux ? &da : nullptr, s);
     }
     if (kernelId >= 5 && kernelId <= 7) {
         // CUDA-core FMA kernel for 1..4 tokens; 5 / 6 / 7 = 256 / 128 / 64 threads; kernelParam1 = row groups per

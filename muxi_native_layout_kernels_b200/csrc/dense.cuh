@@ -35,7 +35,8 @@ struct DenseAux {
 
 // wt: kBF16 / kFP16 / kE4M3.  Returns an mlk status code.
 int launch_dense_mma(int wt, const DenseParams& p, cudaStream_t stream);
-int launch_dense_umma(int wt, const DenseParams& p, int sk, int stages, const DenseAux* aux, cudaStream_t stream);
+int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages, int cluster_k, const DenseAux* aux,
+                      cudaStream_t stream);
 long long umma_workspace_bytes(int m, int n, int k, int sms, int ctas_per_sm);
 int launch_gemv_simt(int wt, const DenseParams& p, int rows_per_warp_log2, cudaStream_t stream);
 

@@ -10,12 +10,13 @@
 // Activations are row-major; a 2-D tensor map with the 128-byte swizzle delivers the [N x 64] tile in the
 // canonical K-major SW128 layout (rows beyond n are zero-filled by the TMA unit).
 //
-// Structure per CTA (128 threads): lane 0 of warp 0 issues TMA loads into a ring of stages, lane 0 of warp 1
-// issues tcgen05.mma (4 per stage, K = 16 each) and releases stages with tcgen05.commit, then all four warps read
-// the accumulator with tcgen05.ld and write the output.  K is split over gridDim.y CTAs; partial tiles go to an
-// fp32 workspace and the CTA that arrives last at a per-tile counter adds them in a fixed order (no spinning,
-// bit-reproducible).  Every mbarrier wait is bounded: on expiry the kernel records a code in *status, stops, waits
-// (bounded) for its own TMA copies, frees its tensor memory and returns.
+// Structure per CTA (192 threads): lane 0 of warp 0 issues TMA loads into a ring of stages, lane 0 of warp 1
+// issues tcgen05.mma (4 per stage, K = 16 each) and releases stages with tcgen05.commit, four epilogue warps read
+// the accumulator with tcgen05.ld, stage the tile in shared memory and write C with 16-byte stores.  The grid is
+// persistent (a multiple of the SM count) and splits the work stream-K fashion; tiles shared by several CTAs are
+// combined through an fp32 workspace in a fixed order (no CTA ever waits for another one, bit-reproducible).
+// Every wait is bounded: on expiry the kernel records a code in *status, stops, waits (bounded) for its own TMA
+// copies, frees its tensor memory and returns.
 //
 // Role in the reference: the CTA-tile kernel GemmMmaJustLayoutAKernel2 (csrc/gemm_layout_A.cu:296) -- weights and
 // tokens staged through shared memory, tile_m in {64,128}, tile_k 128 -- selected by kernelId 2 in the tables.
@@ -137,18 +138,66 @@ constexpr uint32_t instr_desc() {
 // Work decomposition ("stream-K"): the unit of work is (128-row tile, 64-wide k block); units are numbered
 // tile-major and split into gridDim.x contiguous, equally long ranges, one per CTA, so every SM streams the same
 // number of weight bytes whatever the shape.  A CTA's range decomposes into segments (one tile each).  A segment
-// that covers all k blocks of its tile is written straight to C; otherwise the fp32 partial tile goes to the
-// workspace slot (tile, j), j = CTA index minus the first CTA that touches the tile, and the CTA that arrives last
-// at the tile's counter adds the slots in ascending j and writes C.
+// that covers all k blocks of its tile is written straight to C.  Otherwise the tile is shared by `parts` CTAs;
+// part j = CTA index minus the first CTA that touches the tile, so part 0 owns the head of the k range and is the
+// last thing its CTA computes, while the other parts are finished earlier in their CTAs' runs.  Protocol:
+//   * a CTA parks its fp32 partial tile in workspace slot (tile, j) and bumps the tile's counter; the CTA that
+//     arrives last adds the slots in descending j and writes C (no spinning, bit-reproducible);
+//   * shortcut for part 0: while its MMAs are still running, its epilogue warps watch the counter; once all other
+//     parts have arrived they are summed (descending j) into registers ahead of time, and when the accumulator is
+//     ready the result is own + sum -- the same additions in the same order, without the store / atomic / load
+//     round trips at the very end of the kernel, where nothing else hides them.
 //
 // Warp roles (192 threads): warp 0 lane 0 = TMA producer, warp 1 = tensor-memory owner and (lane 0) MMA issuer,
 // warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4)...).  Two accumulators in tensor memory alternate
 // between segments so the MMAs of the next segment overlap the epilogue of the previous one.
+//
+// Overlap with the preceding kernel of the stream: under the static-weights promise the producer fills the whole
+// ring with weight tiles before it waits for the preceding kernel (griddepcontrol.wait); activations are only
+// touched after that wait.  With a ring of at most about 110 KB two consecutive launches are resident on an SM at
+// the same time, so this start-up runs under the predecessor's tail.  (Asking L2 to prefetch further ahead with
+// cp.async.bulk.prefetch.tensor was measured and made every case slower; it is not used.)
+
+#ifdef MLK_UMMA_TIMELINE
+// Developer instrumentation (compiled out by default): per-CTA %globaltimer stamps of the pipeline milestones.
+__device__ long long g_timeline[1024 * 16];
+#define MLK_TL(slot)                                                                        \
+    do {                                                                                    \
+        long long t_;                                                                       \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+        const unsigned b_ = blockIdx.x * gridDim.y + blockIdx.y;                            \
+        if (b_ < 1024) g_timeline[b_ * 16 + (slot)] = t_;                                   \
+    } while (0)
+#define MLK_TLV(slot, v) do { const unsigned b_ = blockIdx.x * gridDim.y + blockIdx.y; if (b_ < 1024) g_timeline[b_ * 16 + (slot)] = (v); } while (0)
+#else
+#define MLK_TL(slot) do { } while (0)
+#define MLK_TLV(slot, v) do { } while (0)
+#endif
 
 __device__ __forceinline__ int cta_of_unit(long long u, long long U, int G) {
     // the g with floor(U*g/G) <= u < floor(U*(g+1)/G)
     return (int)(((u + 1) * G - 1) / U);
 }
+
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ int ld_acquire(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+constexpr uint32_t kPollLimit = 1u << 22;   // counter polls (64 ns apart) before the early fix-up gives up
 
 template <int WT, int NP, int STAGES>
 __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -160,18 +209,22 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
     __shared__ uint32_t tmem_slot;
     __shared__ int last_flag;
-    __shared__ volatile int ep_go;
+    __shared__ volatile int ep_mode;
     __shared__ volatile int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, g = blockIdx.x;
     const int KB = p.kblocks;
     const long long U = (long long)(p.m / kTileM) * KB;
-    const long long u0 = U * g / G, u1 = U * (g + 1) / G;
+    const int SK = gridDim.y;     // > 1: cluster split-K, blockIdx.x = tile, blockIdx.y = rank in the cluster
+    const long long u0 = SK > 1 ? (long long)g * KB + (long long)KB * blockIdx.y / SK : U * g / G;
+    const long long u1 = SK > 1 ? (long long)g * KB + (long long)KB * (blockIdx.y + 1) / SK : U * (g + 1) / G;
+    if (tid == 0) MLK_TL(0);
 
-    // 1024-byte aligned operand ring: all A stages, then all B stages
+    // 1024-byte aligned operand ring (all A stages, then all B stages), then the output staging tile
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t a_base = base, b_base = base + STAGES * kABytes;
+    uint8_t* const out_stage = smem_raw + (base - smem_u32(smem_raw)) + STAGES * (kABytes + kBBytes);
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
@@ -200,20 +253,42 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_slot;
+    if (tid == 0) MLK_TL(1);
 
     int issued = 0;
     if (warp == 0 && lane == 0) {
         // ---- TMA producer: one stage per unit, running ahead of the MMAs by up to STAGES units ----
-        // Weights may stream before the preceding kernel has finished only under the static-weights promise;
-        // activations never do.
-        if (!static_weights) pdl_wait();
-        pdl_launch_dependents();
-        bool waited = !static_weights;
         // (tile, k block) advance by increment: a 64-bit division per stage in this single thread would cost more
-        // than the stage's memory time
-        int tile = (int)(u0 / KB), kb = (int)(u0 - (long long)tile * KB);
+        // than the stage's memory time.
+        const int tile0 = (int)(u0 / KB), kb0 = (int)(u0 - (long long)tile0 * KB);
         const int nunits = (int)(u1 - u0);
-        for (int i = 0; i < nunits; ++i) {
+        int lt = tile0, lk = kb0;     // next unit whose weights are loaded
+        auto load_a = [&](int s) {
+            tma_load_4d(a_base + s * kABytes, &map_a, full_bar(s), 0, lk * (kBlockK / 8), lt * (kTileM / 16), 0);
+        };
+        int i = 0;
+        if (static_weights) {
+            // weights may stream before the preceding kernel has finished; activations never do
+            pdl_launch_dependents();
+            const int pre = nunits < STAGES ? nunits : STAGES;
+            for (; i < pre; ++i) {
+                mbar_expect_tx(full_bar(i), kABytes + kBBytes);
+                load_a(i);
+                if (++lk == KB) { lk = 0; ++lt; }
+            }
+            pdl_wait();
+            int bk = kb0;
+            for (int j = 0; j < pre; ++j) {
+                tma_load_2d(b_base + j * kBBytes, &map_x, full_bar(j), bk * kBlockK, 0);
+                if (++bk == KB) bk = 0;
+            }
+            issued = pre;
+            MLK_TL(2);
+        } else {
+            pdl_wait();
+            pdl_launch_dependents();
+        }
+        for (; i < nunits; ++i) {
             const int s = i % STAGES;
             if (i >= STAGES && !mbar_wait(empty_bar(s), ((i / STAGES) - 1) & 1)) {
                 abort_flag = 1;
@@ -221,13 +296,12 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
             }
             if (abort_flag) break;
             mbar_expect_tx(full_bar(s), kABytes + kBBytes);
-            tma_load_4d(a_base + s * kABytes, &map_a, full_bar(s), 0, kb * (kBlockK / 8), tile * (kTileM / 16), 0);
-            if (!waited) { pdl_wait(); waited = true; }
-            tma_load_2d(b_base + s * kBBytes, &map_x, full_bar(s), kb * kBlockK, 0);
+            load_a(s);
+            tma_load_2d(b_base + s * kBBytes, &map_x, full_bar(s), lk * kBlockK, 0);
+            if (++lk == KB) { lk = 0; ++lt; }
             ++issued;
-            if (++kb == KB) { kb = 0; ++tile; }
         }
-        if (!waited) pdl_wait();
+        MLK_TL(3);
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
         constexpr uint32_t idesc = instr_desc<WT, NP>();
@@ -265,6 +339,7 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
             umma_commit(acc_full(b));          // arrives when this segment's accumulation is complete
             u += kb_end - kb_begin;
         }
+        MLK_TL(4);
     } else if (warp >= 2) {
         // ---- epilogue warps ----
         const int quad = warp & 3;
@@ -272,97 +347,269 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
         // accumulator row rho holds weight row 16*(rho%64 / 8) + 8*(rho / 64) + rho%8 of the tile (see make_map_a)
         const int wrow = ((lrow & 63) >> 3) * 16 + (lrow >> 6) * 8 + (lrow & 7);
         const int etid = tid - 64;
-        int seg = 0;
-        for (long long u = u0; u < u1; ++seg) {
-            const int tile = (int)(u / KB), kb_begin = (int)(u - (long long)tile * KB);
-            const int kb_end = (int)min((long long)KB, kb_begin + (u1 - u));
-            const int b = seg & 1;
-            if (lane == 0 && !mbar_wait(acc_full(b), (seg >> 1) & 1)) {
+        const size_t part_elems = (size_t)NP * kTileM;
+        if (SK > 1) {
+            // cluster split-K: park the fp32 partial tile [token][accumulator row] in this CTA's (now idle) ring
+            if (lane == 0 && !mbar_wait(acc_full(0), 0)) {
                 abort_flag = 1;
                 if (p.status) atomicExch(p.status, 3);
             }
-            // The four epilogue warps must leave together (they share named barrier 1): one thread reads the
-            // abort flag and publishes the decision.
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (etid == 0) ep_go = abort_flag ? 0 : 1;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (!ep_go) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float v[NP];
+            __syncwarp();
+            if (!abort_flag) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                float* const red = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
 #pragma unroll
-            for (int c = 0; c < NP; c += 16) {
+                for (int c0 = 0; c0 < NP; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + c0, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) red[(c0 + i) * kTileM + lrow] = __uint_as_float(r[i]);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+        }
+        // counters and workspace belong to the preceding kernel of the stream until it has finished
+        pdl_wait();
+        int seg = 0;
+        for (long long u = u0; u < u1 && SK == 1; ++seg) {
+            const int tile = (int)(u / KB), kb_begin = (int)(u - (long long)tile * KB);
+            const int kb_end = (int)min((long long)KB, kb_begin + (u1 - u));
+            const int b = seg & 1;
+            const uint32_t acc_parity = (seg >> 1) & 1;
+            const uint32_t tacc = tmem + ((uint32_t)(quad * 32) << 16) + b * NP;
+            const bool partial = !(kb_begin == 0 && kb_end == KB);
+            int parts = 1, part = 0;
+            if (partial) {
+                const int g_first = cta_of_unit((long long)tile * KB, U, G);
+                parts = cta_of_unit((long long)(tile + 1) * KB - 1, U, G) - g_first + 1;
+                part = g - g_first;
+            }
+            float* const ws_tile = p.ws + (size_t)tile * p.max_parts * part_elems + lrow;
+
+            // ---- part 0: look for the other parts while the MMAs are still running ----
+            bool early = false;
+            float hi[NP];
+            if (partial && part == 0) {
+                if (etid == 0) {
+                    int mode = 0;                     // 0 = accumulator came first, 1 = other parts are all there
+                    for (uint32_t it = 0;; ++it) {
+                        if (abort_flag || mbar_test_wait(acc_full(b), acc_parity)) break;
+                        if (ld_acquire(p.counters + tile) == parts - 1) { mode = 1; break; }
+                        if (it >= kPollLimit) {
+                            abort_flag = 1;
+                            if (p.status) atomicExch(p.status, 5);
+                            break;
+                        }
+                        __nanosleep(64);
+                    }
+                    ep_mode = mode;
+                }
+                epi_bar();
+                early = ep_mode == 1;
+                epi_bar();                            // ep_mode is rewritten below
+                if (early) {
+                    __threadfence();
+                    // descending j, all loads of a part in flight together
+#pragma unroll
+                    for (int c = 0; c < NP; ++c) hi[c] = __ldcg(ws_tile + (size_t)(parts - 1) * part_elems + (size_t)c * kTileM);
+                    for (int j = parts - 2; j >= 1; --j) {
+                        float t[NP];
+#pragma unroll
+                        for (int c = 0; c < NP; ++c) t[c] = __ldcg(ws_tile + (size_t)j * part_elems + (size_t)c * kTileM);
+#pragma unroll
+                        for (int c = 0; c < NP; ++c) hi[c] += t[c];
+                    }
+                }
+            }
+
+            // ---- wait for the accumulator; the four warps leave together (they share named barrier 1) ----
+            if (lane == 0 && !abort_flag && !mbar_wait(acc_full(b), acc_parity)) {
+                abort_flag = 1;
+                if (p.status) atomicExch(p.status, 3);
+            }
+            epi_bar();
+            if (etid == 0) ep_mode = abort_flag ? 2 : 0;
+            epi_bar();
+            if (ep_mode == 2) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (etid == 0) { MLK_TL(7); MLK_TLV(9, (long long)(!partial ? 0 : (early ? 1 : 2)) + 10 * parts + 100 * part); }
+
+            // emits 16 finished columns (tokens c0 .. c0+15) of this thread's accumulator row
+            const int row = tile * kTileM + wrow;
+            const float bia = (p.bias != nullptr) ? load_scalar16<WT>(p.bias, row) : 0.f;
+            auto emit16 = [&](int c0, const float (&o)[16]) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int c = c0 + i;
+                    const float val = fmaf(p.alpha, o[i], bia);
+                    if (p.c_layout == 0) {
+                        if constexpr (WT == kFP16)
+                            reinterpret_cast<__half*>(out_stage)[c * kTileM + wrow] = __float2half_rn(val);
+                        else
+                            reinterpret_cast<__nv_bfloat16*>(out_stage)[c * kTileM + wrow] = __float2bfloat16_rn(val);
+                    } else if (c < p.n) {
+                        const int NB = p.n >> 4;
+                        const size_t idx = ((((size_t)(row >> 5) * NB + (c >> 4)) * 4 + ((row >> 3) & 3)) * 16 + (c & 15)) * 8 + (row & 7);
+                        if constexpr (WT == kFP16)
+                            reinterpret_cast<__half*>(p.C)[idx] = __float2half_rn(val);
+                        else
+                            reinterpret_cast<__nv_bfloat16*>(p.C)[idx] = __float2bfloat16_rn(val);
+                    }
+                }
+            };
+            auto load_acc16 = [&](int c0, float (&o)[16]) {
                 uint32_t r[16];
-                tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + b * NP + c, r);
+                tmem_ld16(tacc + c0, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[c + i] = __uint_as_float(r[i]);
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(b)) : "memory");
+                for (int i = 0; i < 16; ++i) o[i] = __uint_as_float(r[i]);
+            };
+            auto release_acc = [&]() {
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(b)) : "memory");
+            };
 
-            bool do_store = true;
-            if (!(kb_begin == 0 && kb_end == KB)) {
-                // partial tile: park it in the workspace; the last arriver adds all parts in CTA order
-                const int g_first = cta_of_unit((long long)tile * KB, U, G);
-                const int g_last = cta_of_unit((long long)(tile + 1) * KB - 1, U, G);
-                const int parts = g_last - g_first + 1;
-                float* wsp = p.ws + ((size_t)(tile * p.max_parts + (g - g_first)) * NP) * kTileM + lrow;
+            bool wrote = true;
+            if (!partial) {
 #pragma unroll
-                for (int c = 0; c < NP; ++c) __stcg(wsp + (size_t)c * kTileM, v[c]);
+                for (int c0 = 0; c0 < NP; c0 += 16) {
+                    float o[16];
+                    load_acc16(c0, o);
+                    emit16(c0, o);
+                }
+                release_acc();
+            } else if (early) {
+#pragma unroll
+                for (int c0 = 0; c0 < NP; c0 += 16) {
+                    float o[16];
+                    load_acc16(c0, o);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] = hi[c0 + i] + o[i];    // part 0 is the last addend
+                    emit16(c0, o);
+                }
+                release_acc();
+                if (etid == 0) p.counters[tile] = 0;   // ready for the next launch
+            } else {
+                // park this part
+                float* const mine = ws_tile + (size_t)part * part_elems;
+#pragma unroll
+                for (int c0 = 0; c0 < NP; c0 += 16) {
+                    float o[16];
+                    load_acc16(c0, o);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) __stcg(mine + (size_t)(c0 + i) * kTileM, o[i]);
+                }
+                release_acc();
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                epi_bar();
                 if (etid == 0) last_flag = (atomicAdd(p.counters + tile, 1) == parts - 1) ? 1 : 0;
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                do_store = last_flag != 0;
-                if (do_store) {
+                epi_bar();
+                wrote = last_flag != 0;          // the last arriver adds all parts in descending order
+                if (wrote) {
                     __threadfence();
-#pragma unroll
-                    for (int c = 0; c < NP; ++c) v[c] = 0.f;
-                    // The adds keep ascending part order; the loads of UN parts are issued together so that
-                    // their L2 latencies overlap (UN * NP values in flight per thread).
+                    // 64 loads in flight per thread (whole parts); the adds keep descending part order
                     constexpr int UN = 64 / NP;
-                    const float* q0 = p.ws + ((size_t)(tile * p.max_parts) * NP) * kTileM + lrow;
-                    for (int j = 0; j < parts; j += UN) {
+                    float acc[NP];
+                    for (int jb = parts - 1; jb >= 0; jb -= UN) {
                         float t[UN][NP];
 #pragma unroll
                         for (int jj = 0; jj < UN; ++jj)
 #pragma unroll
                             for (int c = 0; c < NP; ++c)
-                                t[jj][c] = (j + jj < parts) ? __ldcg(q0 + ((size_t)(j + jj) * NP + c) * kTileM) : 0.f;
+                                t[jj][c] = (jb - jj >= 0) ? __ldcg(ws_tile + (size_t)(jb - jj) * part_elems + (size_t)c * kTileM) : 0.f;
 #pragma unroll
                         for (int jj = 0; jj < UN; ++jj)
 #pragma unroll
-                            for (int c = 0; c < NP; ++c) v[c] += t[jj][c];
+                            for (int c = 0; c < NP; ++c) {
+                                if (jb == parts - 1 && jj == 0) acc[c] = t[0][c];
+                                else if (jb - jj >= 0) acc[c] += t[jj][c];
+                            }
+                    }
+#pragma unroll
+                    for (int c0 = 0; c0 < NP; c0 += 16) {
+                        float o[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) o[i] = acc[c0 + i];
+                        emit16(c0, o);
                     }
                     if (etid == 0) p.counters[tile] = 0;   // ready for the next launch
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag may be rewritten by the next segment
+                epi_bar();                               // last_flag may be rewritten by the next segment
             }
-            if (do_store) {
-                const int row = tile * kTileM + wrow;
-                const float bia = (p.bias != nullptr) ? load_scalar16<WT>(p.bias, row) : 0.f;
-#pragma unroll
-                for (int c = 0; c < NP; ++c) {
-                    if (c < p.n) {
-                        const float o = fmaf(p.alpha, v[c], bia);
-                        size_t idx;
-                        if (p.c_layout == 0) {
-                            idx = (size_t)c * p.m + row;
-                        } else {
-                            const int NB = p.n >> 4;
-                            idx = ((((size_t)(row >> 5) * NB + (c >> 4)) * 4 + ((row >> 3) & 3)) * 16 + (c & 15)) * 8 + (row & 7);
-                        }
-                        if constexpr (WT == kFP16)
-                            reinterpret_cast<__half*>(p.C)[idx] = __float2half_rn(o);
-                        else
-                            reinterpret_cast<__nv_bfloat16*>(p.C)[idx] = __float2bfloat16_rn(o);
+
+            if (etid == 0) { MLK_TL(8); MLK_TLV(10, (long long)wrote); }
+            if (p.c_layout == 0) {
+                // staged tile [token][128 rows] -> C[token][tile rows]: 256 contiguous bytes per token
+                epi_bar();
+                if (wrote) {
+                    uint8_t* const cbase = reinterpret_cast<uint8_t*>(p.C) + (size_t)tile * kTileM * 2;
+                    for (int idx = etid; idx < p.n * 16; idx += 128) {
+                        const int c = idx >> 4, ch = idx & 15;
+                        const uint4 val = *reinterpret_cast<const uint4*>(out_stage + c * (kTileM * 2) + ch * 16);
+                        *reinterpret_cast<uint4*>(cbase + (size_t)c * p.m * 2 + ch * 16) = val;
                     }
                 }
+                epi_bar();                               // the staging tile is reused by the next segment
             }
             u += kb_end - kb_begin;
         }
+        if (etid == 0) MLK_TL(5);
     }
     __syncwarp();
+
+    if (SK > 1) {
+        // ---- cluster split-K: every CTA of the cluster adds one slice of accumulator rows over all ranks
+        // (descending rank, fixed order) through distributed shared memory and writes that slice of C ----
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (warp >= 2) {
+            const int etid = tid - 64;
+            const int rank = blockIdx.y;
+            const int r0 = kTileM * rank / SK, rows = kTileM * (rank + 1) / SK - r0;
+            uint32_t remote[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[q]) : "r"(base), "r"(q < SK ? q : 0));
+            const int total = p.n * rows;
+            for (int idx = etid; idx < total; idx += 128) {
+                const int c = idx / rows, rho = r0 + idx - c * rows;
+                const uint32_t off = (uint32_t)(c * kTileM + rho) * 4u;
+                float t[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    t[q] = 0.f;
+                    if (q < SK) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(t[q]) : "r"(remote[q] + off) : "memory");
+                }
+                float acc = 0.f;
+                bool first = true;
+#pragma unroll
+                for (int q = 7; q >= 0; --q) {
+                    if (q < SK) {
+                        acc = first ? t[q] : acc + t[q];
+                        first = false;
+                    }
+                }
+                const int row = g * kTileM + ((rho & 63) >> 3) * 16 + (rho >> 6) * 8 + (rho & 7);
+                const float bia = (p.bias != nullptr) ? load_scalar16<WT>(p.bias, row) : 0.f;
+                const float val = fmaf(p.alpha, acc, bia);
+                size_t o;
+                if (p.c_layout == 0) {
+                    o = (size_t)c * p.m + row;
+                } else {
+                    const int NB = p.n >> 4;
+                    o = ((((size_t)(row >> 5) * NB + (c >> 4)) * 4 + ((row >> 3) & 3)) * 16 + (c & 15)) * 8 + (row & 7);
+                }
+                if constexpr (WT == kFP16)
+                    reinterpret_cast<__half*>(p.C)[o] = __float2half_rn(val);
+                else
+                    reinterpret_cast<__nv_bfloat16*>(p.C)[o] = __float2bfloat16_rn(val);
+            }
+            if (etid == 0) MLK_TL(5);
+        }
+        // nobody leaves while its shared memory may still be read
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
 
     // ---- teardown ----
     // If the pipeline stopped early, wait (bounded) until every TMA copy this CTA issued has landed, so that no
@@ -375,6 +622,7 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
+    if (tid == 0) MLK_TL(6);
 }
 
 // ---- host ------------------------------------------------------------------------------------------------
@@ -423,52 +671,51 @@ bool make_map_x(CUtensorMap* map, const void* X, int n, int k, int wt, int np) {
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int WT, int NP, int STAGES>
-int launch_inst(const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& up, int G, cudaStream_t s) {
-    auto kern = dense_umma_kernel<WT, NP, STAGES>;
-    const size_t smem = (size_t)STAGES * (kABytes + NP * 128) + 1024;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (!attr_set[dev & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return fail(kCudaError, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        attr_set[dev & 63] = true;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(G, 1, 1);
-    cfg.blockDim = dim3(192);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[2];
-    cfg.attrs = attr;
-    cfg.numAttrs = launch_attrs(attr, 1);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mx, up, option(kOptStaticWeights));
-    if (e != cudaSuccess) return fail(kCudaError, "dense_umma launch: %s", cudaGetErrorString(e));
-    return kOk;
-}
-
 template <int WT, int NP>
-int launch_stages(int stages, const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& up, int G,
-                  cudaStream_t s) {
+const void* kernel_for_stages(int stages) {
     switch (stages) {
-        case 2: return launch_inst<WT, NP, 2>(ma, mx, up, G, s);
-        case 4: return launch_inst<WT, NP, 4>(ma, mx, up, G, s);
-        case 6: return launch_inst<WT, NP, 6>(ma, mx, up, G, s);
-        case 8: return launch_inst<WT, NP, 8>(ma, mx, up, G, s);
+        case 2: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 2>);
+        case 3: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 3>);
+        case 4: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 4>);
+        case 5: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 5>);
+        case 6: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 6>);
+        case 8: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 8>);
     }
-    return fail(kInvalidArg, "dense (tcgen05): stages must be one of 2, 4, 6, 8 (got %d)", stages);
+    return nullptr;
 }
 
 template <int WT>
-int launch_np(int np, int stages, const CUtensorMap& ma, const CUtensorMap& mx, const UmmaParams& up, int G,
-              cudaStream_t s) {
+const void* kernel_for(int np, int stages) {
     switch (np) {
-        case 16: return launch_stages<WT, 16>(stages, ma, mx, up, G, s);
-        case 32: return launch_stages<WT, 32>(stages, ma, mx, up, G, s);
-        case 64: return launch_stages<WT, 64>(stages, ma, mx, up, G, s);
+        case 16: return kernel_for_stages<WT, 16>(stages);
+        case 32: return kernel_for_stages<WT, 32>(stages);
+        case 64: return kernel_for_stages<WT, 64>(stages);
     }
-    return fail(kInvalidArg, "dense (tcgen05): bad token tile %d", np);
+    return nullptr;
+}
+
+size_t smem_bytes(int np, int stages) {
+    return (size_t)stages * (kABytes + np * 128) + (size_t)np * kTileM * 2 + 1024;
+}
+
+// Resident CTAs per SM of one kernel instantiation on the current device (0 = error); the first call also raises
+// the kernel's dynamic shared-memory limit.  The grid is persistent: it is never made larger than what is
+// resident at once.
+int resident_ctas_per_sm(const void* kern, size_t smem) {
+    static std::mutex mu;
+    static std::unordered_map<unsigned long long, int> cache;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const unsigned long long key = (unsigned long long)(uintptr_t)kern * 64ull + (unsigned)(dev & 63);
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    int occ = 0;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, 192, smem) != cudaSuccess)
+        occ = 0;
+    cache[key] = occ;
+    return occ;
 }
 
 }  // namespace
@@ -486,20 +733,35 @@ int umma_max_parts(int tiles, int kblocks, int G) {
 }
 
 // ctas_per_sm: resident CTAs per SM the grid is sized for (grid = ctas_per_sm * SM count, capped by the number of
-// work units); stages: 2, 4, 6 or 8 (two CTAs per SM fit with at most 4).
-int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages, const DenseAux* aux, cudaStream_t stream) {
+// work units); stages: ring depth (2, 3, 4, 5, 6 or 8; a ring of at most about 110 KB lets two launches share an
+// SM); cluster_k: 0 or 1 = the persistent stream-K grid described above, 2..8 = one thread-block cluster of that
+// many CTAs per 128-row tile, each CTA taking an equal share of k, partial tiles added through distributed shared
+// memory (no workspace; meant for shapes with few tiles and a long k, where stream-K would share every tile among
+// many CTAs that all finish at the same moment).
+int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages, int cluster_k, const DenseAux* aux,
+                      cudaStream_t stream) {
     if (wt != kBF16 && wt != kFP16) return fail(kUnsupported, "dense (tcgen05): 16-bit weights only");
     if (!p.A || !p.X || !p.C) return fail(kInvalidArg, "dense: null pointer");
     if (p.x_layout != 0) return fail(kUnsupported, "dense (tcgen05): activations must be row-major");
     if (p.m % kTileM != 0 || p.k % kBlockK != 0) return fail(kInvalidArg, "dense (tcgen05): need m %% 128 == 0 and k %% 64 == 0");
     if (p.n < 1 || p.n > 64) return fail(kUnsupported, "dense (tcgen05): 1..64 tokens per launch (got %d)", p.n);
     if (p.c_layout == 1 && p.n % 16 != 0) return fail(kInvalidArg, "dense: layout C needs n %% 16 == 0");
-    if (((uintptr_t)p.A & 15) || ((uintptr_t)p.X & 15)) return fail(kInvalidArg, "dense (tcgen05): operands must be 16-byte aligned");
+    if (((uintptr_t)p.A & 15) || ((uintptr_t)p.X & 15) || ((uintptr_t)p.C & 15))
+        return fail(kInvalidArg, "dense (tcgen05): A, B and C must be 16-byte aligned");
     if (encode_fn() == nullptr) return fail(kUnsupported, "dense (tcgen05): cuTensorMapEncodeTiled is not available");
     if (ctas_per_sm < 1 || ctas_per_sm > 4) return fail(kInvalidArg, "dense (tcgen05): CTAs per SM must be 1..4 (got %d)", ctas_per_sm);
     const int np = p.n <= 16 ? 16 : (p.n <= 32 ? 32 : 64);
     const int tiles = p.m / kTileM;
     const int kblocks = p.k / kBlockK;
+    const void* kern = wt == kFP16 ? kernel_for<kFP16>(np, stages) : kernel_for<kBF16>(np, stages);
+    if (kern == nullptr) return fail(kInvalidArg, "dense (tcgen05): stages must be one of 2, 3, 4, 5, 6, 8 (got %d)", stages);
+    const size_t smem = smem_bytes(np, stages);
+    const int resident = resident_ctas_per_sm(kern, smem);
+    if (resident < 1) return fail(kCudaError, "dense (tcgen05): a CTA with %d stages does not fit on this device", stages);
+    if (ctas_per_sm > resident) ctas_per_sm = resident;
+    if (cluster_k < 0 || cluster_k > 8) return fail(kInvalidArg, "dense (tcgen05): cluster split must be 0..8 (got %d)", cluster_k);
+    const bool clustered = cluster_k > 1;
+    if (clustered && cluster_k > p.k / kBlockK) return fail(kInvalidArg, "dense (tcgen05): cluster split %d exceeds the %d k blocks", cluster_k, p.k / kBlockK);
     static int sm_count[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -509,7 +771,7 @@ int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages,
     if (G > U) G = U;
     // Without scratch only whole tiles can be handed out: one CTA per tile.
     const bool have_aux = aux && aux->workspace && aux->counters;
-    if (!have_aux) G = tiles;
+    if (!have_aux || clustered) G = tiles;
     const int max_parts = umma_max_parts(tiles, kblocks, (int)G);
     if (have_aux && max_parts > 1) {
         const long long need = (long long)tiles * max_parts * np * kTileM * 4;
@@ -527,8 +789,19 @@ int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages,
     up.max_parts = max_parts;
     up.counters = have_aux ? aux->counters : nullptr;
     up.status = aux ? aux->status : nullptr;
-    if (wt == kFP16) return launch_np<kFP16>(np, stages, ma, mx, up, (int)G, stream);
-    return launch_np<kBF16>(np, stages, ma, mx, up, (int)G, stream);
+    int static_weights = option(kOptStaticWeights);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)G, clustered ? cluster_k : 1, 1);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    cfg.attrs = attr;
+    cfg.numAttrs = launch_attrs(attr, clustered ? cluster_k : 1);
+    void* args[4] = {&ma, &mx, &up, &static_weights};
+    const cudaError_t e = cudaLaunchKernelExC(&cfg, kern, args);
+    if (e != cudaSuccess) return fail(kCudaError, "dense_umma launch: %s", cudaGetErrorString(e));
+    return kOk;
 }
 
 // Upper bound of the workspace launch_dense_umma can need for this shape on a device with `sms` SMs.
@@ -541,3 +814,9 @@ long long umma_workspace_bytes(int m, int n, int k, int sms, int ctas_per_sm) {
 }
 
 }  // namespace mlk
+
+#ifdef MLK_UMMA_TIMELINE
+extern "C" int mlk_umma_timeline_read(long long* host) {
+    return (int)cudaMemcpyFromSymbol(host, mlk::g_timeline, sizeof(long long) * 1024 * 16);
+}
+#endif

@@ -129,8 +129,15 @@ def scan_one(kind, m, n, k, dtype, log):
         if kind == "a" and n <= 4:
             cands += [(kid, rg, 0, sk) for kid, rg, sk in itertools.product([5, 6, 7], [1, 2], [1, 2, 4]) if m % (16 * rg) == 0]
         if kind == "a" and n <= 64:
-            # tcgen05 tile kernel: CTAs per SM x pipeline stages (two CTAs share an SM only with <= 4 stages)
-            cands += [(2, 1, 4, 0), (2, 1, 6, 0), (2, 1, 8, 0), (2, 2, 2, 0), (2, 2, 4, 0), (2, 3, 2, 0)]
+            # tcgen05 tile kernel: (CTAs per SM, ring stages, 0) = persistent stream-K grid;
+            # (1, ring stages, cluster size) = one cluster per 128-row tile, k split inside the cluster
+            cands += [(2, 1, 4, 0), (2, 1, 5, 0), (2, 1, 6, 0), (2, 1, 8, 0), (2, 2, 3, 0), (2, 2, 4, 0)]
+            for ck in (2, 3, 4, 5, 6, 7, 8):
+                for st in (2, 3, 4, 5, 6, 8):
+                    np_ = 16 if n <= 16 else (32 if n <= 32 else 64)
+                    smem = st * (16384 + np_ * 128) + np_ * 256 + 2048
+                    if ck <= k // 64 and (m // 128) * ck <= 148 * max(1, (227 * 1024) // smem):
+                        cands.append((2, 1, st, ck))
     best, best_t = None, float("inf")
     for c in cands:
         if kind.startswith("gemv"):

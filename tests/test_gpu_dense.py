@@ -228,9 +228,16 @@ def test_gemm_tcgen05_tile_kernel(dt):
             X = randn((n, k), 97 + n, 1.0, DT[dt])
             want = odense.gemm_ref(X, W)
             want_b = odense.gemm_ref(X, W, alpha=0.5, bias=bias)
-            for sk, stages in [(1, 2), (1, 8), (2, 4), (3, 6), (4, 2)]:
+            for sk, stages in [(1, 2), (1, 8), (2, 4), (3, 6), (4, 2), (1, 3), (2, 5)]:
                 C = mlk.gemm_layoutA_wapper(A, X.to(dev), m, n, k, kernelParam1=sk, kernelParam2=stages, kernelId=2)
                 assert_close(C, want, f"tcgen05 {dt} m={m} k={k} n={n} sk={sk} stages={stages}")
+            # thread-block-cluster split-K: partial tiles are added through distributed shared memory
+            for ck, stages in [(2, 4), (3, 2), (4, 6), (8, 8)]:
+                if ck > k // 64:
+                    continue
+                C = mlk.gemm_layoutA_wapper(A, X.to(dev), m, n, k, kernelParam1=1, kernelParam2=stages, kernelParam3=ck,
+                                            kernelId=2)
+                assert_close(C, want, f"tcgen05 cluster {dt} m={m} k={k} n={n} cluster={ck} stages={stages}")
             C = mlk.gemm_layoutA_wapper(A, X.to(dev), m, n, k, alpha=0.5, kernelParam1=2, kernelParam2=4, kernelId=2,
                                         bias=bias.to(dev))
             assert_close(C, want_b, f"tcgen05 bias {dt} m={m} k={k} n={n}")
@@ -239,9 +246,12 @@ def test_gemm_tcgen05_tile_kernel(dt):
     ref = mlk.gemm_layoutA_wapper(A, X, 1024, 40, 4096, kernelParam1=2, kernelParam2=4, kernelId=2)
     for _ in range(5):
         assert torch.equal(ref, mlk.gemm_layoutA_wapper(A, X, 1024, 40, 4096, kernelParam1=2, kernelParam2=4, kernelId=2))
+    refc = mlk.gemm_layoutA_wapper(A, X, 1024, 40, 4096, kernelParam1=1, kernelParam2=4, kernelParam3=4, kernelId=2)
+    for _ in range(3):
+        assert torch.equal(refc, mlk.gemm_layoutA_wapper(A, X, 1024, 40, 4096, kernelParam1=1, kernelParam2=4, kernelParam3=4, kernelId=2))
     assert mlk.kernel_status() == 0, "a bounded wait inside the tcgen05 kernel expired"
     with pytest.raises(RuntimeError, match="stages"):
-        mlk.gemm_layoutA_wapper(A, X, 1024, 40, 4096, kernelParam1=1, kernelParam2=3, kernelId=2)
+        mlk.gemm_layoutA_wapper(A, X, 1024, 40, 4096, kernelParam1=1, kernelParam2=7, kernelId=2)
 
 
 @pytest.mark.parametrize("dt", ["bf16", "fp16"])
