@@ -102,6 +102,30 @@ def make_pool(W, copies):
     return [mlk.layoutA(W) if i == 0 else None for i in range(copies)]
 
 
+def candidates(kind, m, n, k):
+    """Launch-argument tuples to try for one table key (GeMV: blockDimX, kernelId, p1, p2; GEMM: kernelId, p1, p2, p3)."""
+    fp8 = kind in ("a_fp8", "gemv_fp8")
+    if kind.startswith("gemv"):
+        return [(t, kid, rg, sk) for t, kid, rg, sk in itertools.product([64, 128, 256], [1, 2], [1, 2], [1, 2, 4, 8])
+                if not (fp8 and kid == 2) and m % (16 * rg) == 0]
+    # kernelId 1 / 3 / 4: the warp-level kernel with 8 / 4 / 2 warps per CTA
+    cands = [(kid, rg, wm, sk) for kid, rg, wm, sk in itertools.product([1, 3, 4], [1, 2], [1, 2, 4, 8], [1, 2, 4])
+             if m % (16 * rg * wm) == 0 and wm <= {1: 8, 3: 4, 4: 2}[kid]]
+    if kind == "a" and n <= 4:
+        cands += [(kid, rg, 0, sk) for kid, rg, sk in itertools.product([5, 6, 7], [1, 2], [1, 2, 4]) if m % (16 * rg) == 0]
+    if kind == "a" and n <= 64:
+        # tcgen05 tile kernel: (CTAs per SM, ring stages, 0) = persistent stream-K grid;
+        # (1, ring stages, cluster size) = one cluster per 128-row tile, k split inside the cluster
+        cands += [(2, 1, 4, 0), (2, 1, 5, 0), (2, 1, 6, 0), (2, 1, 8, 0), (2, 2, 3, 0), (2, 2, 4, 0)]
+        for ck in (2, 3, 4, 5, 6, 7, 8):
+            for st in (2, 3, 4, 5, 6, 8):
+                np_ = 16 if n <= 16 else (32 if n <= 32 else 64)
+                smem = st * (16384 + np_ * 128) + np_ * 256 + 2048
+                if ck <= k // 64 and (m // 128) * ck <= 148 * max(1, (227 * 1024) // smem):
+                    cands.append((2, 1, st, ck))
+    return cands
+
+
 def scan_one(kind, m, n, k, dtype, log):
     dev = torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(m * 31 + k)
@@ -119,25 +143,7 @@ def scan_one(kind, m, n, k, dtype, log):
     pool = [A0] + [A0.clone() for _ in range(copies - 1)]
     XB = mlk.layoutB(X) if kind in ("abc", "conc") else None
 
-    if kind.startswith("gemv"):
-        cands = [(t, kid, rg, sk) for t, kid, rg, sk in itertools.product([64, 128, 256], [1, 2], [1, 2], [1, 2, 4, 8])
-                 if not (fp8 and kid == 2) and m % (16 * rg) == 0]
-    else:
-        # kernelId 1 / 3 / 4: the warp-level kernel with 8 / 4 / 2 warps per CTA
-        cands = [(kid, rg, wm, sk) for kid, rg, wm, sk in itertools.product([1, 3, 4], [1, 2], [1, 2, 4, 8], [1, 2, 4])
-                 if m % (16 * rg * wm) == 0 and wm <= {1: 8, 3: 4, 4: 2}[kid]]
-        if kind == "a" and n <= 4:
-            cands += [(kid, rg, 0, sk) for kid, rg, sk in itertools.product([5, 6, 7], [1, 2], [1, 2, 4]) if m % (16 * rg) == 0]
-        if kind == "a" and n <= 64:
-            # tcgen05 tile kernel: (CTAs per SM, ring stages, 0) = persistent stream-K grid;
-            # (1, ring stages, cluster size) = one cluster per 128-row tile, k split inside the cluster
-            cands += [(2, 1, 4, 0), (2, 1, 5, 0), (2, 1, 6, 0), (2, 1, 8, 0), (2, 2, 3, 0), (2, 2, 4, 0)]
-            for ck in (2, 3, 4, 5, 6, 7, 8):
-                for st in (2, 3, 4, 5, 6, 8):
-                    np_ = 16 if n <= 16 else (32 if n <= 32 else 64)
-                    smem = st * (16384 + np_ * 128) + np_ * 256 + 2048
-                    if ck <= k // 64 and (m // 128) * ck <= 148 * max(1, (227 * 1024) // smem):
-                        cands.append((2, 1, st, ck))
+    cands = candidates(kind, m, n, k)
     best, best_t = None, float("inf")
     for c in cands:
         if kind.startswith("gemv"):
