@@ -199,8 +199,10 @@ __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: 
 
 constexpr uint32_t kPollLimit = 1u << 22;   // counter polls (64 ns apart) before the early fix-up gives up
 
-template <int WT, int NP, int STAGES>
-__global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__ CUtensorMap map_a,
+// CLUSTER = false: persistent stream-K grid; true: one cluster per tile (gridDim.y = cluster size), which needs none of
+// the workspace code paths and so fits two 64-token CTAs per SM.
+template <int WT, int NP, int STAGES, bool CLUSTER>
+__global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const __grid_constant__ CUtensorMap map_a,
                                                          const __grid_constant__ CUtensorMap map_x, const UmmaParams p,
                                                          const int static_weights) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -216,9 +218,9 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
     const int G = gridDim.x, g = blockIdx.x;
     const int KB = p.kblocks;
     const long long U = (long long)(p.m / kTileM) * KB;
-    const int SK = gridDim.y;     // > 1: cluster split-K, blockIdx.x = tile, blockIdx.y = rank in the cluster
-    const long long u0 = SK > 1 ? (long long)g * KB + (long long)KB * blockIdx.y / SK : U * g / G;
-    const long long u1 = SK > 1 ? (long long)g * KB + (long long)KB * (blockIdx.y + 1) / SK : U * (g + 1) / G;
+    const int SK = CLUSTER ? (int)gridDim.y : 1;   // cluster split-K: blockIdx.x = tile, blockIdx.y = rank in the cluster
+    const long long u0 = CLUSTER ? (long long)g * KB + (long long)KB * blockIdx.y / SK : U * g / G;
+    const long long u1 = CLUSTER ? (long long)g * KB + (long long)KB * (blockIdx.y + 1) / SK : U * (g + 1) / G;
     if (tid == 0) MLK_TL(0);
 
     // 1024-byte aligned operand ring (all A stages, then all B stages), then the output staging tile
@@ -348,7 +350,7 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
         const int wrow = ((lrow & 63) >> 3) * 16 + (lrow >> 6) * 8 + (lrow & 7);
         const int etid = tid - 64;
         const size_t part_elems = (size_t)NP * kTileM;
-        if (SK > 1) {
+        if constexpr (CLUSTER) {
             // cluster split-K: park the fp32 partial tile [token][accumulator row] in this CTA's (now idle) ring
             if (lane == 0 && !mbar_wait(acc_full(0), 0)) {
                 abort_flag = 1;
@@ -372,7 +374,7 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
         // counters and workspace belong to the preceding kernel of the stream until it has finished
         pdl_wait();
         int seg = 0;
-        for (long long u = u0; u < u1 && SK == 1; ++seg) {
+        for (long long u = u0; u < u1 && !CLUSTER; ++seg) {
             const int tile = (int)(u / KB), kb_begin = (int)(u - (long long)tile * KB);
             const int kb_end = (int)min((long long)KB, kb_begin + (u1 - u));
             const int b = seg & 1;
@@ -559,7 +561,7 @@ __global__ void __launch_bounds__(192) dense_umma_kernel(const __grid_constant__
     }
     __syncwarp();
 
-    if (SK > 1) {
+    if constexpr (CLUSTER) {
         // ---- cluster split-K: every CTA of the cluster adds one slice of accumulator rows over all ranks
         // (descending rank, fixed order) through distributed shared memory and writes that slice of C ----
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -671,31 +673,33 @@ bool make_map_x(CUtensorMap* map, const void* X, int n, int k, int wt, int np) {
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int WT, int NP>
+template <int WT, int NP, bool CLUSTER>
 const void* kernel_for_stages(int stages) {
     switch (stages) {
-        case 2: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 2>);
-        case 3: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 3>);
-        case 4: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 4>);
-        case 5: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 5>);
-        case 6: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 6>);
-        case 8: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 8>);
+        case 2: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 2, CLUSTER>);
+        case 3: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 3, CLUSTER>);
+        case 4: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 4, CLUSTER>);
+        case 5: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 5, CLUSTER>);
+        case 6: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 6, CLUSTER>);
+        case 8: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 8, CLUSTER>);
     }
     return nullptr;
 }
 
-template <int WT>
+template <int WT, bool CLUSTER>
 const void* kernel_for(int np, int stages) {
     switch (np) {
-        case 16: return kernel_for_stages<WT, 16>(stages);
-        case 32: return kernel_for_stages<WT, 32>(stages);
-        case 64: return kernel_for_stages<WT, 64>(stages);
+        case 16: return kernel_for_stages<WT, 16, CLUSTER>(stages);
+        case 32: return kernel_for_stages<WT, 32, CLUSTER>(stages);
+        case 64: return kernel_for_stages<WT, 64, CLUSTER>(stages);
     }
     return nullptr;
 }
 
-size_t smem_bytes(int np, int stages) {
-    return (size_t)stages * (kABytes + np * 128) + (size_t)np * kTileM * 2 + 1024;
+// ring + (stream-K only) the output staging tile + alignment slack; the cluster mode parks its fp32 partial tile
+// (np * 512 bytes) in the idle ring, which two stages always cover
+size_t smem_bytes(int np, int stages, bool clustered) {
+    return (size_t)stages * (kABytes + np * 128) + (clustered ? 0 : (size_t)np * kTileM * 2) + 1024;
 }
 
 // Resident CTAs per SM of one kernel instantiation on the current device (0 = error); the first call also raises
@@ -753,14 +757,15 @@ int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages,
     const int np = p.n <= 16 ? 16 : (p.n <= 32 ? 32 : 64);
     const int tiles = p.m / kTileM;
     const int kblocks = p.k / kBlockK;
-    const void* kern = wt == kFP16 ? kernel_for<kFP16>(np, stages) : kernel_for<kBF16>(np, stages);
+    if (cluster_k < 0 || cluster_k > 8) return fail(kInvalidArg, "dense (tcgen05): cluster split must be 0..8 (got %d)", cluster_k);
+    const bool clustered = cluster_k > 1;
+    const void* kern = clustered ? (wt == kFP16 ? kernel_for<kFP16, true>(np, stages) : kernel_for<kBF16, true>(np, stages))
+                                 : (wt == kFP16 ? kernel_for<kFP16, false>(np, stages) : kernel_for<kBF16, false>(np, stages));
     if (kern == nullptr) return fail(kInvalidArg, "dense (tcgen05): stages must be one of 2, 3, 4, 5, 6, 8 (got %d)", stages);
-    const size_t smem = smem_bytes(np, stages);
+    const size_t smem = smem_bytes(np, stages, clustered);
     const int resident = resident_ctas_per_sm(kern, smem);
     if (resident < 1) return fail(kCudaError, "dense (tcgen05): a CTA with %d stages does not fit on this device", stages);
     if (ctas_per_sm > resident) ctas_per_sm = resident;
-    if (cluster_k < 0 || cluster_k > 8) return fail(kInvalidArg, "dense (tcgen05): cluster split must be 0..8 (got %d)", cluster_k);
-    const bool clustered = cluster_k > 1;
     if (clustered && cluster_k > p.k / kBlockK) return fail(kInvalidArg, "dense (tcgen05): cluster split %d exceeds the %d k blocks", cluster_k, p.k / kBlockK);
     static int sm_count[64] = {};
     int dev = 0;

@@ -120,7 +120,7 @@ def candidates(kind, m, n, k):
         for ck in (2, 3, 4, 5, 6, 7, 8):
             for st in (2, 3, 4, 5, 6, 8):
                 np_ = 16 if n <= 16 else (32 if n <= 32 else 64)
-                smem = st * (16384 + np_ * 128) + np_ * 256 + 2048
+                smem = st * (16384 + np_ * 128) + 2048
                 if ck <= k // 64 and (m // 128) * ck <= 148 * max(1, (227 * 1024) // smem):
                     cands.append((2, 1, st, ck))
     return cands
