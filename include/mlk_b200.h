@@ -90,6 +90,9 @@ int mlk_fp8_weight_repack(const void* weight, void* out, int64_t nbytes, mlk_str
 /* Explicit tuning arguments.  Reference: gemv_layoutA_wapper, csrc/gemv_layout_a.cu:17-71.
  *   kernelId 1: tensor-core streaming kernel, kernelParam1 = row groups per warp (1,2), kernelParam2 = split-K (1,2,4,8)
  *   kernelId 2: CUDA-core FMA + shuffle kernel, same two parameters (bf16/fp16 only)
+ *   kernelId 3: e4m3 only, no block scales, m % 128 == 0, k % 64 == 0: the TMA -> convert -> tcgen05 pipeline of the
+ *               soft-FP8 GEMM (see kernelId 2 there); kernelParam1 = raw ring stages (2,3,4,6,8), kernelParam2 =
+ *               cluster size (1..8), blockDimX ignored
  *   scale_matrix: e4m3 only, fp32 [ceil(m/128)][ceil(k/128)], may be NULL (= all ones)
  *   fp8_order: 0 natural bytes, 1 bytes as written by mlk_fp8_weight_repack
  *   beta is accepted and ignored, as in the reference kernels. */
@@ -112,6 +115,9 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
  *   kernelParam3 = 2..8 selects the other decomposition of the same kernel: one thread-block cluster of that many
  *   CTAs per 128-row tile, each CTA streaming an equal share of k, partial tiles added through distributed shared
  *   memory (no scratch needed; kernelParam1 is ignored).
+ *   With e4m3 weights (soft_fp8 entry points, no block scales) kernelId 2 is the TMA -> convert -> tcgen05
+ *   pipeline: the e4m3 tile is decoded to bf16 in shared memory by the four warps that later run the epilogue;
+ *   kernelParam2 = stages of the raw e4m3 ring (2,3,4,6,8), kernelParam3 = cluster size (1..8), kernelParam1 ignored.
  * kernelId 5, 6, 7 (CUDA-core FMA + shuffle kernel with 256, 128, 64 threads; 16-bit weights, row-major B and C,
  *   n <= 4): kernelParam1 = row groups per warp (1,2), kernelParam2 unused, kernelParam3 = cluster split-K. */
 

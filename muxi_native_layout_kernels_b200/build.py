@@ -26,6 +26,7 @@ SOURCES = [
     "abi.cu",
     "dense.cu",
     "dense_umma.cu",
+    "dense_umma_f8.cu",
     "prepack.cu",
     "moe_router.cu",
     "moe_align.cu",

@@ -69,6 +69,13 @@ int gemm_common(int variant_x, int variant_c, const void* A, const float* scale,
     p.A = A; p.X = B; p.C = C; p.bias = bias; p.scale = scale;
     p.m = m; p.n = n; p.k = k; p.alpha = alpha;
     p.x_layout = variant_x; p.c_layout = variant_c; p.fp8_order = fp8_order;
+    if (kernelId == 2 && wt == kE4M3) {
+        // TMA -> convert -> tcgen05 pipeline for e4m3 weights: kernelParam2 = raw ring stages, kernelParam3 = cluster
+        // size; weights with block scales stay on the warp-level kernel
+        if (scale != nullptr) return fail(kUnsupported, "gemm: kernelId 2 does not apply block scales; use kernelId 1, 3 or 4");
+        if (variant_c != 0 && n % 16 != 0) return fail(kInvalidArg, "gemm: layout C needs n %% 16 == 0");
+        return launch_dense_umma_f8(p, p2, p3 < 1 ? 1 : p3, aux ? aux->status : nullptr, s);
+    }
     if (kernelId == 2) {
         DenseAux da{};
         if (aux) {
@@ -100,8 +107,10 @@ int gemm_table(int table, int variant_x, int variant_c, const void* A, const flo
     const int twarps = t.a == 1 ? 8 : (t.a == 3 ? 4 : (t.a == 4 ? 2 : 0));
     const bool ok1 = twarps > 0 && (t.b == 1 || t.b == 2) && (t.c == 1 || t.c == 2 || t.c == 4 || t.c == 8) &&
                      t.c <= twarps && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b * t.c) == 0;
-    const bool ok2 = t.a == 2 && variant_x == 0 && dtype != MLK_E4M3 && n <= 64 && t.b >= 1 && t.b <= 4 &&
-                     ((t.c >= 2 && t.c <= 6) || t.c == 8) && t.d >= 0 && t.d <= 8;
+    const bool ok2 = t.a == 2 && variant_x == 0 && n <= 64 &&
+                     (dtype != MLK_E4M3
+                          ? (t.b >= 1 && t.b <= 4 && ((t.c >= 2 && t.c <= 6) || t.c == 8) && t.d >= 0 && t.d <= 8)
+                          : (scale == nullptr && (t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 && t.d <= 8));
     const bool ok5 = t.a >= 5 && t.a <= 7 && n <= 4 && variant_x == 0 && variant_c == 0 && dtype != MLK_E4M3 &&
                      (t.b == 1 || t.b == 2) && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b) == 0;
     if (!ok1 && !ok2 && !ok5) t = default_args(table, m, n, k);
@@ -206,7 +215,12 @@ int mlk_gemv_layoutA_wapper(const void* A, const void* x, void* y, int m, int k,
     p.rg = kernelParam1; p.wm = 1; p.sk = kernelParam2; p.threads = blockDimX;
     if (kernelId == 1) return launch_dense_mma(wt, p, (cudaStream_t)s);
     if (kernelId == 2) return launch_gemv_simt(wt, p, 0, (cudaStream_t)s);
-    return fail(kUnsupported, "gemv: kernelId %d is not built (1 = tensor-core, 2 = CUDA-core)", kernelId);
+    if (kernelId == 3 && wt == kE4M3) {
+        // TMA -> convert -> tcgen05 pipeline: kernelParam1 = raw ring stages, kernelParam2 = cluster size
+        if (scale_matrix != nullptr) return fail(kUnsupported, "gemv: kernelId 3 does not apply block scales; use kernelId 1");
+        return launch_dense_umma_f8(p, kernelParam1, kernelParam2, nullptr, (cudaStream_t)s);
+    }
+    return fail(kUnsupported, "gemv: kernelId %d is not built (1 = tensor-core, 2 = CUDA-core, 3 = tcgen05 for e4m3)", kernelId);
 }
 
 int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dtype, float alpha, float beta,
@@ -220,7 +234,9 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
     // Same safety net as the reference (csrc/gemv_layout_a.cu:132-143): a row that cannot run falls back.
     const bool ok = (t.a == 64 || t.a == 128 || t.a == 256) && (t.b == 1 || (t.b == 2 && dtype != MLK_E4M3)) &&
                     (t.c == 1 || t.c == 2) && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.c) == 0;
-    if (!ok) t = default_args(table, m, 1, k);
+    const bool ok3 = dtype == MLK_E4M3 && t.b == 3 && scale_matrix == nullptr && m % 128 == 0 && k % 64 == 0 &&
+                     (t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 && t.d <= 8;
+    if (!ok && !ok3) t = default_args(table, m, 1, k);
     return mlk_gemv_layoutA_wapper(A, x, y, m, k, dtype, alpha, beta, t.a, t.b, t.c, t.d, scale_matrix, bias,
                                    fp8_order, s);
 }

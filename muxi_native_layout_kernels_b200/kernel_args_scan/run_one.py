@@ -50,7 +50,8 @@ def main(argv=None):
             return mlk.gemv_layoutA(A, X)
         if a.dtype == "fp8":
             if args:
-                return mlk.gemm_layoutA_soft_fp8_wapper(A, None, X, m, n, k, kernelParam1=args[0], kernelParam2=args[1], kernelParam3=args[2])
+                return mlk.gemm_layoutA_soft_fp8_wapper(A, None, X, m, n, k, kernelParam1=args[0], kernelParam2=args[1], kernelParam3=args[2],
+                                                        kernelId=args[3] if len(args) > 3 else 1)
             return mlk.gemm_layoutA_soft_fp8(A, None, X)
         fn = getattr(mlk, a.op + ("_wapper" if args else ""))
         xin = XB if XB is not None else X

@@ -106,11 +106,21 @@ def candidates(kind, m, n, k):
     """Launch-argument tuples to try for one table key (GeMV: blockDimX, kernelId, p1, p2; GEMM: kernelId, p1, p2, p3)."""
     fp8 = kind in ("a_fp8", "gemv_fp8")
     if kind.startswith("gemv"):
-        return [(t, kid, rg, sk) for t, kid, rg, sk in itertools.product([64, 128, 256], [1, 2], [1, 2], [1, 2, 4, 8])
-                if not (fp8 and kid == 2) and m % (16 * rg) == 0]
+        cands = [(t, kid, rg, sk) for t, kid, rg, sk in itertools.product([64, 128, 256], [1, 2], [1, 2], [1, 2, 4, 8])
+                 if not (fp8 and kid == 2) and m % (16 * rg) == 0]
+        if fp8 and m % 128 == 0 and k % 64 == 0:
+            # KernelId 3: tcgen05 pipeline for e4m3 weights, (raw ring stages, cluster size)
+            cands += [(256, 3, st, ck) for st in (2, 3, 4, 6, 8) for ck in range(1, 9)
+                      if (m // 128) * ck <= 148 * min(4, max(1, (227 * 1024) // (max(st * 8192, 8192) + 4096 + 2048)))]
+        return cands
     # kernelId 1 / 3 / 4: the warp-level kernel with 8 / 4 / 2 warps per CTA
     cands = [(kid, rg, wm, sk) for kid, rg, wm, sk in itertools.product([1, 3, 4], [1, 2], [1, 2, 4, 8], [1, 2, 4])
              if m % (16 * rg * wm) == 0 and wm <= {1: 8, 3: 4, 4: 2}[kid]]
+    if kind == "a_fp8" and n <= 64:
+        # tcgen05 pipeline for e4m3 weights: (unused, raw ring stages, cluster size)
+        np_ = 16 if n <= 16 else (32 if n <= 32 else 64)
+        cands += [(2, 1, st, ck) for st in (2, 3, 4, 6, 8) for ck in range(1, 9)
+                  if (m // 128) * ck <= 148 * min(4, max(1, (227 * 1024) // (max(st * 8192, np_ * 512) + 2 * np_ * 128 + 2048)))]
     if kind == "a" and n <= 4:
         cands += [(kid, rg, 0, sk) for kid, rg, sk in itertools.product([5, 6, 7], [1, 2], [1, 2, 4]) if m % (16 * rg) == 0]
     if kind == "a" and n <= 64:

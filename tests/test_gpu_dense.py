@@ -196,6 +196,44 @@ def test_gemm_soft_fp8(repacked):
                 assert_close(mlk.gemm_layoutA_linear(A, X.to(dev), scale_matrix=scale.to(dev)), want_s, "linear fp8")
 
 
+@pytest.mark.parametrize("repacked", [False, True])
+def test_soft_fp8_tcgen05_pipeline(repacked):
+    """kernelId 2 (GEMM) / 3 (GeMV) with e4m3 weights: TMA -> decode in shared memory -> tcgen05, cluster split-K."""
+    dev = require_gpu()
+    for (m, k) in [(128, 128), (256, 384), (512, 1024), (1024, 4096)]:
+        W8 = rand_e4m3((m, k), 170 + m)
+        A = mlk.layoutA(W8.to(dev))
+        if repacked:
+            A = mlk.fp8_weight_repack(A)
+        bias = randn((1, m), 171, 1.0, torch.bfloat16)
+        for n in [1, 7, 16, 17, 32, 48, 64]:
+            X = randn((n, k), 172 + n, 1.0, torch.bfloat16)
+            want = odense.gemm_ref(X, W8.to(torch.bfloat16))
+            for stages, ck in [(2, 1), (3, 2), (4, 4), (6, 3), (8, 8)]:
+                if ck > k // 64:
+                    continue
+                C = mlk.gemm_layoutA_soft_fp8_wapper(A, None, X.to(dev), m, n, k, kernelParam1=1, kernelParam2=stages,
+                                                     kernelParam3=ck, kernelId=2, fp8_repacked=repacked)
+                assert_close(C, want, f"fp8 tcgen05 m={m} k={k} n={n} stages={stages} cluster={ck}")
+            C = mlk.gemm_layoutA_soft_fp8_wapper(A, None, X.to(dev), m, n, k, alpha=0.5, kernelParam2=4, kernelParam3=2,
+                                                 kernelId=2, bias=bias.to(dev), fp8_repacked=repacked)
+            assert_close(C, odense.gemm_ref(X, W8.to(torch.bfloat16), alpha=0.5, bias=bias), f"fp8 tcgen05 bias m={m} n={n}")
+        x = randn((1, k), 173, 1.0, torch.bfloat16)
+        for stages, ck in [(2, 2), (4, 1), (8, 2)]:
+            y = mlk.gemv_layoutA_wapper(A, x.to(dev), m, k, kernelId=3, kernelParam1=stages, kernelParam2=ck,
+                                        fp8_repacked=repacked)
+            assert_close(y, odense.gemm_ref(x, W8.to(torch.bfloat16)), f"gemv fp8 tcgen05 m={m} k={k} {stages},{ck}")
+    # bit-identical from run to run; block scales are refused (they stay on the warp-level kernel)
+    X = randn((40, 4096), 174, 1.0, torch.bfloat16).to(dev)
+    ref = mlk.gemm_layoutA_soft_fp8_wapper(A, None, X, 1024, 40, 4096, kernelParam2=4, kernelParam3=4, kernelId=2, fp8_repacked=repacked)
+    for _ in range(3):
+        assert torch.equal(ref, mlk.gemm_layoutA_soft_fp8_wapper(A, None, X, 1024, 40, 4096, kernelParam2=4, kernelParam3=4,
+                                                                 kernelId=2, fp8_repacked=repacked))
+    scale = torch.ones(8, 32, device=dev)
+    with pytest.raises(RuntimeError, match="block scales"):
+        mlk.gemm_layoutA_soft_fp8_wapper(A, scale, X, 1024, 40, 4096, kernelParam2=4, kernelParam3=4, kernelId=2)
+
+
 def test_gemm_errors_and_determinism():
     dev = require_gpu()
     W, A = _weights(256, 256, 80, torch.bfloat16, dev)
