@@ -39,9 +39,9 @@ if str(ROOT) not in sys.path:
 
 TOKENS = [1, 2, 4, 8, 16, 32, 64]
 SHAPES = [(4096, 4096), (14336, 4096), (4096, 14336)]
-# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, ncu captures of the three dense kernels on the
-# 14336 x 4096 weight: 123.4/117.5, 122.0/117.8, 123.1/119.8
-NCU_TRAFFIC_RATIO = 1.04
+# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, ncu captures of the dense kernels on the
+# 117.4 MB weights: CUDA-core n=1 123.4/117.5, tcgen05 cluster n=16 121.6/118.0, n=64 122.9/119.8
+NCU_TRAFFIC_RATIO = 1.03
 NOMINAL_HBM_GBS = 8000.0
 
 
@@ -284,10 +284,10 @@ def run_ours(args):
             "gpu_launches": len(order) * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_RATIO * per_rank_bytes / len(order),
-                         "traffic_source": "average bytes per launch = algorithmic bytes x 1.04, the dram read+write / "
-                                           "algorithmic ratio ncu measured on the three dense kernels (profiles/dense_kernels_14336x4096.md)",
+                         "traffic_source": "average bytes per launch = algorithmic bytes x 1.03, the dram read+write / "
+                                           "algorithmic ratio ncu measured on the dense kernels (profiles/dense_kernels_bf16.md)",
                          "peak_source": f"of {peak_kind}",
-                         "kernel": "dense_mma_kernel / dense_umma_kernel / gemv_simt_kernel (21 launches, averaged)"},
+                         "kernel": "dense_umma_kernel (17 launches) / gemv_simt_kernel (3) / dense_mma_kernel (1-2), averaged"},
         }
         if world == 1 and not args.no_moe:
             # second half of the metric: fused-MoE layer time (router + alignment + experts + combine), CUDA-graph

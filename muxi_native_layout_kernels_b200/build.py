@@ -31,6 +31,7 @@ SOURCES = [
     "moe_router.cu",
     "moe_align.cu",
     "moe_experts.cu",
+    "moe_umma.cu",
     "moe_exchange.cu",
     "selector.cpp",
 ]

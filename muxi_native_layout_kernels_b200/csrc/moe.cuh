@@ -43,10 +43,20 @@ struct MoeParams {
     int experts_map_len;
     float* scratch;               // optional [T*topk, H] fp32 for the deterministic combine
     long long scratch_bytes;
-    int nt, wm1, sk1, rg, wm2, sk2;   // tuning (0 = choose by shape): token tiles, GEMM1 row warps / split-K, GEMM2 row groups / row warps / split-K
+    int nt, wm1, sk1, rg, wm2, sk2;   // tuning (0 = choose by shape): token tiles, GEMM1 row warps / split-K, GEMM2 row groups / row warps / split-K;
+                                      // wm1 = 100 + s1 and wm2 = 100 + s2 select the tcgen05 kernels (16-bit weights, combine scratch given)
+                                      // with s1 / s2 ring stages and sk1 / sk2 CTAs per cluster
 };
 
 int launch_fused_experts(const MoeParams& p, cudaStream_t s);
+
+// tcgen05 expert GEMMs (moe_umma.cu): gather of the routed token rows into position order, and one grouped GEMM
+// (mode 1: gate/up + SiLU*up into the [position, I] activation; mode 2: routing-weighted fp32 rows per slot).
+int launch_moe_gather_positions(const void* x, const int32_t* sorted, const int32_t* cumsum, int E, int topk, int n_slots,
+                                int H, void* xg, long long max_pos, cudaStream_t s);
+int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, const void* X, long long x_rows, void* out,
+                    const int4* worklist, const int32_t* sorted, const void* topk_weights, int n_slots, int np, int stages,
+                    int cluster_k, int max_items, int* status, cudaStream_t s);
 int launch_fused_experts_static(const MoeParams& p, cudaStream_t s);   // combine scratch in a built-in device array
 
 // Expert-parallel exchange helpers (moe_exchange.cu).

@@ -274,7 +274,8 @@ int pick_sk(int ctas, int chunks, int wk) {
 
 }  // namespace
 
-int launch_fused_experts(const MoeParams& m, cudaStream_t s) {
+int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
+    MoeParams m = m0;
     if (!m.w1 || !m.w2 || !m.x || !m.topk_ids || !m.topk_weights || !m.sorted_token_ids || !m.cumsum ||
         !m.padded_num_experts || !m.experts_ids || !m.C || !m.y)
         return fail(kInvalidArg, "fused_experts_compute: null pointer");
@@ -305,12 +306,26 @@ int launch_fused_experts(const MoeParams& m, cudaStream_t s) {
     const int block_slots = nt_tiles * 8;
     const int max_items = (int)std::min<long long>(slots, (long long)std::min<long long>(m.E, slots) + slots / block_slots);
 
+    // tcgen05 path (moe_umma.cu): asked for by the tuning arguments, 16-bit weights, fp32 combine scratch present.
+    // Its buffers are indexed by position (padded, at most slots + E * (mbs - 1) rows): the [position, I] activation
+    // takes the front of C, the gathered token rows [position, H] borrow the combine scratch until the second GEMM
+    // overwrites it, and the work list moves to the very end of C.
+    const long long max_pos = slots + (long long)m.E * (mbs - 1);
+    const size_t c_bytes = (size_t)slots * 2 * m.I * 2;
+    const size_t wl_bytes = 16 * (size_t)(max_items + 1);
+    bool umma = wt != kE4M3 && m.wm1 >= 100 && m.wm2 >= 100 && m.scratch != nullptr && m.I % 128 == 0 && m.H % 128 == 0 &&
+                (size_t)max_pos * m.I * 2 + wl_bytes + 16 <= c_bytes &&
+                (long long)max_pos * m.H * 2 <= m.scratch_bytes && (long long)slots * m.H * 4 <= m.scratch_bytes;
+
+    if (!umma && (m.wm1 >= 100 || m.wm2 >= 100)) {
+        // tuned for the tcgen05 kernels but this call cannot use them: the warp-level kernels choose for themselves
+        m.wm1 = m.sk1 = m.rg = m.wm2 = m.sk2 = 0;
+    }
+
     // work list lives in the half of C that the fused activation does not need
     uint8_t* cbytes = reinterpret_cast<uint8_t*>(m.C);
-    size_t wl_off = (size_t)slots * m.I * 2;
-    wl_off = (wl_off + 15) & ~(size_t)15;
-    const size_t c_bytes = (size_t)slots * 2 * m.I * 2;
-    if (wl_off + 16 * (size_t)(max_items + 1) > c_bytes)
+    size_t wl_off = umma ? ((c_bytes - wl_bytes) & ~(size_t)15) : (((size_t)slots * m.I * 2 + 15) & ~(size_t)15);
+    if (wl_off + wl_bytes > c_bytes)
         return fail(kInvalidArg, "fused_experts_compute: workspace C too small for the work list");
     void* worklist = cbytes + wl_off;
 
@@ -318,6 +333,30 @@ int launch_fused_experts(const MoeParams& m, cudaStream_t s) {
                                   m.padded_num_experts, m.experts_ids, m.experts_map, m.experts_map_len, s, worklist,
                                   block_slots))
         return st;
+
+    if (umma) {
+        const int np = block_slots < 16 ? 16 : block_slots;
+        if (int st = launch_moe_gather_positions(m.x, m.sorted_token_ids, m.cumsum, m.E, m.topk, (int)slots, m.H, m.scratch,
+                                                 max_pos, s))
+            return st;
+        if (int st = launch_moe_umma(1, wt, m.w1, m.E, m.I, m.H, m.scratch, max_pos, m.C, reinterpret_cast<const int4*>(worklist),
+                                     m.sorted_token_ids, m.topk_weights, (int)slots, np, m.wm1 - 100, m.sk1 > 0 ? m.sk1 : 1,
+                                     max_items, nullptr, s))
+            return st;
+        if (int st = launch_moe_umma(2, wt, m.w2, m.E, m.H, m.I, m.C, max_pos, m.scratch, reinterpret_cast<const int4*>(worklist),
+                                     m.sorted_token_ids, m.topk_weights, (int)slots, np, m.wm2 - 100, m.sk2 > 0 ? m.sk2 : 1,
+                                     max_items, nullptr, s))
+            return st;
+        const long long total = (long long)m.T * (m.H / 8);
+        const int grid = (int)std::min<long long>((total + 255) / 256, 148LL * 8);
+        if (wt == kFP16)
+            moe_combine_kernel<kFP16><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
+                                                          m.topk, m.H, m.y);
+        else
+            moe_combine_kernel<kBF16><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
+                                                          m.topk, m.H, m.y);
+        return check_launch("moe_combine");
+    }
 
     // ---- GEMM1: act[slot, 0..I) = silu(x W1_gate^T) * (x W1_up^T)
     MoeGemmParams g1{};

@@ -1,0 +1,343 @@
+// Fused-MoE expert GEMMs on the 5th-generation tensor cores (16-bit weights, 16..64 slots per work item).
+//
+// Same tile and pipeline as dense_umma.cu in cluster mode: 128 weight rows are the UMMA M dimension, the slots of one
+// work item (one expert, up to 64 of its routed slots) the N dimension, TMA feeds a shared-memory ring, one thread
+// issues tcgen05.mma into tensor memory, the k range is split over the CTAs of a cluster and the partial tiles are
+// added through distributed shared memory in a fixed order.  What is specific to the MoE:
+//   * the grid is (row tiles, cluster, work items); the work list is the one the alignment kernel writes, items past
+//     its length leave at once;
+//   * the weight tensor map covers all experts ([E * rows, k]); the item's expert selects the tile rows;
+//   * the activation rows of an item must be contiguous for the TMA tile, so a gather pass first copies the routed
+//     token rows into position order (position = index into sorted_token_ids);
+//   * MODE 1 (first GEMM): every CTA holds the gate tile and the matching up tile of W1 (two accumulators fed by the
+//     same token tile) and writes silu(gate) * up of the fp32 sums as the [position, I] activation;
+//   * MODE 2 (second GEMM): reads that activation by position, multiplies by the slot's routing weight and writes the
+//     fp32 row of the slot into the combine scratch (the fixed-order combine kernel adds a token's top-k rows).
+// Slots beyond the item's count inside the 16/32/64-wide tile belong to other items: they are computed and dropped.
+//
+// Role in the reference: fused_moe_first/second_group_gemm_kernel (csrc/moe_kernels/group_gemm_first.h:355,
+// group_gemm_second.h:356) for the token counts where its CTA-tile kernels are used.
+#include <algorithm>
+
+#include "moe.cuh"
+#include "umma_common.cuh"
+
+namespace mlk {
+
+namespace {
+
+using namespace umma;
+
+struct MoeUmmaParams {
+    const int4* worklist;       // [0] = {n_items,..}; then {expert, first position, slots, 0}
+    const int32_t* sorted;      // slot id of every position; >= n_slots marks padding
+    const void* topk_weights;   // [n_slots] activation dtype (MODE 2)
+    void* out;                  // MODE 1: act [positions, rows] 16-bit; MODE 2: scratch [n_slots, rows] fp32
+    int rows;                   // output features: I (MODE 1) or H (MODE 2)
+    int tiles_per_expert;       // weight row tiles of one expert in the tensor map: 2I/128 (MODE 1) or H/128
+    int up_tile_offset;         // MODE 1: I/128
+    int kblocks;
+    int n_slots;
+    int* status;
+};
+
+template <int WT, int NP, int STAGES, int MODE>
+__global__ void __launch_bounds__(192, 2) moe_umma_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                          const __grid_constant__ CUtensorMap map_x,
+                                                          const MoeUmmaParams p, const int static_weights) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr int NA = MODE == 1 ? 2 : 1;               // weight tiles (and accumulators) per CTA
+    constexpr int kBBytes = NP * 128;
+    constexpr int kStageBytes = NA * kABytes + kBBytes;
+    constexpr uint32_t kTmemCols = NA * NP < 32 ? 32 : NA * NP;
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = blockIdx.x, rank = blockIdx.y, SK = gridDim.y;
+
+    // the work list comes from the alignment kernel earlier in the stream: nothing can start before it
+    pdl_wait();
+    pdl_launch_dependents();
+    const int n_items = p.worklist[0].x;
+    if ((int)blockIdx.z >= n_items) return;             // uniform over the cluster (clusters span y only)
+    const int4 item = p.worklist[1 + blockIdx.z];
+    const int expert = item.x, pos0 = item.y, nslots = item.z;
+
+    const int KB = p.kblocks;
+    const int kb0 = (int)((long long)KB * rank / SK), kb1 = (int)((long long)KB * (rank + 1) / SK);
+    const int nunits = kb1 - kb0;
+    const int a_tile = expert * p.tiles_per_expert + tile;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* const base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    const uint32_t acc_full = bar0 + 8u * (2 * STAGES);
+    auto a_addr = [&](int s, int which) { return base + s * kStageBytes + which * kABytes; };
+    auto b_addr = [&](int s) { return base + s * kStageBytes + NA * kABytes; };
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(acc_full, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+
+    int issued = 0;
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer ----
+        for (int i = 0; i < nunits; ++i) {
+            const int s = i % STAGES;
+            if (i >= STAGES && !mbar_wait(empty_bar(s), ((i / STAGES) - 1) & 1)) {
+                abort_flag = 1;
+                if (p.status) atomicExch(p.status, 1);
+            }
+            if (abort_flag) break;
+            mbar_expect_tx(full_bar(s), kStageBytes);
+            tma_load_4d(a_addr(s, 0), &map_a, full_bar(s), 0, (kb0 + i) * (kBlockK / 8), a_tile * (kTileM / 16), 0);
+            if constexpr (MODE == 1)
+                tma_load_4d(a_addr(s, 1), &map_a, full_bar(s), 0, (kb0 + i) * (kBlockK / 8),
+                            (a_tile + p.up_tile_offset) * (kTileM / 16), 0);
+            tma_load_2d(b_addr(s), &map_x, full_bar(s), (kb0 + i) * kBlockK, pos0);
+            ++issued;
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        constexpr uint32_t idesc = instr_desc<WT, NP>();
+        for (int i = 0; i < nunits; ++i) {
+            const int s = i % STAGES;
+            if (abort_flag || !mbar_wait(full_bar(s), (i / STAGES) & 1)) {
+                if (!abort_flag && p.status) atomicExch(p.status, 2);
+                abort_flag = 1;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int kk = 0; kk < kBlockK / 16; ++kk) {
+                const uint64_t db = smem_desc(b_addr(s) + kk * 32, 16, 1024, 2);
+#pragma unroll
+                for (int w = 0; w < NA; ++w) {
+                    const uint64_t da = smem_desc(a_addr(s, w) + kk * 256, 128, 1024, 0);
+                    umma_f16(tmem + w * NP, da, db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+                }
+            }
+            umma_commit(empty_bar(s));
+        }
+        if (!abort_flag) umma_commit(acc_full);
+    } else if (warp >= 2) {
+        // ---- epilogue warps: accumulators -> fp32 partial tiles [which][slot][accumulator row] in the idle ring ----
+        if (lane == 0 && (abort_flag || !mbar_wait(acc_full, 0))) {
+            if (!abort_flag && p.status) atomicExch(p.status, 3);
+            abort_flag = 1;
+        }
+        __syncwarp();
+        if (!abort_flag) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int quad = warp & 3, lrow = quad * 32 + lane;
+            float* const red = reinterpret_cast<float*>(base_ptr);
+#pragma unroll
+            for (int c0 = 0; c0 < NA * NP; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + c0, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; ++i) red[(c0 + i) * kTileM + lrow] = __uint_as_float(r[i]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        }
+    }
+    __syncwarp();
+
+    // ---- every CTA of the cluster adds one slice of accumulator rows over all ranks (descending rank) ----
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (warp >= 2) {
+        const int etid = tid - 64;
+        const int r0 = kTileM * rank / SK, rows = kTileM * (rank + 1) / SK - r0;
+        uint32_t remote[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[q]) : "r"(base), "r"(q < SK ? q : 0));
+        auto cluster_sum = [&](uint32_t off) {
+            float t[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                t[q] = 0.f;
+                if (q < SK) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(t[q]) : "r"(remote[q] + off) : "memory");
+            }
+            float acc = 0.f;
+            bool first = true;
+#pragma unroll
+            for (int q = 7; q >= 0; --q) {
+                if (q < SK) {
+                    acc = first ? t[q] : acc + t[q];
+                    first = false;
+                }
+            }
+            return acc;
+        };
+        const int total = nslots * rows;
+        for (int idx = etid; idx < total; idx += 128) {
+            const int c = idx / rows, rho = r0 + idx - c * rows;
+            // accumulator row rho holds weight row 16*(rho%64 / 8) + 8*(rho / 64) + rho%8 of the tile
+            const int row = tile * kTileM + ((rho & 63) >> 3) * 16 + (rho >> 6) * 8 + (rho & 7);
+            const uint32_t off = (uint32_t)(c * kTileM + rho) * 4u;
+            if constexpr (MODE == 1) {
+                const float gate = cluster_sum(off);
+                const float up = cluster_sum(off + (uint32_t)NP * kTileM * 4u);
+                const float v = gate / (1.f + __expf(-gate)) * up;
+                const size_t o = (size_t)(pos0 + c) * p.rows + row;
+                if constexpr (WT == kFP16)
+                    reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(v);
+                else
+                    reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
+            } else {
+                const int slot = p.sorted[pos0 + c];
+                if (slot < p.n_slots) {
+                    const float w = load_scalar16<WT>(p.topk_weights, slot);
+                    reinterpret_cast<float*>(p.out)[(size_t)slot * p.rows + row] = w * cluster_sum(off);
+                }
+            }
+        }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+
+    // ---- teardown ----
+    if (warp == 0 && lane == 0 && abort_flag) {
+        for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(full_bar(i % STAGES), (i / STAGES) & 1);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// Routed token rows in position order: xg[pos] = x[sorted[pos] / topk], zero rows for padding positions.
+__global__ void __launch_bounds__(256) moe_gather_positions_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ sorted,
+                                                                   const int32_t* __restrict__ cumsum, int E, int topk,
+                                                                   int n_slots, int h8, uint4* __restrict__ xg, long long max_pos) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long n_pos = min((long long)cumsum[E], max_pos);
+    const long long total = n_pos * h8;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long pos = i / h8;
+        const int u = (int)(i - pos * h8);
+        const int slot = sorted[pos];
+        xg[i] = (slot < n_slots) ? x[(size_t)(slot / topk) * h8 + u] : make_uint4(0, 0, 0, 0);
+    }
+}
+
+// Weight tile map over all experts: the 4-D view of dense_umma.cu with E * rows rows.
+bool make_map_w(CUtensorMap* map, const void* W, long long rows_total, int k, int wt) {
+    const cuuint64_t dims[4] = {64, (cuuint64_t)(k / 8), (cuuint64_t)(rows_total / 16), 2};
+    const cuuint64_t strides[3] = {256, (cuuint64_t)16 * k * 2, 128};
+    const cuuint32_t box[4] = {64, kBlockK / 8, kTileM / 16, 2};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return encode_fn()(map, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                       const_cast<void*>(W), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int WT, int NP, int MODE>
+const void* moe_kernel_for_stages(int stages) {
+    switch (stages) {
+        case 2: return reinterpret_cast<const void*>(moe_umma_kernel<WT, NP, 2, MODE>);
+        case 3: return reinterpret_cast<const void*>(moe_umma_kernel<WT, NP, 3, MODE>);
+        case 4: return reinterpret_cast<const void*>(moe_umma_kernel<WT, NP, 4, MODE>);
+        case 6: return reinterpret_cast<const void*>(moe_umma_kernel<WT, NP, 6, MODE>);
+    }
+    return nullptr;
+}
+template <int WT, int MODE>
+const void* moe_kernel_for(int np, int stages) {
+    switch (np) {
+        case 16: return moe_kernel_for_stages<WT, 16, MODE>(stages);
+        case 32: return moe_kernel_for_stages<WT, 32, MODE>(stages);
+        case 64: return moe_kernel_for_stages<WT, 64, MODE>(stages);
+    }
+    return nullptr;
+}
+
+}  // namespace
+
+int launch_moe_gather_positions(const void* x, const int32_t* sorted, const int32_t* cumsum, int E, int topk, int n_slots,
+                                int H, void* xg, long long max_pos, cudaStream_t s) {
+    if (H % 8 != 0) return fail(kInvalidArg, "moe gather: H must be a multiple of 8");
+    const long long total = max_pos * (H / 8);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)std::min<long long>((total + 255) / 256, 148LL * 8));
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    cfg.attrs = attr;
+    cfg.numAttrs = launch_attrs(attr, 1);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, moe_gather_positions_kernel, reinterpret_cast<const uint4*>(x), sorted, cumsum, E,
+                                       topk, n_slots, H / 8, reinterpret_cast<uint4*>(xg), max_pos);
+    if (e != cudaSuccess) return fail(kCudaError, "moe gather launch: %s", cudaGetErrorString(e));
+    return kOk;
+}
+
+// One grouped GEMM.  mode 1: W = w1 [E, 2I, k=H], X = gathered tokens [max_pos, H], out = act [max_pos, I];
+// mode 2: W = w2 [E, H, k=I], X = act [max_pos, I], out = scratch [n_slots, H] fp32.
+int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, const void* X, long long x_rows, void* out,
+                    const int4* worklist, const int32_t* sorted, const void* topk_weights, int n_slots, int np, int stages,
+                    int cluster_k, int max_items, int* status, cudaStream_t s) {
+    if (wt != kBF16 && wt != kFP16) return fail(kUnsupported, "moe (tcgen05): 16-bit weights only");
+    if (rows % kTileM != 0 || k % kBlockK != 0) return fail(kInvalidArg, "moe (tcgen05): sizes must be multiples of 128 (rows) and 64 (k)");
+    if (cluster_k < 1 || cluster_k > 8 || cluster_k > k / kBlockK) return fail(kInvalidArg, "moe (tcgen05): cluster size %d out of range", cluster_k);
+    if (encode_fn() == nullptr) return fail(kUnsupported, "moe (tcgen05): cuTensorMapEncodeTiled is not available");
+    const void* kern = nullptr;
+    if (mode == 1) kern = wt == kFP16 ? moe_kernel_for<kFP16, 1>(np, stages) : moe_kernel_for<kBF16, 1>(np, stages);
+    else kern = wt == kFP16 ? moe_kernel_for<kFP16, 2>(np, stages) : moe_kernel_for<kBF16, 2>(np, stages);
+    if (kern == nullptr) return fail(kInvalidArg, "moe (tcgen05): token tile %d / stages %d not built", np, stages);
+    const int na = mode == 1 ? 2 : 1;
+    const size_t smem = std::max((size_t)stages * (na * kABytes + np * 128), (size_t)na * np * 512) + 1024;
+    if (smem > 227 * 1024) return fail(kUnsupported, "moe (tcgen05): %d stages do not fit in shared memory", stages);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(kCudaError, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    const long long w_rows = (long long)E * (mode == 1 ? 2 * rows : rows);
+    CUtensorMap ma, mx;
+    if (!make_map_w(&ma, W, w_rows, k, wt)) return fail(kUnsupported, "moe (tcgen05): weight tensor map rejected");
+    if (!make_map_x(&mx, X, (int)x_rows, k, wt, np)) return fail(kUnsupported, "moe (tcgen05): activation tensor map rejected");
+    MoeUmmaParams mp{};
+    mp.worklist = worklist; mp.sorted = sorted; mp.topk_weights = topk_weights; mp.out = out;
+    mp.rows = rows;
+    mp.tiles_per_expert = (mode == 1 ? 2 * rows : rows) / kTileM;
+    mp.up_tile_offset = rows / kTileM;
+    mp.kblocks = k / kBlockK;
+    mp.n_slots = n_slots;
+    mp.status = status;
+    int static_weights = option(kOptStaticWeights);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(rows / kTileM), (unsigned)cluster_k, (unsigned)max_items);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    cfg.attrs = attr;
+    cfg.numAttrs = launch_attrs(attr, cluster_k);
+    void* args[4] = {&ma, &mx, &mp, &static_weights};
+    e = cudaLaunchKernelExC(&cfg, kern, args);
+    if (e != cudaSuccess) return fail(kCudaError, "moe_umma launch: %s", cudaGetErrorString(e));
+    return kOk;
+}
+
+}  // namespace mlk

@@ -157,7 +157,7 @@ def _kernel_routing(x, logits, topk, renorm, groups, kept, bias, score, dev):
 
 
 def _moe_compare(x, w1, w2, logits, topk, what, renorm=True, groups=1, kept=1, bias=None, score="softmax", fp8=False,
-                 scales=None, repack=False, dev=None):
+                 scales=None, repack=False, dev=None, tune=None):
     dev = dev or require_gpu()
     E = w1.shape[0]
     w1d, w2d = mlk.layoutA(w1.to(dev)), mlk.layoutA(w2.to(dev))
@@ -169,7 +169,7 @@ def _moe_compare(x, w1, w2, logits, topk, what, renorm=True, groups=1, kept=1, b
     y = planC_moe(x.to(dev), w1d, w2d, logits.to(dev), topk, renorm, use_grouped_topk=groups > 1,
                   num_expert_group=groups, topk_group=kept, w1_scale=s1, w2_scale=s2,
                   block_shape=[128, 128] if fp8 else None, gating_bias=None if bias is None else bias.to(dev),
-                  score_func=score, soft_fp8=fp8, fp8_repacked=repack)
+                  score_func=score, soft_fp8=fp8, fp8_repacked=repack, tune=tune)
     torch.cuda.synchronize()
     # oracle weights: e4m3 (+ scales) dequantised as the reference's test does (scale_whole_tensor)
     if fp8 and scales is not None:
@@ -217,6 +217,23 @@ def test_moe_16bit_random(dt, T):
     w2 = randn((E, H, I), 502, 0.05, DT[dt])
     logits = randn((T, E), 503 + T, 1.0, DT[dt])
     _moe_compare(x, w1, w2, logits, topk, f"moe {dt} T={T}")
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+@pytest.mark.parametrize("T", [40, 64, 100, 257, 600])
+def test_moe_16bit_tcgen05_expert_gemms(dt, T):
+    """tune = (token tiles, 100 + stages, cluster, -, 100 + stages, cluster): the tcgen05 expert GEMMs (gathered token
+    rows, gate/up tile pair with fused SiLU*up, routing-weighted fp32 rows), same oracle and tolerance."""
+    E, topk, H, I = 8, 2, 256, 384
+    x = randn((T, H), 700 + T, 1.0, DT[dt])
+    w1 = randn((E, 2 * I, H), 701, 0.05, DT[dt])
+    w2 = randn((E, H, I), 702, 0.05, DT[dt])
+    logits = randn((T, E), 703 + T, 1.0, DT[dt])
+    for tune in [(2, 102, 1, 0, 102, 1), (4, 103, 2, 0, 104, 3), (8, 104, 4, 0, 106, 6), (1, 102, 2, 0, 103, 2)]:
+        y = _moe_compare(x, w1, w2, logits, topk, f"moe tcgen05 {dt} T={T} tune={tune}", tune=tune)
+        y0 = _moe_compare(x, w1, w2, logits, topk, f"moe warp-level {dt} T={T}", tune=(tune[0], 2, 1, 1, 2, 1))
+        # both paths sum the same fp32 products in different orders: results agree to rounding
+        assert_close(y, y0.cpu(), f"tcgen05 vs warp-level {dt} T={T} tune={tune}", scale_atol=True)
 
 
 @pytest.mark.parametrize("T", [1, 8, 32, 130])
