@@ -18,7 +18,8 @@ int launch_moe_align(int T, int E, int topk, int mbs, const int32_t* topk_ids, i
                      int block_slots = 0);
 
 // Work list written by the alignment kernel into the spare half of the caller's workspace C:
-//   int32 header[4] = {n_items, 0, 0, 0}; then n_items x int4 {expert, first position in sorted_token_ids, slots, 0}
+//   int32 header[4] = {n_items, 0, 0, 0}; then n_items x int4 {expert, first position in sorted_token_ids, slots,
+//   first compact position}: compact positions number the routed slots expert by expert without the padding
 struct MoeWorkHeader {
     int n_items, pad0, pad1, pad2;
 };
@@ -52,8 +53,8 @@ int launch_fused_experts(const MoeParams& p, cudaStream_t s);
 
 // tcgen05 expert GEMMs (moe_umma.cu): gather of the routed token rows into position order, and one grouped GEMM
 // (mode 1: gate/up + SiLU*up into the [position, I] activation; mode 2: routing-weighted fp32 rows per slot).
-int launch_moe_gather_positions(const void* x, const int32_t* sorted, const int32_t* cumsum, int E, int topk, int n_slots,
-                                int H, void* xg, long long max_pos, cudaStream_t s);
+int launch_moe_gather_positions(const void* x, const int32_t* sorted, const int4* worklist, int topk, int H, void* xg,
+                                int max_items, cudaStream_t s);
 int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, const void* X, long long x_rows, void* out,
                     const int4* worklist, const int32_t* sorted, const void* topk_weights, int n_slots, int np, int stages,
                     int cluster_k, int max_items, int* status, cudaStream_t s);

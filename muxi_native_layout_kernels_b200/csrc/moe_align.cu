@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
     __shared__ int start[kMaxExperts];    // padded exclusive prefix
     __shared__ int cursor[kMaxExperts];
     __shared__ int item0[kMaxExperts];    // exclusive prefix of work items
-    __shared__ int warp_tot[32], warp_tot2[32];
+    __shared__ int warp_tot[32], warp_tot2[32], warp_tot3[32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     for (int e = tid; e < E; e += blockDim.x) cnt[e] = 0;
@@ -49,33 +49,37 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
     const int c = (tid < E) ? cnt[tid] : 0;
     const int padded = ((c + mbs - 1) / mbs) * mbs;
     const int items = (block_slots > 0) ? (c + block_slots - 1) / block_slots : 0;
-    int incl = padded, incl2 = items;
+    int incl = padded, incl2 = items, incl3 = c;      // incl3: unpadded ("compact") positions
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         const int v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
         const int v2 = __shfl_up_sync(0xFFFFFFFFu, incl2, o);
-        if (lane >= o) { incl += v; incl2 += v2; }
+        const int v3 = __shfl_up_sync(0xFFFFFFFFu, incl3, o);
+        if (lane >= o) { incl += v; incl2 += v2; incl3 += v3; }
     }
-    if (lane == 31) { warp_tot[warp] = incl; warp_tot2[warp] = incl2; }
+    if (lane == 31) { warp_tot[warp] = incl; warp_tot2[warp] = incl2; warp_tot3[warp] = incl3; }
     __syncthreads();
     if (warp == 0) {
-        int w = warp_tot[lane], w2 = warp_tot2[lane];
+        int w = warp_tot[lane], w2 = warp_tot2[lane], w3 = warp_tot3[lane];
         const int nw = blockDim.x >> 5;
-        if (lane >= nw) { w = 0; w2 = 0; }
+        if (lane >= nw) { w = 0; w2 = 0; w3 = 0; }
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const int v = __shfl_up_sync(0xFFFFFFFFu, w, o);
             const int v2 = __shfl_up_sync(0xFFFFFFFFu, w2, o);
-            if (lane >= o) { w += v; w2 += v2; }
+            const int v3 = __shfl_up_sync(0xFFFFFFFFu, w3, o);
+            if (lane >= o) { w += v; w2 += v2; w3 += v3; }
         }
         warp_tot[lane] = w;
         warp_tot2[lane] = w2;
+        warp_tot3[lane] = w3;
     }
     __syncthreads();
     const int base = (warp > 0) ? warp_tot[warp - 1] : 0;
     const int base2 = (warp > 0) ? warp_tot2[warp - 1] : 0;
     const int excl = base + incl - padded;
     const int excl2 = base2 + incl2 - items;
+    const int excl3 = ((warp > 0) ? warp_tot3[warp - 1] : 0) + incl3 - c;
     if (tid < E) {
         start[tid] = excl;
         cursor[tid] = excl;
@@ -84,7 +88,8 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
         for (int b = excl / mbs; b < (excl + padded) / mbs; ++b) block_expert[b] = tid;
         if (worklist != nullptr)
             for (int j = 0; j < items; ++j)
-                worklist[1 + excl2 + j] = make_int4(tid, excl + j * block_slots, min(block_slots, c - j * block_slots), 0);
+                worklist[1 + excl2 + j] = make_int4(tid, excl + j * block_slots, min(block_slots, c - j * block_slots),
+                                                    excl3 + j * block_slots);
     }
     if (tid == E - 1) {
         cumsum[E] = excl + padded;

@@ -307,15 +307,13 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
     const int max_items = (int)std::min<long long>(slots, (long long)std::min<long long>(m.E, slots) + slots / block_slots);
 
     // tcgen05 path (moe_umma.cu): asked for by the tuning arguments, 16-bit weights, fp32 combine scratch present.
-    // Its buffers are indexed by position (padded, at most slots + E * (mbs - 1) rows): the [position, I] activation
-    // takes the front of C, the gathered token rows [position, H] borrow the combine scratch until the second GEMM
-    // overwrites it, and the work list moves to the very end of C.
-    const long long max_pos = slots + (long long)m.E * (mbs - 1);
+    // Its buffers are indexed by compact position (the routed slots expert by expert, no padding): the [slots, I]
+    // activation takes the front of C like the warp-level path's, and the gathered token rows [slots, H] borrow the
+    // combine scratch until the second GEMM overwrites it.
     const size_t c_bytes = (size_t)slots * 2 * m.I * 2;
     const size_t wl_bytes = 16 * (size_t)(max_items + 1);
-    bool umma = wt != kE4M3 && m.wm1 >= 100 && m.wm2 >= 100 && m.scratch != nullptr && m.I % 128 == 0 && m.H % 128 == 0 &&
-                (size_t)max_pos * m.I * 2 + wl_bytes + 16 <= c_bytes &&
-                (long long)max_pos * m.H * 2 <= m.scratch_bytes && (long long)slots * m.H * 4 <= m.scratch_bytes;
+    const bool umma = wt != kE4M3 && m.wm1 >= 100 && m.wm2 >= 100 && m.scratch != nullptr && m.I % 128 == 0 &&
+                      m.H % 128 == 0 && (long long)slots * m.H * 4 <= m.scratch_bytes;
 
     if (!umma && (m.wm1 >= 100 || m.wm2 >= 100)) {
         // tuned for the tcgen05 kernels but this call cannot use them: the warp-level kernels choose for themselves
@@ -324,7 +322,7 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
 
     // work list lives in the half of C that the fused activation does not need
     uint8_t* cbytes = reinterpret_cast<uint8_t*>(m.C);
-    size_t wl_off = umma ? ((c_bytes - wl_bytes) & ~(size_t)15) : (((size_t)slots * m.I * 2 + 15) & ~(size_t)15);
+    const size_t wl_off = ((size_t)slots * m.I * 2 + 15) & ~(size_t)15;
     if (wl_off + wl_bytes > c_bytes)
         return fail(kInvalidArg, "fused_experts_compute: workspace C too small for the work list");
     void* worklist = cbytes + wl_off;
@@ -336,14 +334,14 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
 
     if (umma) {
         const int np = block_slots < 16 ? 16 : block_slots;
-        if (int st = launch_moe_gather_positions(m.x, m.sorted_token_ids, m.cumsum, m.E, m.topk, (int)slots, m.H, m.scratch,
-                                                 max_pos, s))
+        if (int st = launch_moe_gather_positions(m.x, m.sorted_token_ids, reinterpret_cast<const int4*>(worklist), m.topk, m.H,
+                                                 m.scratch, max_items, s))
             return st;
-        if (int st = launch_moe_umma(1, wt, m.w1, m.E, m.I, m.H, m.scratch, max_pos, m.C, reinterpret_cast<const int4*>(worklist),
+        if (int st = launch_moe_umma(1, wt, m.w1, m.E, m.I, m.H, m.scratch, slots, m.C, reinterpret_cast<const int4*>(worklist),
                                      m.sorted_token_ids, m.topk_weights, (int)slots, np, m.wm1 - 100, m.sk1 > 0 ? m.sk1 : 1,
                                      max_items, nullptr, s))
             return st;
-        if (int st = launch_moe_umma(2, wt, m.w2, m.E, m.H, m.I, m.C, max_pos, m.scratch, reinterpret_cast<const int4*>(worklist),
+        if (int st = launch_moe_umma(2, wt, m.w2, m.E, m.H, m.I, m.C, slots, m.scratch, reinterpret_cast<const int4*>(worklist),
                                      m.sorted_token_ids, m.topk_weights, (int)slots, np, m.wm2 - 100, m.sk2 > 0 ? m.sk2 : 1,
                                      max_items, nullptr, s))
             return st;

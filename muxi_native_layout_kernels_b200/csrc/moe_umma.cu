@@ -8,7 +8,8 @@
 //     its length leave at once;
 //   * the weight tensor map covers all experts ([E * rows, k]); the item's expert selects the tile rows;
 //   * the activation rows of an item must be contiguous for the TMA tile, so a gather pass first copies the routed
-//     token rows into position order (position = index into sorted_token_ids);
+//     token rows into compact position order (the routed slots numbered expert by expert, without the padding of
+//     sorted_token_ids; the work item carries its first compact position);
 //   * MODE 1 (first GEMM): every CTA holds the gate tile and the matching up tile of W1 (two accumulators fed by the
 //     same token tile) and writes silu(gate) * up of the fp32 sums as the [position, I] activation;
 //   * MODE 2 (second GEMM): reads that activation by position, multiplies by the slot's routing weight and writes the
@@ -29,10 +30,10 @@ namespace {
 using namespace umma;
 
 struct MoeUmmaParams {
-    const int4* worklist;       // [0] = {n_items,..}; then {expert, first position, slots, 0}
+    const int4* worklist;       // [0] = {n_items,..}; then {expert, first position, slots, first compact position}
     const int32_t* sorted;      // slot id of every position; >= n_slots marks padding
     const void* topk_weights;   // [n_slots] activation dtype (MODE 2)
-    void* out;                  // MODE 1: act [positions, rows] 16-bit; MODE 2: scratch [n_slots, rows] fp32
+    void* out;                  // MODE 1: act [compact positions, rows] 16-bit; MODE 2: scratch [n_slots, rows] fp32
     int rows;                   // output features: I (MODE 1) or H (MODE 2)
     int tiles_per_expert;       // weight row tiles of one expert in the tensor map: 2I/128 (MODE 1) or H/128
     int up_tile_offset;         // MODE 1: I/128
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__(192, 2) moe_umma_kernel(const __grid_constant_
     const int n_items = p.worklist[0].x;
     if ((int)blockIdx.z >= n_items) return;             // uniform over the cluster (clusters span y only)
     const int4 item = p.worklist[1 + blockIdx.z];
-    const int expert = item.x, pos0 = item.y, nslots = item.z;
+    const int expert = item.x, pos0 = item.y, nslots = item.z, cpos0 = item.w;
 
     const int KB = p.kblocks;
     const int kb0 = (int)((long long)KB * rank / SK), kb1 = (int)((long long)KB * (rank + 1) / SK);
@@ -114,7 +115,7 @@ __global__ void __launch_bounds__(192, 2) moe_umma_kernel(const __grid_constant_
             if constexpr (MODE == 1)
                 tma_load_4d(a_addr(s, 1), &map_a, full_bar(s), 0, (kb0 + i) * (kBlockK / 8),
                             (a_tile + p.up_tile_offset) * (kTileM / 16), 0);
-            tma_load_2d(b_addr(s), &map_x, full_bar(s), (kb0 + i) * kBlockK, pos0);
+            tma_load_2d(b_addr(s), &map_x, full_bar(s), (kb0 + i) * kBlockK, cpos0);
             ++issued;
         }
     } else if (warp == 1 && lane == 0) {
@@ -201,7 +202,7 @@ __global__ void __launch_bounds__(192, 2) moe_umma_kernel(const __grid_constant_
                 const float gate = cluster_sum(off);
                 const float up = cluster_sum(off + (uint32_t)NP * kTileM * 4u);
                 const float v = gate / (1.f + __expf(-gate)) * up;
-                const size_t o = (size_t)(pos0 + c) * p.rows + row;
+                const size_t o = (size_t)(cpos0 + c) * p.rows + row;
                 if constexpr (WT == kFP16)
                     reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(v);
                 else
@@ -228,19 +229,20 @@ __global__ void __launch_bounds__(192, 2) moe_umma_kernel(const __grid_constant_
     }
 }
 
-// Routed token rows in position order: xg[pos] = x[sorted[pos] / topk], zero rows for padding positions.
+// Routed token rows in compact position order: xg[first compact position + c] = x[sorted[first position + c] / topk]
+// for every slot c of every work item; one CTA per item.
 __global__ void __launch_bounds__(256) moe_gather_positions_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ sorted,
-                                                                   const int32_t* __restrict__ cumsum, int E, int topk,
-                                                                   int n_slots, int h8, uint4* __restrict__ xg, long long max_pos) {
+                                                                   const int4* __restrict__ worklist, int topk, int h8,
+                                                                   uint4* __restrict__ xg) {
     pdl_wait();
     pdl_launch_dependents();
-    const long long n_pos = min((long long)cumsum[E], max_pos);
-    const long long total = n_pos * h8;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const long long pos = i / h8;
-        const int u = (int)(i - pos * h8);
-        const int slot = sorted[pos];
-        xg[i] = (slot < n_slots) ? x[(size_t)(slot / topk) * h8 + u] : make_uint4(0, 0, 0, 0);
+    if ((int)blockIdx.x >= worklist[0].x) return;
+    const int4 item = worklist[1 + blockIdx.x];
+    const int total = item.z * h8;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int c = i / h8, u = i - c * h8;
+        const int slot = sorted[item.y + c];
+        xg[(size_t)(item.w + c) * h8 + u] = x[(size_t)(slot / topk) * h8 + u];
     }
 }
 
@@ -278,25 +280,24 @@ const void* moe_kernel_for(int np, int stages) {
 
 }  // namespace
 
-int launch_moe_gather_positions(const void* x, const int32_t* sorted, const int32_t* cumsum, int E, int topk, int n_slots,
-                                int H, void* xg, long long max_pos, cudaStream_t s) {
+int launch_moe_gather_positions(const void* x, const int32_t* sorted, const int4* worklist, int topk, int H, void* xg,
+                                int max_items, cudaStream_t s) {
     if (H % 8 != 0) return fail(kInvalidArg, "moe gather: H must be a multiple of 8");
-    const long long total = max_pos * (H / 8);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)std::min<long long>((total + 255) / 256, 148LL * 8));
+    cfg.gridDim = dim3((unsigned)max_items);
     cfg.blockDim = dim3(256);
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
     cfg.attrs = attr;
     cfg.numAttrs = launch_attrs(attr, 1);
-    cudaError_t e = cudaLaunchKernelEx(&cfg, moe_gather_positions_kernel, reinterpret_cast<const uint4*>(x), sorted, cumsum, E,
-                                       topk, n_slots, H / 8, reinterpret_cast<uint4*>(xg), max_pos);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, moe_gather_positions_kernel, reinterpret_cast<const uint4*>(x), sorted, worklist, topk,
+                                       H / 8, reinterpret_cast<uint4*>(xg));
     if (e != cudaSuccess) return fail(kCudaError, "moe gather launch: %s", cudaGetErrorString(e));
     return kOk;
 }
 
-// One grouped GEMM.  mode 1: W = w1 [E, 2I, k=H], X = gathered tokens [max_pos, H], out = act [max_pos, I];
-// mode 2: W = w2 [E, H, k=I], X = act [max_pos, I], out = scratch [n_slots, H] fp32.
+// One grouped GEMM.  mode 1: W = w1 [E, 2I, k=H], X = gathered tokens [n_slots, H], out = act [n_slots, I] (both in
+// compact position order); mode 2: W = w2 [E, H, k=I], X = act [n_slots, I], out = scratch [n_slots, H] fp32 by slot.
 int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, const void* X, long long x_rows, void* out,
                     const int4* worklist, const int32_t* sorted, const void* topk_weights, int n_slots, int np, int stages,
                     int cluster_k, int max_items, int* status, cudaStream_t s) {
