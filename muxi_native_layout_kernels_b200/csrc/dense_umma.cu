@@ -44,6 +44,7 @@ struct UmmaParams {
     float alpha;
     int m, n, k;
     int c_layout;
+    int x_layout;      // 0 row-major activations, 1 layout B
     int kblocks;       // k / 64
     float* ws;         // [tiles][max_parts][NP][128] fp32 partial tiles
     int max_parts;     // workspace slots per tile
@@ -188,7 +189,8 @@ __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const 
             pdl_wait();
             int bk = kb0;
             for (int j = 0; j < pre; ++j) {
-                tma_load_2d(b_base + j * kBBytes, &map_x, full_bar(j), bk * kBlockK, 0);
+                if (p.x_layout == 0) tma_load_2d(b_base + j * kBBytes, &map_x, full_bar(j), bk * kBlockK, 0);
+                else tma_load_5d(b_base + j * kBBytes, &map_x, full_bar(j), 0, 0, 0, 0, bk * (kBlockK / 32));
                 if (++bk == KB) bk = 0;
             }
             issued = pre;
@@ -206,7 +208,8 @@ __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const 
             if (abort_flag) break;
             mbar_expect_tx(full_bar(s), kABytes + kBBytes);
             load_a(s);
-            tma_load_2d(b_base + s * kBBytes, &map_x, full_bar(s), lk * kBlockK, 0);
+            if (p.x_layout == 0) tma_load_2d(b_base + s * kBBytes, &map_x, full_bar(s), lk * kBlockK, 0);
+            else tma_load_5d(b_base + s * kBBytes, &map_x, full_bar(s), 0, 0, 0, 0, lk * (kBlockK / 32));
             if (++lk == KB) { lk = 0; ++lt; }
             ++issued;
         }
@@ -239,7 +242,9 @@ __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const 
                     // one MMA consumes two k-octets
                     const uint64_t da = smem_desc(a_base + s * kABytes + kk * 256, 128, 1024, 0);
                     // B: 128-byte swizzle, 8-token step 1024 B; one MMA consumes 32 bytes of each 128-byte row
-                    const uint64_t db = smem_desc(b_base + s * kBBytes + kk * 32, 16, 1024, 2);
+                    // (layout-B activations: no swizzle, k-octet step NP * 16 bytes, 8-token step 128 bytes)
+                    const uint64_t db = p.x_layout == 0 ? smem_desc(b_base + s * kBBytes + kk * 32, 16, 1024, 2)
+                                                        : smem_desc(b_base + s * kBBytes + kk * (NP * 32), NP * 16, 128, 0);
                     umma_f16(tmem + b * NP, da, db, idesc, (kb > kb_begin || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(empty_bar(s));     // arrives when the MMAs above have finished reading the stage
@@ -625,7 +630,7 @@ int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages,
                       cudaStream_t stream) {
     if (wt != kBF16 && wt != kFP16) return fail(kUnsupported, "dense (tcgen05): 16-bit weights only");
     if (!p.A || !p.X || !p.C) return fail(kInvalidArg, "dense: null pointer");
-    if (p.x_layout != 0) return fail(kUnsupported, "dense (tcgen05): activations must be row-major");
+    if (p.x_layout == 1 && p.n % 16 != 0) return fail(kInvalidArg, "dense: layout B needs n %% 16 == 0");
     if (p.m % kTileM != 0 || p.k % kBlockK != 0) return fail(kInvalidArg, "dense (tcgen05): need m %% 128 == 0 and k %% 64 == 0");
     if (p.n < 1 || p.n > 64) return fail(kUnsupported, "dense (tcgen05): 1..64 tokens per launch (got %d)", p.n);
     if (p.c_layout == 1 && p.n % 16 != 0) return fail(kInvalidArg, "dense: layout C needs n %% 16 == 0");
@@ -665,8 +670,9 @@ int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages,
     }
     CUtensorMap ma, mx;
     if (!make_map_a(&ma, p.A, p.m, p.k, wt)) return fail(kUnsupported, "dense (tcgen05): weight tensor map rejected");
-    if (!make_map_x(&mx, p.X, p.n, p.k, wt, np)) return fail(kUnsupported, "dense (tcgen05): activation tensor map rejected");
+    if (!(p.x_layout == 0 ? make_map_x(&mx, p.X, p.n, p.k, wt, np) : make_map_xb(&mx, p.X, p.n, p.k, wt, np))) return fail(kUnsupported, "dense (tcgen05): activation tensor map rejected");
     UmmaParams up{};
+    up.x_layout = p.x_layout;
     up.C = p.C; up.bias = p.bias; up.alpha = p.alpha; up.m = p.m; up.n = p.n; up.k = p.k; up.c_layout = p.c_layout;
     up.kblocks = kblocks;
     up.ws = have_aux ? reinterpret_cast<float*>(aux->workspace) : nullptr;

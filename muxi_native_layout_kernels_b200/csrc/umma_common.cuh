@@ -55,6 +55,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -156,6 +162,21 @@ inline bool make_map_x(CUtensorMap* map, const void* X, int n, int k, int wt, in
     return encode_fn()(map, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                        const_cast<void*>(X), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Token tile map for activations in layout B [k/32][n/16][4 k-octets][16 tokens][8 k]: viewed as (one 8-token x 8-k
+// core matrix of 128 bytes, token half, 16-token block, k-octet, 32-k chunk) with box (64, 2, np/16, 4, 2), the tile
+// of np tokens x 64 k lands as [k-octet (8)][8-token group (np/8)][128 B]: the UMMA no-swizzle K-major layout with a
+// k-octet step of np * 16 bytes and an 8-token step of 128 bytes.  Token blocks beyond n are zero-filled.
+inline bool make_map_xb(CUtensorMap* map, const void* X, int n, int k, int wt, int np) {
+    const cuuint64_t dims[5] = {64, 2, (cuuint64_t)(n / 16), 4, (cuuint64_t)(k / 32)};
+    const cuuint64_t strides[4] = {128, 1024, 256, (cuuint64_t)(n / 16) * 1024};
+    const cuuint32_t box[5] = {64, 2, (cuuint32_t)(np / 16), 4, kBlockK / 32};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return encode_fn()(map, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5,
+                       const_cast<void*>(X), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

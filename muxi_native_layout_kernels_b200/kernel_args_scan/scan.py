@@ -123,10 +123,11 @@ def candidates(kind, m, n, k):
                   if (m // 128) * ck <= 148 * min(4, max(1, (227 * 1024) // (max(st * 8192, np_ * 512) + 2 * np_ * 128 + 2048)))]
     if kind == "a" and n <= 4:
         cands += [(kid, rg, 0, sk) for kid, rg, sk in itertools.product([5, 6, 7], [1, 2], [1, 2, 4]) if m % (16 * rg) == 0]
-    if kind == "a" and n <= 64:
+    if kind in ("a", "conc", "abc") and n <= 64 and (kind == "a" or n % 16 == 0):
         # tcgen05 tile kernel: (CTAs per SM, ring stages, 0) = persistent stream-K grid;
         # (1, ring stages, cluster size) = one cluster per 128-row tile, k split inside the cluster
-        cands += [(2, 1, 4, 0), (2, 1, 5, 0), (2, 1, 6, 0), (2, 1, 8, 0), (2, 2, 3, 0), (2, 2, 4, 0)]
+        if kind == "a":       # the persistent grid needs the scratch only the layout-A entry points pass
+            cands += [(2, 1, 4, 0), (2, 1, 5, 0), (2, 1, 6, 0), (2, 1, 8, 0), (2, 2, 3, 0), (2, 2, 4, 0)]
         for ck in (2, 3, 4, 5, 6, 7, 8):
             for st in (2, 3, 4, 5, 6, 8):
                 np_ = 16 if n <= 16 else (32 if n <= 32 else 64)

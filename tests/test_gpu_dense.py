@@ -167,6 +167,15 @@ def test_gemm_layoutB_variants(dt):
                 assert_close(mlk.reLayoutC(C5), want, f"ABC {dt} m={m} k={k} n={n} {(rg, wm, sk)}")
                 # the reference's own un-permute recipe (benchmark_and_test/gemm_benchmark.py:74-76)
                 assert torch.equal(C5.permute(1, 3, 0, 2, 4).reshape(n, m), mlk.reLayoutC(C5))
+            if n <= 64:
+                # kernelId 2: the tcgen05 kernel reads layout-B activations through a 5-D tensor map
+                for (cps, stages, ck) in [(1, 2, 0), (2, 4, 0), (1, 3, 2), (1, 4, 4)]:
+                    C = mlk.gemm_layoutAB_ContinuousC_wapper(A, XB, m, n, k, alpha=1.5, kernelParam1=cps, kernelParam2=stages,
+                                                             kernelParam3=ck, kernelId=2, bias=bias.to(dev))
+                    assert_close(C, want, f"ContinuousC tcgen05 {dt} m={m} k={k} n={n} {(cps, stages, ck)}")
+                    C5 = mlk.gemm_layoutABC_wapper(A, XB, m, n, k, alpha=1.5, kernelParam1=cps, kernelParam2=stages,
+                                                   kernelParam3=ck, kernelId=2, bias=bias.to(dev))
+                    assert_close(mlk.reLayoutC(C5), want, f"ABC tcgen05 {dt} m={m} k={k} n={n} {(cps, stages, ck)}")
             assert_close(mlk.gemm_layoutAB_ContinuousC(A, XB, alpha=1.5, bias=bias.to(dev)), want, "ContinuousC table")
             assert_close(mlk.reLayoutC(mlk.gemm_layoutABC(A, XB, alpha=1.5, bias=bias.to(dev))), want, "ABC table")
 
