@@ -286,18 +286,6 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8_kernel(const __grid_cons
     }
 }
 
-// e4m3 weight tile map: global layout A is [row group][k-octet][16 rows][8 bytes]; a 3-D view (128-byte block,
-// k-octet, row group) with box (128, 8, 8) lands a 128 x 64 tile as [row group][k-octet][16 rows x 8 bytes].
-bool make_map_a8(CUtensorMap* map, const void* A, int m, int k) {
-    const cuuint64_t dims[3] = {128, (cuuint64_t)(k / 8), (cuuint64_t)(m / 16)};
-    const cuuint64_t strides[2] = {128, (cuuint64_t)16 * k};
-    const cuuint32_t box[3] = {128, kBlockK / 8, kTileM / 16};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(A), dims, strides, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int NP>
 const void* f8_kernel_for_stages(int stages) {
     switch (stages) {

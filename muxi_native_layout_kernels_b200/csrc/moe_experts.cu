@@ -306,13 +306,14 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
     const int block_slots = nt_tiles * 8;
     const int max_items = (int)std::min<long long>(slots, (long long)std::min<long long>(m.E, slots) + slots / block_slots);
 
-    // tcgen05 path (moe_umma.cu): asked for by the tuning arguments, 16-bit weights, fp32 combine scratch present.
+    // tcgen05 path (moe_umma.cu): asked for by the tuning arguments, 16-bit weights or e4m3 weights without block
+    // scales, fp32 combine scratch present.
     // Its buffers are indexed by compact position (the routed slots expert by expert, no padding): the [slots, I]
     // activation takes the front of C like the warp-level path's, and the gathered token rows [slots, H] borrow the
     // combine scratch until the second GEMM overwrites it.
     const size_t c_bytes = (size_t)slots * 2 * m.I * 2;
     const size_t wl_bytes = 16 * (size_t)(max_items + 1);
-    const bool umma = wt != kE4M3 && m.wm1 >= 100 && m.wm2 >= 100 && m.scratch != nullptr && m.I % 128 == 0 &&
+    const bool umma = (wt != kE4M3 || !scale) && m.wm1 >= 100 && m.wm2 >= 100 && m.scratch != nullptr && m.I % 128 == 0 &&
                       m.H % 128 == 0 && (long long)slots * m.H * 4 <= m.scratch_bytes;
 
     if (!umma && (m.wm1 >= 100 || m.wm2 >= 100)) {
@@ -339,11 +340,11 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
             return st;
         if (int st = launch_moe_umma(1, wt, m.w1, m.E, m.I, m.H, m.scratch, slots, m.C, reinterpret_cast<const int4*>(worklist),
                                      m.sorted_token_ids, m.topk_weights, (int)slots, np, m.wm1 - 100, m.sk1 > 0 ? m.sk1 : 1,
-                                     max_items, nullptr, s))
+                                     max_items, m.fp8_order, nullptr, s))
             return st;
         if (int st = launch_moe_umma(2, wt, m.w2, m.E, m.H, m.I, m.C, slots, m.scratch, reinterpret_cast<const int4*>(worklist),
                                      m.sorted_token_ids, m.topk_weights, (int)slots, np, m.wm2 - 100, m.sk2 > 0 ? m.sk2 : 1,
-                                     max_items, nullptr, s))
+                                     max_items, m.fp8_order, nullptr, s))
             return st;
         const long long total = (long long)m.T * (m.H / 8);
         const int grid = (int)std::min<long long>((total + 255) / 256, 148LL * 8);

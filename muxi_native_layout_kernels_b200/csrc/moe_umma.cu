@@ -39,8 +39,70 @@ struct MoeUmmaParams {
     int up_tile_offset;         // MODE 1: I/128
     int kblocks;
     int n_slots;
+    uint32_t sel01, sel23;      // e4m3 kernels: byte selectors of the decode (natural or repacked order)
     int* status;
 };
+
+// Cluster epilogue shared by the two kernels: after a cluster barrier every CTA adds one slice of accumulator rows over
+// all ranks (descending rank, fixed order) through distributed shared memory and emits it.  The partial tiles sit at
+// `base` in every CTA as fp32 [which][slot][accumulator row].  NATURAL: accumulator row = tile row; otherwise row rho
+// holds weight row 16*(rho%64 / 8) + 8*(rho / 64) + rho%8 of the tile (layout of the TMA-loaded 16-bit tile).
+template <int WT, int NP, int MODE, bool NATURAL>
+__device__ __forceinline__ void moe_cluster_epilogue(const MoeUmmaParams& p, uint32_t base, int tile, int rank, int SK,
+                                                     int nslots, int pos0, int cpos0, int tid) {
+    const int warp = tid >> 5;
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (warp >= 2) {
+        const int etid = tid - 64;
+        const int r0 = kTileM * rank / SK, rows = kTileM * (rank + 1) / SK - r0;
+        uint32_t remote[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[q]) : "r"(base), "r"(q < SK ? q : 0));
+        auto cluster_sum = [&](uint32_t off) {
+            float t[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                t[q] = 0.f;
+                if (q < SK) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(t[q]) : "r"(remote[q] + off) : "memory");
+            }
+            float acc = 0.f;
+            bool first = true;
+#pragma unroll
+            for (int q = 7; q >= 0; --q) {
+                if (q < SK) {
+                    acc = first ? t[q] : acc + t[q];
+                    first = false;
+                }
+            }
+            return acc;
+        };
+        const int total = nslots * rows;
+        for (int idx = etid; idx < total; idx += 128) {
+            const int c = idx / rows, rho = r0 + idx - c * rows;
+            const int row = tile * kTileM + (NATURAL ? rho : ((rho & 63) >> 3) * 16 + (rho >> 6) * 8 + (rho & 7));
+            const uint32_t off = (uint32_t)(c * kTileM + rho) * 4u;
+            if constexpr (MODE == 1) {
+                const float gate = cluster_sum(off);
+                const float up = cluster_sum(off + (uint32_t)NP * kTileM * 4u);
+                const float v = gate / (1.f + __expf(-gate)) * up;
+                const size_t o = (size_t)(cpos0 + c) * p.rows + row;
+                if constexpr (WT == kFP16)
+                    reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(v);
+                else
+                    reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
+            } else {
+                const int slot = p.sorted[pos0 + c];
+                if (slot < p.n_slots) {
+                    const float w = load_scalar16<WT>(p.topk_weights, slot);
+                    reinterpret_cast<float*>(p.out)[(size_t)slot * p.rows + row] = w * cluster_sum(off);
+                }
+            }
+        }
+    }
+    // nobody leaves while its shared memory may still be read
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 template <int WT, int NP, int STAGES, int MODE>
 __global__ void __launch_bounds__(192, 2) moe_umma_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -165,62 +227,210 @@ __global__ void __launch_bounds__(192, 2) moe_umma_kernel(const __grid_constant_
     }
     __syncwarp();
 
-    // ---- every CTA of the cluster adds one slice of accumulator rows over all ranks (descending rank) ----
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    if (warp >= 2) {
-        const int etid = tid - 64;
-        const int r0 = kTileM * rank / SK, rows = kTileM * (rank + 1) / SK - r0;
-        uint32_t remote[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[q]) : "r"(base), "r"(q < SK ? q : 0));
-        auto cluster_sum = [&](uint32_t off) {
-            float t[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                t[q] = 0.f;
-                if (q < SK) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(t[q]) : "r"(remote[q] + off) : "memory");
-            }
-            float acc = 0.f;
-            bool first = true;
-#pragma unroll
-            for (int q = 7; q >= 0; --q) {
-                if (q < SK) {
-                    acc = first ? t[q] : acc + t[q];
-                    first = false;
-                }
-            }
-            return acc;
-        };
-        const int total = nslots * rows;
-        for (int idx = etid; idx < total; idx += 128) {
-            const int c = idx / rows, rho = r0 + idx - c * rows;
-            // accumulator row rho holds weight row 16*(rho%64 / 8) + 8*(rho / 64) + rho%8 of the tile
-            const int row = tile * kTileM + ((rho & 63) >> 3) * 16 + (rho >> 6) * 8 + (rho & 7);
-            const uint32_t off = (uint32_t)(c * kTileM + rho) * 4u;
-            if constexpr (MODE == 1) {
-                const float gate = cluster_sum(off);
-                const float up = cluster_sum(off + (uint32_t)NP * kTileM * 4u);
-                const float v = gate / (1.f + __expf(-gate)) * up;
-                const size_t o = (size_t)(cpos0 + c) * p.rows + row;
-                if constexpr (WT == kFP16)
-                    reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(v);
-                else
-                    reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
-            } else {
-                const int slot = p.sorted[pos0 + c];
-                if (slot < p.n_slots) {
-                    const float w = load_scalar16<WT>(p.topk_weights, slot);
-                    reinterpret_cast<float*>(p.out)[(size_t)slot * p.rows + row] = w * cluster_sum(off);
-                }
-            }
-        }
-    }
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    moe_cluster_epilogue<WT, NP, MODE, false>(p, base, tile, rank, SK, nslots, pos0, cpos0, tid);
 
     // ---- teardown ----
     if (warp == 0 && lane == 0 && abort_flag) {
         for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(full_bar(i % STAGES), (i / STAGES) & 1);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- e4m3 weights: TMA -> raw ring -> decode into tensor memory -> tcgen05.mma with A from tensor memory ----
+// (pipeline of dense_umma_f8.cu; NA weight tiles per stage share the token tile; activations are bf16)
+constexpr int kRawBytes = kTileM * kBlockK;      // 8 KB of e4m3 per tile and stage
+constexpr int kAColumns = kBlockK / 2;           // 32-bit tensor-memory columns of one decoded tile
+constexpr int kF8ConvStages = 2;
+
+template <int NP, int STAGES, int MODE>
+__global__ void __launch_bounds__(192, 2) moe_umma_f8_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                             const __grid_constant__ CUtensorMap map_x,
+                                                             const MoeUmmaParams p, const int static_weights) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr int NA = MODE == 1 ? 2 : 1;
+    constexpr int S2 = kF8ConvStages;
+    constexpr int kBBytes = NP * 128;
+    constexpr int kStageBytes = NA * kRawBytes;
+    constexpr int kRingBytes = STAGES * kStageBytes > NA * NP * 512 ? STAGES * kStageBytes : NA * NP * 512;
+    constexpr uint32_t kTmemCols = (NA * NP + S2 * NA * kAColumns) <= 128 ? 128 : 256;
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 2 * S2 + 1];
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = blockIdx.x, rank = blockIdx.y, SK = gridDim.y;
+
+    pdl_wait();
+    pdl_launch_dependents();
+    const int n_items = p.worklist[0].x;
+    if ((int)blockIdx.z >= n_items) return;
+    const int4 item = p.worklist[1 + blockIdx.z];
+    const int expert = item.x, pos0 = item.y, nslots = item.z, cpos0 = item.w;
+
+    const int KB = p.kblocks;
+    const int kb0 = (int)((long long)KB * rank / SK), kb1 = (int)((long long)KB * (rank + 1) / SK);
+    const int nunits = kb1 - kb0;
+    const int a_tile = expert * p.tiles_per_expert + tile;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* const base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t b_base = base + kRingBytes;
+    const uint32_t bar0 = smem_u32(bars);
+    auto raw_full = [&](int s) { return bar0 + 8u * s; };
+    auto raw_empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto cv_full = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };
+    auto cv_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + S2 + s); };
+    const uint32_t acc_full = bar0 + 8u * (2 * STAGES + 2 * S2);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(raw_full(s), 1);
+            mbar_init(raw_empty(s), 4);
+        }
+        for (int s = 0; s < S2; ++s) {
+            mbar_init(cv_full(s), 5);
+            mbar_init(cv_empty(s), 1);
+        }
+        mbar_init(acc_full, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+
+    int raw_issued = 0;
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer: raw weight tiles and token tiles are two independent streams, polled without blocking ----
+        int ri = 0, bi = 0;
+        uint32_t idle = 0;
+        while ((bi < nunits || ri < nunits) && !abort_flag) {
+            bool progressed = false;
+            if (bi < nunits && (bi < S2 || mbar_test_wait(cv_empty(bi % S2), ((bi / S2) - 1) & 1))) {
+                const int s2 = bi % S2;
+                mbar_expect_tx(cv_full(s2), kBBytes);
+                tma_load_2d(b_base + s2 * kBBytes, &map_x, cv_full(s2), (kb0 + bi) * kBlockK, cpos0);
+                ++bi;
+                progressed = true;
+            }
+            if (ri < nunits && (ri < STAGES || mbar_test_wait(raw_empty(ri % STAGES), ((ri / STAGES) - 1) & 1))) {
+                const int s = ri % STAGES;
+                mbar_expect_tx(raw_full(s), kStageBytes);
+                tma_load_3d(base + s * kStageBytes, &map_a, raw_full(s), 0, (kb0 + ri) * (kBlockK / 8), a_tile * (kTileM / 16));
+                if constexpr (MODE == 1)
+                    tma_load_3d(base + s * kStageBytes + kRawBytes, &map_a, raw_full(s), 0, (kb0 + ri) * (kBlockK / 8),
+                                (a_tile + p.up_tile_offset) * (kTileM / 16));
+                ++raw_issued;
+                ++ri;
+                progressed = true;
+            }
+            if (progressed) {
+                idle = 0;
+            } else if (++idle > 4 * kSpinLimit) {
+                abort_flag = 1;
+                if (p.status) atomicExch(p.status, 1);
+            } else {
+                __nanosleep(32);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        constexpr uint32_t idesc = instr_desc<kBF16, NP>();
+        for (int i = 0; i < nunits; ++i) {
+            const int s2 = i % S2;
+            if (abort_flag || !mbar_wait(cv_full(s2), (i / S2) & 1)) {
+                if (!abort_flag && p.status) atomicExch(p.status, 2);
+                abort_flag = 1;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int kk = 0; kk < kBlockK / 16; ++kk) {
+                const uint64_t db = smem_desc(b_base + s2 * kBBytes + kk * 32, 16, 1024, 2);
+#pragma unroll
+                for (int w = 0; w < NA; ++w) {
+                    const uint32_t ta = tmem + NA * NP + (s2 * NA + w) * kAColumns + kk * 8;
+                    umma_f16_ts(tmem + w * NP, ta, db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+                }
+            }
+            umma_commit(cv_empty(s2));
+        }
+        if (!abort_flag) umma_commit(acc_full);
+    } else if (warp >= 2) {
+        // ---- converter warps (thread = tile row = tensor-memory lane), then epilogue ----
+        const int quad = warp & 3, lrow = quad * 32 + lane;
+        for (int i = 0; i < nunits; ++i) {
+            const int s = i % STAGES, s2 = i % S2;
+            bool ok = true;
+            if (lane == 0) {
+                ok = !abort_flag && mbar_wait(raw_full(s), (i / STAGES) & 1);
+                if (ok && i >= S2) ok = mbar_wait(cv_empty(s2), ((i / S2) - 1) & 1);
+                if (!ok) {
+                    if (!abort_flag && p.status) atomicExch(p.status, 8);
+                    abort_flag = 1;
+                }
+            }
+            ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int w = 0; w < NA; ++w) {
+                const uint8_t* raw = base_ptr + s * kStageBytes + w * kRawBytes + (lrow >> 4) * 1024 + (lrow & 15) * 8;
+                uint32_t v[32];
+#pragma unroll
+                for (int o = 0; o < 8; ++o) {
+                    const uint2 x = *reinterpret_cast<const uint2*>(raw + o * 128);
+                    v[4 * o + 0] = e4m3x2_to_bf16x2(x.x, p.sel01);
+                    v[4 * o + 1] = e4m3x2_to_bf16x2(x.x, p.sel23);
+                    v[4 * o + 2] = e4m3x2_to_bf16x2(x.y, p.sel01);
+                    v[4 * o + 3] = e4m3x2_to_bf16x2(x.y, p.sel23);
+                }
+                tmem_st32(tmem + ((uint32_t)(quad * 32) << 16) + NA * NP + (s2 * NA + w) * kAColumns, v);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(cv_full(s2)) : "memory");
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(raw_empty(s)) : "memory");
+            }
+        }
+        if (lane == 0 && (abort_flag || !mbar_wait(acc_full, 0))) {
+            if (!abort_flag && p.status) atomicExch(p.status, 3);
+            abort_flag = 1;
+        }
+        __syncwarp();
+        if (!abort_flag) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float* const red = reinterpret_cast<float*>(base_ptr);
+#pragma unroll
+            for (int c0 = 0; c0 < NA * NP; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + c0, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; ++i) red[(c0 + i) * kTileM + lrow] = __uint_as_float(r[i]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        }
+    }
+    __syncwarp();
+
+    moe_cluster_epilogue<kBF16, NP, MODE, true>(p, base, tile, rank, SK, nslots, pos0, cpos0, tid);
+
+    if (warp == 0 && lane == 0 && abort_flag) {
+        for (int i = max(0, raw_issued - STAGES); i < raw_issued; ++i) mbar_wait(raw_full(i % STAGES), (i / STAGES) & 1);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -268,6 +478,25 @@ const void* moe_kernel_for_stages(int stages) {
     }
     return nullptr;
 }
+template <int NP, int MODE>
+const void* moe_f8_kernel_for_stages(int stages) {
+    switch (stages) {
+        case 2: return reinterpret_cast<const void*>(moe_umma_f8_kernel<NP, 2, MODE>);
+        case 3: return reinterpret_cast<const void*>(moe_umma_f8_kernel<NP, 3, MODE>);
+        case 4: return reinterpret_cast<const void*>(moe_umma_f8_kernel<NP, 4, MODE>);
+        case 6: return reinterpret_cast<const void*>(moe_umma_f8_kernel<NP, 6, MODE>);
+    }
+    return nullptr;
+}
+template <int MODE>
+const void* moe_f8_kernel_for(int np, int stages) {
+    switch (np) {
+        case 16: return moe_f8_kernel_for_stages<16, MODE>(stages);
+        case 32: return moe_f8_kernel_for_stages<32, MODE>(stages);
+        case 64: return moe_f8_kernel_for_stages<64, MODE>(stages);
+    }
+    return nullptr;
+}
 template <int WT, int MODE>
 const void* moe_kernel_for(int np, int stages) {
     switch (np) {
@@ -300,24 +529,28 @@ int launch_moe_gather_positions(const void* x, const int32_t* sorted, const int4
 // compact position order); mode 2: W = w2 [E, H, k=I], X = act [n_slots, I], out = scratch [n_slots, H] fp32 by slot.
 int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, const void* X, long long x_rows, void* out,
                     const int4* worklist, const int32_t* sorted, const void* topk_weights, int n_slots, int np, int stages,
-                    int cluster_k, int max_items, int* status, cudaStream_t s) {
-    if (wt != kBF16 && wt != kFP16) return fail(kUnsupported, "moe (tcgen05): 16-bit weights only");
+                    int cluster_k, int max_items, int fp8_order, int* status, cudaStream_t s) {
+    const bool f8 = wt == kE4M3;
+    if (wt != kBF16 && wt != kFP16 && !f8) return fail(kUnsupported, "moe (tcgen05): unsupported weight type");
     if (rows % kTileM != 0 || k % kBlockK != 0) return fail(kInvalidArg, "moe (tcgen05): sizes must be multiples of 128 (rows) and 64 (k)");
     if (cluster_k < 1 || cluster_k > 8 || cluster_k > k / kBlockK) return fail(kInvalidArg, "moe (tcgen05): cluster size %d out of range", cluster_k);
     if (encode_fn() == nullptr) return fail(kUnsupported, "moe (tcgen05): cuTensorMapEncodeTiled is not available");
     const void* kern = nullptr;
-    if (mode == 1) kern = wt == kFP16 ? moe_kernel_for<kFP16, 1>(np, stages) : moe_kernel_for<kBF16, 1>(np, stages);
+    if (f8) kern = mode == 1 ? moe_f8_kernel_for<1>(np, stages) : moe_f8_kernel_for<2>(np, stages);
+    else if (mode == 1) kern = wt == kFP16 ? moe_kernel_for<kFP16, 1>(np, stages) : moe_kernel_for<kBF16, 1>(np, stages);
     else kern = wt == kFP16 ? moe_kernel_for<kFP16, 2>(np, stages) : moe_kernel_for<kBF16, 2>(np, stages);
     if (kern == nullptr) return fail(kInvalidArg, "moe (tcgen05): token tile %d / stages %d not built", np, stages);
     const int na = mode == 1 ? 2 : 1;
-    const size_t smem = std::max((size_t)stages * (na * kABytes + np * 128), (size_t)na * np * 512) + 1024;
+    const size_t smem = f8 ? std::max((size_t)stages * na * kRawBytes, (size_t)na * np * 512) + (size_t)kF8ConvStages * np * 128 + 1024
+                           : std::max((size_t)stages * (na * kABytes + np * 128), (size_t)na * np * 512) + 1024;
     if (smem > 227 * 1024) return fail(kUnsupported, "moe (tcgen05): %d stages do not fit in shared memory", stages);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(kCudaError, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     const long long w_rows = (long long)E * (mode == 1 ? 2 * rows : rows);
     CUtensorMap ma, mx;
-    if (!make_map_w(&ma, W, w_rows, k, wt)) return fail(kUnsupported, "moe (tcgen05): weight tensor map rejected");
-    if (!make_map_x(&mx, X, (int)x_rows, k, wt, np)) return fail(kUnsupported, "moe (tcgen05): activation tensor map rejected");
+    if (!(f8 ? make_map_a8(&ma, W, w_rows, k) : make_map_w(&ma, W, w_rows, k, wt)))
+        return fail(kUnsupported, "moe (tcgen05): weight tensor map rejected");
+    if (!make_map_x(&mx, X, (int)x_rows, k, f8 ? kBF16 : wt, np)) return fail(kUnsupported, "moe (tcgen05): activation tensor map rejected");
     MoeUmmaParams mp{};
     mp.worklist = worklist; mp.sorted = sorted; mp.topk_weights = topk_weights; mp.out = out;
     mp.rows = rows;
@@ -325,6 +558,8 @@ int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, con
     mp.up_tile_offset = rows / kTileM;
     mp.kblocks = k / kBlockK;
     mp.n_slots = n_slots;
+    mp.sel01 = fp8_order ? kSelRep01 : kSelNat01;
+    mp.sel23 = fp8_order ? kSelRep23 : kSelNat23;
     mp.status = status;
     int static_weights = option(kOptStaticWeights);
     cudaLaunchConfig_t cfg = {};

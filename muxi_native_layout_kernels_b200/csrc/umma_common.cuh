@@ -165,6 +165,18 @@ inline bool make_map_x(CUtensorMap* map, const void* X, int n, int k, int wt, in
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// e4m3 weight tile map: global layout A is [row group][k-octet][16 rows][8 bytes]; a 3-D view (128-byte block,
+// k-octet, row group) with box (128, 8, 8) lands a 128 x 64 tile as [row group][k-octet][16 rows x 8 bytes].
+inline bool make_map_a8(CUtensorMap* map, const void* A, long long m, int k) {
+    const cuuint64_t dims[3] = {128, (cuuint64_t)(k / 8), (cuuint64_t)(m / 16)};
+    const cuuint64_t strides[2] = {128, (cuuint64_t)16 * k};
+    const cuuint32_t box[3] = {128, kBlockK / 8, kTileM / 16};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(A), dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Token tile map for activations in layout B [k/32][n/16][4 k-octets][16 tokens][8 k]: viewed as (one 8-token x 8-k
 // core matrix of 128 bytes, token half, 16-token block, k-octet, 32-k chunk) with box (64, 2, np/16, 4, 2), the tile
 // of np tokens x 64 k lands as [k-octet (8)][8-token group (np/8)][128 B]: the UMMA no-swizzle K-major layout with a

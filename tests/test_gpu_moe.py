@@ -236,6 +236,24 @@ def test_moe_16bit_tcgen05_expert_gemms(dt, T):
         assert_close(y, y0.cpu(), f"tcgen05 vs warp-level {dt} T={T} tune={tune}", scale_atol=True)
 
 
+@pytest.mark.parametrize("T", [1, 8, 32, 130, 520])
+@pytest.mark.parametrize("repack", [False, True])
+def test_moe_soft_fp8_tcgen05_expert_gemms(T, repack):
+    """e4m3 experts without block scales on the tcgen05 kernels (decode into tensor memory), against the same oracle
+    and against the warp-level kernels."""
+    E, topk, H, I = 32, 8, 256, 128
+    x = randn((T, H), 800 + T, 1.0)
+    w1 = rand_e4m3((E, 2 * I, H), 801, 0.25)
+    w2 = rand_e4m3((E, H, I), 802, 0.25)
+    logits = randn((T, E), 803 + T, 1.0)
+    for tune in [(1, 102, 1, 0, 102, 1), (2, 103, 2, 0, 104, 2), (4, 104, 4, 0, 106, 1), (8, 102, 2, 0, 103, 2)]:
+        y = _moe_compare(x, w1, w2, logits, topk, f"moe fp8 tcgen05 T={T} repack={repack} tune={tune}", fp8=True,
+                         repack=repack, tune=tune)
+        y0 = _moe_compare(x, w1, w2, logits, topk, f"moe fp8 warp-level T={T}", fp8=True, repack=repack,
+                          tune=(tune[0], 2, 1, 1, 2, 1))
+        assert_close(y, y0.cpu(), f"fp8 tcgen05 vs warp-level T={T} tune={tune}", scale_atol=True)
+
+
 @pytest.mark.parametrize("T", [1, 8, 32, 130])
 @pytest.mark.parametrize("repack", [False, True])
 def test_moe_soft_fp8_random(T, repack):
