@@ -261,6 +261,15 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(t[0]), float(t[1])
 
+    moe_ep = None
+    if world > 1 and not args.no_moe:
+        # every rank takes part (collectives inside); rank 0 reports
+        from muxi_native_layout_kernels_b200.kernel_args_scan import moe_bench
+        try:
+            moe_ep = moe_bench.run_ep("both", rank, world, None, 24, dev, graphs=True)
+        except Exception as exc:       # the dense line must still be printed
+            moe_ep = {"error": repr(exc)[:300]}
+
     if rank == 0:
         ms_step = ms / args.steps
         value = step_bytes_total / (ms_step * 1e-3) / 1e9
@@ -294,6 +303,10 @@ def run_ours(args):
             # replay over 8 different activation batches, see kernel_args_scan/moe_bench.py
             from muxi_native_layout_kernels_b200.kernel_args_scan import moe_bench
             line["moe_layer_us"] = moe_bench.run("both", None, 24, dev)
+        if world > 1 and not args.no_moe:
+            line["moe_layer_us"] = moe_ep
+            line["moe_layer_mode"] = (f"expert parallel over {world} GPUs: E/{world} experts per rank, tokens replicated, "
+                                      "NCCL all-reduce of the fp32 shares; us_eager = eager calls (host launch overhead included), us_graph = CUDA-graph replays; max over ranks")
         if world == 1 and not args.no_cpu:
             gbs, dt = time_cpu(passes=args.cpu_passes)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",

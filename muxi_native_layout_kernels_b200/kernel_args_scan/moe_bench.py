@@ -99,6 +99,76 @@ def run(config="both", tokens=None, iters=24, dev=None):
     return out
 
 
+def run_ep(config, rank, world, tokens=None, iters=24, dev=None, graphs=False):
+    """Expert-parallel layer time on `world` ranks (one process per GPU, torch.distributed initialised): every rank
+    holds E / world experts, tokens and router logits are replicated, each rank adds its experts' share
+    (parallel.fused_moe_ep_replicated: experts_map + NCCL all-reduce of the fp32 sums).  Timed with CUDA events
+    around `iters` eager layer calls over 8 activation batches after a barrier (us_eager, host launch overhead included)
+    and, with graphs=True, around replays of a CUDA graph holding the 8 calls and their all-reduces (us_graph); max over ranks.
+    Weights are random per rank (timing only; parity of this mode is covered by tests/test_gpu_multi.py)."""
+    import torch.distributed as dist
+
+    from muxi_native_layout_kernels_b200.parallel import fused_moe_ep_replicated
+    dev = dev or torch.device("cuda")
+    mlk.set_static_weights(True)
+    out = {}
+    for name in (["mixtral", "fine"] if config == "both" else [config]):
+        cfg = dict(CONFIGS[name])
+        E, H, I, topk, fp8 = cfg["E"], cfg["H"], cfg["I"], cfg["topk"], cfg["fp8"]
+        if E % world != 0:
+            continue
+        local = dict(cfg, E=E // world, seed=cfg["seed"] * 100 + rank)
+        w1, w2, _, _ = build(local, dev)
+        g = torch.Generator(device=dev).manual_seed(cfg["seed"])          # same on every rank
+        wg = (torch.randn(E, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        kw = dict(block_shape=[128, 128], soft_fp8=True, fp8_repacked=True) if fp8 else {}
+        rows = []
+        for T in (tokens or cfg["tokens"]):
+            xs = [torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16) for _ in range(NBATCH)]
+            logits = [(x.float() @ wg.float().t()).to(torch.bfloat16) for x in xs]
+            for i in range(NBATCH):
+                fused_moe_ep_replicated(xs[i], w1, w2, logits[i], topk, True, **kw)
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for it in range(iters):
+                fused_moe_ep_replicated(xs[it % NBATCH], w1, w2, logits[it % NBATCH], topk, True, **kw)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            row = {"T": T, "us_eager": round(float(t[0]), 2), "experts_per_rank": E // world}
+            if graphs:
+                # the same 8 layer calls (all-reduce included) captured in one CUDA graph: no host launch overhead
+                graph = torch.cuda.CUDAGraph()
+                s = torch.cuda.Stream()
+                s.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(s):
+                    with torch.cuda.graph(graph, stream=s):
+                        for i in range(NBATCH):
+                            fused_moe_ep_replicated(xs[i], w1, w2, logits[i], topk, True, **kw)
+                torch.cuda.current_stream().wait_stream(s)
+                graph.replay()
+                torch.cuda.synchronize()
+                dist.barrier()
+                reps = max(1, iters // NBATCH)
+                e0.record()
+                for _ in range(reps):
+                    graph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (reps * NBATCH)], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                row["us_graph"] = round(float(t[0]), 2)
+                del graph
+            rows.append(row)
+        out[name] = rows
+        del w1, w2
+        torch.cuda.empty_cache()
+    return out
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", default="both", choices=["mixtral", "fine", "both"])

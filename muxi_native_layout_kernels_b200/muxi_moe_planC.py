@@ -133,7 +133,9 @@ def fused_moe(
     y = torch.empty_like(hidden_states) if deterministic else torch.zeros_like(hidden_states)
 
     if tune is None:
-        tune = lookup_moe_args(e1, topk, H, k2, soft_fp8, B)
+        # with an experts_map (expert parallelism) the work per local expert is that of the full layer: the row of
+        # the global expert count applies
+        tune = lookup_moe_args(gating_output.shape[1] if experts_map is not None else e1, topk, H, k2, soft_fp8, B)
     if experts_map is not None and experts_map.dtype != torch.int:
         experts_map = experts_map.to(torch.int)
     if soft_fp8:
