@@ -242,22 +242,25 @@ def _gemm_checks(A, B, b_layout: bool):
     return m, n, A_k
 
 
-_SYNC_BUFFERS = {}   # (device index, stream handle) -> (counters, status)
+_SYNC_BUFFERS = {}   # (device index, stream handle) -> [counters, status, workspace, MlkAux]
 _WS_BYTES = {}       # (device index, m, n-tile, k) -> workspace bytes of the tcgen05 kernel
 
 
 def _aux(B: torch.Tensor, m: int, n: int, k: int):
-    """Scratch for kernels that split K over independent CTAs: a per-call fp32 workspace from torch's caching
-    allocator (stream-ordered, so concurrent streams never share it) and, per (device, stream), a persistent block of
-    counters that every kernel leaves zeroed plus the sticky status word of the kernels' bounded waits."""
+    """Scratch for the tcgen05 kernel's persistent stream-K grid, kept per (device, stream): a block of counters that
+    every kernel leaves zeroed, the sticky status word of the kernels' bounded waits, and an fp32 workspace that only
+    grows.  Successive launches of one stream may share the workspace: a kernel touches it only after the preceding
+    kernel of the stream has completed (griddepcontrol.wait), and kernels of one stream never run concurrently
+    otherwise; another stream gets its own."""
     if n > 64:
         return None, None
-    key = (B.device.index, _stream(B))
+    stream = _stream(B)
+    key = (B.device.index, stream)
     tiles = m // 128
     bufs = _SYNC_BUFFERS.get(key)
     if bufs is None or bufs[0].numel() < tiles:
-        bufs = (torch.zeros(max(4096, tiles), dtype=torch.int32, device=B.device),
-                torch.zeros(1, dtype=torch.int32, device=B.device))
+        bufs = [torch.zeros(max(4096, tiles), dtype=torch.int32, device=B.device),
+                torch.zeros(1, dtype=torch.int32, device=B.device), None, None]
         _SYNC_BUFFERS[key] = bufs
     npad = 16 if n <= 16 else (32 if n <= 32 else 64)
     wkey = (B.device.index, m, npad, k)
@@ -267,9 +270,15 @@ def _aux(B: torch.Tensor, m: int, n: int, k: int):
             nbytes = _WS_BYTES[wkey] = int(lib.mlk_gemm_workspace_bytes(m, n, k))
     if nbytes == 0:
         return None, None
-    ws = torch.empty(nbytes // 4, dtype=torch.float32, device=B.device)
-    aux = MlkAux(ws.data_ptr(), ws.numel() * 4, bufs[0].data_ptr(), bufs[0].numel(), bufs[1].data_ptr())
-    return aux, ws
+    ws = bufs[2]
+    if ws is None or ws.numel() * 4 < nbytes:
+        # the old buffer may still be in use by kernels already queued on this stream: torch's allocator keeps a freed
+        # block stream-ordered, so dropping the reference here is safe
+        ws = bufs[2] = torch.empty(max(nbytes // 4, 1 << 20), dtype=torch.float32, device=B.device)
+        bufs[3] = None
+    if bufs[3] is None:
+        bufs[3] = MlkAux(ws.data_ptr(), ws.numel() * 4, bufs[0].data_ptr(), bufs[0].numel(), bufs[1].data_ptr())
+    return bufs[3], ws
 
 
 def kernel_status(device=None) -> int:

@@ -79,6 +79,60 @@ def test_packaged_tables_exist_with_reference_headers():
         assert f.read_text().splitlines()[0].strip() == (gemv_hdr if t >= 4 else gemm_hdr)
 
 
+def test_packaged_table_rows_name_launches_the_library_accepts():
+    """Every row of the packaged tables must pass the validity rules of the table-driven entry points (a row that
+    fails them silently falls back to the shape-based default and loses the tuned performance)."""
+    import csv
+    pkg = Path(__file__).resolve().parents[1] / "muxi_native_layout_kernels_b200"
+
+    def rows(name):
+        with open(pkg / name) as f:
+            r = csv.reader(f)
+            next(r)
+            return [[int(v) for v in row] for row in r if row]
+
+    for name, fp8, layout_a in [("layout_gemm_dispatch_arg.csv", False, False), ("continuous_gemm_dispatch_arg.csv", False, False),
+                                ("layoutA_gemm_dispatch_arg.csv", False, True), ("layoutA_Soft_Fp8_gemm_dispatch_arg.csv", True, True)]:
+        table = rows(name)
+        assert table, name
+        for m, n, k, kid, p1, p2, p3 in table:
+            what = (name, m, n, k, kid, p1, p2, p3)
+            assert m % 128 == 0 and k % 128 == 0 and 1 <= n <= 256, what
+            if kid in (1, 3, 4):
+                assert p1 in (1, 2) and p2 in (1, 2, 4, 8) and p2 <= {1: 8, 3: 4, 4: 2}[kid] and p3 in (1, 2, 4, 8), what
+                assert m % (16 * p1 * p2) == 0, what
+            elif kid == 2 and not fp8:
+                assert n <= 64 and 1 <= p1 <= 4 and p2 in (2, 3, 4, 5, 6, 8) and 0 <= p3 <= 8, what
+                assert layout_a or (n % 16 == 0 and p3 >= 2), what     # layout-B variants pass no scratch: cluster mode
+                assert p3 < 2 or p3 <= k // 64, what
+            elif kid == 2 and fp8:
+                assert n <= 64 and p2 in (2, 3, 4, 6, 8) and 1 <= p3 <= min(8, k // 64), what
+            elif kid in (5, 6, 7):
+                assert layout_a and not fp8 and n <= 4 and p1 in (1, 2) and p3 in (1, 2, 4, 8) and m % (16 * p1) == 0, what
+            else:
+                raise AssertionError(what)
+    for name, fp8 in [("layout_gemv_dispatch_arg.csv", False), ("layout_gemv_bf16_dispatch_arg.csv", False),
+                      ("layout_gemv_soft_fp8_dispatch_arg.csv", True)]:
+        table = rows(name)
+        assert table, name
+        for m, k, block, kid, p1, p2 in table:
+            what = (name, m, k, block, kid, p1, p2)
+            if kid == 3:
+                assert fp8 and m % 128 == 0 and k % 64 == 0 and p1 in (2, 3, 4, 6, 8) and 1 <= p2 <= 8, what
+            else:
+                assert block in (64, 128, 256) and (kid == 1 or (kid == 2 and not fp8)), what
+                assert p1 in (1, 2) and p2 in (1, 2, 4, 8) and m % (16 * p1) == 0, what
+    for E, topk, H, I, fp8, T, nt, wm1, sk1, rg2, wm2, sk2 in rows("moe_dispatch_arg.csv"):
+        what = (E, topk, H, I, fp8, T, nt, wm1, sk1, rg2, wm2, sk2)
+        assert nt in (1, 2, 4, 8), what
+        assert (wm1 >= 100) == (wm2 >= 100), what
+        if wm1 >= 100:       # tcgen05 expert GEMMs: 100 + ring stages, CTAs per cluster
+            assert H % 128 == 0 and I % 128 == 0, what
+            assert wm1 - 100 in (2, 3, 4, 6) and wm2 - 100 in (2, 3, 4, 6) and 1 <= sk1 <= min(8, H // 64) and 1 <= sk2 <= min(8, I // 64), what
+        else:
+            assert wm1 in (1, 2, 4, 8) and wm2 in (1, 2, 4, 8) and sk1 in (1, 2, 4, 8) and sk2 in (1, 2, 4, 8) and rg2 in (1, 2), what
+
+
 def test_argument_errors_surface_as_runtime_error_without_a_gpu():
     import muxi_native_layout_kernels_b200 as mlk
     A = torch.zeros(8, 16, 16, 8, dtype=torch.bfloat16)
