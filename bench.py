@@ -193,7 +193,23 @@ def run_ours(args):
         for K in (4096, 14336):
             host_acts[(n, K)] = torch.randn(n, K, generator=g).to(torch.bfloat16).pin_memory()
     dev_acts = {k: v.to(dev) for k, v in host_acts.items()}
-    host_out = {(n, N): torch.empty(n, N // world, dtype=torch.bfloat16).pin_memory() for n in TOKENS for (N, _) in SHAPES}
+    # end-to-end buffers: the step's activations packed in one pinned host buffer (one H2D copy per step) and the
+    # step's 21 results packed in one device buffer that is read back with one D2H copy
+    in_off, off = {}, 0
+    for key, v in host_acts.items():
+        in_off[key] = off
+        off += v.numel()
+    host_in = torch.empty(off, dtype=torch.bfloat16).pin_memory()
+    for key, v in host_acts.items():
+        host_in[in_off[key]:in_off[key] + v.numel()].copy_(v.reshape(-1))
+    dev_in = torch.empty(off, dtype=torch.bfloat16, device=dev)
+    dev_in_view = {key: dev_in[in_off[key]:in_off[key] + v.numel()].view(v.shape) for key, v in host_acts.items()}
+    out_off, off = {}, 0
+    for (n, N, K) in case_order():
+        out_off[(n, N, K)] = off
+        off += n * (N // world)
+    dev_out = torch.empty(off, dtype=torch.bfloat16, device=dev)
+    host_out = torch.empty(off, dtype=torch.bfloat16).pin_memory()
     order = case_order()
     step_bytes_total = sum(algorithmic_bytes(n, N, K) for (n, N, K) in order)
 
@@ -204,10 +220,12 @@ def run_ours(args):
         return out
 
     def step_e2e():
+        dev_in.copy_(host_in, non_blocking=True)
         for (n, N, K) in order:
-            x = host_acts[(n, K)].to(dev, non_blocking=True)
-            c = mlk.gemm_layoutA(weights[(N, K)], x)
-            host_out[(n, N)].copy_(c, non_blocking=True)
+            c = mlk.gemm_layoutA(weights[(N, K)], dev_in_view[(n, K)])
+            o = out_off[(n, N, K)]
+            dev_out[o:o + c.numel()].view(c.shape).copy_(c)
+        host_out.copy_(dev_out, non_blocking=True)
 
     def barrier():
         if world > 1:
@@ -243,7 +261,10 @@ def run_ours(args):
     barrier()
     ms = ev0.elapsed_time(ev1)
 
-    # end-to-end through the public API with host buffers
+    # end-to-end through the public API with host buffers: every case copies its activations from pinned host memory,
+    # runs, and copies its result back to pinned host memory, all inside the timed region.  Timed twice: as eager
+    # Python calls (host submission cost included) and as a CUDA graph of the same calls and copies (what a serving
+    # loop with static buffers replays); the graph number is the one reported as e2e.
     for _ in range(2):
         step_e2e()
     barrier()
@@ -253,13 +274,29 @@ def run_ours(args):
         step_e2e()
     e1.record()
     barrier()
+    ms_e2e_eager = e0.elapsed_time(e1)
+    graph_e2e = torch.cuda.CUDAGraph()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step_e2e()
+        with torch.cuda.graph(graph_e2e, stream=side):
+            step_e2e()
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(2):
+        graph_e2e.replay()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        graph_e2e.replay()
+    e1.record()
+    barrier()
     ms_e2e = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
 
     if world > 1:
-        t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms, ms_e2e, ms_e2e_eager], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = float(t[0]), float(t[1])
+        ms, ms_e2e, ms_e2e_eager = float(t[0]), float(t[1]), float(t[2])
 
     moe_ep = None
     if world > 1 and not args.no_moe:
@@ -287,9 +324,9 @@ def run_ours(args):
                        "l2": "consecutive launches use different weight matrices; >= 235 MB stream between two uses of one matrix (L2 is 126 MB)",
                        "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS},
             "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "GB/s",
-                    "h2d_bytes_per_step": sum(n * K * 2 for (n, N, K) in order),
-                    "d2h_bytes_per_step": sum(n * (N // world) * 2 for (n, N, K) in order)},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "mode": "CUDA graph of one step: one packed H2D copy of the activations, the 21 public API calls, one packed D2H copy of the results",
+                    "eager_value": step_bytes_total / (ms_e2e_eager / args.steps * 1e-3) / 1e9,
+                    "h2d_bytes_per_step": host_in.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2},
             "gpu_launches": len(order) * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_RATIO * per_rank_bytes / len(order),
