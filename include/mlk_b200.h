@@ -185,6 +185,16 @@ int mlk_fused_routing_gate_renorm(const void* gating_output, int score_fun, int 
                                   int n_groups, int topK_groups, int32_t* experts_ids, void* selected_experts_weights,
                                   int topK, const void* load_balance_bias, int dtype, int renormalize, mlk_stream_t s);
 
+/* Router GEMM fused with the routing (no counterpart in the reference, whose fused_moe starts from gating_output):
+ * logits[t, e] = sum_h x[t, h] * gate_weight[e, h] in fp32, rounded once to the activation dtype -- what a 16-bit linear
+ * layer would hand to the router -- followed by exactly the routing of mlk_fused_routing_gate_renorm.  x [T, H] and
+ * gate_weight [E, H] row-major in the activation dtype, 16-byte aligned, H % 8 == 0.  logits_out: optional [T, E] copy
+ * of the rounded logits (NULL to skip).  Meant for decode batches: one CTA per four tokens re-reads the gate matrix. */
+int mlk_fused_router_gemm_gate(const void* x, const void* gate_weight, int score_fun, int batch_size, int hidden_size,
+                               int num_experts, int n_groups, int topK_groups, int32_t* experts_ids,
+                               void* selected_experts_weights, int topK, const void* load_balance_bias, int dtype,
+                               int renormalize, void* logits_out, mlk_stream_t s);
+
 /* Token alignment: groups the flat slots i = token*topK + j by (mapped) expert, pads every expert's run to a
  * multiple of microBatchSize with the caller's sentinel, and records one expert id per block.
  *   sorted_token_ids  [T*topK + E*(mbs-1)]  every position that holds no slot is set to the sentinel T*topK (the

@@ -48,6 +48,8 @@ PROTOTYPES = {
     "mlk_gemm_layoutABC": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_vp]),
     "mlk_fused_routing_gate": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_vp, c_int,
                                        c_vp]),
+    "mlk_fused_router_gemm_gate": (c_int, [c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_vp,
+                                           c_int, c_int, c_vp, c_vp]),
     "mlk_fused_routing_gate_renorm": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_vp, c_int,
                                               c_int, c_vp]),
     "mlk_moe_align": (c_int, [c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_vp]),

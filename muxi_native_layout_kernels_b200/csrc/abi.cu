@@ -300,6 +300,16 @@ int mlk_fused_routing_gate_renorm(const void* gating_output, int score_fun, int 
                          selected_experts_weights, topK, load_balance_bias, dtype, (cudaStream_t)s, renormalize);
 }
 
+int mlk_fused_router_gemm_gate(const void* x, const void* gate_weight, int score_fun, int batch_size, int hidden_size,
+                               int num_experts, int n_groups, int topK_groups, int32_t* experts_ids,
+                               void* selected_experts_weights, int topK, const void* load_balance_bias, int dtype,
+                               int renormalize, void* logits_out, mlk_stream_t s) {
+    clear_error();
+    return launch_router_gemm(x, gate_weight, score_fun, batch_size, hidden_size, num_experts, n_groups, topK_groups,
+                              experts_ids, selected_experts_weights, topK, load_balance_bias, dtype, renormalize,
+                              logits_out, (cudaStream_t)s);
+}
+
 int mlk_moe_align(int batchSize, int expertCount, int topK, int microBatchSize, const int32_t* topk_ids,
                   int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
                   int32_t* experts_ids_out, const int32_t* experts_map, int experts_map_len, mlk_stream_t s) {

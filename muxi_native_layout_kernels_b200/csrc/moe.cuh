@@ -10,6 +10,11 @@ int launch_router(const void* gating_output, int score_fun, int T, int E, int n_
                   int32_t* experts_ids, void* weights, int topk, const void* bias, int dtype, cudaStream_t s,
                   int renormalize = 0);
 
+// Router GEMM (x [T,H] times gate_weight [E,H]^T, rounded to the 16-bit type) fused with the routing above.
+int launch_router_gemm(const void* x, const void* gate_weight, int score_fun, int T, int H, int E, int n_groups,
+                       int topk_groups, int32_t* experts_ids, void* weights, int topk, const void* bias, int dtype,
+                       int renormalize, void* logits_out, cudaStream_t s);
+
 // worklist == nullptr: alignment only (the stand-alone reference op).  Otherwise the kernel also writes
 // the expert-compute work list (see MoeWorkHeader) for blocks of `block_slots` slots.
 int launch_moe_align(int T, int E, int topk, int mbs, const int32_t* topk_ids, int32_t* sorted_token_ids,

@@ -29,25 +29,15 @@ __device__ __forceinline__ void argmax_pair(float& v, int& e) {
     }
 }
 
+// Routing of one token by one warp.  x[i] = logit of expert lane + 32*i (already a value of the 16-bit type, -inf
+// beyond E); ssel / sg / gmask: this warp's scratch of E + 2*G floats in shared memory.
 template <int WT>
-__global__ void __launch_bounds__(128) router_kernel(const void* __restrict__ logits, int score_fun, int T, int E,
-                                                     int G, int KG, int32_t* __restrict__ ids, void* __restrict__ wts,
-                                                     int topk, const void* __restrict__ bias, int renormalize) {
-    extern __shared__ float sm[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int row = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (row >= T) return;
-    float* ssel = sm + warp * (E + 2 * G);
-    float* sg = ssel + E;
-    int* gmask = reinterpret_cast<int*>(sg + G);
+__device__ __forceinline__ void route_token(const float (&x)[kVPT], int row, int lane, int score_fun, int E, int G, int KG,
+                                            int32_t* __restrict__ ids, void* __restrict__ wts, int topk,
+                                            const void* __restrict__ bias, int renormalize, float* ssel, float* sg,
+                                            int* gmask) {
     const float NEG = -INFINITY;
-
-    float x[kVPT], score[kVPT], sel[kVPT];
-#pragma unroll
-    for (int i = 0; i < kVPT; ++i) {
-        const int e = lane + 32 * i;
-        x[i] = (e < E) ? load_scalar16<WT>(logits, (int64_t)row * E + e) : NEG;
-    }
+    float score[kVPT], sel[kVPT];
     if (score_fun == 0) {
         float mx = x[0];
 #pragma unroll
@@ -162,7 +152,134 @@ __global__ void __launch_bounds__(128) router_kernel(const void* __restrict__ lo
     }
 }
 
+template <int WT>
+__global__ void __launch_bounds__(128) router_kernel(const void* __restrict__ logits, int score_fun, int T, int E,
+                                                     int G, int KG, int32_t* __restrict__ ids, void* __restrict__ wts,
+                                                     int topk, const void* __restrict__ bias, int renormalize) {
+    extern __shared__ float sm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (row >= T) return;
+    float* ssel = sm + warp * (E + 2 * G);
+    float* sg = ssel + E;
+    int* gmask = reinterpret_cast<int*>(sg + G);
+    float x[kVPT];
+#pragma unroll
+    for (int i = 0; i < kVPT; ++i) {
+        const int e = lane + 32 * i;
+        x[i] = (e < E) ? load_scalar16<WT>(logits, (int64_t)row * E + e) : -INFINITY;
+    }
+    route_token<WT>(x, row, lane, score_fun, E, G, KG, ids, wts, topk, bias, renormalize, ssel, sg, gmask);
+}
+
+// Router GEMM fused with the routing: logits[t, e] = sum_h x[t, h] * Wg[e, h] (fp32 sum, rounded once to the 16-bit
+// type, exactly what a 16-bit linear layer hands to the router), then route_token.  One CTA of 8 warps handles
+// kTokPerCta tokens: every warp takes the experts e = warp, warp + 8, ... and computes their dot products with all the
+// CTA's tokens at once (the gate weights are read once per CTA, 16-byte loads, lanes along h), the logits meet in
+// shared memory, then warp t routes token t.  Meant for decode batches; the gate matrix (E x H) stays in L2.
+constexpr int kTokPerCta = 4;
+
+template <int WT>
+__global__ void __launch_bounds__(256) router_gemm_kernel(const void* __restrict__ xin, const void* __restrict__ wg,
+                                                          int score_fun, int T, int H, int E, int G, int KG,
+                                                          int32_t* __restrict__ ids, void* __restrict__ wts, int topk,
+                                                          const void* __restrict__ bias, int renormalize,
+                                                          void* __restrict__ logits_out) {
+    extern __shared__ float sm[];
+    float* slog = sm;                                   // [kTokPerCta][E]
+    float* scratch = sm + kTokPerCta * E;               // [kTokPerCta][E + 2 * G]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t0 = blockIdx.x * kTokPerCta;
+    const int nt = min(kTokPerCta, T - t0);
+    pdl_wait();
+    pdl_launch_dependents();
+    const uint4* x4 = reinterpret_cast<const uint4*>(xin);
+    const uint4* w4 = reinterpret_cast<const uint4*>(wg);
+    const int h8 = H >> 3;
+    for (int e = warp; e < E; e += 8) {
+        float acc[kTokPerCta];
+#pragma unroll
+        for (int t = 0; t < kTokPerCta; ++t) acc[t] = 0.f;
+        for (int u = lane; u < h8; u += 32) {
+            const uint4 w = w4[(size_t)e * h8 + u];
+            const float2 w0 = unpack2<WT>(w.x), w1 = unpack2<WT>(w.y), w2 = unpack2<WT>(w.z), w3 = unpack2<WT>(w.w);
+#pragma unroll
+            for (int t = 0; t < kTokPerCta; ++t) {
+                if (t < nt) {
+                    const uint4 v = x4[(size_t)(t0 + t) * h8 + u];
+                    const float2 v0 = unpack2<WT>(v.x), v1 = unpack2<WT>(v.y), v2 = unpack2<WT>(v.z), v3 = unpack2<WT>(v.w);
+                    float a = acc[t];
+                    a = fmaf(w0.x, v0.x, a); a = fmaf(w0.y, v0.y, a); a = fmaf(w1.x, v1.x, a); a = fmaf(w1.y, v1.y, a);
+                    a = fmaf(w2.x, v2.x, a); a = fmaf(w2.y, v2.y, a); a = fmaf(w3.x, v3.x, a); a = fmaf(w3.y, v3.y, a);
+                    acc[t] = a;
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < kTokPerCta; ++t) {
+            const float v = round16<WT>(warp_sum(acc[t]));
+            if (lane == 0 && t < nt) {
+                slog[t * E + e] = v;
+                if (logits_out != nullptr) {
+                    if constexpr (WT == kFP16)
+                        reinterpret_cast<__half*>(logits_out)[(size_t)(t0 + t) * E + e] = __float2half_rn(v);
+                    else
+                        reinterpret_cast<__nv_bfloat16*>(logits_out)[(size_t)(t0 + t) * E + e] = __float2bfloat16_rn(v);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (warp < nt) {
+        float x[kVPT];
+#pragma unroll
+        for (int i = 0; i < kVPT; ++i) {
+            const int e = lane + 32 * i;
+            x[i] = (e < E) ? slog[warp * E + e] : -INFINITY;
+        }
+        float* ssel = scratch + warp * (E + 2 * G);
+        float* sg = ssel + E;
+        int* gmask = reinterpret_cast<int*>(sg + G);
+        route_token<WT>(x, t0 + warp, lane, score_fun, E, G, KG, ids, wts, topk, bias, renormalize, ssel, sg, gmask);
+    }
+}
+
 }  // namespace
+
+int launch_router_gemm(const void* x, const void* gate_weight, int score_fun, int T, int H, int E, int n_groups,
+                       int topk_groups, int32_t* experts_ids, void* weights, int topk, const void* bias, int dtype,
+                       int renormalize, void* logits_out, cudaStream_t s) {
+    if (!x || !gate_weight || !experts_ids || !weights) return fail(kInvalidArg, "fused_router_gemm_gate: null pointer");
+    if (T < 0) return fail(kInvalidArg, "fused_router_gemm_gate: negative batch size");
+    if (T == 0) return kOk;
+    if (H <= 0 || H % 8 != 0) return fail(kInvalidArg, "fused_router_gemm_gate: hidden size must be a positive multiple of 8 (got %d)", H);
+    if (((uintptr_t)x & 15) || ((uintptr_t)gate_weight & 15)) return fail(kInvalidArg, "fused_router_gemm_gate: x and the gate weight must be 16-byte aligned");
+    if (score_fun != 0 && score_fun != 1) return fail(kInvalidArg, "fused_router_gemm_gate: score_fun must be 0 (softmax) or 1 (sigmoid)");
+    if (E <= 0 || E > 32 * kVPT) return fail(kUnsupported, "fused_router_gemm_gate: 1 <= num_experts <= 256 (got %d)", E);
+    if (n_groups <= 0 || E % n_groups != 0) return fail(kInvalidArg, "fused_router_gemm_gate: n_groups=%d must divide num_experts=%d", n_groups, E);
+    if (topk_groups <= 0 || topk_groups > n_groups) return fail(kInvalidArg, "fused_router_gemm_gate: topK_groups=%d out of range", topk_groups);
+    if (topk <= 0 || topk > 32 || topk > E) return fail(kInvalidArg, "fused_router_gemm_gate: topK=%d out of range (1..min(32,E))", topk);
+    if (dtype != 0 && dtype != 1) return fail(kInvalidArg, "fused_router_gemm_gate: activations must be bf16 or fp16");
+    const int grid = (T + kTokPerCta - 1) / kTokPerCta;
+    const size_t smem = (size_t)kTokPerCta * (2 * E + 2 * n_groups) * sizeof(float);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    cfg.attrs = attr;
+    cfg.numAttrs = launch_attrs(attr, 1);
+    cudaError_t e;
+    if (dtype == 1)
+        e = cudaLaunchKernelEx(&cfg, router_gemm_kernel<kFP16>, x, gate_weight, score_fun, T, H, E, n_groups, topk_groups,
+                               experts_ids, weights, topk, bias, renormalize, logits_out);
+    else
+        e = cudaLaunchKernelEx(&cfg, router_gemm_kernel<kBF16>, x, gate_weight, score_fun, T, H, E, n_groups, topk_groups,
+                               experts_ids, weights, topk, bias, renormalize, logits_out);
+    if (e != cudaSuccess) return fail(kCudaError, "fused_router_gemm_gate launch: %s", cudaGetErrorString(e));
+    return kOk;
+}
 
 int launch_router(const void* gating_output, int score_fun, int T, int E, int n_groups, int topk_groups,
                   int32_t* experts_ids, void* weights, int topk, const void* bias, int dtype, cudaStream_t s,

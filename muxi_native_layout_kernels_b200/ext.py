@@ -25,7 +25,8 @@ __all__ = [
     "gemm_layoutA", "gemm_layoutA_wapper", "gemm_layoutA_soft_fp8", "gemm_layoutA_soft_fp8_wapper",
     "gemm_layoutA_linear", "gemm_layoutAB_ContinuousC", "gemm_layoutAB_ContinuousC_wapper",
     "gemm_layoutABC", "gemm_layoutABC_wapper",
-    "fused_routing_gate", "batched_routed_activation_indexed_to_expert_block_indexed", "fused_experts_compute",
+    "fused_routing_gate", "fused_router_gemm_gate", "batched_routed_activation_indexed_to_expert_block_indexed",
+    "fused_experts_compute",
     "gemmEx", "muxi_hgemm", "muxi_hgemm_layout", "muxi_hgemm_layoutA", "muxi_hgemm_layoutC", "routing_gate",
     "experts_compute", "MlkError",
 ]
@@ -409,6 +410,41 @@ def gemm_layoutABC_wapper(A, B, m: int, n: int, k: int, alpha: float = 1, beta: 
 # ---------------------------------------------------------------------------------------------------
 # fused MoE
 # ---------------------------------------------------------------------------------------------------
+
+def fused_router_gemm_gate(hidden_states, gate_weight, score_fun: int, n_groups: int, topK_groups: int, experts_ids,
+                           selected_experts_weights, topK: int, load_balance_bias=None, *, renormalize: bool = False,
+                           logits_out=None) -> None:
+    """Router GEMM fused with the routing: ``logits = hidden_states @ gate_weight.T`` (fp32 sums rounded once to the
+    activation dtype) followed by ``fused_routing_gate``; writes ``experts_ids`` and ``selected_experts_weights`` in
+    place and, if given, the rounded logits into ``logits_out`` [T, E].  No counterpart in the reference, whose layer
+    starts from ``gating_output``; meant for decode batches."""
+    _cuda_contig(hidden_states, "hidden_states")
+    _cuda_contig(gate_weight, "gate_weight")
+    _cuda_contig(experts_ids, "experts_ids")
+    _cuda_contig(selected_experts_weights, "selected_experts_weights")
+    _chk(hidden_states.dim() == 2 and gate_weight.dim() == 2 and hidden_states.size(1) == gate_weight.size(1),
+         "hidden_states [T, H] and gate_weight [E, H] must share H")
+    _chk(gate_weight.dtype == hidden_states.dtype and selected_experts_weights.dtype == hidden_states.dtype,
+         "hidden_states, gate_weight and selected_experts_weights must have the same data type.")
+    _chk(experts_ids.dtype == torch.int32, "experts_ids must be of type torch::kInt32.")
+    T, H = hidden_states.shape
+    E = gate_weight.size(0)
+    _chk(experts_ids.numel() == T * topK and selected_experts_weights.numel() == T * topK,
+         "experts_ids / selected_experts_weights must be [batch_size, topK]")
+    code = _act_code(hidden_states)
+    if load_balance_bias is not None:
+        _cuda_contig(load_balance_bias, "load_balance_bias")
+        _chk(load_balance_bias.dtype == hidden_states.dtype and load_balance_bias.numel() == E,
+             "load_balance_bias must be [E] in the gating dtype")
+    if logits_out is not None:
+        _cuda_contig(logits_out, "logits_out")
+        _chk(logits_out.dtype == hidden_states.dtype and tuple(logits_out.shape) == (T, E), "logits_out must be [T, E]")
+    check(lib.mlk_fused_router_gemm_gate(hidden_states.data_ptr(), gate_weight.data_ptr(), score_fun, T, H, E, n_groups,
+                                         topK_groups, experts_ids.data_ptr(), selected_experts_weights.data_ptr(), topK,
+                                         None if load_balance_bias is None else load_balance_bias.data_ptr(), code,
+                                         int(bool(renormalize)), None if logits_out is None else logits_out.data_ptr(),
+                                         _stream(hidden_states)))
+
 
 def fused_routing_gate(gating_output, score_fun: int, batch_size: int, hidden_size: int, n_groups: int,
                        topK_groups: int, experts_ids, selected_experts_weights, topK: int,

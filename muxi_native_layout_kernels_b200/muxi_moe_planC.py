@@ -84,8 +84,11 @@ def fused_moe(
     fp8_repacked: bool = False,
     deterministic: bool = True,
     tune=None,
+    gate_weight: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
-    assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
+    # gate_weight [E, H] (extension): the router GEMM runs fused with the routing kernel and `gating_output` is not
+    # read (pass None)
+    assert gate_weight is not None or hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
     if num_expert_group is None:
         num_expert_group = 1
     if topk_group is None:
@@ -95,7 +98,7 @@ def fused_moe(
 
     shape = hidden_states.size()
     B, H = hidden_states.shape
-    num_experts = gating_output.shape[1]
+    num_experts = gate_weight.shape[0] if gate_weight is not None else gating_output.shape[1]
     dev = hidden_states.device
 
     if score_func == "softmax":
@@ -110,8 +113,12 @@ def fused_moe(
     topk_weights = torch.empty(B, topk, dtype=hidden_states.dtype, device=dev)
     # renormalisation (reference: two torch ops, muxi_moe_planC.py:69-70) happens inside the router kernel, with the
     # same roundings
-    ext.fused_routing_gate(gating_output, score_fun, B, H, num_expert_group, topk_group, topk_ids, topk_weights,
-                           topk, gating_bias, renormalize=bool(renormalize))
+    if gate_weight is not None:
+        ext.fused_router_gemm_gate(hidden_states, gate_weight, score_fun, num_expert_group, topk_group, topk_ids,
+                                   topk_weights, topk, gating_bias, renormalize=bool(renormalize))
+    else:
+        ext.fused_routing_gate(gating_output, score_fun, B, H, num_expert_group, topk_group, topk_ids, topk_weights,
+                               topk, gating_bias, renormalize=bool(renormalize))
 
     # 2. experts
     e1, m1, k1 = w1.shape
@@ -135,7 +142,7 @@ def fused_moe(
     if tune is None:
         # with an experts_map (expert parallelism) the work per local expert is that of the full layer: the row of
         # the global expert count applies
-        tune = lookup_moe_args(gating_output.shape[1] if experts_map is not None else e1, topk, H, k2, soft_fp8, B)
+        tune = lookup_moe_args(num_experts if experts_map is not None else e1, topk, H, k2, soft_fp8, B)
     if experts_map is not None and experts_map.dtype != torch.int:
         experts_map = experts_map.to(torch.int)
     if soft_fp8:
@@ -151,3 +158,39 @@ def fused_moe(
                                   block_dim_x_gemm=block_dim_x_gemm, experts_map=experts_map,
                                   deterministic=deterministic, tune=tune)
     return y.view(shape)
+
+
+class GraphedFusedMoE:
+    """``fused_moe`` for a fixed token count, captured once in a CUDA graph.
+
+    The eager call spends more time in Python, the allocator and the launches (eight ``torch.empty`` and five to six
+    kernel launches) than the GPU spends on the layer when the batch is small.  This object owns static input, routing and
+    workspace buffers, captures the layer's launches once, and replays them: ``layer(hidden_states, gating_output)``
+    copies the two inputs into the static buffers, replays the graph on the current stream and returns the static
+    output tensor (valid until the next call; clone it to keep it).  Weights, scales, bias and the expert map are
+    captured by address: update them in place.  The reference has no counterpart (its planC is eager only).
+    """
+
+    def __init__(self, w1, w2, tokens: int, num_experts: int, topk: int, renormalize: bool, dtype=torch.bfloat16, **kwargs):
+        dev = w1.device
+        H = w1.shape[2]
+        self.x = torch.zeros(tokens, H, dtype=dtype, device=dev)
+        self.logits = torch.zeros(tokens, num_experts, dtype=dtype, device=dev)
+        self._args = (w1, w2, topk, renormalize, kwargs)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):                      # warm-up: table loading, attribute setting, allocator growth
+                fused_moe(self.x, w1, w2, self.logits, topk, renormalize, **kwargs)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=side):
+                self.y = fused_moe(self.x, w1, w2, self.logits, topk, renormalize, **kwargs)
+        torch.cuda.current_stream(dev).wait_stream(side)
+
+    def __call__(self, hidden_states: torch.Tensor, gating_output: torch.Tensor) -> torch.Tensor:
+        if hidden_states.shape != self.x.shape or gating_output.shape != self.logits.shape:
+            raise ValueError(f"captured for {tuple(self.x.shape)} tokens x hidden and {tuple(self.logits.shape)} logits")
+        self.x.copy_(hidden_states)
+        self.logits.copy_(gating_output)
+        self.graph.replay()
+        return self.y

@@ -61,6 +61,48 @@ def test_router_matches_oracle(case, dt):
             assert bool((ids[:, 1:] > ids[:, :-1]).all()) or topk == 1
 
 
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+@pytest.mark.parametrize("T,E,H,topk,groups,kept,score", [(1, 8, 4096, 2, 1, 1, 0), (5, 128, 2048, 8, 8, 4, 1),
+                                                         (33, 64, 512, 6, 1, 1, 0), (130, 256, 256, 8, 4, 2, 1)])
+def test_router_gemm_fused_with_routing(dt, T, E, H, topk, groups, kept, score):
+    """fused_router_gemm_gate: the logits it produces are the fp32 dot products rounded once (within one ulp of the
+    torch linear layer, which sums in another order), and its routing is bit-identical to fused_routing_gate applied
+    to those logits."""
+    dev = require_gpu()
+    x = randn((T, H), 950 + T, 1.0, DT[dt]).to(dev)
+    wg = randn((E, H), 951, 0.05, DT[dt]).to(dev)
+    bias = (randn((E,), 952, 0.1, DT[dt]).to(dev)) if score == 1 else None
+    ids = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    wts = torch.empty(T, topk, dtype=DT[dt], device=dev)
+    logits = torch.empty(T, E, dtype=DT[dt], device=dev)
+    mlk.fused_router_gemm_gate(x, wg, score, groups, kept, ids, wts, topk, bias, renormalize=True, logits_out=logits)
+    want = (x.float() @ wg.float().t())
+    ulp = 2.0 ** (-7 if dt == "bf16" else -10)      # spacing of the 16-bit type relative to the value
+    assert bool(((logits.float() - want).abs() <= ulp * want.abs().clamp_min(2.0 ** -14) * 1.01 + 1e-6).all())
+    ids2 = torch.empty_like(ids)
+    wts2 = torch.empty_like(wts)
+    mlk.fused_routing_gate(logits, score, T, H, groups, kept, ids2, wts2, topk, bias, renormalize=True)
+    torch.cuda.synchronize()
+    assert torch.equal(ids, ids2) and torch.equal(wts, wts2)
+
+
+def test_fused_moe_with_gate_weight_matches_layer_on_its_logits():
+    dev = require_gpu()
+    E, topk, H, I, T = 16, 4, 256, 128, 21
+    x = randn((T, H), 960, 1.0).to(dev)
+    wg = randn((E, H), 961, 0.05).to(dev)
+    w1 = mlk.layoutA(randn((E, 2 * I, H), 962, 0.05).to(dev))
+    w2 = mlk.layoutA(randn((E, H, I), 963, 0.05).to(dev))
+    ids = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    wts = torch.empty(T, topk, dtype=torch.bfloat16, device=dev)
+    logits = torch.empty(T, E, dtype=torch.bfloat16, device=dev)
+    mlk.fused_router_gemm_gate(x, wg, 0, 1, 1, ids, wts, topk, renormalize=True, logits_out=logits)
+    y_fused = planC_moe(x, w1, w2, None, topk, True, gate_weight=wg)
+    y_plain = planC_moe(x, w1, w2, logits, topk, True)
+    torch.cuda.synchronize()
+    assert torch.equal(y_fused, y_plain)
+
+
 def test_router_ties_prefer_lower_id():
     dev = require_gpu()
     logits = torch.zeros(3, 64, dtype=torch.bfloat16)
@@ -267,6 +309,25 @@ def test_moe_soft_fp8_random(T, repack):
     scales = (torch.rand(E, 2 * I // 128, H // 128, generator=g) * 2, torch.rand(E, H // 128, I // 128, generator=g) * 2)
     _moe_compare(x, w1, w2, logits, topk, f"moe fp8 scaled T={T} repack={repack}", fp8=True, scales=scales, repack=repack,
                  groups=8, kept=4, score="sigmoid")
+
+
+def test_graphed_fused_moe_replays_bit_exactly():
+    """GraphedFusedMoE: the layer captured once, replayed on new inputs, equals the eager call bit for bit."""
+    from muxi_native_layout_kernels_b200.muxi_moe_planC import GraphedFusedMoE
+    dev = require_gpu()
+    E, topk, H, I, T = 16, 4, 256, 128, 24
+    w1 = mlk.layoutA(randn((E, 2 * I, H), 901, 0.05).to(dev))
+    w2 = mlk.layoutA(randn((E, H, I), 902, 0.05).to(dev))
+    layer = GraphedFusedMoE(w1, w2, T, E, topk, True)
+    for seed in (903, 904, 905):
+        x = randn((T, H), seed, 1.0).to(dev)
+        logits = randn((T, E), seed + 10, 1.0).to(dev)
+        want = planC_moe(x, w1, w2, logits, topk, True)
+        got = layer(x, logits)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    with pytest.raises(ValueError, match="captured for"):
+        layer(x[:3], logits[:3])
 
 
 def test_moe_expert_parallel_map_sums_to_full_layer():
