@@ -10,6 +10,8 @@
 //   output order: ascending expert id for softmax, selection order for sigmoid (fused_topK.h:294-306, :575-586)
 // Unlike the reference launcher (fused_gating.h:22: only 8 groups / 4 kept / top-8), any E <= 256 that the
 // group count divides is accepted.
+#include <algorithm>
+
 #include "common.cuh"
 #include "moe.cuh"
 #include "status.h"
@@ -174,9 +176,8 @@ __global__ void __launch_bounds__(128) router_kernel(const void* __restrict__ lo
 
 // Router GEMM fused with the routing: logits[t, e] = sum_h x[t, h] * Wg[e, h] (fp32 sum, rounded once to the 16-bit
 // type, exactly what a 16-bit linear layer hands to the router), then route_token.  One CTA of 8 warps handles
-// kTokPerCta tokens: every warp takes the experts e = warp, warp + 8, ... and computes their dot products with all the
-// CTA's tokens at once (the gate weights are read once per CTA, 16-byte loads, lanes along h), the logits meet in
-// shared memory, then warp t routes token t.  Meant for decode batches; the gate matrix (E x H) stays in L2.
+// kTokPerCta tokens (the gate weights are read once per CTA, 16-byte loads, lanes along h), the logits meet in shared
+// memory, then warp t routes token t.  Meant for decode batches; the gate matrix (E x H) stays in L2.
 constexpr int kTokPerCta = 4;
 
 template <int WT>
@@ -193,40 +194,66 @@ __global__ void __launch_bounds__(256) router_gemm_kernel(const void* __restrict
     const int nt = min(kTokPerCta, T - t0);
     pdl_wait();
     pdl_launch_dependents();
+    // Every warp owns one eighth of h for all experts and all of the CTA's tokens: its activations stay in registers,
+    // and the loads of the gate rows of different experts are independent, so many are in flight at once.  Partial
+    // dot products meet in shared memory (one row of E sums per warp and token), then are added in warp order.
     const uint4* x4 = reinterpret_cast<const uint4*>(xin);
     const uint4* w4 = reinterpret_cast<const uint4*>(wg);
     const int h8 = H >> 3;
-    for (int e = warp; e < E; e += 8) {
-        float acc[kTokPerCta];
+    float* part = scratch;                               // [8 warps][kTokPerCta][E] (routing scratch is used later)
+    constexpr int EB = 16;                               // experts per pass: EB independent gate-row loads per lane
+    for (int e0 = 0; e0 < E; e0 += EB) {
+        float acc[EB][kTokPerCta];
 #pragma unroll
-        for (int t = 0; t < kTokPerCta; ++t) acc[t] = 0.f;
-        for (int u = lane; u < h8; u += 32) {
-            const uint4 w = w4[(size_t)e * h8 + u];
-            const float2 w0 = unpack2<WT>(w.x), w1 = unpack2<WT>(w.y), w2 = unpack2<WT>(w.z), w3 = unpack2<WT>(w.w);
+        for (int j = 0; j < EB; ++j)
+#pragma unroll
+            for (int t = 0; t < kTokPerCta; ++t) acc[j][t] = 0.f;
+        for (int u = warp * 32 + lane; u < h8; u += 256) {
+            float2 xv[kTokPerCta][4];
 #pragma unroll
             for (int t = 0; t < kTokPerCta; ++t) {
-                if (t < nt) {
-                    const uint4 v = x4[(size_t)(t0 + t) * h8 + u];
-                    const float2 v0 = unpack2<WT>(v.x), v1 = unpack2<WT>(v.y), v2 = unpack2<WT>(v.z), v3 = unpack2<WT>(v.w);
-                    float a = acc[t];
-                    a = fmaf(w0.x, v0.x, a); a = fmaf(w0.y, v0.y, a); a = fmaf(w1.x, v1.x, a); a = fmaf(w1.y, v1.y, a);
-                    a = fmaf(w2.x, v2.x, a); a = fmaf(w2.y, v2.y, a); a = fmaf(w3.x, v3.x, a); a = fmaf(w3.y, v3.y, a);
-                    acc[t] = a;
+                const uint4 v = (t < nt) ? x4[(size_t)(t0 + t) * h8 + u] : make_uint4(0, 0, 0, 0);
+                xv[t][0] = unpack2<WT>(v.x); xv[t][1] = unpack2<WT>(v.y); xv[t][2] = unpack2<WT>(v.z); xv[t][3] = unpack2<WT>(v.w);
+            }
+            uint4 wv[EB];
+#pragma unroll
+            for (int j = 0; j < EB; ++j) wv[j] = (e0 + j < E) ? w4[(size_t)(e0 + j) * h8 + u] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int j = 0; j < EB; ++j) {
+                {
+                    const uint4 w = wv[j];
+                    const float2 w0 = unpack2<WT>(w.x), w1 = unpack2<WT>(w.y), w2 = unpack2<WT>(w.z), w3 = unpack2<WT>(w.w);
+#pragma unroll
+                    for (int t = 0; t < kTokPerCta; ++t) {
+                        float a = acc[j][t];
+                        a = fmaf(w0.x, xv[t][0].x, a); a = fmaf(w0.y, xv[t][0].y, a); a = fmaf(w1.x, xv[t][1].x, a); a = fmaf(w1.y, xv[t][1].y, a);
+                        a = fmaf(w2.x, xv[t][2].x, a); a = fmaf(w2.y, xv[t][2].y, a); a = fmaf(w3.x, xv[t][3].x, a); a = fmaf(w3.y, xv[t][3].y, a);
+                        acc[j][t] = a;
+                    }
                 }
             }
         }
 #pragma unroll
-        for (int t = 0; t < kTokPerCta; ++t) {
-            const float v = round16<WT>(warp_sum(acc[t]));
-            if (lane == 0 && t < nt) {
-                slog[t * E + e] = v;
-                if (logits_out != nullptr) {
-                    if constexpr (WT == kFP16)
-                        reinterpret_cast<__half*>(logits_out)[(size_t)(t0 + t) * E + e] = __float2half_rn(v);
-                    else
-                        reinterpret_cast<__nv_bfloat16*>(logits_out)[(size_t)(t0 + t) * E + e] = __float2bfloat16_rn(v);
-                }
+        for (int j = 0; j < EB; ++j)
+#pragma unroll
+            for (int t = 0; t < kTokPerCta; ++t) {
+                const float v = warp_sum(acc[j][t]);
+                if (lane == 0 && e0 + j < E) part[(warp * kTokPerCta + t) * E + e0 + j] = v;
             }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * E; i += blockDim.x) {
+        const int t = i / E, e = i - t * E;
+        float v = part[t * E + e];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) v += part[(w * kTokPerCta + t) * E + e];
+        v = round16<WT>(v);
+        slog[t * E + e] = v;
+        if (logits_out != nullptr) {
+            if constexpr (WT == kFP16)
+                reinterpret_cast<__half*>(logits_out)[(size_t)(t0 + t) * E + e] = __float2half_rn(v);
+            else
+                reinterpret_cast<__nv_bfloat16*>(logits_out)[(size_t)(t0 + t) * E + e] = __float2bfloat16_rn(v);
         }
     }
     __syncthreads();
@@ -261,7 +288,8 @@ int launch_router_gemm(const void* x, const void* gate_weight, int score_fun, in
     if (topk <= 0 || topk > 32 || topk > E) return fail(kInvalidArg, "fused_router_gemm_gate: topK=%d out of range (1..min(32,E))", topk);
     if (dtype != 0 && dtype != 1) return fail(kInvalidArg, "fused_router_gemm_gate: activations must be bf16 or fp16");
     const int grid = (T + kTokPerCta - 1) / kTokPerCta;
-    const size_t smem = (size_t)kTokPerCta * (2 * E + 2 * n_groups) * sizeof(float);
+    // logits [tokens][E] + the larger of the per-warp partial sums [8][tokens][E] and the routing scratch
+    const size_t smem = (size_t)kTokPerCta * (E + std::max(8 * E, E + 2 * n_groups)) * sizeof(float);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(256);
