@@ -27,9 +27,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
                                                         const int32_t* __restrict__ experts_map, int n_global,
                                                         int4* __restrict__ worklist, int block_slots) {
     __shared__ int cnt[kMaxExperts];
-    __shared__ int start[kMaxExperts];    // padded exclusive prefix
     __shared__ int cursor[kMaxExperts];
-    __shared__ int item0[kMaxExperts];    // exclusive prefix of work items
     __shared__ int warp_tot[32], warp_tot2[32], warp_tot3[32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
@@ -81,9 +79,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
     const int excl2 = base2 + incl2 - items;
     const int excl3 = ((warp > 0) ? warp_tot3[warp - 1] : 0) + incl3 - c;
     if (tid < E) {
-        start[tid] = excl;
         cursor[tid] = excl;
-        item0[tid] = excl2;
         cumsum[tid] = excl + c;
         for (int b = excl / mbs; b < (excl + padded) / mbs; ++b) block_expert[b] = tid;
         if (worklist != nullptr)
