@@ -303,6 +303,8 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
     const long long want = std::min<long long>(m.T, mean2);
     int nt_tiles = want <= 8 ? 1 : (want <= 16 ? 2 : (want <= 32 ? 4 : 8));
     if (m.nt == 1 || m.nt == 2 || m.nt == 4 || m.nt == 8) nt_tiles = m.nt;
+    // 16 tiles (128 slots per work item) exist for the tcgen05 kernels with 16-bit weights only
+    if (m.nt == 16) nt_tiles = (wt != kE4M3 && m.wm1 >= 100 && m.wm2 >= 100 && m.scratch != nullptr) ? 16 : 8;
     const int block_slots = nt_tiles * 8;
     const int max_items = (int)std::min<long long>(slots, (long long)std::min<long long>(m.E, slots) + slots / block_slots);
 
@@ -315,6 +317,7 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
     const size_t wl_bytes = 16 * (size_t)(max_items + 1);
     const bool umma = (wt != kE4M3 || !scale) && m.wm1 >= 100 && m.wm2 >= 100 && m.scratch != nullptr && m.I % 128 == 0 &&
                       m.H % 128 == 0 && (long long)slots * m.H * 4 <= m.scratch_bytes;
+    if (nt_tiles == 16 && !umma) return fail(kInvalidArg, "fused_experts_compute: 128-slot work items need the tcgen05 kernels (sizes multiples of 128, combine scratch)");
 
     if (!umma && (m.wm1 >= 100 || m.wm2 >= 100)) {
         // tuned for the tcgen05 kernels but this call cannot use them: the warp-level kernels choose for themselves

@@ -1,7 +1,7 @@
-// Fused-MoE expert GEMMs on the 5th-generation tensor cores (16-bit weights, 16..64 slots per work item).
+// Fused-MoE expert GEMMs on the 5th-generation tensor cores (16..128 slots per work item; 16..64 with e4m3 weights).
 //
 // Same tile and pipeline as dense_umma.cu in cluster mode: 128 weight rows are the UMMA M dimension, the slots of one
-// work item (one expert, up to 64 of its routed slots) the N dimension, TMA feeds a shared-memory ring, one thread
+// work item (one expert, up to 128 of its routed slots) the N dimension, TMA feeds a shared-memory ring, one thread
 // issues tcgen05.mma into tensor memory, the k range is split over the CTAs of a cluster and the partial tiles are
 // added through distributed shared memory in a fixed order.  What is specific to the MoE:
 //   * the grid is (row tiles, cluster, work items); the work list is the one the alignment kernel writes, items past
@@ -210,24 +210,35 @@ __global__ void __launch_bounds__(192, 2) moe_umma_kernel(const __grid_constant_
             abort_flag = 1;
         }
         __syncwarp();
-        if (!abort_flag) {
+    }
+    __syncwarp();
+
+    // Epilogue in chunks of at most 64 slots, so that the partial tiles [which][slot][accumulator row] of a chunk fit
+    // in the idle ring even for 128-slot work items.
+    constexpr int CHUNK = NP > 64 ? 64 : NP;
+#pragma unroll 1
+    for (int cb = 0; cb < NP; cb += CHUNK) {
+        if (warp >= 2 && !abort_flag) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int quad = warp & 3, lrow = quad * 32 + lane;
             float* const red = reinterpret_cast<float*>(base_ptr);
 #pragma unroll
-            for (int c0 = 0; c0 < NA * NP; c0 += 16) {
-                uint32_t r[16];
-                tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + c0, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            for (int w = 0; w < NA; ++w)
 #pragma unroll
-                for (int i = 0; i < 16; ++i) red[(c0 + i) * kTileM + lrow] = __uint_as_float(r[i]);
-            }
+                for (int c0 = 0; c0 < CHUNK; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + w * NP + cb + c0, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) red[(w * CHUNK + c0 + i) * kTileM + lrow] = __uint_as_float(r[i]);
+                }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         }
+        __syncwarp();
+        const int left = nslots - cb;
+        moe_cluster_epilogue<WT, CHUNK, MODE, false>(p, base, tile, rank, SK, left < 0 ? 0 : (left > CHUNK ? CHUNK : left),
+                                                     pos0 + cb, cpos0 + cb, tid);
     }
-    __syncwarp();
-
-    moe_cluster_epilogue<WT, NP, MODE, false>(p, base, tile, rank, SK, nslots, pos0, cpos0, tid);
 
     // ---- teardown ----
     if (warp == 0 && lane == 0 && abort_flag) {
@@ -503,6 +514,7 @@ const void* moe_kernel_for(int np, int stages) {
         case 16: return moe_kernel_for_stages<WT, 16, MODE>(stages);
         case 32: return moe_kernel_for_stages<WT, 32, MODE>(stages);
         case 64: return moe_kernel_for_stages<WT, 64, MODE>(stages);
+        case 128: return moe_kernel_for_stages<WT, 128, MODE>(stages);
     }
     return nullptr;
 }
@@ -542,7 +554,7 @@ int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, con
     if (kern == nullptr) return fail(kInvalidArg, "moe (tcgen05): token tile %d / stages %d not built", np, stages);
     const int na = mode == 1 ? 2 : 1;
     const size_t smem = f8 ? std::max((size_t)stages * na * kRawBytes, (size_t)na * np * 512) + (size_t)kF8ConvStages * np * 128 + 1024
-                           : std::max((size_t)stages * (na * kABytes + np * 128), (size_t)na * np * 512) + 1024;
+                           : std::max((size_t)stages * (na * kABytes + np * 128), (size_t)na * std::min(np, 64) * 512) + 1024;
     if (smem > 227 * 1024) return fail(kUnsupported, "moe (tcgen05): %d stages do not fit in shared memory", stages);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(kCudaError, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));

@@ -79,7 +79,7 @@ def scan_case(cfg, T, w1, w2, wg, g, dev):
                 best_args, best_us = args, us
     if H % 128 == 0 and I % 128 == 0:
         # tcgen05 expert GEMMs (16-bit weights, or e4m3 without block scales): wm = 100 + ring stages, sk = CTAs per cluster
-        for nt in [n for n in (1, 2, 4, 8) if n * 8 <= max(8, 2 * T)]:
+        for nt in [n for n in (1, 2, 4, 8) + (() if fp8 else (16,)) if n * 8 <= max(8, 2 * T)]:
             g1_best, g1_us = None, float("inf")
             for st1, ck1 in itertools.product([2, 3, 4], [1, 2, 4]):
                 us = try_args((nt, 100 + st1, ck1, 0, 103, 4))

@@ -271,9 +271,10 @@ def test_moe_16bit_tcgen05_expert_gemms(dt, T):
     w1 = randn((E, 2 * I, H), 701, 0.05, DT[dt])
     w2 = randn((E, H, I), 702, 0.05, DT[dt])
     logits = randn((T, E), 703 + T, 1.0, DT[dt])
-    for tune in [(2, 102, 1, 0, 102, 1), (4, 103, 2, 0, 104, 3), (8, 104, 4, 0, 106, 6), (1, 102, 2, 0, 103, 2)]:
+    for tune in [(2, 102, 1, 0, 102, 1), (4, 103, 2, 0, 104, 3), (8, 104, 4, 0, 106, 6), (1, 102, 2, 0, 103, 2),
+                 (16, 102, 2, 0, 103, 2)]:
         y = _moe_compare(x, w1, w2, logits, topk, f"moe tcgen05 {dt} T={T} tune={tune}", tune=tune)
-        y0 = _moe_compare(x, w1, w2, logits, topk, f"moe warp-level {dt} T={T}", tune=(tune[0], 2, 1, 1, 2, 1))
+        y0 = _moe_compare(x, w1, w2, logits, topk, f"moe warp-level {dt} T={T}", tune=(min(tune[0], 8), 2, 1, 1, 2, 1))
         # both paths sum the same fp32 products in different orders: results agree to rounding
         assert_close(y, y0.cpu(), f"tcgen05 vs warp-level {dt} T={T} tune={tune}", scale_atol=True)
 
