@@ -255,7 +255,11 @@ __global__ void __launch_bounds__(192, 2) moe_umma_kernel(const __grid_constant_
 // (pipeline of dense_umma_f8.cu; NA weight tiles per stage share the token tile; activations are bf16)
 constexpr int kRawBytes = kTileM * kBlockK;      // 8 KB of e4m3 per tile and stage
 constexpr int kAColumns = kBlockK / 2;           // 32-bit tensor-memory columns of one decoded tile
-constexpr int kF8ConvStages = 2;
+// Decoded weight tiles kept in tensor memory (= depth of the token-tile ring): as many as fit beside the accumulators
+// in 128 columns, so that four CTAs share an SM's tensor memory; the 64-slot gate/up kernel needs 256 columns anyway.
+constexpr int f8_conv_stages(int na, int np) {
+    return na == 2 ? (np <= 32 ? 1 : 2) : (np <= 32 ? 3 : 2);
+}
 
 template <int NP, int STAGES, int MODE>
 __global__ void __launch_bounds__(192, 2) moe_umma_f8_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -263,7 +267,7 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8_kernel(const __grid_consta
                                                              const MoeUmmaParams p, const int static_weights) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int NA = MODE == 1 ? 2 : 1;
-    constexpr int S2 = kF8ConvStages;
+    constexpr int S2 = f8_conv_stages(NA, NP);
     constexpr int kBBytes = NP * 128;
     constexpr int kStageBytes = NA * kRawBytes;
     constexpr int kRingBytes = STAGES * kStageBytes > NA * NP * 512 ? STAGES * kStageBytes : NA * NP * 512;
@@ -553,7 +557,7 @@ int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, con
     else kern = wt == kFP16 ? moe_kernel_for<kFP16, 2>(np, stages) : moe_kernel_for<kBF16, 2>(np, stages);
     if (kern == nullptr) return fail(kInvalidArg, "moe (tcgen05): token tile %d / stages %d not built", np, stages);
     const int na = mode == 1 ? 2 : 1;
-    const size_t smem = f8 ? std::max((size_t)stages * na * kRawBytes, (size_t)na * np * 512) + (size_t)kF8ConvStages * np * 128 + 1024
+    const size_t smem = f8 ? std::max((size_t)stages * na * kRawBytes, (size_t)na * np * 512) + (size_t)f8_conv_stages(na, np) * np * 128 + 1024
                            : std::max((size_t)stages * (na * kABytes + np * 128), (size_t)na * std::min(np, 64) * 512) + 1024;
     if (smem > 227 * 1024) return fail(kUnsupported, "moe (tcgen05): %d stages do not fit in shared memory", stages);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
