@@ -331,11 +331,12 @@ def test_graphed_fused_moe_replays_bit_exactly():
         layer(x[:3], logits[:3])
 
 
-def test_moe_expert_parallel_map_sums_to_full_layer():
+@pytest.mark.parametrize("tune", [None, (2, 102, 2, 0, 103, 2)])
+def test_moe_expert_parallel_map_sums_to_full_layer(tune):
     """experts_map is the reference's only multi-GPU hook (csrc/moe_kernels/moe_align_tokens.h:46-49): each rank
-    computes its local experts' share of y; the shares add up to the full layer."""
+    computes its local experts' share of y; the shares add up to the full layer (warp-level and tcgen05 kernels)."""
     dev = require_gpu()
-    E, topk, H, I, T = 16, 4, 128, 64, 40
+    E, topk, H, I, T = 16, 4, 128, 128, 40
     x = randn((T, H), 700).to(dev)
     w1 = mlk.layoutA(randn((E, 2 * I, H), 701, 0.05).to(dev))
     w2 = mlk.layoutA(randn((E, H, I), 702, 0.05).to(dev))
@@ -347,7 +348,7 @@ def test_moe_expert_parallel_map_sums_to_full_layer():
         emap = torch.full((E,), -1, dtype=torch.int32)
         emap[lo:lo + 4] = torch.arange(4, dtype=torch.int32)
         part = planC_moe(x, w1[lo:lo + 4].contiguous(), w2[lo:lo + 4].contiguous(), logits, topk, True,
-                         experts_map=emap.to(dev))
+                         experts_map=emap.to(dev), tune=tune)
         acc += part.float()
     assert_close(acc, full.cpu(), "EP shares", atol=2e-2, rtol=2e-2)
 
