@@ -110,7 +110,9 @@ def golden_dense():
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference project>")
+    ref_root = sys.argv[1]
     ref_utils = import_reference(ref_root)
     torch.set_num_threads(1)   # fixed summation order inside torch's CPU GEMM
     golden_layouts()
