@@ -112,7 +112,7 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
  *   the (128-row tile, 64-wide k block) work units evenly; kernelParam1 = CTAs per SM the grid is sized for (1..4),
  *   kernelParam2 = TMA pipeline stages (2,3,4,5,6,8), kernelParam3 = 0 or 1.  Splitting tiles between CTAs needs
  *   the caller-provided scratch below; without it the kernel runs one CTA per tile.
- *   kernelParam3 = 2..8 selects the other decomposition of the same kernel: one thread-block cluster of that many
+ *   kernelParam3 = 2..16 selects the other decomposition of the same kernel: one thread-block cluster of that many
  *   CTAs per 128-row tile, each CTA streaming an equal share of k, partial tiles added through distributed shared
  *   memory (no scratch needed; kernelParam1 is ignored).
  *   With e4m3 weights (soft_fp8 entry points, no block scales) kernelId 2 is the TMA -> convert -> tcgen05

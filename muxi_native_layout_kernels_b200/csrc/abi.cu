@@ -109,7 +109,7 @@ int gemm_table(int table, int variant_x, int variant_c, const void* A, const flo
                      t.c <= twarps && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b * t.c) == 0;
     const bool ok2 = t.a == 2 && (variant_x == 0 || dtype != MLK_E4M3) && n <= 64 &&
                      (dtype != MLK_E4M3
-                          ? (t.b >= 1 && t.b <= 4 && ((t.c >= 2 && t.c <= 6) || t.c == 8) && t.d >= 0 && t.d <= 8)
+                          ? (t.b >= 1 && t.b <= 4 && ((t.c >= 2 && t.c <= 6) || t.c == 8) && t.d >= 0 && t.d <= 16)
                           : (scale == nullptr && (t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 && t.d <= 8));
     const bool ok5 = t.a >= 5 && t.a <= 7 && n <= 4 && variant_x == 0 && variant_c == 0 && dtype != MLK_E4M3 &&
                      (t.b == 1 || t.b == 2) && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b) == 0;

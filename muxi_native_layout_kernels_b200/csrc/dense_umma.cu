@@ -109,7 +109,9 @@ constexpr uint32_t kPollLimit = 1u << 22;   // counter polls (64 ns apart) befor
 
 // CLUSTER = false: persistent stream-K grid; true: one cluster per tile (gridDim.y = cluster size), which needs none of
 // the workspace code paths and so fits two 64-token CTAs per SM.
-template <int WT, int NP, int STAGES, bool CLUSTER>
+// (CLUSTER = 2: clusters of up to 16 CTAs, a non-portable size that needs its own kernel attribute; kept apart
+// because the attribute and the longer reduction loop cost the ordinary cluster kernel 0.3-1 us per launch)
+template <int WT, int NP, int STAGES, int CLUSTER>
 __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const __grid_constant__ CUtensorMap map_a,
                                                          const __grid_constant__ CUtensorMap map_x, const UmmaParams p,
                                                          const int static_weights) {
@@ -481,24 +483,25 @@ __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const 
             const int etid = tid - 64;
             const int rank = blockIdx.y;
             const int r0 = kTileM * rank / SK, rows = kTileM * (rank + 1) / SK - r0;
-            uint32_t remote[8];
+            constexpr int kMaxSK = CLUSTER == 2 ? 16 : 8;
+            uint32_t remote[kMaxSK];
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
+            for (int q = 0; q < kMaxSK; ++q)
                 asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[q]) : "r"(base), "r"(q < SK ? q : 0));
             const int total = p.n * rows;
             for (int idx = etid; idx < total; idx += 128) {
                 const int c = idx / rows, rho = r0 + idx - c * rows;
                 const uint32_t off = (uint32_t)(c * kTileM + rho) * 4u;
-                float t[8];
+                float t[kMaxSK];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
+                for (int q = 0; q < kMaxSK; ++q) {
                     t[q] = 0.f;
                     if (q < SK) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(t[q]) : "r"(remote[q] + off) : "memory");
                 }
                 float acc = 0.f;
                 bool first = true;
 #pragma unroll
-                for (int q = 7; q >= 0; --q) {
+                for (int q = kMaxSK - 1; q >= 0; --q) {
                     if (q < SK) {
                         acc = first ? t[q] : acc + t[q];
                         first = false;
@@ -557,7 +560,7 @@ bool make_map_a(CUtensorMap* map, const void* A, int m, int k, int wt) {
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int WT, int NP, bool CLUSTER>
+template <int WT, int NP, int CLUSTER>
 const void* kernel_for_stages(int stages) {
     switch (stages) {
         case 2: return reinterpret_cast<const void*>(dense_umma_kernel<WT, NP, 2, CLUSTER>);
@@ -570,7 +573,7 @@ const void* kernel_for_stages(int stages) {
     return nullptr;
 }
 
-template <int WT, bool CLUSTER>
+template <int WT, int CLUSTER>
 const void* kernel_for(int np, int stages) {
     switch (np) {
         case 16: return kernel_for_stages<WT, 16, CLUSTER>(stages);
@@ -589,7 +592,7 @@ size_t smem_bytes(int np, int stages, bool clustered) {
 // Resident CTAs per SM of one kernel instantiation on the current device (0 = error); the first call also raises
 // the kernel's dynamic shared-memory limit.  The grid is persistent: it is never made larger than what is
 // resident at once.
-int resident_ctas_per_sm(const void* kern, size_t smem) {
+int resident_ctas_per_sm(const void* kern, size_t smem, bool big_clusters) {
     static std::mutex mu;
     static std::unordered_map<unsigned long long, int> cache;
     int dev = 0;
@@ -599,6 +602,7 @@ int resident_ctas_per_sm(const void* kern, size_t smem) {
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
     int occ = 0;
+    if (big_clusters) cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);   // up to 16 CTAs
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, 192, smem) != cudaSuccess)
         occ = 0;
@@ -622,7 +626,7 @@ int umma_max_parts(int tiles, int kblocks, int G) {
 
 // ctas_per_sm: resident CTAs per SM the grid is sized for (grid = ctas_per_sm * SM count, capped by the number of
 // work units); stages: ring depth (2, 3, 4, 5, 6 or 8; a ring of at most about 110 KB lets two launches share an
-// SM); cluster_k: 0 or 1 = the persistent stream-K grid described above, 2..8 = one thread-block cluster of that
+// SM); cluster_k: 0 or 1 = the persistent stream-K grid described above, 2..16 = one thread-block cluster of that
 // many CTAs per 128-row tile, each CTA taking an equal share of k, partial tiles added through distributed shared
 // memory (no workspace; meant for shapes with few tiles and a long k, where stream-K would share every tile among
 // many CTAs that all finish at the same moment).
@@ -641,13 +645,14 @@ int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages,
     const int np = p.n <= 16 ? 16 : (p.n <= 32 ? 32 : 64);
     const int tiles = p.m / kTileM;
     const int kblocks = p.k / kBlockK;
-    if (cluster_k < 0 || cluster_k > 8) return fail(kInvalidArg, "dense (tcgen05): cluster split must be 0..8 (got %d)", cluster_k);
+    if (cluster_k < 0 || cluster_k > 16) return fail(kInvalidArg, "dense (tcgen05): cluster split must be 0..16 (got %d)", cluster_k);
     const bool clustered = cluster_k > 1;
-    const void* kern = clustered ? (wt == kFP16 ? kernel_for<kFP16, true>(np, stages) : kernel_for<kBF16, true>(np, stages))
-                                 : (wt == kFP16 ? kernel_for<kFP16, false>(np, stages) : kernel_for<kBF16, false>(np, stages));
+    const void* kern = cluster_k > 8 ? (wt == kFP16 ? kernel_for<kFP16, 2>(np, stages) : kernel_for<kBF16, 2>(np, stages))
+                       : clustered   ? (wt == kFP16 ? kernel_for<kFP16, 1>(np, stages) : kernel_for<kBF16, 1>(np, stages))
+                                     : (wt == kFP16 ? kernel_for<kFP16, 0>(np, stages) : kernel_for<kBF16, 0>(np, stages));
     if (kern == nullptr) return fail(kInvalidArg, "dense (tcgen05): stages must be one of 2, 3, 4, 5, 6, 8 (got %d)", stages);
     const size_t smem = smem_bytes(np, stages, clustered);
-    const int resident = resident_ctas_per_sm(kern, smem);
+    const int resident = resident_ctas_per_sm(kern, smem, cluster_k > 8);
     if (resident < 1) return fail(kCudaError, "dense (tcgen05): a CTA with %d stages does not fit on this device", stages);
     if (ctas_per_sm > resident) ctas_per_sm = resident;
     if (clustered && cluster_k > p.k / kBlockK) return fail(kInvalidArg, "dense (tcgen05): cluster split %d exceeds the %d k blocks", cluster_k, p.k / kBlockK);

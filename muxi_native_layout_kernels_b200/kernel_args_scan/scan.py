@@ -128,7 +128,7 @@ def candidates(kind, m, n, k):
         # (1, ring stages, cluster size) = one cluster per 128-row tile, k split inside the cluster
         if kind == "a":       # the persistent grid needs the scratch only the layout-A entry points pass
             cands += [(2, 1, 4, 0), (2, 1, 5, 0), (2, 1, 6, 0), (2, 1, 8, 0), (2, 2, 3, 0), (2, 2, 4, 0)]
-        for ck in (2, 3, 4, 5, 6, 7, 8):
+        for ck in (2, 3, 4, 5, 6, 7, 8, 12, 16):
             for st in (2, 3, 4, 5, 6, 8):
                 np_ = 16 if n <= 16 else (32 if n <= 32 else 64)
                 smem = st * (16384 + np_ * 128) + 2048

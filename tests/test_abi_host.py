@@ -102,7 +102,7 @@ def test_packaged_table_rows_name_launches_the_library_accepts():
                 assert p1 in (1, 2) and p2 in (1, 2, 4, 8) and p2 <= {1: 8, 3: 4, 4: 2}[kid] and p3 in (1, 2, 4, 8), what
                 assert m % (16 * p1 * p2) == 0, what
             elif kid == 2 and not fp8:
-                assert n <= 64 and 1 <= p1 <= 4 and p2 in (2, 3, 4, 5, 6, 8) and 0 <= p3 <= 8, what
+                assert n <= 64 and 1 <= p1 <= 4 and p2 in (2, 3, 4, 5, 6, 8) and 0 <= p3 <= 16, what
                 assert layout_a or (n % 16 == 0 and p3 >= 2), what     # layout-B variants pass no scratch: cluster mode
                 assert p3 < 2 or p3 <= k // 64, what
             elif kid == 2 and fp8:

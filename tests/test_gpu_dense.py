@@ -279,7 +279,7 @@ def test_gemm_tcgen05_tile_kernel(dt):
                 C = mlk.gemm_layoutA_wapper(A, X.to(dev), m, n, k, kernelParam1=sk, kernelParam2=stages, kernelId=2)
                 assert_close(C, want, f"tcgen05 {dt} m={m} k={k} n={n} sk={sk} stages={stages}")
             # thread-block-cluster split-K: partial tiles are added through distributed shared memory
-            for ck, stages in [(2, 4), (3, 2), (4, 6), (8, 8)]:
+            for ck, stages in [(2, 4), (3, 2), (4, 6), (8, 8), (16, 3)]:
                 if ck > k // 64:
                     continue
                 C = mlk.gemm_layoutA_wapper(A, X.to(dev), m, n, k, kernelParam1=1, kernelParam2=stages, kernelParam3=ck,
