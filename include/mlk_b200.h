@@ -57,8 +57,17 @@ const char* mlk_build_info(void);
  *   MLK_OPT_STATIC_WEIGHTS (default 0): promise that weight tensors (A, w1, w2, block scales) are not written by any
  *     kernel of the calling stream while these ops are in flight (weights prepacked once, the serving situation).
  *     The dense kernels then start streaming weights before that wait.  Leave it 0 if a kernel that produces
- *     weights (e.g. mlk_layoutA) can immediately precede a GEMM on the same stream. */
-enum { MLK_OPT_PDL = 0, MLK_OPT_STATIC_WEIGHTS = 1 };
+ *     weights (e.g. mlk_layoutA) can immediately precede a GEMM on the same stream.
+ *   MLK_OPT_FULL_SCALES (default 0): how the tcgen05 e4m3 kernels apply a 128x128 block scale s in the decode.
+ *     0: s is rounded to bf16 and folded into the decode's one packed multiply: weight = rne_bf16(w * bf16(s)), no
+ *        extra instruction (unit scales, powers of two and other 8-bit scales are exact);
+ *     1: s enters as two bf16 terms (16 significant bits) through a packed multiply and a packed fused multiply-add:
+ *        weight = rne_bf16(w * s) up to a 2^-17 slip of the rounding boundary, what the reference's torch recipe
+ *        dequantises to (muxi_layout_kernels/utils.py:14-25); the decode is the bottleneck of these kernels, so
+ *        this costs throughput (measured: 1.2-1.6x the time).
+ *     The reference's kernels truncate fp32(w) * s to bf16; every form stays within one bf16 ulp per weight of the
+ *     exact product.  The warp-level kernels (kernelId 1, 3, 4) apply s to the fp32 sums of each 128-wide k block. */
+enum { MLK_OPT_PDL = 0, MLK_OPT_STATIC_WEIGHTS = 1, MLK_OPT_FULL_SCALES = 2 };
 int mlk_set_option(int option_id, int value);
 int mlk_get_option(int option_id);
 
@@ -90,7 +99,7 @@ int mlk_fp8_weight_repack(const void* weight, void* out, int64_t nbytes, mlk_str
 /* Explicit tuning arguments.  Reference: gemv_layoutA_wapper, csrc/gemv_layout_a.cu:17-71.
  *   kernelId 1: tensor-core streaming kernel, kernelParam1 = row groups per warp (1,2), kernelParam2 = split-K (1,2,4,8)
  *   kernelId 2: CUDA-core FMA + shuffle kernel, same two parameters (bf16/fp16 only)
- *   kernelId 3: e4m3 only, no block scales, m % 128 == 0, k % 64 == 0: the TMA -> convert -> tcgen05 pipeline of the
+ *   kernelId 3: e4m3 only, m % 128 == 0, k % 64 == 0: the TMA -> convert -> tcgen05 pipeline of the
  *               soft-FP8 GEMM (see kernelId 2 there); kernelParam1 = raw ring stages (2,3,4,6,8), kernelParam2 =
  *               cluster size (1..8), blockDimX ignored
  *   scale_matrix: e4m3 only, fp32 [ceil(m/128)][ceil(k/128)], may be NULL (= all ones)
@@ -115,9 +124,12 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
  *   kernelParam3 = 2..16 selects the other decomposition of the same kernel: one thread-block cluster of that many
  *   CTAs per 128-row tile, each CTA streaming an equal share of k, partial tiles added through distributed shared
  *   memory (no scratch needed; kernelParam1 is ignored).
- *   With e4m3 weights (soft_fp8 entry points, no block scales) kernelId 2 is the TMA -> convert -> tcgen05
- *   pipeline: the e4m3 tile is decoded to bf16 in shared memory by the four warps that later run the epilogue;
+ *   With e4m3 weights (soft_fp8 entry points) kernelId 2 is the TMA -> convert -> tcgen05 pipeline: the e4m3
+ *   tile is decoded to bf16 into tensor memory by the four warps that later run the epilogue;
  *   kernelParam2 = stages of the raw e4m3 ring (2,3,4,6,8), kernelParam3 = cluster size (1..8), kernelParam1 ignored.
+ *   Block scales are applied in the decode as rne_bf16(w * s), the weight the reference's torch recipe
+ *   (muxi_layout_kernels/utils.py:14-25) dequantises to; kernelId 1, 3, 4 apply s to the fp32 sums of each 128-wide
+ *   k block instead, and the reference's kernels truncate fp32(w) * s to bf16: all within one bf16 ulp per weight.
  * kernelId 5, 6, 7 (CUDA-core FMA + shuffle kernel with 256, 128, 64 threads; 16-bit weights, row-major B and C,
  *   n <= 4): kernelParam1 = row groups per warp (1,2), kernelParam2 unused, kernelParam3 = cluster split-K. */
 

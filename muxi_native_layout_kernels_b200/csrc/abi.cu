@@ -27,7 +27,7 @@ const char* last_error() { return g_err; }
 void clear_error() { g_err[0] = 0; }
 
 namespace {
-int g_options[kNumOptions] = {1, 0};
+int g_options[kNumOptions] = {1, 0, 0};
 }
 int option(int which) { return (which >= 0 && which < kNumOptions) ? g_options[which] : 0; }
 void set_option(int which, int value) {
@@ -71,8 +71,7 @@ int gemm_common(int variant_x, int variant_c, const void* A, const float* scale,
     p.x_layout = variant_x; p.c_layout = variant_c; p.fp8_order = fp8_order;
     if (kernelId == 2 && wt == kE4M3) {
         // TMA -> convert -> tcgen05 pipeline for e4m3 weights: kernelParam2 = raw ring stages, kernelParam3 = cluster
-        // size; weights with block scales stay on the warp-level kernel
-        if (scale != nullptr) return fail(kUnsupported, "gemm: kernelId 2 does not apply block scales; use kernelId 1, 3 or 4");
+        // size; block scales ride on the decode (rounded to bf16 first, as the reference's torch check does)
         if (variant_c != 0 && n % 16 != 0) return fail(kInvalidArg, "gemm: layout C needs n %% 16 == 0");
         return launch_dense_umma_f8(p, p2, p3 < 1 ? 1 : p3, aux ? aux->status : nullptr, s);
     }
@@ -110,10 +109,14 @@ int gemm_table(int table, int variant_x, int variant_c, const void* A, const flo
     const bool ok2 = t.a == 2 && (variant_x == 0 || dtype != MLK_E4M3) && n <= 64 &&
                      (dtype != MLK_E4M3
                           ? (t.b >= 1 && t.b <= 4 && ((t.c >= 2 && t.c <= 6) || t.c == 8) && t.d >= 0 && t.d <= 16)
-                          : (scale == nullptr && (t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 && t.d <= 8));
+                          : ((t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 && t.d <= 8));
     const bool ok5 = t.a >= 5 && t.a <= 7 && n <= 4 && variant_x == 0 && variant_c == 0 && dtype != MLK_E4M3 &&
                      (t.b == 1 || t.b == 2) && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b) == 0;
     if (!ok1 && !ok2 && !ok5) t = default_args(table, m, n, k);
+    // the tcgen05 kernel reads through tensor maps, which want 16-byte aligned bases; e4m3 activations in layout B
+    // have no tcgen05 variant
+    if (t.a == 2 && ((((uintptr_t)A | (uintptr_t)B) & 15) != 0 || (variant_x != 0 && dtype == MLK_E4M3)))
+        t = warp_level_default_args(table, m, n, k);
     return gemm_common(variant_x, variant_c, A, scale, B, C, m, n, k, dtype, alpha, t.b, t.c, t.d, t.a, bias,
                        fp8_order, s, aux);
 }
@@ -217,7 +220,6 @@ int mlk_gemv_layoutA_wapper(const void* A, const void* x, void* y, int m, int k,
     if (kernelId == 2) return launch_gemv_simt(wt, p, 0, (cudaStream_t)s);
     if (kernelId == 3 && wt == kE4M3) {
         // TMA -> convert -> tcgen05 pipeline: kernelParam1 = raw ring stages, kernelParam2 = cluster size
-        if (scale_matrix != nullptr) return fail(kUnsupported, "gemv: kernelId 3 does not apply block scales; use kernelId 1");
         return launch_dense_umma_f8(p, kernelParam1, kernelParam2, nullptr, (cudaStream_t)s);
     }
     return fail(kUnsupported, "gemv: kernelId %d is not built (1 = tensor-core, 2 = CUDA-core, 3 = tcgen05 for e4m3)", kernelId);
@@ -234,7 +236,7 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
     // Same safety net as the reference (csrc/gemv_layout_a.cu:132-143): a row that cannot run falls back.
     const bool ok = (t.a == 64 || t.a == 128 || t.a == 256) && (t.b == 1 || (t.b == 2 && dtype != MLK_E4M3)) &&
                     (t.c == 1 || t.c == 2) && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.c) == 0;
-    const bool ok3 = dtype == MLK_E4M3 && t.b == 3 && scale_matrix == nullptr && m % 128 == 0 && k % 64 == 0 &&
+    const bool ok3 = dtype == MLK_E4M3 && t.b == 3 && m % 128 == 0 && k % 64 == 0 &&
                      (t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 && t.d <= 8;
     if (!ok && !ok3) t = default_args(table, m, 1, k);
     return mlk_gemv_layoutA_wapper(A, x, y, m, k, dtype, alpha, beta, t.a, t.b, t.c, t.d, scale_matrix, bias,

@@ -96,13 +96,73 @@ constexpr uint32_t kSelNat23 = 0x4342;  // natural order: bytes 2,3
 constexpr uint32_t kSelRep01 = 0x4240;  // "1324" repacked word [b0,b2,b1,b3]: elements 0,1
 constexpr uint32_t kSelRep23 = 0x4341;  // repacked: elements 2,3
 
-__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t w, uint32_t sel) {
+constexpr uint32_t kRebias2 = 0x7B807B80u;   // 2^120 in both halves
+
+// The same decode with the re-biasing factor supplied by the caller: `c2` holds one bf16 in both halves.  With
+// c2 = 2^120 the result is the exact value.
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2_by(uint32_t w, uint32_t sel, uint32_t c2) {
     uint32_t v = __byte_perm(w, 0u, sel);        // [b_lo, 0, b_hi, 0]
     uint32_t x = (v << 4) + 0x78007800u;         // carries the sign from bit 11 up to bit 15
     x &= 0x87F087F0u;                            // s0000eeeemmm0000 per half
     uint32_t r;
-    asm("mul.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(0x7B807B80u));  // * 2^120, exact
+    asm("mul.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(c2));
     return r;
+}
+
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t w, uint32_t sel) {
+    return e4m3x2_to_bf16x2_by(w, sel, kRebias2);   // * 2^120, exact
+}
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+
+// Block-scaled decode.  The scale s of a 128 x 128 block enters the packed arithmetic of the decode in one of two forms:
+//   one term   bf16(s) folded into the re-biasing factor: rne_bf16(value * bf16(s)), the same instruction count as
+//              the unscaled decode;
+//   two terms  s = hi + lo in bf16 (16 significant bits): value * hi is exact inside the fused multiply-add (4 x 8
+//              bits), value * lo is a correction below half an ulp of the result, so the sum is rne_bf16(value * s)
+//              up to a 2^-17 relative slip of the rounding boundary: the number the reference's torch check
+//              dequantises to (muxi_layout_kernels/utils.py:14-25).
+// The reference's kernels truncate fp32(value) * s to bf16; all forms are within one bf16 ulp of the exact product.
+struct ScaledRebias {
+    uint32_t pre2;         // first factor, both halves: 2^120 (exact decode) or 1.0 when 2^120 is folded into hi/lo
+    uint32_t hi2, lo2;     // the two terms of the scale, both halves
+    bool one_multiply;     // value = raw * hi2 is all there is to do
+};
+
+__device__ __forceinline__ ScaledRebias scaled_rebias(float s, bool two_terms) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(s);
+    const float rest = (two_terms && fabsf(s) <= 3.0e38f) ? s - __bfloat162float(h) : 0.f;
+    const __nv_bfloat16 l = __float2bfloat16_rn(rest);
+    const uint32_t hb = (uint32_t)__bfloat16_as_ushort(h), lb = (uint32_t)__bfloat16_as_ushort(l);
+    const uint32_t he = (hb >> 7) & 0xFFu, le = (lb >> 7) & 0xFFu;
+    const bool lzero = (lb & 0x7FFFu) == 0u;
+    // multiplying a normal bf16 by 2^120 adds 120 to its exponent field; terms that leave the normal range that way
+    // (|s| >= 256, zero, subnormal) are applied after an exact decode instead
+    const bool folded = he >= 1u && he < 127u + 8u && (le >= 1u || lzero);
+    const uint32_t hx = folded ? hb + (120u << 7) : hb;
+    const uint32_t lx = (folded && le >= 1u) ? lb + (120u << 7) : lb;
+    ScaledRebias r;
+    r.pre2 = folded ? 0x3F803F80u : kRebias2;
+    r.hi2 = hx | (hx << 16);
+    r.lo2 = lx | (lx << 16);
+    r.one_multiply = folded && lzero;
+    return r;
+}
+
+// general form: (raw * pre) * hi + (raw * pre) * lo, three packed operations
+__device__ __forceinline__ uint32_t e4m3x2_scaled(uint32_t w, uint32_t sel, const ScaledRebias& r) {
+    const uint32_t e = e4m3x2_to_bf16x2_by(w, sel, r.pre2);
+    return fma_bf16x2(e, r.hi2, mul_bf16x2(e, r.lo2));
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -15,7 +15,13 @@
 // converter warps are the epilogue warps, idle until the accumulator is complete), and the decoded weights never
 // touch shared memory: staging them there as well (raw write + raw read + bf16 write + bf16 read per byte) was
 // measured to run into the shared-memory bandwidth before HBM.
-// Block scales are not handled here (the table-driven entry points keep the warp-level kernel for scaled weights).
+// Block scales (one fp32 per 128 x 128 weights, so one per tile and k block pair) are applied in the decode.  By
+// default the scale is rounded to bf16 and folded into the factor of the decode's one packed multiply, which costs
+// nothing: weight = rne_bf16(w * bf16(s)).  With the full-scales option the scale enters as two bf16 terms (a packed
+// multiply and a packed fused multiply-add more), which yields rne_bf16(w * s), the value the reference's torch
+// check dequantises to; the decode being the bottleneck, that costs throughput (common.cuh, scaled_rebias).  The
+// reference's kernels truncate fp32(w) * s to bf16; the warp-level kernel here applies s to the fp32 sums of each
+// 128-wide k block.
 //
 // Role in the reference: GemmMmaJustLayoutASoftFp8Kernel (csrc/gemm_layout_A_soft_fp8.cu), which decodes in registers.
 #include <algorithm>
@@ -43,6 +49,9 @@ struct F8Params {
     int c_layout;
     int kblocks;
     uint32_t sel01, sel23;   // byte selectors of the decode (natural or repacked order)
+    const float* scale;      // fp32 block scales [m/128][scale_ld], one per 128 x 128 weights, or null
+    int scale_ld;
+    int full_scales;         // block scales with two bf16 terms instead of one (see common.cuh, scaled_rebias)
     int* status;
 };
 
@@ -173,8 +182,16 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8_kernel(const __grid_cons
     } else if (warp >= 2) {
         // ---- converter warps, then epilogue ----
         const int quad = warp & 3, lrow = quad * 32 + lane;     // tile row = tensor-memory lane
+        // block scale of a unit: one 128-row tile is one scale row, a 64-wide k block half a scale column; the value
+        // for the next unit is requested before this unit's waits
+        const float* const srow = p.scale ? p.scale + (size_t)tile * p.scale_ld : nullptr;
+        float sc_next = (srow && nunits > 0) ? __ldg(srow + (kb0 >> 1)) : 1.f;
+        uint32_t c2 = kRebias2;
+        ScaledRebias sr{};
         for (int i = 0; i < nunits; ++i) {
             const int s = i % STAGES, s2 = i % S2;
+            const float sc = sc_next;
+            if (srow && i + 1 < nunits) sc_next = __ldg(srow + ((kb0 + i + 1) >> 1));
             bool ok = true;
             if (lane == 0) {
                 ok = !abort_flag && mbar_wait(raw_full(s), (i / STAGES) & 1);
@@ -191,13 +208,29 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8_kernel(const __grid_cons
             // [row group][k-octet][16 rows x 8 bytes]
             const uint8_t* raw = base_ptr + s * kRawBytes + (lrow >> 4) * 1024 + (lrow & 15) * 8;
             uint32_t v[32];
+            // c2: the factor of the decode's one multiply (2^120, or that times a block scale rounded to bf16); 0 = general form
+            if (srow && (i == 0 || ((kb0 + i) & 1) == 0)) {     // a scale column spans two k blocks
+                sr = scaled_rebias(sc, p.full_scales != 0);
+                c2 = sr.one_multiply ? sr.hi2 : 0u;
+            }
+            if (c2 != 0u) {
 #pragma unroll
-            for (int o = 0; o < 8; ++o) {
-                const uint2 w = *reinterpret_cast<const uint2*>(raw + o * 128);
-                v[4 * o + 0] = e4m3x2_to_bf16x2(w.x, p.sel01);
-                v[4 * o + 1] = e4m3x2_to_bf16x2(w.x, p.sel23);
-                v[4 * o + 2] = e4m3x2_to_bf16x2(w.y, p.sel01);
-                v[4 * o + 3] = e4m3x2_to_bf16x2(w.y, p.sel23);
+                for (int o = 0; o < 8; ++o) {
+                    const uint2 w = *reinterpret_cast<const uint2*>(raw + o * 128);
+                    v[4 * o + 0] = e4m3x2_to_bf16x2_by(w.x, p.sel01, c2);
+                    v[4 * o + 1] = e4m3x2_to_bf16x2_by(w.x, p.sel23, c2);
+                    v[4 * o + 2] = e4m3x2_to_bf16x2_by(w.y, p.sel01, c2);
+                    v[4 * o + 3] = e4m3x2_to_bf16x2_by(w.y, p.sel23, c2);
+                }
+            } else {
+#pragma unroll
+                for (int o = 0; o < 8; ++o) {
+                    const uint2 w = *reinterpret_cast<const uint2*>(raw + o * 128);
+                    v[4 * o + 0] = e4m3x2_scaled(w.x, p.sel01, sr);
+                    v[4 * o + 1] = e4m3x2_scaled(w.x, p.sel23, sr);
+                    v[4 * o + 2] = e4m3x2_scaled(w.y, p.sel01, sr);
+                    v[4 * o + 3] = e4m3x2_scaled(w.y, p.sel23, sr);
+                }
             }
             tmem_st32(tmem + ((uint32_t)(quad * 32) << 16) + NP + s2 * kAColumns, v);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -303,7 +336,6 @@ const void* f8_kernel_for_stages(int stages) {
 // stages: depth of the raw e4m3 ring (2, 3, 4, 6, 8; 8 KB each); cluster_k: 1..8 CTAs per 128-row tile.
 int launch_dense_umma_f8(const DenseParams& p, int stages, int cluster_k, int* status, cudaStream_t stream) {
     if (!p.A || !p.X || !p.C) return fail(kInvalidArg, "dense: null pointer");
-    if (p.scale != nullptr) return fail(kUnsupported, "dense (tcgen05, e4m3): block scales are handled by the warp-level kernel");
     if (p.x_layout != 0) return fail(kUnsupported, "dense (tcgen05): activations must be row-major");
     if (p.m % kTileM != 0 || p.k % kBlockK != 0) return fail(kInvalidArg, "dense (tcgen05): need m %% 128 == 0 and k %% 64 == 0");
     if (p.n < 1 || p.n > 64) return fail(kUnsupported, "dense (tcgen05): 1..64 tokens per launch (got %d)", p.n);
@@ -337,6 +369,9 @@ int launch_dense_umma_f8(const DenseParams& p, int stages, int cluster_k, int* s
     fp.kblocks = p.k / kBlockK;
     fp.sel01 = p.fp8_order ? kSelRep01 : kSelNat01;
     fp.sel23 = p.fp8_order ? kSelRep23 : kSelNat23;
+    fp.scale = p.scale;
+    fp.scale_ld = (p.k + 127) / 128;
+    fp.full_scales = option(kOptFullScales);
     fp.status = status;
     int static_weights = option(kOptStaticWeights);
     cudaLaunchConfig_t cfg = {};

@@ -62,7 +62,7 @@ int launch_moe_gather_positions(const void* x, const int32_t* sorted, const int4
                                 int max_items, cudaStream_t s);
 int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, const void* X, long long x_rows, void* out,
                     const int4* worklist, const int32_t* sorted, const void* topk_weights, int n_slots, int np, int stages,
-                    int cluster_k, int max_items, int fp8_order, int* status, cudaStream_t s);
+                    int cluster_k, int max_items, int fp8_order, const float* scale, int* status, cudaStream_t s);
 int launch_fused_experts_static(const MoeParams& p, cudaStream_t s);   // combine scratch in a built-in device array
 
 // Expert-parallel exchange helpers (moe_exchange.cu).

@@ -301,6 +301,23 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
     const long long slots = (long long)m.T * m.topk;
     const long long mean2 = (2 * slots + m.E - 1) / m.E;
     const long long want = std::min<long long>(m.T, mean2);
+    // No tuning arguments at all (a geometry without a row in the table): the tcgen05 kernels where they apply.
+    // 16-bit weights always; e4m3 from about 16 slots per expert on (below that the warp-level kernels, which
+    // decode in the registers of many small CTAs, measured faster).  One cluster per (work item, 128-row tile):
+    // enough CTAs for about four per SM, every CTA with at least four k blocks; three ring stages.
+    if (m.nt == 0 && m.wm1 == 0 && m.sk1 == 0 && m.rg == 0 && m.wm2 == 0 && m.sk2 == 0 && m.scratch != nullptr &&
+        m.I % 128 == 0 && m.H % 128 == 0 && slots * m.H * 4 <= m.scratch_bytes && (wt != kE4M3 || want > 16)) {
+        const long long items = std::min<long long>(m.E, slots);
+        auto cluster = [&](int tiles, int kblocks) {
+            const long long ctas = items * tiles;
+            int sk = (int)std::min<long long>(8, (600 + ctas - 1) / ctas);
+            while (sk > 1 && kblocks / sk < 4) --sk;
+            return sk;
+        };
+        m.wm1 = 103; m.sk1 = cluster(m.I / 128, m.H / 64);
+        m.wm2 = 103; m.sk2 = cluster(m.H / 128, m.I / 64);
+        if (wt != kE4M3 && want > 64) m.nt = 16;
+    }
     int nt_tiles = want <= 8 ? 1 : (want <= 16 ? 2 : (want <= 32 ? 4 : 8));
     if (m.nt == 1 || m.nt == 2 || m.nt == 4 || m.nt == 8) nt_tiles = m.nt;
     // 16 tiles (128 slots per work item) exist for the tcgen05 kernels with 16-bit weights only
@@ -308,14 +325,14 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
     const int block_slots = nt_tiles * 8;
     const int max_items = (int)std::min<long long>(slots, (long long)std::min<long long>(m.E, slots) + slots / block_slots);
 
-    // tcgen05 path (moe_umma.cu): asked for by the tuning arguments, 16-bit weights or e4m3 weights without block
-    // scales, fp32 combine scratch present.
+    // tcgen05 path (moe_umma.cu): asked for by the tuning arguments, 16-bit or e4m3 weights (block scales ride on the
+    // decode), fp32 combine scratch present.
     // Its buffers are indexed by compact position (the routed slots expert by expert, no padding): the [slots, I]
     // activation takes the front of C like the warp-level path's, and the gathered token rows [slots, H] borrow the
     // combine scratch until the second GEMM overwrites it.
     const size_t c_bytes = (size_t)slots * 2 * m.I * 2;
     const size_t wl_bytes = 16 * (size_t)(max_items + 1);
-    const bool umma = (wt != kE4M3 || !scale) && m.wm1 >= 100 && m.wm2 >= 100 && m.scratch != nullptr && m.I % 128 == 0 &&
+    const bool umma = m.wm1 >= 100 && m.wm2 >= 100 && m.scratch != nullptr && m.I % 128 == 0 &&
                       m.H % 128 == 0 && (long long)slots * m.H * 4 <= m.scratch_bytes;
     if (nt_tiles == 16 && !umma) return fail(kInvalidArg, "fused_experts_compute: 128-slot work items need the tcgen05 kernels (sizes multiples of 128, combine scratch)");
 
@@ -343,11 +360,11 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
             return st;
         if (int st = launch_moe_umma(1, wt, m.w1, m.E, m.I, m.H, m.scratch, slots, m.C, reinterpret_cast<const int4*>(worklist),
                                      m.sorted_token_ids, m.topk_weights, (int)slots, np, m.wm1 - 100, m.sk1 > 0 ? m.sk1 : 1,
-                                     max_items, m.fp8_order, nullptr, s))
+                                     max_items, m.fp8_order, scale ? m.w1_scale : nullptr, nullptr, s))
             return st;
         if (int st = launch_moe_umma(2, wt, m.w2, m.E, m.H, m.I, m.C, slots, m.scratch, reinterpret_cast<const int4*>(worklist),
                                      m.sorted_token_ids, m.topk_weights, (int)slots, np, m.wm2 - 100, m.sk2 > 0 ? m.sk2 : 1,
-                                     max_items, m.fp8_order, nullptr, s))
+                                     max_items, m.fp8_order, scale ? m.w2_scale : nullptr, nullptr, s))
             return st;
         const long long total = (long long)m.T * (m.H / 8);
         const int grid = (int)std::min<long long>((total + 255) / 256, 148LL * 8);

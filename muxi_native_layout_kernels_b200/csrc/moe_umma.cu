@@ -40,6 +40,8 @@ struct MoeUmmaParams {
     int kblocks;
     int n_slots;
     uint32_t sel01, sel23;      // e4m3 kernels: byte selectors of the decode (natural or repacked order)
+    const float* scale;         // e4m3 kernels: fp32 block scales [experts * tiles_per_expert][kblocks / 2], or null
+    int full_scales;            // block scales with two bf16 terms instead of one (see common.cuh, scaled_rebias)
     int* status;
 };
 
@@ -385,8 +387,28 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8_kernel(const __grid_consta
     } else if (warp >= 2) {
         // ---- converter warps (thread = tile row = tensor-memory lane), then epilogue ----
         const int quad = warp & 3, lrow = quad * 32 + lane;
+        // block scales: a 128-row tile is one scale row, a 64-wide k block half a scale column; the values of the
+        // next unit are requested before this unit's waits
+        const int scale_ld = KB >> 1;
+        const float* srow[NA];
+        float sc_next[NA];
+        uint32_t c2[NA];
+        ScaledRebias sr[NA];
+#pragma unroll
+        for (int w = 0; w < NA; ++w) {
+            srow[w] = p.scale ? p.scale + (size_t)(a_tile + w * p.up_tile_offset) * scale_ld : nullptr;
+            sc_next[w] = (p.scale && nunits > 0) ? __ldg(srow[w] + (kb0 >> 1)) : 1.f;
+            c2[w] = kRebias2;
+            sr[w] = ScaledRebias{};
+        }
         for (int i = 0; i < nunits; ++i) {
             const int s = i % STAGES, s2 = i % S2;
+            float sc[NA];
+#pragma unroll
+            for (int w = 0; w < NA; ++w) {
+                sc[w] = sc_next[w];
+                if (p.scale && i + 1 < nunits) sc_next[w] = __ldg(srow[w] + ((kb0 + i + 1) >> 1));
+            }
             bool ok = true;
             if (lane == 0) {
                 ok = !abort_flag && mbar_wait(raw_full(s), (i / STAGES) & 1);
@@ -403,13 +425,29 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8_kernel(const __grid_consta
             for (int w = 0; w < NA; ++w) {
                 const uint8_t* raw = base_ptr + s * kStageBytes + w * kRawBytes + (lrow >> 4) * 1024 + (lrow & 15) * 8;
                 uint32_t v[32];
+                // c2: the factor of the decode's one multiply (2^120, or that times a block scale rounded to bf16); 0 = general form
+                if (p.scale && (i == 0 || ((kb0 + i) & 1) == 0)) {     // a scale column spans two k blocks
+                    sr[w] = scaled_rebias(sc[w], p.full_scales != 0);
+                    c2[w] = sr[w].one_multiply ? sr[w].hi2 : 0u;
+                }
+                if (c2[w] != 0u) {
 #pragma unroll
-                for (int o = 0; o < 8; ++o) {
-                    const uint2 x = *reinterpret_cast<const uint2*>(raw + o * 128);
-                    v[4 * o + 0] = e4m3x2_to_bf16x2(x.x, p.sel01);
-                    v[4 * o + 1] = e4m3x2_to_bf16x2(x.x, p.sel23);
-                    v[4 * o + 2] = e4m3x2_to_bf16x2(x.y, p.sel01);
-                    v[4 * o + 3] = e4m3x2_to_bf16x2(x.y, p.sel23);
+                    for (int o = 0; o < 8; ++o) {
+                        const uint2 x = *reinterpret_cast<const uint2*>(raw + o * 128);
+                        v[4 * o + 0] = e4m3x2_to_bf16x2_by(x.x, p.sel01, c2[w]);
+                        v[4 * o + 1] = e4m3x2_to_bf16x2_by(x.x, p.sel23, c2[w]);
+                        v[4 * o + 2] = e4m3x2_to_bf16x2_by(x.y, p.sel01, c2[w]);
+                        v[4 * o + 3] = e4m3x2_to_bf16x2_by(x.y, p.sel23, c2[w]);
+                    }
+                } else {
+#pragma unroll
+                    for (int o = 0; o < 8; ++o) {
+                        const uint2 x = *reinterpret_cast<const uint2*>(raw + o * 128);
+                        v[4 * o + 0] = e4m3x2_scaled(x.x, p.sel01, sr[w]);
+                        v[4 * o + 1] = e4m3x2_scaled(x.x, p.sel23, sr[w]);
+                        v[4 * o + 2] = e4m3x2_scaled(x.y, p.sel01, sr[w]);
+                        v[4 * o + 3] = e4m3x2_scaled(x.y, p.sel23, sr[w]);
+                    }
                 }
                 tmem_st32(tmem + ((uint32_t)(quad * 32) << 16) + NA * NP + (s2 * NA + w) * kAColumns, v);
             }
@@ -545,7 +583,7 @@ int launch_moe_gather_positions(const void* x, const int32_t* sorted, const int4
 // compact position order); mode 2: W = w2 [E, H, k=I], X = act [n_slots, I], out = scratch [n_slots, H] fp32 by slot.
 int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, const void* X, long long x_rows, void* out,
                     const int4* worklist, const int32_t* sorted, const void* topk_weights, int n_slots, int np, int stages,
-                    int cluster_k, int max_items, int fp8_order, int* status, cudaStream_t s) {
+                    int cluster_k, int max_items, int fp8_order, const float* scale, int* status, cudaStream_t s) {
     const bool f8 = wt == kE4M3;
     if (wt != kBF16 && wt != kFP16 && !f8) return fail(kUnsupported, "moe (tcgen05): unsupported weight type");
     if (rows % kTileM != 0 || k % kBlockK != 0) return fail(kInvalidArg, "moe (tcgen05): sizes must be multiples of 128 (rows) and 64 (k)");
@@ -576,6 +614,8 @@ int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, con
     mp.n_slots = n_slots;
     mp.sel01 = fp8_order ? kSelRep01 : kSelNat01;
     mp.sel23 = fp8_order ? kSelRep23 : kSelNat23;
+    mp.scale = (wt == kE4M3) ? scale : nullptr;
+    mp.full_scales = option(kOptFullScales);
     mp.status = status;
     int static_weights = option(kOptStaticWeights);
     cudaLaunchConfig_t cfg = {};

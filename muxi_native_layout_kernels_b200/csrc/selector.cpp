@@ -53,6 +53,27 @@ TuneArgs default_args(int table, int m, int n, int k) {
         while (sk < 8 && ctas * sk < target_ctas && (k / 32) / (8 * sk * 2) >= 4) sk *= 2;
         return TuneArgs{256, 1, rg, sk};
     }
+    if (m % 128 == 0 && k % 64 == 0 && n >= 2 && n <= 64) {
+        // tcgen05 tile kernel, one cluster per 128-row tile: enough CTAs for three to four per SM (they are small, and
+        // the start and tail of one overlap the streaming of the others), every CTA with at least four k blocks;
+        // kernelParam2 = ring stages, kernelParam3 = CTAs per cluster (the 16-bit kernel wants 2 or more)
+        const int tiles = m / 128, kblocks = k / 64;
+        int ck = (512 + tiles - 1) / tiles;
+        if (ck > 8) ck = 8;
+        while (ck > 1 && kblocks / ck < 4) --ck;
+        if (table != kTableGemmLayoutASoftFp8 && ck < 2) ck = kblocks >= 2 ? 2 : 0;
+        // ring depth: 16-bit 4 (3 for the 64-token tile, whose stages are 24 KB); e4m3 stages are 8 KB, 6 for the
+        // 16-token tile, 4 above
+        const int stages = table == kTableGemmLayoutASoftFp8 ? (n <= 16 ? 6 : 4) : (n > 32 ? 3 : 4);
+        return TuneArgs{2, 1, stages, ck};
+    }
+    return warp_level_default_args(table, m, n, k);
+}
+
+// Launch arguments of the warp-level streaming kernel (kernelId 1) for any shape it accepts.
+TuneArgs warp_level_default_args(int table, int m, int n, int k) {
+    const int target_ctas = 2 * 148;
+    (void)table;
     int rg = (n > 8 && m % 32 == 0) ? 2 : 1;
     int wm = 1;
     if (n > 32) wm = 4;

@@ -28,6 +28,7 @@ struct TuneArgs {
 
 const char* table_file_name(int table);
 TuneArgs default_args(int table, int m, int n, int k);
+TuneArgs warp_level_default_args(int table, int m, int n, int k);   // GEMM tables: kernelId 1 arguments
 
 class DispatchTable {
   public:

@@ -27,7 +27,8 @@ void clear_error();
 enum Option : int {
     kOptPdl = 0,            // launch kernels with programmatic stream serialization (default 1)
     kOptStaticWeights = 1,  // weight tensors are never written by kernels of the calling stream (default 0)
-    kNumOptions = 2,
+    kOptFullScales = 2,     // tcgen05 e4m3 kernels: block scales with 16 significant bits instead of 8 (default 0)
+    kNumOptions = 3,
 };
 int option(int which);
 void set_option(int which, int value);

@@ -19,7 +19,7 @@ import ctypes
 from ._lib import MlkAux, MlkError, check, lib
 
 __all__ = [
-    "set_static_weights", "set_pdl", "kernel_status",
+    "set_static_weights", "set_pdl", "set_full_scales", "kernel_status",
     "layoutA", "layoutA_inverse", "layoutB", "reLayoutC", "fp8_weight_repack",
     "gemv_layoutA", "gemv_layoutA_wapper",
     "gemm_layoutA", "gemm_layoutA_wapper", "gemm_layoutA_soft_fp8", "gemm_layoutA_soft_fp8_wapper",
@@ -39,6 +39,13 @@ def set_static_weights(enabled: bool) -> None:
     in flight (weights prepacked once, then only read).  The dense kernels then begin streaming weights while the
     preceding kernel is still draining.  Off by default."""
     check(lib.mlk_set_option(1, int(bool(enabled))))
+
+
+def set_full_scales(enabled: bool) -> None:
+    """How the tcgen05 e4m3 kernels apply 128x128 block scales: False (default) rounds the scale to bf16 and folds it
+    into the decode at no cost; True keeps 16 significant bits of the scale (two more packed instructions per weight
+    pair; the result is the weight the reference's torch recipe dequantises to, rne_bf16(w * s))."""
+    check(lib.mlk_set_option(2, int(bool(enabled))))
 
 
 def set_pdl(enabled: bool) -> None:

@@ -42,11 +42,15 @@ def build(cfg, dev):
     return w1, w2, wg, g
 
 
-def run_case(cfg, T, w1, w2, wg, g, dev, iters):
+def run_case(cfg, T, w1, w2, wg, g, dev, iters, scales=False):
     E, H, I, topk, fp8 = cfg["E"], cfg["H"], cfg["I"], cfg["topk"], cfg["fp8"]
     xs = [torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16) for _ in range(NBATCH)]
     logits = [(x.float() @ wg.float().t()).to(torch.bfloat16) for x in xs]
     kw = dict(block_shape=[128, 128], soft_fp8=True, fp8_repacked=True) if fp8 else {}
+    if fp8 and scales:
+        # block-scale tensors as the reference's interface wants them (all ones: the weights are synthetic)
+        kw.update(w1_scale=torch.ones(E, 2 * I // 128, H // 128, device=dev),
+                  w2_scale=torch.ones(E, H // 128, I // 128, device=dev))
 
     def call(i):
         return fused_moe(xs[i], w1, w2, logits[i], topk, True, **kw)
@@ -86,14 +90,14 @@ def run_case(cfg, T, w1, w2, wg, g, dev, iters):
             "algorithmic_mb": round(nbytes / 1e6, 1), "gbs": round(nbytes / us_graph / 1e3, 1)}
 
 
-def run(config="both", tokens=None, iters=24, dev=None):
+def run(config="both", tokens=None, iters=24, dev=None, scales=False):
     dev = dev or torch.device("cuda")
     mlk.set_static_weights(True)
     out = {}
     for name in (["mixtral", "fine"] if config == "both" else [config]):
         cfg = CONFIGS[name]
         w1, w2, wg, g = build(cfg, dev)
-        out[name] = [run_case(cfg, T, w1, w2, wg, g, dev, iters) for T in (tokens or cfg["tokens"])]
+        out[name] = [run_case(cfg, T, w1, w2, wg, g, dev, iters, scales) for T in (tokens or cfg["tokens"])]
         del w1, w2
         torch.cuda.empty_cache()
     return out
@@ -175,8 +179,9 @@ if __name__ == "__main__":
     ap.add_argument("--tokens", default=None)
     ap.add_argument("--iters", type=int, default=24)
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--scales", action="store_true", help="e4m3 configs: pass block-scale tensors (all ones)")
     a = ap.parse_args()
-    res = run(a.config, [int(t) for t in a.tokens.split(",")] if a.tokens else None, a.iters)
+    res = run(a.config, [int(t) for t in a.tokens.split(",")] if a.tokens else None, a.iters, scales=a.scales)
     if a.json:
         print(json.dumps(res))
     else:

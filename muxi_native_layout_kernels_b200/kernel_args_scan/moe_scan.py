@@ -78,7 +78,7 @@ def scan_case(cfg, T, w1, w2, wg, g, dev):
             if us is not None and us < best_us:
                 best_args, best_us = args, us
     if H % 128 == 0 and I % 128 == 0:
-        # tcgen05 expert GEMMs (16-bit weights, or e4m3 without block scales): wm = 100 + ring stages, sk = CTAs per cluster
+        # tcgen05 expert GEMMs (16-bit or e4m3 weights): wm = 100 + ring stages, sk = CTAs per cluster
         for nt in [n for n in (1, 2, 4, 8) + (() if fp8 else (16,)) if n * 8 <= max(8, 2 * T)]:
             g1_best, g1_us = None, float("inf")
             for st1, ck1 in itertools.product([2, 3, 4], [1, 2, 4]):

@@ -27,6 +27,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--copies", type=int, default=3)
     ap.add_argument("--static-weights", action="store_true")
+    ap.add_argument("--scales", action="store_true", help="fp8: pass a block-scale tensor (all ones)")
     a = ap.parse_args(argv)
     mlk.set_static_weights(a.static_weights)
     m, k = (int(v) for v in a.shape.split("x"))
@@ -42,17 +43,19 @@ def main(argv=None):
     X = torch.randn(n, k, generator=g, device=dev).to(adt)
     XB = mlk.layoutB(X) if a.op in ("gemm_layoutAB_ContinuousC", "gemm_layoutABC") else None
     args = [int(v) for v in a.args.split(",")] if a.args else None
+    S = torch.ones((m + 127) // 128, (k + 127) // 128, device=dev) if (a.scales and a.dtype == "fp8") else None
 
     def call(A):
         if a.op == "gemv":
             if args:
-                return mlk.gemv_layoutA_wapper(A, X, m, k, blockDimX=args[0], kernelId=args[1], kernelParam1=args[2], kernelParam2=args[3])
-            return mlk.gemv_layoutA(A, X)
+                return mlk.gemv_layoutA_wapper(A, X, m, k, blockDimX=args[0], kernelId=args[1], kernelParam1=args[2], kernelParam2=args[3],
+                                               scale_matrix=S)
+            return mlk.gemv_layoutA(A, X, scale_matrix=S)
         if a.dtype == "fp8":
             if args:
-                return mlk.gemm_layoutA_soft_fp8_wapper(A, None, X, m, n, k, kernelParam1=args[0], kernelParam2=args[1], kernelParam3=args[2],
+                return mlk.gemm_layoutA_soft_fp8_wapper(A, S, X, m, n, k, kernelParam1=args[0], kernelParam2=args[1], kernelParam3=args[2],
                                                         kernelId=args[3] if len(args) > 3 else 1)
-            return mlk.gemm_layoutA_soft_fp8(A, None, X)
+            return mlk.gemm_layoutA_soft_fp8(A, S, X)
         fn = getattr(mlk, a.op + ("_wapper" if args else ""))
         xin = XB if XB is not None else X
         if args:

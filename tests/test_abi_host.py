@@ -50,8 +50,15 @@ def test_table_load_lookup_and_miss_default(tmp_path, capfd):
     # miss: warns once, returns a runnable default, then remembers it
     assert lib.mlk_table_lookup(2, 8192, 8, 1024, out, ctypes.byref(hit)) == 0
     first = list(out)
-    assert hit.value == 0 and first[0] == 1 and first[1] in (1, 2) and first[2] in (1, 2, 4, 8) and first[3] in (1, 2, 4, 8)
+    # 128-row tiles, 2..64 tokens: the tcgen05 tile kernel, cluster mode (ring stages, CTAs per cluster)
+    assert hit.value == 0 and first[0] == 2 and first[2] in (3, 4) and 2 <= first[3] <= 8
     assert "No matching arguments" in capfd.readouterr().err
+    # any other shape: the warp-level kernel
+    assert lib.mlk_table_lookup(2, 8192 + 16, 8, 1024, out, ctypes.byref(hit)) == 0
+    w = list(out)
+    assert hit.value == 0 and w[0] == 1 and w[1] in (1, 2) and w[2] in (1, 2, 4, 8) and w[3] in (1, 2, 4, 8)
+    assert lib.mlk_table_lookup(2, 8192, 128, 1024, out, ctypes.byref(hit)) == 0 and list(out)[0] == 1
+    capfd.readouterr()
     assert lib.mlk_table_lookup(2, 8192, 8, 1024, out, ctypes.byref(hit)) == 0
     assert list(out) == first and hit.value == 1
     assert capfd.readouterr().err == ""

@@ -200,9 +200,11 @@ def test_gemm_soft_fp8(repacked):
                 Cs = mlk.gemm_layoutA_soft_fp8_wapper(A, scale.to(dev), X.to(dev), m, n, k, kernelParam1=rg,
                                                       kernelParam2=wm, kernelParam3=sk, fp8_repacked=repacked)
                 assert_close(Cs, want_s, f"fp8 scaled gemm m={m} k={k} n={n} {(rg, wm, sk)}")
-            assert_close(mlk.gemm_layoutA_soft_fp8(A, scale.to(dev), X.to(dev), fp8_repacked=repacked), want_s, "fp8 table")
+            # table-driven entry points: these shapes have no row, so 2..64 tokens run on the tcgen05 kernel, which
+            # rounds the scaled weight to bf16 (as the reference does): tolerance relative to the output scale
+            _close_rel(mlk.gemm_layoutA_soft_fp8(A, scale.to(dev), X.to(dev), fp8_repacked=repacked), want_s, "fp8 table")
             if not repacked:
-                assert_close(mlk.gemm_layoutA_linear(A, X.to(dev), scale_matrix=scale.to(dev)), want_s, "linear fp8")
+                _close_rel(mlk.gemm_layoutA_linear(A, X.to(dev), scale_matrix=scale.to(dev)), want_s, "linear fp8")
 
 
 @pytest.mark.parametrize("repacked", [False, True])
@@ -232,15 +234,80 @@ def test_soft_fp8_tcgen05_pipeline(repacked):
             y = mlk.gemv_layoutA_wapper(A, x.to(dev), m, k, kernelId=3, kernelParam1=stages, kernelParam2=ck,
                                         fp8_repacked=repacked)
             assert_close(y, odense.gemm_ref(x, W8.to(torch.bfloat16)), f"gemv fp8 tcgen05 m={m} k={k} {stages},{ck}")
-    # bit-identical from run to run; block scales are refused (they stay on the warp-level kernel)
+    # bit-identical from run to run
     X = randn((40, 4096), 174, 1.0, torch.bfloat16).to(dev)
     ref = mlk.gemm_layoutA_soft_fp8_wapper(A, None, X, 1024, 40, 4096, kernelParam2=4, kernelParam3=4, kernelId=2, fp8_repacked=repacked)
     for _ in range(3):
         assert torch.equal(ref, mlk.gemm_layoutA_soft_fp8_wapper(A, None, X, 1024, 40, 4096, kernelParam2=4, kernelParam3=4,
                                                                  kernelId=2, fp8_repacked=repacked))
-    scale = torch.ones(8, 32, device=dev)
-    with pytest.raises(RuntimeError, match="block scales"):
-        mlk.gemm_layoutA_soft_fp8_wapper(A, scale, X, 1024, 40, 4096, kernelParam2=4, kernelParam3=4, kernelId=2)
+    # unit block scales change nothing, bit for bit
+    ones = torch.ones(8, 32, device=dev)
+    assert torch.equal(ref, mlk.gemm_layoutA_soft_fp8_wapper(A, ones, X, 1024, 40, 4096, kernelParam2=4, kernelParam3=4,
+                                                             kernelId=2, fp8_repacked=repacked))
+
+
+def _close_rel(got, want, what, tol=1e-2):
+    """|got - want| <= tol * (rms(want) + |want|): the absolute part follows the output scale, which block scales
+    move by orders of magnitude."""
+    rms = float(want.double().pow(2).mean().sqrt())
+    rep = odense.error_report(got.detach().cpu(), want, atol=tol * rms, rtol=tol)
+    assert rep["ok"], f"{what}: {rep}"
+
+
+@pytest.fixture
+def full_scales(request):
+    mlk.set_full_scales(request.param)
+    yield request.param
+    mlk.set_full_scales(False)
+
+
+@pytest.mark.parametrize("full_scales", [False, True], indirect=True)
+@pytest.mark.parametrize("repacked", [False, True])
+def test_soft_fp8_tcgen05_block_scales(repacked, full_scales):
+    """Block scales in the decode.  Default: the scale rounded to bf16, rne_bf16(w * bf16(s)), inside the parity
+    tolerance of the path.  Full scales: rne_bf16(w * s), so the GEMM equals, to accumulation order and the final
+    rounding (one bf16 ulp, 2^-8), a bf16 GEMM on the weights the reference's torch recipe dequantises to
+    (muxi_layout_kernels/utils.py:14-25)."""
+    dev = require_gpu()
+    # default: up to one bf16 ulp per weight (2^-8) on top of the rounding of the output, measured against the output
+    # scale (these outputs are far below 1, where the path's absolute bar of 1e-2 says nothing)
+    # full scales: the two bf16 outputs may still sit on either side of a rounding boundary (one ulp = 2^-7 of the value)
+    tol = 8e-3 if full_scales else 2e-2
+    g = torch.Generator().manual_seed(177)
+    for (m, k) in [(128, 128), (256, 1024), (1024, 4096), (384, 4224)]:
+        W8 = rand_e4m3((m, k), 175 + m)
+        A = mlk.layoutA(W8.to(dev))
+        if repacked:
+            A = mlk.fp8_weight_repack(A)
+        sm, sk_ = (m + 127) // 128, (k + 127) // 128
+        scales = {
+            "quant": torch.rand(sm, sk_, generator=g) * 0.01 + 1e-4,                  # amax / 448 style
+            "wide": torch.exp2(torch.randint(-40, 20, (sm, sk_), generator=g).float()) * (1 + torch.rand(sm, sk_, generator=g)),
+            "signed": (torch.rand(sm, sk_, generator=g) - 0.5) * 4,
+        }
+        # values outside the folded range of the decode: huge, tiny, zero
+        edge = torch.rand(sm, sk_, generator=g) + 0.5
+        edge.view(-1)[0::3] *= 2.0 ** 20
+        edge.view(-1)[1::3] *= 2.0 ** -130
+        if edge.numel() > 4:
+            edge.view(-1)[4] = 0.0
+        scales["edge"] = edge
+        for name, scale in scales.items():
+            scale = scale.float().contiguous()
+            Wd = odense.dequant_block_scaled(W8, scale)
+            for n in (1, 8, 24, 64):
+                X = randn((n, k), 176 + n, 1.0, torch.bfloat16)
+                want = odense.gemm_ref(X, Wd)
+                for stages, ck in [(2, 1), (4, 2), (6, 1)]:
+                    if ck > k // 64:
+                        continue
+                    C = mlk.gemm_layoutA_soft_fp8_wapper(A, scale.to(dev), X.to(dev), m, n, k, kernelParam2=stages,
+                                                         kernelParam3=ck, kernelId=2, fp8_repacked=repacked)
+                    _close_rel(C, want, f"fp8 tcgen05 scaled[{name}] m={m} k={k} n={n} stages={stages} cluster={ck}", tol)
+            x = randn((1, k), 178, 1.0, torch.bfloat16)
+            y = mlk.gemv_layoutA_wapper(A, x.to(dev), m, k, kernelId=3, kernelParam1=4, kernelParam2=2,
+                                        scale_matrix=scale.to(dev), fp8_repacked=repacked)
+            _close_rel(y, odense.gemm_ref(x, Wd), f"gemv fp8 tcgen05 scaled[{name}] m={m} k={k}", tol)
 
 
 def test_gemm_errors_and_determinism():

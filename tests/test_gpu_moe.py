@@ -229,7 +229,9 @@ def _moe_compare(x, w1, w2, logits, topk, what, renorm=True, groups=1, kept=1, b
     rep32 = odense.error_report(y.cpu(), y32, scale_atol=True)
     rep16 = odense.error_report(y.cpu(), y16, scale_atol=True)
     print(what, "kernel-vs-fp32", rep32, "kernel-vs-16bit", rep16, "floor", floor)
-    assert rep32["ok"], (what, rep32)
+    # within the path's tolerance of the fp32 yardstick, or (kernels that round the block-scaled weights to bf16, as the
+    # reference's do) at least as close to it as the reference's own 16-bit recipe is
+    assert rep32["ok"] or rep32["max_abs"] <= 1.1 * floor["max_abs"], (what, rep32, floor)
     assert rep16["max_abs"] <= floor["max_abs"] * 1.5 + 1e-2 * max(1.0, float(y32.abs().max())), (what, rep16, floor)
     return y
 
@@ -282,7 +284,7 @@ def test_moe_16bit_tcgen05_expert_gemms(dt, T):
 @pytest.mark.parametrize("T", [1, 8, 32, 130, 520])
 @pytest.mark.parametrize("repack", [False, True])
 def test_moe_soft_fp8_tcgen05_expert_gemms(T, repack):
-    """e4m3 experts without block scales on the tcgen05 kernels (decode into tensor memory), against the same oracle
+    """e4m3 experts with unit scales on the tcgen05 kernels (decode into tensor memory), against the same oracle
     and against the warp-level kernels."""
     E, topk, H, I = 32, 8, 256, 128
     x = randn((T, H), 800 + T, 1.0)
@@ -295,6 +297,27 @@ def test_moe_soft_fp8_tcgen05_expert_gemms(T, repack):
         y0 = _moe_compare(x, w1, w2, logits, topk, f"moe fp8 warp-level T={T}", fp8=True, repack=repack,
                           tune=(tune[0], 2, 1, 1, 2, 1))
         assert_close(y, y0.cpu(), f"fp8 tcgen05 vs warp-level T={T} tune={tune}", scale_atol=True)
+
+
+@pytest.mark.parametrize("T", [1, 32, 130])
+@pytest.mark.parametrize("repack", [False, True])
+def test_moe_soft_fp8_tcgen05_block_scales(T, repack):
+    """e4m3 experts WITH 128x128 block scales on the tcgen05 kernels: the decode yields rne_bf16(w * s), the weights
+    the reference's torch recipe dequantises to; compared with the oracle and with the warp-level kernels."""
+    E, topk, H, I = 32, 8, 256, 256
+    x = randn((T, H), 810 + T, 1.0)
+    w1 = rand_e4m3((E, 2 * I, H), 811, 0.25)
+    w2 = rand_e4m3((E, H, I), 812, 0.25)
+    logits = randn((T, E), 813 + T, 1.0)
+    g = torch.Generator().manual_seed(814)
+    scales = (torch.rand(E, 2 * I // 128, H // 128, generator=g) * 0.5 + 0.01,
+              torch.rand(E, H // 128, I // 128, generator=g) * 0.5 + 0.01)
+    for tune in [(1, 102, 1, 0, 102, 1), (2, 103, 2, 0, 104, 2), (8, 104, 4, 0, 103, 2)]:
+        y = _moe_compare(x, w1, w2, logits, topk, f"moe fp8 tcgen05 scaled T={T} repack={repack} tune={tune}", fp8=True,
+                         scales=scales, repack=repack, tune=tune)
+        y0 = _moe_compare(x, w1, w2, logits, topk, f"moe fp8 warp-level scaled T={T}", fp8=True, scales=scales,
+                          repack=repack, tune=(tune[0], 2, 1, 1, 2, 1))
+        assert_close(y, y0.cpu(), f"fp8 tcgen05 vs warp-level, scaled, T={T} tune={tune}", scale_atol=True)
 
 
 @pytest.mark.parametrize("T", [1, 8, 32, 130])
