@@ -130,6 +130,10 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
  *   Block scales are applied in the decode as rne_bf16(w * s), the weight the reference's torch recipe
  *   (muxi_layout_kernels/utils.py:14-25) dequantises to; kernelId 1, 3, 4 apply s to the fp32 sums of each 128-wide
  *   k block instead, and the reference's kernels truncate fp32(w) * s to bf16: all within one bf16 ulp per weight.
+ * kernelId 8 (16-bit weights, row-major B, m % 256 == 0, n <= 64): the tcgen05 cluster kernel with 256 weight rows per
+ *   CTA, two accumulators fed by the same token tile, which halves the token-tile traffic from L2 (no row of
+ *   the packaged tables uses it: on those shapes the 128-row kernel is faster); kernelParam2 = ring stages (2, 3, 4; 32 KB of weights each), kernelParam3 =
+ *   CTAs per cluster (1..8), kernelParam1 ignored.
  * kernelId 5, 6, 7 (CUDA-core FMA + shuffle kernel with 256, 128, 64 threads; 16-bit weights, row-major B and C,
  *   n <= 4): kernelParam1 = row groups per warp (1,2), kernelParam2 unused, kernelParam3 = cluster split-K. */
 

@@ -83,6 +83,14 @@ int gemm_common(int variant_x, int variant_c, const void* A, const float* scale,
         }
         return launch_dense_umma(wt, p, p1, p2, p3, aux ? &da : nullptr, s);
     }
+    if (kernelId == 8) {
+        // tcgen05 tile kernel with 256 weight rows per CTA (two accumulators share the token tile): kernelParam2 =
+        // ring stages (2, 3, 4), kernelParam3 = CTAs per cluster (1..8)
+        if (wt == kE4M3) return fail(kUnsupported, "gemm: kernelId 8 takes 16-bit weights");
+        if (variant_x != 0) return fail(kUnsupported, "gemm: kernelId 8 needs row-major B");
+        if (variant_c != 0 && n % 16 != 0) return fail(kInvalidArg, "gemm: layout C needs n %% 16 == 0");
+        return launch_dense_umma_pair(wt, p, p2, p3 < 1 ? 1 : p3, aux ? aux->status : nullptr, s);
+    }
     if (kernelId >= 5 && kernelId <= 7) {
         // CUDA-core FMA kernel for 1..4 tokens; 5 / 6 / 7 = 256 / 128 / 64 threads; kernelParam1 = row groups per
         // warp, kernelParam3 = cluster split-K
@@ -112,10 +120,13 @@ int gemm_table(int table, int variant_x, int variant_c, const void* A, const flo
                           : ((t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 && t.d <= 8));
     const bool ok5 = t.a >= 5 && t.a <= 7 && n <= 4 && variant_x == 0 && variant_c == 0 && dtype != MLK_E4M3 &&
                      (t.b == 1 || t.b == 2) && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b) == 0;
-    if (!ok1 && !ok2 && !ok5) t = default_args(table, m, n, k);
+    const bool ok8 = t.a == 8 && variant_x == 0 && dtype != MLK_E4M3 && n <= 64 && m % 256 == 0 && k % 64 == 0 &&
+                     t.c >= 2 && t.c <= 4 && t.d >= 1 && t.d <= 8 && t.d <= k / 64 &&
+                     (size_t)t.c * (32768 + (n <= 16 ? 16 : (n <= 32 ? 32 : 64)) * 128) >= (size_t)(n <= 16 ? 16 : (n <= 32 ? 32 : 64)) * 1024;
+    if (!ok1 && !ok2 && !ok5 && !ok8) t = default_args(table, m, n, k);
     // the tcgen05 kernel reads through tensor maps, which want 16-byte aligned bases; e4m3 activations in layout B
     // have no tcgen05 variant
-    if (t.a == 2 && ((((uintptr_t)A | (uintptr_t)B) & 15) != 0 || (variant_x != 0 && dtype == MLK_E4M3)))
+    if ((t.a == 2 || t.a == 8) && ((((uintptr_t)A | (uintptr_t)B) & 15) != 0 || (variant_x != 0 && dtype == MLK_E4M3)))
         t = warp_level_default_args(table, m, n, k);
     return gemm_common(variant_x, variant_c, A, scale, B, C, m, n, k, dtype, alpha, t.b, t.c, t.d, t.a, bias,
                        fp8_order, s, aux);

@@ -64,15 +64,17 @@ def scan_case(cfg, T, w1, w2, wg, g, dev):
 
     best_args, best_us = (0, 0, 0, 0, 0, 0), try_args((0, 0, 0, 0, 0, 0))
     nts = [n for n in (1, 2, 4, 8) if n * 8 <= max(8, 2 * T)]
+    # few routed slots leave few work items: deeper split-K is then the only source of CTAs
+    few = T * topk <= 64
     for nt in nts:
         g1_best, g1_us = None, float("inf")
-        for wm1, sk1 in itertools.product([1, 2, 4], [1, 2]):
+        for wm1, sk1 in itertools.product([1, 2, 4], [1, 2, 4, 8] if few else [1, 2]):
             us = try_args((nt, wm1, sk1, 0, 0, 0))
             if us is not None and us < g1_us:
                 g1_best, g1_us = (wm1, sk1), us
         if g1_best is None:
             continue
-        for rg2, wm2, sk2 in itertools.product([1, 2], [1, 2, 4], [1, 2, 4]):
+        for rg2, wm2, sk2 in itertools.product([1, 2], [1, 2, 4], [1, 2, 4, 8] if few else [1, 2, 4]):
             args = (nt, g1_best[0], g1_best[1], rg2, wm2, sk2)
             us = try_args(args)
             if us is not None and us < best_us:
@@ -81,7 +83,7 @@ def scan_case(cfg, T, w1, w2, wg, g, dev):
         # tcgen05 expert GEMMs (16-bit or e4m3 weights): wm = 100 + ring stages, sk = CTAs per cluster
         for nt in [n for n in (1, 2, 4, 8) + (() if fp8 else (16,)) if n * 8 <= max(8, 2 * T)]:
             g1_best, g1_us = None, float("inf")
-            for st1, ck1 in itertools.product([2, 3, 4], [1, 2, 4]):
+            for st1, ck1 in itertools.product([2, 3, 4], [1, 2, 4, 8] if few else [1, 2, 4]):
                 us = try_args((nt, 100 + st1, ck1, 0, 103, 4))
                 if us is not None and us < g1_us:
                     g1_best, g1_us = (100 + st1, ck1), us

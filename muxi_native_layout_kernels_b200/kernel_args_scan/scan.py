@@ -134,6 +134,13 @@ def candidates(kind, m, n, k):
                 smem = st * (16384 + np_ * 128) + 2048
                 if ck <= k // 64 and (m // 128) * ck <= 148 * max(1, (227 * 1024) // smem):
                     cands.append((2, 1, st, ck))
+    if kind == "a" and 16 < n <= 64 and m % 256 == 0:
+        # kernelId 8: the cluster kernel with 256 rows per CTA (two accumulators share the token tile)
+        np_ = 32 if n <= 32 else 64
+        for ck in range(1, 9):
+            for st in (2, 3, 4):
+                if ck <= k // 64 and st * (32768 + np_ * 128) >= np_ * 1024:
+                    cands.append((8, 1, st, ck))
     return cands
 
 

@@ -114,6 +114,10 @@ def test_packaged_table_rows_name_launches_the_library_accepts():
                 assert p3 < 2 or p3 <= k // 64, what
             elif kid == 2 and fp8:
                 assert n <= 64 and p2 in (2, 3, 4, 6, 8) and 1 <= p3 <= min(8, k // 64), what
+            elif kid == 8:
+                assert layout_a and not fp8 and n <= 64 and m % 256 == 0 and p2 in (2, 3, 4) and 1 <= p3 <= min(8, k // 64), what
+                np_ = 16 if n <= 16 else (32 if n <= 32 else 64)
+                assert p2 * (32768 + np_ * 128) >= np_ * 1024, what     # the ring holds the fp32 partial tiles
             elif kid in (5, 6, 7):
                 assert layout_a and not fp8 and n <= 4 and p1 in (1, 2) and p3 in (1, 2, 4, 8) and m % (16 * p1) == 0, what
             else:
