@@ -268,33 +268,41 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8_kernel(const __grid_cons
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (warp >= 2) {
         const int etid = tid - 64;
-        const int r0 = kTileM * rank / SK, rows = kTileM * (rank + 1) / SK - r0;
+        // slices in units of four accumulator rows: one 16-byte distributed-shared-memory load per rank brings four
+        // rows of one token, which are four consecutive weight rows (and output elements)
+        const int q0 = (kTileM / 4) * rank / SK, quads = (kTileM / 4) * (rank + 1) / SK - q0;
         uint32_t remote[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q)
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[q]) : "r"(base), "r"(q < SK ? q : 0));
-        const int total = p.n * rows;
+        const int total = p.n * quads;
         for (int idx = etid; idx < total; idx += 128) {
-            const int c = idx / rows, rho = r0 + idx - c * rows;
+            const int c = idx / quads, rho = 4 * (q0 + idx - c * quads);
             const uint32_t off = (uint32_t)(c * kTileM + rho) * 4u;
-            float t[8];
+            float4 t[8];
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-                t[q] = 0.f;
-                if (q < SK) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(t[q]) : "r"(remote[q] + off) : "memory");
+                t[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (q < SK)
+                    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                 : "=f"(t[q].x), "=f"(t[q].y), "=f"(t[q].z), "=f"(t[q].w)
+                                 : "r"(remote[q] + off)
+                                 : "memory");
             }
-            float acc = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             bool first = true;
 #pragma unroll
             for (int q = 7; q >= 0; --q) {
                 if (q < SK) {
-                    acc = first ? t[q] : acc + t[q];
+                    acc = first ? t[q] : make_float4(acc.x + t[q].x, acc.y + t[q].y, acc.z + t[q].z, acc.w + t[q].w);
                     first = false;
                 }
             }
             const int row = tile * kTileM + rho;       // accumulator rows are the tile's rows in natural order
-            const float bia = (p.bias != nullptr) ? load_scalar16<kBF16>(p.bias, row) : 0.f;
-            const float val = fmaf(p.alpha, acc, bia);
+            float4 bia = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p.bias != nullptr)
+                bia = make_float4(load_scalar16<kBF16>(p.bias, row), load_scalar16<kBF16>(p.bias, row + 1),
+                                  load_scalar16<kBF16>(p.bias, row + 2), load_scalar16<kBF16>(p.bias, row + 3));
             size_t o;
             if (p.c_layout == 0) {
                 o = (size_t)c * p.m + row;
@@ -302,7 +310,11 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8_kernel(const __grid_cons
                 const int NB = p.n >> 4;
                 o = ((((size_t)(row >> 5) * NB + (c >> 4)) * 4 + ((row >> 3) & 3)) * 16 + (c & 15)) * 8 + (row & 7);
             }
-            reinterpret_cast<__nv_bfloat16*>(p.C)[o] = __float2bfloat16_rn(val);
+            // four consecutive bf16 outputs, 8-byte aligned (row is a multiple of 4, m a multiple of 128)
+            uint2 packed;
+            packed.x = pack2<kBF16>(fmaf(p.alpha, acc.x, bia.x), fmaf(p.alpha, acc.y, bia.y));
+            packed.y = pack2<kBF16>(fmaf(p.alpha, acc.z, bia.z), fmaf(p.alpha, acc.w, bia.w));
+            *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.C) + o) = packed;
         }
     }
     // nobody leaves while its shared memory may still be read

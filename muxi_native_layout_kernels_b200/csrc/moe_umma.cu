@@ -56,48 +56,57 @@ __device__ __forceinline__ void moe_cluster_epilogue(const MoeUmmaParams& p, uin
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (warp >= 2) {
         const int etid = tid - 64;
-        const int r0 = kTileM * rank / SK, rows = kTileM * (rank + 1) / SK - r0;
+        // slices in units of four accumulator rows: one 16-byte distributed-shared-memory load per rank brings four
+        // rows of one slot, which are four consecutive weight rows (and output elements)
+        const int q0 = (kTileM / 4) * rank / SK, quads = (kTileM / 4) * (rank + 1) / SK - q0;
         uint32_t remote[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q)
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[q]) : "r"(base), "r"(q < SK ? q : 0));
         auto cluster_sum = [&](uint32_t off) {
-            float t[8];
+            float4 t[8];
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-                t[q] = 0.f;
-                if (q < SK) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(t[q]) : "r"(remote[q] + off) : "memory");
+                t[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (q < SK)
+                    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                 : "=f"(t[q].x), "=f"(t[q].y), "=f"(t[q].z), "=f"(t[q].w)
+                                 : "r"(remote[q] + off)
+                                 : "memory");
             }
-            float acc = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             bool first = true;
 #pragma unroll
             for (int q = 7; q >= 0; --q) {
                 if (q < SK) {
-                    acc = first ? t[q] : acc + t[q];
+                    acc = first ? t[q] : make_float4(acc.x + t[q].x, acc.y + t[q].y, acc.z + t[q].z, acc.w + t[q].w);
                     first = false;
                 }
             }
             return acc;
         };
-        const int total = nslots * rows;
+        auto silu_mul = [](float gate, float up) { return gate / (1.f + __expf(-gate)) * up; };
+        const int total = nslots * quads;
         for (int idx = etid; idx < total; idx += 128) {
-            const int c = idx / rows, rho = r0 + idx - c * rows;
+            const int c = idx / quads, rho = 4 * (q0 + idx - c * quads);
             const int row = tile * kTileM + (NATURAL ? rho : ((rho & 63) >> 3) * 16 + (rho >> 6) * 8 + (rho & 7));
             const uint32_t off = (uint32_t)(c * kTileM + rho) * 4u;
             if constexpr (MODE == 1) {
-                const float gate = cluster_sum(off);
-                const float up = cluster_sum(off + (uint32_t)NP * kTileM * 4u);
-                const float v = gate / (1.f + __expf(-gate)) * up;
+                const float4 gate = cluster_sum(off);
+                const float4 up = cluster_sum(off + (uint32_t)NP * kTileM * 4u);
+                // four consecutive 16-bit outputs, 8-byte aligned (row is a multiple of 4, p.rows of 128)
+                uint2 packed;
+                packed.x = pack2<WT>(silu_mul(gate.x, up.x), silu_mul(gate.y, up.y));
+                packed.y = pack2<WT>(silu_mul(gate.z, up.z), silu_mul(gate.w, up.w));
                 const size_t o = (size_t)(cpos0 + c) * p.rows + row;
-                if constexpr (WT == kFP16)
-                    reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(v);
-                else
-                    reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
+                *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + o) = packed;
             } else {
                 const int slot = p.sorted[pos0 + c];
                 if (slot < p.n_slots) {
                     const float w = load_scalar16<WT>(p.topk_weights, slot);
-                    reinterpret_cast<float*>(p.out)[(size_t)slot * p.rows + row] = w * cluster_sum(off);
+                    const float4 v = cluster_sum(off);
+                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)slot * p.rows + row) =
+                        make_float4(w * v.x, w * v.y, w * v.z, w * v.w);
                 }
             }
         }
