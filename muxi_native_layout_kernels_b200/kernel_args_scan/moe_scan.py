@@ -89,7 +89,7 @@ def scan_case(cfg, T, w1, w2, wg, g, dev):
                     g1_best, g1_us = (100 + st1, ck1), us
             if g1_best is None:
                 continue
-            for st2, ck2 in itertools.product([2, 3, 4, 6], [2, 4, 8]):
+            for st2, ck2 in itertools.product([2, 3, 4, 6], [1, 2, 4, 8]):
                 args = (nt, g1_best[0], g1_best[1], 0, 100 + st2, ck2)
                 us = try_args(args)
                 if us is not None and us < best_us:
