@@ -482,54 +482,99 @@ __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const 
         if (warp >= 2) {
             const int etid = tid - 64;
             const int rank = blockIdx.y;
-            // slices in units of four accumulator rows: one 16-byte distributed-shared-memory load per rank brings four
-            // rows of one token, which are four consecutive weight rows (and output elements)
-            const int q0 = (kTileM / 4) * rank / SK, quads = (kTileM / 4) * (rank + 1) / SK - q0;
-            constexpr int kMaxSK = CLUSTER == 2 ? 16 : 8;
-            uint32_t remote[kMaxSK];
+            if constexpr (CLUSTER == 2) {
+                // clusters of up to 16 CTAs: one accumulator row per thread and step (the 16-byte form below would hold
+                // 64 partial sums per thread and cost this kernel a resident CTA per SM)
+                const int r0 = kTileM * rank / SK, rows = kTileM * (rank + 1) / SK - r0;
+                constexpr int kMaxSK = CLUSTER == 2 ? 16 : 8;
+                uint32_t remote[kMaxSK];
 #pragma unroll
-            for (int q = 0; q < kMaxSK; ++q)
-                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[q]) : "r"(base), "r"(q < SK ? q : 0));
-            const int total = p.n * quads;
-            for (int idx = etid; idx < total; idx += 128) {
-                const int c = idx / quads, rho = 4 * (q0 + idx - c * quads);
-                const uint32_t off = (uint32_t)(c * kTileM + rho) * 4u;
-                float4 t[kMaxSK];
+                for (int q = 0; q < kMaxSK; ++q)
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[q]) : "r"(base), "r"(q < SK ? q : 0));
+                const int total = p.n * rows;
+                for (int idx = etid; idx < total; idx += 128) {
+                    const int c = idx / rows, rho = r0 + idx - c * rows;
+                    const uint32_t off = (uint32_t)(c * kTileM + rho) * 4u;
+                    float t[kMaxSK];
 #pragma unroll
-                for (int q = 0; q < kMaxSK; ++q) {
-                    t[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (q < SK)
-                        asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                                     : "=f"(t[q].x), "=f"(t[q].y), "=f"(t[q].z), "=f"(t[q].w)
-                                     : "r"(remote[q] + off)
-                                     : "memory");
-                }
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                bool first = true;
-#pragma unroll
-                for (int q = kMaxSK - 1; q >= 0; --q) {
-                    if (q < SK) {
-                        acc = first ? t[q] : make_float4(acc.x + t[q].x, acc.y + t[q].y, acc.z + t[q].z, acc.w + t[q].w);
-                        first = false;
+                    for (int q = 0; q < kMaxSK; ++q) {
+                        t[q] = 0.f;
+                        if (q < SK) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(t[q]) : "r"(remote[q] + off) : "memory");
                     }
+                    float acc = 0.f;
+                    bool first = true;
+#pragma unroll
+                    for (int q = kMaxSK - 1; q >= 0; --q) {
+                        if (q < SK) {
+                            acc = first ? t[q] : acc + t[q];
+                            first = false;
+                        }
+                    }
+                    const int row = g * kTileM + ((rho & 63) >> 3) * 16 + (rho >> 6) * 8 + (rho & 7);
+                    const float bia = (p.bias != nullptr) ? load_scalar16<WT>(p.bias, row) : 0.f;
+                    const float val = fmaf(p.alpha, acc, bia);
+                    size_t o;
+                    if (p.c_layout == 0) {
+                        o = (size_t)c * p.m + row;
+                    } else {
+                        const int NB = p.n >> 4;
+                        o = ((((size_t)(row >> 5) * NB + (c >> 4)) * 4 + ((row >> 3) & 3)) * 16 + (c & 15)) * 8 + (row & 7);
+                    }
+                    if constexpr (WT == kFP16)
+                        reinterpret_cast<__half*>(p.C)[o] = __float2half_rn(val);
+                    else
+                        reinterpret_cast<__nv_bfloat16*>(p.C)[o] = __float2bfloat16_rn(val);
                 }
-                const int row = g * kTileM + ((rho & 63) >> 3) * 16 + (rho >> 6) * 8 + (rho & 7);
-                float4 bia = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (p.bias != nullptr)
-                    bia = make_float4(load_scalar16<WT>(p.bias, row), load_scalar16<WT>(p.bias, row + 1),
-                                      load_scalar16<WT>(p.bias, row + 2), load_scalar16<WT>(p.bias, row + 3));
-                size_t o;
-                if (p.c_layout == 0) {
-                    o = (size_t)c * p.m + row;
-                } else {
-                    const int NB = p.n >> 4;
-                    o = ((((size_t)(row >> 5) * NB + (c >> 4)) * 4 + ((row >> 3) & 3)) * 16 + (c & 15)) * 8 + (row & 7);
+            } else {
+                // slices in units of four accumulator rows: one 16-byte distributed-shared-memory load per rank brings four
+                // rows of one token, which are four consecutive weight rows (and output elements)
+                const int q0 = (kTileM / 4) * rank / SK, quads = (kTileM / 4) * (rank + 1) / SK - q0;
+                constexpr int kMaxSK = CLUSTER == 2 ? 16 : 8;
+                uint32_t remote[kMaxSK];
+#pragma unroll
+                for (int q = 0; q < kMaxSK; ++q)
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[q]) : "r"(base), "r"(q < SK ? q : 0));
+                const int total = p.n * quads;
+                for (int idx = etid; idx < total; idx += 128) {
+                    const int c = idx / quads, rho = 4 * (q0 + idx - c * quads);
+                    const uint32_t off = (uint32_t)(c * kTileM + rho) * 4u;
+                    float4 t[kMaxSK];
+#pragma unroll
+                    for (int q = 0; q < kMaxSK; ++q) {
+                        t[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (q < SK)
+                            asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                         : "=f"(t[q].x), "=f"(t[q].y), "=f"(t[q].z), "=f"(t[q].w)
+                                         : "r"(remote[q] + off)
+                                         : "memory");
+                    }
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    bool first = true;
+#pragma unroll
+                    for (int q = kMaxSK - 1; q >= 0; --q) {
+                        if (q < SK) {
+                            acc = first ? t[q] : make_float4(acc.x + t[q].x, acc.y + t[q].y, acc.z + t[q].z, acc.w + t[q].w);
+                            first = false;
+                        }
+                    }
+                    const int row = g * kTileM + ((rho & 63) >> 3) * 16 + (rho >> 6) * 8 + (rho & 7);
+                    float4 bia = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (p.bias != nullptr)
+                        bia = make_float4(load_scalar16<WT>(p.bias, row), load_scalar16<WT>(p.bias, row + 1),
+                                          load_scalar16<WT>(p.bias, row + 2), load_scalar16<WT>(p.bias, row + 3));
+                    size_t o;
+                    if (p.c_layout == 0) {
+                        o = (size_t)c * p.m + row;
+                    } else {
+                        const int NB = p.n >> 4;
+                        o = ((((size_t)(row >> 5) * NB + (c >> 4)) * 4 + ((row >> 3) & 3)) * 16 + (c & 15)) * 8 + (row & 7);
+                    }
+                    // four consecutive 16-bit outputs, 8-byte aligned (row is a multiple of 4, m a multiple of 128)
+                    uint2 packed;
+                    packed.x = pack2<WT>(fmaf(p.alpha, acc.x, bia.x), fmaf(p.alpha, acc.y, bia.y));
+                    packed.y = pack2<WT>(fmaf(p.alpha, acc.z, bia.z), fmaf(p.alpha, acc.w, bia.w));
+                    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.C) + o) = packed;
                 }
-                // four consecutive 16-bit outputs, 8-byte aligned (row is a multiple of 4, m a multiple of 128)
-                uint2 packed;
-                packed.x = pack2<WT>(fmaf(p.alpha, acc.x, bia.x), fmaf(p.alpha, acc.y, bia.y));
-                packed.y = pack2<WT>(fmaf(p.alpha, acc.z, bia.z), fmaf(p.alpha, acc.w, bia.w));
-                *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.C) + o) = packed;
             }
             if (etid == 0) MLK_TL(5);
         }
