@@ -94,6 +94,24 @@ int mlk_reLayoutC(const void* C_in, void* C_out, int m, int n, mlk_stream_t s);
  * Reference: fp8_weight_repack, csrc/fp8_weight_repack.cu:44-67. */
 int mlk_fp8_weight_repack(const void* weight, void* out, int64_t nbytes, mlk_stream_t s);
 
+/* Scratch lent to one call (device pointers); every GeMV / GEMM entry point takes one, NULL = none.
+ * workspace: fp32 scratch, any content: mlk_gemm_workspace_bytes(m, n, k) bytes cover every kernel of that shape.
+ * counters: >= m/128 ints that are zero on entry; every kernel leaves them zero again, so one block per stream can be
+ * reused by successive calls.  status: one int, sticky error word of the bounded waits inside the tcgen05 kernels
+ * (0 = ok), may be NULL.  A kernel whose wait expired leaves its output unwritten (and, in the persistent stream-K
+ * mode, possibly non-zero counters): clear the counters and the word before the block is used again. */
+typedef struct mlk_aux {
+    void* workspace;
+    int64_t workspace_bytes;
+    int32_t* counters;
+    int32_t n_counters;
+    int32_t* status;
+} mlk_aux;
+
+/* Workspace size (bytes) that covers every kernelId-2 launch of this shape on the current device; 0 if the shape
+ * cannot use that kernel. */
+int64_t mlk_gemm_workspace_bytes(int m, int n, int k);
+
 /* ---- GeMV: y[1,m] = alpha * A x (+ bias) ------------------------------------------------------- */
 
 /* Explicit tuning arguments.  Reference: gemv_layoutA_wapper, csrc/gemv_layout_a.cu:17-71.
@@ -107,10 +125,11 @@ int mlk_fp8_weight_repack(const void* weight, void* out, int64_t nbytes, mlk_str
  *   beta is accepted and ignored, as in the reference kernels. */
 int mlk_gemv_layoutA_wapper(const void* A, const void* x, void* y, int m, int k, int dtype, float alpha, float beta,
                             int blockDimX, int kernelId, int kernelParam1, int kernelParam2,
-                            const float* scale_matrix, const void* bias, int fp8_order, mlk_stream_t s);
+                            const float* scale_matrix, const void* bias, int fp8_order, const mlk_aux* aux,
+                            mlk_stream_t s);
 /* Table-driven.  Reference: gemv_layoutA, csrc/gemv_layout_a.cu:73-150. */
 int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dtype, float alpha, float beta,
-                     const float* scale_matrix, const void* bias, int fp8_order, mlk_stream_t s);
+                     const float* scale_matrix, const void* bias, int fp8_order, const mlk_aux* aux, mlk_stream_t s);
 
 /* ---- narrow GEMM: C[n,m] = alpha * B A^T (+ bias), n <= 256 ------------------------------------------- */
 
@@ -130,28 +149,8 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
  *   Block scales are applied in the decode as rne_bf16(w * s), the weight the reference's torch recipe
  *   (muxi_layout_kernels/utils.py:14-25) dequantises to; kernelId 1, 3, 4 apply s to the fp32 sums of each 128-wide
  *   k block instead, and the reference's kernels truncate fp32(w) * s to bf16: all within one bf16 ulp per weight.
- * kernelId 8 (16-bit weights, row-major B, m % 256 == 0, n <= 64): the tcgen05 cluster kernel with 256 weight rows per
- *   CTA, two accumulators fed by the same token tile, which halves the token-tile traffic from L2 (no row of
- *   the packaged tables uses it: on those shapes the 128-row kernel is faster); kernelParam2 = ring stages (2, 3, 4; 32 KB of weights each), kernelParam3 =
- *   CTAs per cluster (1..8), kernelParam1 ignored.
  * kernelId 5, 6, 7 (CUDA-core FMA + shuffle kernel with 256, 128, 64 threads; 16-bit weights, row-major B and C,
  *   n <= 4): kernelParam1 = row groups per warp (1,2), kernelParam2 unused, kernelParam3 = cluster split-K. */
-
-/* Scratch lent to one call (device pointers).  workspace: mlk_gemm_workspace_bytes(m, n, k) bytes, any content.
- * counters: >= m/128 ints that are zero on entry; every kernel leaves them
- * zero again, so one buffer per stream can be reused by successive calls.  status: one int, sticky error word of the
- * bounded waits inside the kernel (0 = ok), may be NULL. */
-typedef struct mlk_aux {
-    void* workspace;
-    int64_t workspace_bytes;
-    int32_t* counters;
-    int32_t n_counters;
-    int32_t* status;
-} mlk_aux;
-
-/* Workspace size (bytes) that covers every kernelId-2 launch of this shape on the current device; 0 if the shape
- * cannot use that kernel. */
-int64_t mlk_gemm_workspace_bytes(int m, int n, int k);
 
 /* A layout A, B row-major [n,k], C row-major [n,m].  Reference: gemm_layoutA_wapper, csrc/gemm_layout_A.cu:684-750. */
 int mlk_gemm_layoutA_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha,
@@ -164,24 +163,26 @@ int mlk_gemm_layoutA(const void* A, const void* B, void* C, int m, int n, int k,
  * Reference: gemm_layoutA_soft_fp8_wapper, csrc/gemm_layout_A_soft_fp8.cu:749. */
 int mlk_gemm_layoutA_soft_fp8_wapper(const void* A, const float* A_scale, const void* B, void* C, int m, int n, int k,
                                      float alpha, float beta, int kernelParam1, int kernelParam2, int kernelParam3,
-                                     int kernelId, const void* bias, int fp8_order, mlk_stream_t s);
+                                     int kernelId, const void* bias, int fp8_order, const mlk_aux* aux, mlk_stream_t s);
 /* Reference: gemm_layoutA_soft_fp8, csrc/gemm_layout_A_soft_fp8.cu:825. */
 int mlk_gemm_layoutA_soft_fp8(const void* A, const float* A_scale, const void* B, void* C, int m, int n, int k,
-                              float alpha, float beta, const void* bias, int fp8_order, mlk_stream_t s);
+                              float alpha, float beta, const void* bias, int fp8_order, const mlk_aux* aux,
+                              mlk_stream_t s);
 /* A layout A, B layout B, C row-major.  Reference: gemm_layoutAB_ContinuousC_wapper,
  * csrc/gemm_layout_ab_continuous_c.cu:982; table-driven form :1051. */
 int mlk_gemm_layoutAB_ContinuousC_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype,
                                          float alpha, float beta, int kernelParam1, int kernelParam2,
-                                         int kernelParam3, int kernelId, const void* bias, mlk_stream_t s);
+                                         int kernelParam3, int kernelId, const void* bias, const mlk_aux* aux,
+                                         mlk_stream_t s);
 int mlk_gemm_layoutAB_ContinuousC(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha,
-                                  float beta, const void* bias, mlk_stream_t s);
+                                  float beta, const void* bias, const mlk_aux* aux, mlk_stream_t s);
 /* A layout A, B layout B, C layout C.  Reference: gemm_layoutABC_wapper, csrc/gemm_layout_abc.cu:685;
  * table-driven form :754. */
 int mlk_gemm_layoutABC_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha,
                               float beta, int kernelParam1, int kernelParam2, int kernelParam3, int kernelId,
-                              const void* bias, mlk_stream_t s);
+                              const void* bias, const mlk_aux* aux, mlk_stream_t s);
 int mlk_gemm_layoutABC(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha, float beta,
-                       const void* bias, mlk_stream_t s);
+                       const void* bias, const mlk_aux* aux, mlk_stream_t s);
 
 /* ---- fused MoE ("plan C") ------------------------------------------------------------------------ */
 
@@ -234,6 +235,7 @@ int mlk_moe_align(int batchSize, int expertCount, int topK, int microBatchSize, 
  * tune: NULL, or six host ints {token tiles per work item (1,2,4,8 = 8..64 slots), row warps of GEMM1 (1,2,4),
  * cluster split-K of GEMM1 (1,2,4,8), row groups per warp of GEMM2 (1,2), row warps of GEMM2 (1,2,4), cluster split-K of
  * GEMM2}; a 0 lets the library choose that value from the shape.
+ * status: one device int, sticky error word of the bounded waits inside the tcgen05 expert kernels (0 = ok), or NULL.
  * combine_scratch: optional T*topK*H floats.  With it the weighted expert outputs are kept in fp32 and summed per
  * token in a fixed order with one final rounding (bit-reproducible).  With NULL they are accumulated into y with
  * 16-bit atomics, as the reference does (csrc/moe_kernels/group_gemm_second.h:333-346): one rounding per addend
@@ -245,12 +247,12 @@ int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int
                               int32_t* experts_ids, void* C, void* y, const float* w1_scale, const float* w2_scale,
                               int dtype, int fp8_order, int microBatchSize, const int32_t* experts_map,
                               int experts_map_len, float* combine_scratch, int64_t combine_scratch_bytes,
-                              const int32_t* tune, mlk_stream_t s);
+                              const int32_t* tune, int32_t* status, mlk_stream_t s);
 
 /* Expert compute for callers that must not allocate device memory (a plugin running under another runtime's memory
  * pool, a serving loop whose allocator is off limits on the request path).  It has no
- * counterpart in the reference.  Same arguments and results as mlk_fused_experts_compute with a combine scratch,
- * except that the scratch is a device array built into the library: 8 MiB per GPU that loads the library, held
+ * counterpart in the reference.  Same arguments (tune and status included) and results as mlk_fused_experts_compute
+ * with a combine scratch, except that the scratch is a device array built into the library: 8 MiB per GPU that loads the library, held
  * until the process exits, which limits batch_size * topK * hidden to 2 Mi (2097152) floats -- larger calls fail
  * with MLK_ERR_INVALID_ARG.  The first call on a device looks the array's address up; make that call before any
  * stream capture.  All calls share the array: calls that overlap on the GPU (different streams) race on it. */
@@ -259,7 +261,8 @@ int mlk_fused_experts_compute_static(const void* w1, const void* w2, const void*
                                      int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
                                      int32_t* experts_ids, void* C, void* y, const float* w1_scale,
                                      const float* w2_scale, int dtype, int fp8_order, int microBatchSize,
-                                     const int32_t* experts_map, int experts_map_len, mlk_stream_t s);
+                                     const int32_t* experts_map, int experts_map_len, const int32_t* tune,
+                                     int32_t* status, mlk_stream_t s);
 
 /* ---- expert-parallel token exchange (no counterpart in the reference, which is single-GPU) ------------------ */
 

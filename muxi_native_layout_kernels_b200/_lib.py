@@ -30,22 +30,22 @@ PROTOTYPES = {
     "mlk_reLayoutC": (c_int, [c_vp, c_vp, c_int, c_int, c_vp]),
     "mlk_fp8_weight_repack": (c_int, [c_vp, c_vp, c_i64, c_vp]),
     "mlk_gemv_layoutA_wapper": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_f32, c_f32, c_int, c_int, c_int,
-                                        c_int, c_vp, c_vp, c_int, c_vp]),
-    "mlk_gemv_layoutA": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_vp, c_int, c_vp]),
+                                        c_int, c_vp, c_vp, c_int, c_vp, c_vp]),
+    "mlk_gemv_layoutA": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_vp, c_int, c_vp, c_vp]),
     "mlk_gemm_layoutA_wapper": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_int, c_int,
                                         c_int, c_int, c_vp, c_vp, c_vp]),
     "mlk_gemm_layoutA": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_vp, c_vp]),
     "mlk_gemm_layoutA_soft_fp8_wapper": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_f32, c_f32, c_int,
-                                                 c_int, c_int, c_int, c_vp, c_int, c_vp]),
+                                                 c_int, c_int, c_int, c_vp, c_int, c_vp, c_vp]),
     "mlk_gemm_layoutA_soft_fp8": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_int,
-                                          c_vp]),
+                                          c_vp, c_vp]),
     "mlk_gemm_layoutAB_ContinuousC_wapper": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32,
-                                                     c_int, c_int, c_int, c_int, c_vp, c_vp]),
+                                                     c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp]),
     "mlk_gemm_layoutAB_ContinuousC": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_vp,
-                                              c_vp]),
+                                              c_vp, c_vp]),
     "mlk_gemm_layoutABC_wapper": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_int, c_int,
-                                          c_int, c_int, c_vp, c_vp]),
-    "mlk_gemm_layoutABC": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_vp]),
+                                          c_int, c_int, c_vp, c_vp, c_vp]),
+    "mlk_gemm_layoutABC": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_vp, c_vp]),
     "mlk_fused_routing_gate": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_vp, c_int,
                                        c_vp]),
     "mlk_fused_router_gemm_gate": (c_int, [c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_vp,
@@ -55,12 +55,12 @@ PROTOTYPES = {
     "mlk_moe_align": (c_int, [c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_vp]),
     "mlk_fused_experts_compute_static": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp,
                                                  c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp,
-                                                 c_int, c_vp]),
+                                                 c_int, C.POINTER(C.c_int32), c_vp, c_vp]),
     "mlk_moe_gather_rows": (c_int, [c_vp, c_vp, c_vp, c_i64, c_int, c_i64, c_vp]),
     "mlk_moe_unpermute_sum": (c_int, [c_vp, c_vp, c_vp, c_i64, c_int, c_int, c_i64, c_int, c_vp]),
     "mlk_fused_experts_compute": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp,
                                           c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp,
-                                          c_int, c_vp, c_i64, C.POINTER(C.c_int32), c_vp]),
+                                          c_int, c_vp, c_i64, C.POINTER(C.c_int32), c_vp, c_vp]),
 }
 
 

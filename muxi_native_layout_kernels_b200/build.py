@@ -27,7 +27,6 @@ SOURCES = [
     "dense.cu",
     "dense_umma.cu",
     "dense_umma_f8.cu",
-    "dense_umma_pair.cu",
     "prepack.cu",
     "moe_router.cu",
     "moe_align.cu",

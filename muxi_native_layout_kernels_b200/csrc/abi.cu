@@ -34,6 +34,19 @@ void set_option(int which, int value) {
     if (which >= 0 && which < kNumOptions) g_options[which] = value;
 }
 
+int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    int& c = cached[dev & 63];
+    if (c == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        c = v;
+    }
+    return c;
+}
+
 int launch_layout_a(const void*, void*, long long, long long, int, int, cudaStream_t);
 int launch_layout_b(const void*, void*, int, int, cudaStream_t);
 int launch_relayout_c(const void*, void*, int, int, cudaStream_t);
@@ -83,14 +96,6 @@ int gemm_common(int variant_x, int variant_c, const void* A, const float* scale,
         }
         return launch_dense_umma(wt, p, p1, p2, p3, aux ? &da : nullptr, s);
     }
-    if (kernelId == 8) {
-        // tcgen05 tile kernel with 256 weight rows per CTA (two accumulators share the token tile): kernelParam2 =
-        // ring stages (2, 3, 4), kernelParam3 = CTAs per cluster (1..8)
-        if (wt == kE4M3) return fail(kUnsupported, "gemm: kernelId 8 takes 16-bit weights");
-        if (variant_x != 0) return fail(kUnsupported, "gemm: kernelId 8 needs row-major B");
-        if (variant_c != 0 && n % 16 != 0) return fail(kInvalidArg, "gemm: layout C needs n %% 16 == 0");
-        return launch_dense_umma_pair(wt, p, p2, p3 < 1 ? 1 : p3, aux ? aux->status : nullptr, s);
-    }
     if (kernelId >= 5 && kernelId <= 7) {
         // CUDA-core FMA kernel for 1..4 tokens; 5 / 6 / 7 = 256 / 128 / 64 threads; kernelParam1 = row groups per
         // warp, kernelParam3 = cluster split-K
@@ -120,13 +125,10 @@ int gemm_table(int table, int variant_x, int variant_c, const void* A, const flo
                           : ((t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 && t.d <= 8));
     const bool ok5 = t.a >= 5 && t.a <= 7 && n <= 4 && variant_x == 0 && variant_c == 0 && dtype != MLK_E4M3 &&
                      (t.b == 1 || t.b == 2) && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b) == 0;
-    const bool ok8 = t.a == 8 && variant_x == 0 && dtype != MLK_E4M3 && n <= 64 && m % 256 == 0 && k % 64 == 0 &&
-                     t.c >= 2 && t.c <= 4 && t.d >= 1 && t.d <= 8 && t.d <= k / 64 &&
-                     (size_t)t.c * (32768 + (n <= 16 ? 16 : (n <= 32 ? 32 : 64)) * 128) >= (size_t)(n <= 16 ? 16 : (n <= 32 ? 32 : 64)) * 1024;
-    if (!ok1 && !ok2 && !ok5 && !ok8) t = default_args(table, m, n, k);
+    if (!ok1 && !ok2 && !ok5) t = default_args(table, m, n, k);
     // the tcgen05 kernel reads through tensor maps, which want 16-byte aligned bases; e4m3 activations in layout B
     // have no tcgen05 variant
-    if ((t.a == 2 || t.a == 8) && ((((uintptr_t)A | (uintptr_t)B) & 15) != 0 || (variant_x != 0 && dtype == MLK_E4M3)))
+    if (t.a == 2 && ((((uintptr_t)A | (uintptr_t)B) & 15) != 0 || (variant_x != 0 && dtype == MLK_E4M3)))
         t = warp_level_default_args(table, m, n, k);
     return gemm_common(variant_x, variant_c, A, scale, B, C, m, n, k, dtype, alpha, t.b, t.c, t.d, t.a, bias,
                        fp8_order, s, aux);
@@ -215,7 +217,8 @@ int mlk_fp8_weight_repack(const void* weight, void* out, int64_t nbytes, mlk_str
 
 int mlk_gemv_layoutA_wapper(const void* A, const void* x, void* y, int m, int k, int dtype, float alpha, float,
                             int blockDimX, int kernelId, int kernelParam1, int kernelParam2,
-                            const float* scale_matrix, const void* bias, int fp8_order, mlk_stream_t s) {
+                            const float* scale_matrix, const void* bias, int fp8_order, const mlk_aux* aux,
+                            mlk_stream_t s) {
     clear_error();
     const int wt = wt_of(dtype);
     if (wt < 0) return fail(kInvalidArg, "Unsupported data type code %d", dtype);
@@ -231,13 +234,13 @@ int mlk_gemv_layoutA_wapper(const void* A, const void* x, void* y, int m, int k,
     if (kernelId == 2) return launch_gemv_simt(wt, p, 0, (cudaStream_t)s);
     if (kernelId == 3 && wt == kE4M3) {
         // TMA -> convert -> tcgen05 pipeline: kernelParam1 = raw ring stages, kernelParam2 = cluster size
-        return launch_dense_umma_f8(p, kernelParam1, kernelParam2, nullptr, (cudaStream_t)s);
+        return launch_dense_umma_f8(p, kernelParam1, kernelParam2, aux ? aux->status : nullptr, (cudaStream_t)s);
     }
     return fail(kUnsupported, "gemv: kernelId %d is not built (1 = tensor-core, 2 = CUDA-core, 3 = tcgen05 for e4m3)", kernelId);
 }
 
 int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dtype, float alpha, float beta,
-                     const float* scale_matrix, const void* bias, int fp8_order, mlk_stream_t s) {
+                     const float* scale_matrix, const void* bias, int fp8_order, const mlk_aux* aux, mlk_stream_t s) {
     clear_error();
     if (m <= 0 || k <= 0) return fail(kInvalidArg, "gemv: m and k must be positive");
     if (m % 16 != 0) return fail(kInvalidArg, "GEMV m %% 16(at least) must be 0");
@@ -251,7 +254,7 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
                      (t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 && t.d <= 8;
     if (!ok && !ok3) t = default_args(table, m, 1, k);
     return mlk_gemv_layoutA_wapper(A, x, y, m, k, dtype, alpha, beta, t.a, t.b, t.c, t.d, scale_matrix, bias,
-                                   fp8_order, s);
+                                   fp8_order, aux, s);
 }
 
 int mlk_gemm_layoutA_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha, float,
@@ -266,35 +269,36 @@ int mlk_gemm_layoutA(const void* A, const void* B, void* C, int m, int n, int k,
 }
 int mlk_gemm_layoutA_soft_fp8_wapper(const void* A, const float* A_scale, const void* B, void* C, int m, int n, int k,
                                      float alpha, float, int p1, int p2, int p3, int kernelId, const void* bias,
-                                     int fp8_order, mlk_stream_t s) {
+                                     int fp8_order, const mlk_aux* aux, mlk_stream_t s) {
     return gemm_common(0, 0, A, A_scale, B, C, m, n, k, MLK_E4M3, alpha, p1, p2, p3, kernelId, bias, fp8_order,
-                       (cudaStream_t)s);
+                       (cudaStream_t)s, aux);
 }
 int mlk_gemm_layoutA_soft_fp8(const void* A, const float* A_scale, const void* B, void* C, int m, int n, int k,
-                              float alpha, float, const void* bias, int fp8_order, mlk_stream_t s) {
+                              float alpha, float, const void* bias, int fp8_order, const mlk_aux* aux, mlk_stream_t s) {
     return gemm_table(kTableGemmLayoutASoftFp8, 0, 0, A, A_scale, B, C, m, n, k, MLK_E4M3, alpha, bias, fp8_order,
-                      (cudaStream_t)s);
+                      (cudaStream_t)s, aux);
 }
 int mlk_gemm_layoutAB_ContinuousC_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype,
                                          float alpha, float, int p1, int p2, int p3, int kernelId, const void* bias,
-                                         mlk_stream_t s) {
+                                         const mlk_aux* aux, mlk_stream_t s) {
     if (dtype == MLK_E4M3) { clear_error(); return fail(kInvalidArg, "gemm_layoutAB_ContinuousC: 16-bit weights only"); }
-    return gemm_common(1, 0, A, nullptr, B, C, m, n, k, dtype, alpha, p1, p2, p3, kernelId, bias, 0, (cudaStream_t)s);
+    return gemm_common(1, 0, A, nullptr, B, C, m, n, k, dtype, alpha, p1, p2, p3, kernelId, bias, 0, (cudaStream_t)s, aux);
 }
 int mlk_gemm_layoutAB_ContinuousC(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha,
-                                  float, const void* bias, mlk_stream_t s) {
+                                  float, const void* bias, const mlk_aux* aux, mlk_stream_t s) {
     if (dtype == MLK_E4M3) { clear_error(); return fail(kInvalidArg, "gemm_layoutAB_ContinuousC: 16-bit weights only"); }
-    return gemm_table(kTableGemmContinuousC, 1, 0, A, nullptr, B, C, m, n, k, dtype, alpha, bias, 0, (cudaStream_t)s);
+    return gemm_table(kTableGemmContinuousC, 1, 0, A, nullptr, B, C, m, n, k, dtype, alpha, bias, 0, (cudaStream_t)s, aux);
 }
 int mlk_gemm_layoutABC_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha,
-                              float, int p1, int p2, int p3, int kernelId, const void* bias, mlk_stream_t s) {
+                              float, int p1, int p2, int p3, int kernelId, const void* bias, const mlk_aux* aux,
+                              mlk_stream_t s) {
     if (dtype == MLK_E4M3) { clear_error(); return fail(kInvalidArg, "gemm_layoutABC: 16-bit weights only"); }
-    return gemm_common(1, 1, A, nullptr, B, C, m, n, k, dtype, alpha, p1, p2, p3, kernelId, bias, 0, (cudaStream_t)s);
+    return gemm_common(1, 1, A, nullptr, B, C, m, n, k, dtype, alpha, p1, p2, p3, kernelId, bias, 0, (cudaStream_t)s, aux);
 }
 int mlk_gemm_layoutABC(const void* A, const void* B, void* C, int m, int n, int k, int dtype, float alpha, float,
-                       const void* bias, mlk_stream_t s) {
+                       const void* bias, const mlk_aux* aux, mlk_stream_t s) {
     if (dtype == MLK_E4M3) { clear_error(); return fail(kInvalidArg, "gemm_layoutABC: 16-bit weights only"); }
-    return gemm_table(kTableGemmABC, 1, 1, A, nullptr, B, C, m, n, k, dtype, alpha, bias, 0, (cudaStream_t)s);
+    return gemm_table(kTableGemmABC, 1, 1, A, nullptr, B, C, m, n, k, dtype, alpha, bias, 0, (cudaStream_t)s, aux);
 }
 
 int mlk_fused_routing_gate(const void* gating_output, int score_fun, int batch_size, int num_experts, int n_groups,
@@ -343,21 +347,36 @@ int mlk_moe_unpermute_sum(const void* rows, const int32_t* pos, void* y, int64_t
     return launch_unpermute_sum(rows, pos, y, T, topK, hidden, n_rows, dtype, (cudaStream_t)s);
 }
 
-int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int batch_size, int expert_count,
-                              int topK, int hidden, int inter, const int32_t* topk_ids, const void* topk_weights,
-                              int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
-                              int32_t* experts_ids, void* C, void* y, const float* w1_scale, const float* w2_scale,
-                              int dtype, int fp8_order, int microBatchSize, const int32_t* experts_map,
-                              int experts_map_len, float* combine_scratch, int64_t combine_scratch_bytes,
-                              const int32_t* tune, mlk_stream_t s) {
-    clear_error();
+namespace {
+MoeParams moe_params(const void* w1, const void* w2, const void* x, int batch_size, int expert_count, int topK, int hidden,
+                     int inter, const int32_t* topk_ids, const void* topk_weights, int32_t* sorted_token_ids,
+                     int32_t* cumsum_buffer, int32_t* padded_num_experts, int32_t* experts_ids, void* C, void* y,
+                     const float* w1_scale, const float* w2_scale, int dtype, int fp8_order, int microBatchSize,
+                     const int32_t* experts_map, int experts_map_len, const int32_t* tune, int32_t* status) {
     MoeParams p{};
     p.w1 = w1; p.w2 = w2; p.x = x; p.T = batch_size; p.E = expert_count; p.topk = topK; p.H = hidden; p.I = inter;
     p.topk_ids = topk_ids; p.topk_weights = topk_weights; p.sorted_token_ids = sorted_token_ids;
     p.cumsum = cumsum_buffer; p.padded_num_experts = padded_num_experts; p.experts_ids = experts_ids;
     p.C = C; p.y = y; p.w1_scale = w1_scale; p.w2_scale = w2_scale; p.dtype = dtype; p.fp8_order = fp8_order;
     p.mbs = microBatchSize; p.experts_map = experts_map; p.experts_map_len = experts_map_len;
-    p.scratch = combine_scratch; p.scratch_bytes = combine_scratch_bytes; if (tune) { p.nt = tune[0]; p.wm1 = tune[1]; p.sk1 = tune[2]; p.rg = tune[3]; p.wm2 = tune[4]; p.sk2 = tune[5]; }
+    p.status = status;
+    if (tune) { p.nt = tune[0]; p.wm1 = tune[1]; p.sk1 = tune[2]; p.rg = tune[3]; p.wm2 = tune[4]; p.sk2 = tune[5]; }
+    return p;
+}
+}  // namespace
+
+int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int batch_size, int expert_count,
+                              int topK, int hidden, int inter, const int32_t* topk_ids, const void* topk_weights,
+                              int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
+                              int32_t* experts_ids, void* C, void* y, const float* w1_scale, const float* w2_scale,
+                              int dtype, int fp8_order, int microBatchSize, const int32_t* experts_map,
+                              int experts_map_len, float* combine_scratch, int64_t combine_scratch_bytes,
+                              const int32_t* tune, int32_t* status, mlk_stream_t s) {
+    clear_error();
+    MoeParams p = moe_params(w1, w2, x, batch_size, expert_count, topK, hidden, inter, topk_ids, topk_weights,
+                             sorted_token_ids, cumsum_buffer, padded_num_experts, experts_ids, C, y, w1_scale, w2_scale,
+                             dtype, fp8_order, microBatchSize, experts_map, experts_map_len, tune, status);
+    p.scratch = combine_scratch; p.scratch_bytes = combine_scratch_bytes;
     return launch_fused_experts(p, (cudaStream_t)s);
 }
 
@@ -366,14 +385,12 @@ int mlk_fused_experts_compute_static(const void* w1, const void* w2, const void*
                                      int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
                                      int32_t* experts_ids, void* C, void* y, const float* w1_scale,
                                      const float* w2_scale, int dtype, int fp8_order, int microBatchSize,
-                                     const int32_t* experts_map, int experts_map_len, mlk_stream_t s) {
+                                     const int32_t* experts_map, int experts_map_len, const int32_t* tune,
+                                     int32_t* status, mlk_stream_t s) {
     clear_error();
-    MoeParams p{};
-    p.w1 = w1; p.w2 = w2; p.x = x; p.T = batch_size; p.E = expert_count; p.topk = topK; p.H = hidden; p.I = inter;
-    p.topk_ids = topk_ids; p.topk_weights = topk_weights; p.sorted_token_ids = sorted_token_ids;
-    p.cumsum = cumsum_buffer; p.padded_num_experts = padded_num_experts; p.experts_ids = experts_ids;
-    p.C = C; p.y = y; p.w1_scale = w1_scale; p.w2_scale = w2_scale; p.dtype = dtype; p.fp8_order = fp8_order;
-    p.mbs = microBatchSize; p.experts_map = experts_map; p.experts_map_len = experts_map_len;
+    const MoeParams p = moe_params(w1, w2, x, batch_size, expert_count, topK, hidden, inter, topk_ids, topk_weights,
+                                   sorted_token_ids, cumsum_buffer, padded_num_experts, experts_ids, C, y, w1_scale,
+                                   w2_scale, dtype, fp8_order, microBatchSize, experts_map, experts_map_len, tune, status);
     return launch_fused_experts_static(p, (cudaStream_t)s);
 }
 

@@ -38,8 +38,6 @@ int launch_dense_mma(int wt, const DenseParams& p, cudaStream_t stream);
 int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages, int cluster_k, const DenseAux* aux,
                       cudaStream_t stream);
 long long umma_workspace_bytes(int m, int n, int k, int sms, int ctas_per_sm);
-// the same pipeline with two 128-row tiles per CTA sharing one token tile (cluster mode only, m % 256 == 0)
-int launch_dense_umma_pair(int wt, const DenseParams& p, int stages, int cluster_k, int* status, cudaStream_t stream);
 // e4m3 weights through the TMA -> convert -> tcgen05 pipeline (block scales applied in the decode); status may be null
 int launch_dense_umma_f8(const DenseParams& p, int stages, int cluster_k, int* status, cudaStream_t stream);
 int launch_gemv_simt(int wt, const DenseParams& p, int rows_per_warp_log2, cudaStream_t stream);

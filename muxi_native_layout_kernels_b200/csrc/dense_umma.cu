@@ -218,6 +218,9 @@ __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const 
         MLK_TL(3);
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
+        // Its bounded waits must not start counting while the producer still waits for the preceding kernel of the
+        // stream (the token tiles are only requested after that): wait for it here as well.
+        pdl_wait();
         constexpr uint32_t idesc = instr_desc<WT, NP>();
         int i = 0, seg = 0;
         for (long long u = u0; u < u1 && !abort_flag; ++seg) {
@@ -260,10 +263,13 @@ __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const 
         // ---- epilogue warps ----
         const int quad = warp & 3;
         const int lrow = quad * 32 + lane;          // accumulator row = TMEM lane
-        // accumulator row rho holds weight row 16*(rho%64 / 8) + 8*(rho / 64) + rho%8 of the tile (see make_map_a)
+        // accumulator row rho holds weight row 16*(rho%64 / 8) + 8*(rho / 64) + rho%8 of the tile (see make_map_a16)
         const int wrow = ((lrow & 63) >> 3) * 16 + (lrow >> 6) * 8 + (lrow & 7);
         const int etid = tid - 64;
         const size_t part_elems = (size_t)NP * kTileM;
+        // counters and workspace belong to the preceding kernel of the stream until it has finished, and the bounded
+        // waits below must not run out while that kernel is still at work
+        pdl_wait();
         if constexpr (CLUSTER) {
             // cluster split-K: park the fp32 partial tile [token][accumulator row] in this CTA's (now idle) ring
             if (lane == 0 && !mbar_wait(acc_full(0), 0)) {
@@ -285,8 +291,6 @@ __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const 
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
         }
-        // counters and workspace belong to the preceding kernel of the stream until it has finished
-        pdl_wait();
         int seg = 0;
         for (long long u = u0; u < u1 && !CLUSTER; ++seg) {
             const int tile = (int)(u / KB), kb_begin = (int)(u - (long long)tile * KB);
@@ -598,22 +602,6 @@ __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const 
 
 // ---- host ------------------------------------------------------------------------------------------------
 
-// Weight tile map.  Global layout A is [row group][k-octet][half][8 rows][8 k]; the 4-D view (64 elements = one
-// 8-row core matrix, k-octet, row group, half) with box (64, 8, 8, 2) is traversed k-octet first, so each row
-// group's 2 KB run of a k block is fetched as consecutive requests, and lands in shared memory as
-// [half][row group][k-octet][128 B]: core matrix (accumulator 8-row group i = 8*half + row group, k-octet o) sits at
-// i*1024 + o*128, uniform strides for one M = 128 descriptor.
-bool make_map_a(CUtensorMap* map, const void* A, int m, int k, int wt) {
-    const cuuint64_t dims[4] = {64, (cuuint64_t)(k / 8), (cuuint64_t)(m / 16), 2};
-    const cuuint64_t strides[3] = {256, (cuuint64_t)16 * k * 2, 128};
-    const cuuint32_t box[4] = {64, kBlockK / 8, kTileM / 16, 2};
-    const cuuint32_t estr[4] = {1, 1, 1, 1};
-    return encode_fn()(map, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
-                       const_cast<void*>(A), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int WT, int NP, int CLUSTER>
 const void* kernel_for_stages(int stages) {
     switch (stages) {
@@ -641,27 +629,6 @@ const void* kernel_for(int np, int stages) {
 // (np * 512 bytes) in the idle ring, which two stages always cover
 size_t smem_bytes(int np, int stages, bool clustered) {
     return (size_t)stages * (kABytes + np * 128) + (clustered ? 0 : (size_t)np * kTileM * 2) + 1024;
-}
-
-// Resident CTAs per SM of one kernel instantiation on the current device (0 = error); the first call also raises
-// the kernel's dynamic shared-memory limit.  The grid is persistent: it is never made larger than what is
-// resident at once.
-int resident_ctas_per_sm(const void* kern, size_t smem, bool big_clusters) {
-    static std::mutex mu;
-    static std::unordered_map<unsigned long long, int> cache;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    const unsigned long long key = (unsigned long long)(uintptr_t)kern * 64ull + (unsigned)(dev & 63);
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(key);
-    if (it != cache.end()) return it->second;
-    int occ = 0;
-    if (big_clusters) cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);   // up to 16 CTAs
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, 192, smem) != cudaSuccess)
-        occ = 0;
-    cache[key] = occ;
-    return occ;
 }
 
 }  // namespace
@@ -705,16 +672,12 @@ int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages,
                        : clustered   ? (wt == kFP16 ? kernel_for<kFP16, 1>(np, stages) : kernel_for<kBF16, 1>(np, stages))
                                      : (wt == kFP16 ? kernel_for<kFP16, 0>(np, stages) : kernel_for<kBF16, 0>(np, stages));
     if (kern == nullptr) return fail(kInvalidArg, "dense (tcgen05): stages must be one of 2, 3, 4, 5, 6, 8 (got %d)", stages);
-    const size_t smem = smem_bytes(np, stages, clustered);
-    const int resident = resident_ctas_per_sm(kern, smem, cluster_k > 8);
-    if (resident < 1) return fail(kCudaError, "dense (tcgen05): a CTA with %d stages does not fit on this device", stages);
+    int resident = 0;
+    const size_t smem = prepare_kernel(kern, 192, smem_bytes(np, stages, clustered), 2 * np < 32 ? 32 : 2 * np, cluster_k > 8, &resident);
+    if (smem == 0 || resident < 1) return fail(kCudaError, "dense (tcgen05): a CTA with %d stages does not fit on this device", stages);
     if (ctas_per_sm > resident) ctas_per_sm = resident;
     if (clustered && cluster_k > p.k / kBlockK) return fail(kInvalidArg, "dense (tcgen05): cluster split %d exceeds the %d k blocks", cluster_k, p.k / kBlockK);
-    static int sm_count[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (sm_count[dev & 63] == 0) cudaDeviceGetAttribute(&sm_count[dev & 63], cudaDevAttrMultiProcessorCount, dev);
-    long long G = (long long)sm_count[dev & 63] * ctas_per_sm;
+    long long G = (long long)sm_count() * ctas_per_sm;
     const long long U = (long long)tiles * kblocks;
     if (G > U) G = U;
     // Without scratch only whole tiles can be handed out: one CTA per tile.
@@ -728,7 +691,7 @@ int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages,
         if (aux->n_counters < tiles) return fail(kInvalidArg, "dense (tcgen05): %d counters, needs %d", aux->n_counters, tiles);
     }
     CUtensorMap ma, mx;
-    if (!make_map_a(&ma, p.A, p.m, p.k, wt)) return fail(kUnsupported, "dense (tcgen05): weight tensor map rejected");
+    if (!make_map_a16(&ma, p.A, p.m, p.k, wt)) return fail(kUnsupported, "dense (tcgen05): weight tensor map rejected");
     if (!(p.x_layout == 0 ? make_map_x(&mx, p.X, p.n, p.k, wt, np) : make_map_xb(&mx, p.X, p.n, p.k, wt, np))) return fail(kUnsupported, "dense (tcgen05): activation tensor map rejected");
     UmmaParams up{};
     up.x_layout = p.x_layout;

@@ -160,6 +160,9 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8_kernel(const __grid_cons
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
+        // the token tiles are requested only after the preceding kernel of the stream has finished: the bounded waits
+        // below must not start counting before that
+        pdl_wait();
         constexpr uint32_t idesc = instr_desc<kBF16, NP>();
         for (int i = 0; i < nunits; ++i) {
             const int s2 = i % S2;
@@ -188,10 +191,22 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8_kernel(const __grid_cons
         float sc_next = (srow && nunits > 0) ? __ldg(srow + (kb0 >> 1)) : 1.f;
         uint32_t c2 = kRebias2;
         ScaledRebias sr{};
+        // Raw weight tiles may arrive (static weights) and be decoded while the preceding kernel of the stream still
+        // runs; every other wait depends on the token tiles, which follow that kernel: wait for it before the first of
+        // them, so that no bounded wait runs out on the predecessor's account.
+        bool after_pred = false;
+        if (!static_weights) {
+            pdl_wait();
+            after_pred = true;
+        }
         for (int i = 0; i < nunits; ++i) {
             const int s = i % STAGES, s2 = i % S2;
             const float sc = sc_next;
             if (srow && i + 1 < nunits) sc_next = __ldg(srow + ((kb0 + i + 1) >> 1));
+            if (i >= S2 && !after_pred) {
+                pdl_wait();
+                after_pred = true;
+            }
             bool ok = true;
             if (lane == 0) {
                 ok = !abort_flag && mbar_wait(raw_full(s), (i / STAGES) & 1);
@@ -242,6 +257,7 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8_kernel(const __grid_cons
             }
         }
         // accumulator -> fp32 partial tile [token][accumulator row] in this CTA's (now idle) raw ring
+        if (!after_pred) pdl_wait();
         if (lane == 0 && (abort_flag || !mbar_wait(acc_full, 0))) {
             if (!abort_flag && p.status) atomicExch(p.status, 3);
             abort_flag = 1;
@@ -359,20 +375,9 @@ int launch_dense_umma_f8(const DenseParams& p, int stages, int cluster_k, int* s
     const int np = p.n <= 16 ? 16 : (p.n <= 32 ? 32 : 64);
     const void* kern = np == 16 ? f8_kernel_for_stages<16>(stages) : (np == 32 ? f8_kernel_for_stages<32>(stages) : f8_kernel_for_stages<64>(stages));
     if (kern == nullptr) return fail(kInvalidArg, "dense (tcgen05, e4m3): stages must be one of 2, 3, 4, 6, 8 (got %d)", stages);
-    const size_t smem = std::max((size_t)stages * kRawBytes, (size_t)np * 512) + (size_t)conv_stages(np) * np * 128 + 1024;
-    static std::mutex mu;
-    static bool attr_set[5 * 3][64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        const int slot = (stages == 2 ? 0 : stages == 3 ? 1 : stages == 4 ? 2 : stages == 6 ? 3 : 4) * 3 + (np == 16 ? 0 : np == 32 ? 1 : 2);
-        if (!attr_set[slot][dev & 63]) {
-            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return fail(kCudaError, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-            attr_set[slot][dev & 63] = true;
-        }
-    }
+    // 128 tensor-memory columns per CTA: never more than four CTAs on an SM
+    const size_t smem = prepare_kernel(kern, 192, std::max((size_t)stages * kRawBytes, (size_t)np * 512) + (size_t)conv_stages(np) * np * 128 + 1024, 128);
+    if (smem == 0) return fail(kCudaError, "dense (tcgen05, e4m3): a CTA with %d stages does not fit on this device", stages);
     CUtensorMap ma, mx;
     if (!make_map_a8(&ma, p.A, p.m, p.k)) return fail(kUnsupported, "dense (tcgen05): weight tensor map rejected");
     if (!make_map_x(&mx, p.X, p.n, p.k, kBF16, np)) return fail(kUnsupported, "dense (tcgen05): activation tensor map rejected");

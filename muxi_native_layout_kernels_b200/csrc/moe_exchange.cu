@@ -57,7 +57,8 @@ __global__ void __launch_bounds__(256) unpermute_sum_kernel(const uint4* __restr
 
 int grid_for(long long total) {
     long long b = (total + 255) / 256;
-    if (b > 148LL * 8) b = 148LL * 8;
+    const long long cap = 8LL * sm_count();
+    if (b > cap) b = cap;
     return (int)(b < 1 ? 1 : b);
 }
 

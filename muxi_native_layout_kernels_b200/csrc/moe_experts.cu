@@ -13,6 +13,7 @@
 //   The only atomics left are the per-token accumulation of the top-k expert outputs into y, as in the
 //   reference (group_gemm_second.h:333-346).
 #include <algorithm>
+#include <mutex>
 
 #include "moe.cuh"
 #include "status.h"
@@ -268,7 +269,7 @@ int launch_moe_gemm(int wt, bool scale, const MoeGemmParams& p, int nt_tiles, in
 
 int pick_sk(int ctas, int chunks, int wk) {
     int sk = 1;
-    while (sk < 8 && ctas * sk < 2 * 148 && chunks / (wk * sk * 2) >= 4) sk *= 2;
+    while (sk < 8 && ctas * sk < 2 * sm_count() && chunks / (wk * sk * 2) >= 4) sk *= 2;
     return sk;
 }
 
@@ -360,14 +361,14 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
             return st;
         if (int st = launch_moe_umma(1, wt, m.w1, m.E, m.I, m.H, m.scratch, slots, m.C, reinterpret_cast<const int4*>(worklist),
                                      m.sorted_token_ids, m.topk_weights, (int)slots, np, m.wm1 - 100, m.sk1 > 0 ? m.sk1 : 1,
-                                     max_items, m.fp8_order, scale ? m.w1_scale : nullptr, nullptr, s))
+                                     max_items, m.fp8_order, scale ? m.w1_scale : nullptr, m.status, s))
             return st;
         if (int st = launch_moe_umma(2, wt, m.w2, m.E, m.H, m.I, m.C, slots, m.scratch, reinterpret_cast<const int4*>(worklist),
                                      m.sorted_token_ids, m.topk_weights, (int)slots, np, m.wm2 - 100, m.sk2 > 0 ? m.sk2 : 1,
-                                     max_items, m.fp8_order, scale ? m.w2_scale : nullptr, nullptr, s))
+                                     max_items, m.fp8_order, scale ? m.w2_scale : nullptr, m.status, s))
             return st;
         const long long total = (long long)m.T * (m.H / 8);
-        const int grid = (int)std::min<long long>((total + 255) / 256, 148LL * 8);
+        const int grid = (int)std::min<long long>((total + 255) / 256, 8LL * sm_count());
         if (wt == kFP16)
             moe_combine_kernel<kFP16><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
                                                           m.topk, m.H, m.y);
@@ -439,7 +440,7 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
     if (int st = launch_moe_gemm<2>(wt, scale, g2, nt_tiles, rg2, tiles2, sk2, max_items, s)) return st;
     if (!det) return kOk;
     const long long total = (long long)m.T * (m.H / 8);
-    const int grid = (int)std::min<long long>((total + 255) / 256, 148LL * 8);
+    const int grid = (int)std::min<long long>((total + 255) / 256, 8LL * sm_count());
     if (wt == kFP16)
         moe_combine_kernel<kFP16><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
                                                       m.topk, m.H, m.y);
@@ -477,19 +478,25 @@ int launch_fused_experts_static(const MoeParams& p0, cudaStream_t s) {
                     "%lld floats; use mlk_fused_experts_compute with a caller-provided buffer",
                     need, kStaticCombineFloats);
     static float* dev_addr[64] = {};
+    static std::mutex mu;       // host threads may make their first calls at the same time
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail(kCudaError, "cudaGetDevice: %s", cudaGetErrorString(e));
     if (dev < 0 || dev >= 64) return fail(kUnsupported, "fused_experts_compute_static: device index %d out of range", dev);
-    if (dev_addr[dev] == nullptr) {
-        float* ptr = nullptr;
-        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_combine);
-        if (e != cudaSuccess || ptr == nullptr)
-            return fail(kCudaError, "cudaGetSymbolAddress(static combine scratch): %s", cudaGetErrorString(e));
-        dev_addr[dev] = ptr;
+    float* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev_addr[dev] == nullptr) {
+            float* ptr = nullptr;
+            e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_combine);
+            if (e != cudaSuccess || ptr == nullptr)
+                return fail(kCudaError, "cudaGetSymbolAddress(static combine scratch): %s", cudaGetErrorString(e));
+            dev_addr[dev] = ptr;
+        }
+        scratch = dev_addr[dev];
     }
     MoeParams p = p0;
-    p.scratch = dev_addr[dev];
+    p.scratch = scratch;
     p.scratch_bytes = kStaticCombineFloats * (long long)sizeof(float);
     return launch_fused_experts(p, s);
 }

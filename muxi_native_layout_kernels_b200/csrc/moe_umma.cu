@@ -518,18 +518,6 @@ __global__ void __launch_bounds__(256) moe_gather_positions_kernel(const uint4* 
     }
 }
 
-// Weight tile map over all experts: the 4-D view of dense_umma.cu with E * rows rows.
-bool make_map_w(CUtensorMap* map, const void* W, long long rows_total, int k, int wt) {
-    const cuuint64_t dims[4] = {64, (cuuint64_t)(k / 8), (cuuint64_t)(rows_total / 16), 2};
-    const cuuint64_t strides[3] = {256, (cuuint64_t)16 * k * 2, 128};
-    const cuuint32_t box[4] = {64, kBlockK / 8, kTileM / 16, 2};
-    const cuuint32_t estr[4] = {1, 1, 1, 1};
-    return encode_fn()(map, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
-                       const_cast<void*>(W), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int WT, int NP, int MODE>
 const void* moe_kernel_for_stages(int stages) {
     switch (stages) {
@@ -604,14 +592,18 @@ int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, con
     else kern = wt == kFP16 ? moe_kernel_for<kFP16, 2>(np, stages) : moe_kernel_for<kBF16, 2>(np, stages);
     if (kern == nullptr) return fail(kInvalidArg, "moe (tcgen05): token tile %d / stages %d not built", np, stages);
     const int na = mode == 1 ? 2 : 1;
-    const size_t smem = f8 ? std::max((size_t)stages * na * kRawBytes, (size_t)na * np * 512) + (size_t)f8_conv_stages(na, np) * np * 128 + 1024
+    const size_t want = f8 ? std::max((size_t)stages * na * kRawBytes, (size_t)na * np * 512) + (size_t)f8_conv_stages(na, np) * np * 128 + 1024
                            : std::max((size_t)stages * (na * kABytes + np * 128), (size_t)na * std::min(np, 64) * 512) + 1024;
-    if (smem > 227 * 1024) return fail(kUnsupported, "moe (tcgen05): %d stages do not fit in shared memory", stages);
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(kCudaError, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    if (want > 227 * 1024) return fail(kUnsupported, "moe (tcgen05): %d stages do not fit in shared memory", stages);
+    // tensor-memory columns of one CTA (as the kernels compute them): resident CTAs per SM are capped accordingly
+    const int tmem_cols = f8 ? ((na * np + f8_conv_stages(na, np) * na * kAColumns) <= 128 ? 128 : 256)
+                             : (na * np < 32 ? 32 : na * np);
+    const size_t smem = prepare_kernel(kern, 192, want, tmem_cols);
+    if (smem == 0) return fail(kCudaError, "moe (tcgen05): a CTA with %d stages does not fit on this device", stages);
+    cudaError_t e = cudaSuccess;
     const long long w_rows = (long long)E * (mode == 1 ? 2 * rows : rows);
     CUtensorMap ma, mx;
-    if (!(f8 ? make_map_a8(&ma, W, w_rows, k) : make_map_w(&ma, W, w_rows, k, wt)))
+    if (!(f8 ? make_map_a8(&ma, W, w_rows, k) : make_map_a16(&ma, W, w_rows, k, wt)))
         return fail(kUnsupported, "moe (tcgen05): weight tensor map rejected");
     if (!make_map_x(&mx, X, (int)x_rows, k, f8 ? kBF16 : wt, np)) return fail(kUnsupported, "moe (tcgen05): activation tensor map rejected");
     MoeUmmaParams mp{};

@@ -96,7 +96,7 @@ __global__ void fp8_repack_kernel4(const uint32_t* __restrict__ in, uint32_t* __
 
 int grid_for(long long total, int block) {
     long long b = (total + block - 1) / block;
-    const long long cap = 148LL * 16;   // 16 CTAs of 256 threads fill an SM; grid-stride covers the rest
+    const long long cap = 16LL * sm_count();   // 16 CTAs of 256 threads fill an SM; grid-stride covers the rest
     if (b > cap) b = cap;
     if (b < 1) b = 1;
     return (int)b;

@@ -9,8 +9,10 @@
 //   * a miss prints one warning, inserts a default for that key (so the warning appears once) and
 //     returns the default; a missing file only warns.
 // Difference: the default is not the constant (1,1,1,1) / (256,1,1,1) tuned for another GPU but a
-// shape-based choice that keeps all 148 SMs of a B200 busy.
+// shape-based choice that keeps all SMs of the current device (148 on a B200) busy.
 #include "selector.h"
+
+#include "status.h"
 
 #include <cstdio>
 #include <cstdlib>
@@ -45,7 +47,7 @@ const char* table_file_name(int table) {
 //   GeMV tables: {BLOCK_DIM_X, KernelId, APerWarp, splitK}
 TuneArgs default_args(int table, int m, int n, int k) {
     // Target: at least ~2 CTAs of 8 warps per SM so that enough 16-byte loads are in flight.
-    const int target_ctas = 2 * 148;
+    const int target_ctas = 2 * sm_count();
     if (is_gemv(table)) {
         int rg = 1;
         int ctas = m / 16;
@@ -72,7 +74,7 @@ TuneArgs default_args(int table, int m, int n, int k) {
 
 // Launch arguments of the warp-level streaming kernel (kernelId 1) for any shape it accepts.
 TuneArgs warp_level_default_args(int table, int m, int n, int k) {
-    const int target_ctas = 2 * 148;
+    const int target_ctas = 2 * sm_count();
     (void)table;
     int rg = (n > 8 && m % 32 == 0) ? 2 : 1;
     int wm = 1;

@@ -33,6 +33,9 @@ enum Option : int {
 int option(int which);
 void set_option(int which, int value);
 
+// Number of SMs of the current device (queried once per device); 148 if the query fails.
+int sm_count();
+
 // Fills the launch attributes common to the streaming kernels: cluster split-K and programmatic dependent launch.
 inline int launch_attrs(cudaLaunchAttribute* attr, int cluster_y) {
     int n = 0;

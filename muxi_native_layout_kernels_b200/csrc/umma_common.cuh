@@ -5,7 +5,9 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstring>
 #include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 #include "status.h"
@@ -154,27 +156,111 @@ inline EncodeFn encode_fn() {
     return fn;
 }
 
+// ---- host: tensor-map cache ---------------------------------------------------------------------------------
+// Encoding a tensor map costs about a microsecond of host time, and a serving loop launches the same (pointer, shape)
+// pairs over and over: the maps of the last launches are kept per host thread, keyed by what determines them.
+template <class Build>
+inline bool cached_map(CUtensorMap* out, int kind, const void* ptr, long long a, long long b, long long c, Build&& build) {
+    struct Entry {
+        int kind;
+        const void* ptr;
+        long long a, b, c;
+        bool valid;
+        CUtensorMap map;
+    };
+    constexpr int kEntries = 128;
+    thread_local Entry cache[kEntries] = {};
+    unsigned long long h = (unsigned long long)(uintptr_t)ptr * 0x9E3779B97F4A7C15ull;
+    h ^= (unsigned long long)a * 0xC2B2AE3D27D4EB4Full + (unsigned long long)b * 0x165667B19E3779F9ull +
+         (unsigned long long)c * 0x27D4EB2F165667C5ull + (unsigned long long)kind;
+    Entry& e = cache[(h >> 32) % kEntries];
+    if (e.valid && e.kind == kind && e.ptr == ptr && e.a == a && e.b == b && e.c == c) {
+        std::memcpy(out, &e.map, sizeof(CUtensorMap));
+        return true;
+    }
+    if (!build(out)) return false;
+    e.kind = kind; e.ptr = ptr; e.a = a; e.b = b; e.c = c; e.valid = true;
+    std::memcpy(&e.map, out, sizeof(CUtensorMap));
+    return true;
+}
+
+// ---- host: per-kernel launch preparation -------------------------------------------------------------------
+// Tensor memory has 512 columns per SM and tcgen05.alloc blocks until its request fits.  A CTA that holds its columns
+// and waits at a cluster barrier for a peer that is itself blocked in tcgen05.alloc on another SM would never be
+// released, so a launch must not let more CTAs of one kernel become resident on an SM than their allocations allow.
+// prepare_kernel raises the kernel's dynamic shared-memory limit (only ever upwards, once per kernel, device and size)
+// and returns the dynamic shared-memory size to launch with: `smem`, padded where necessary until at most
+// 512 / tmem_cols CTAs fit on an SM (the kernels carve their buffers from the front, the padding stays unused).
+// 0 = the kernel cannot be launched this way on the current device.  *resident receives the CTAs per SM.
+inline size_t prepare_kernel(const void* kern, int threads, size_t smem, int tmem_cols, bool big_clusters = false,
+                             int* resident = nullptr) {
+    struct Prepared {
+        size_t launch_smem;
+        int resident;
+    };
+    static std::mutex mu;
+    static std::unordered_map<unsigned long long, Prepared> done;     // (kernel, device, smem, columns) -> result
+    static std::unordered_map<unsigned long long, size_t> attr_max;   // (kernel, device) -> limit set so far
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    const unsigned long long kd = (unsigned long long)(uintptr_t)kern * 64ull + (unsigned)(dev & 63);
+    const unsigned long long key = kd * 0x9E3779B97F4A7C15ull ^ ((unsigned long long)smem << 12) ^ (unsigned)tmem_cols;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = done.find(key);
+    if (it != done.end()) {
+        if (resident) *resident = it->second.resident;
+        return it->second.launch_smem;
+    }
+    int optin = 0;
+    if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return 0;
+    if (big_clusters) cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);   // up to 16 CTAs
+    const int limit = tmem_cols > 0 ? 512 / tmem_cols : 1 << 30;
+    Prepared r{0, 0};
+    for (size_t s = smem; s <= (size_t)optin; s += 2048) {
+        size_t& cur = attr_max[kd];
+        if (s > cur) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s) != cudaSuccess) break;
+            cur = s;
+        }
+        int occ = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, threads, s) != cudaSuccess || occ < 1) break;
+        if (occ <= limit) {
+            r.launch_smem = s;
+            r.resident = occ;
+            break;
+        }
+    }
+    cudaGetLastError();     // a failed probe must not leak into the caller's next error check
+    done[key] = r;
+    if (resident) *resident = r.resident;
+    return r.launch_smem;
+}
+
 inline bool make_map_x(CUtensorMap* map, const void* X, int n, int k, int wt, int np) {
-    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)n};
-    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-    const cuuint32_t box[2] = {kBlockK, (cuuint32_t)np};
-    const cuuint32_t estr[2] = {1, 1};
-    return encode_fn()(map, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                       const_cast<void*>(X), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return cached_map(map, 1, X, n, k, wt * 1024 + np, [&](CUtensorMap* m) {
+        const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)n};
+        const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+        const cuuint32_t box[2] = {kBlockK, (cuuint32_t)np};
+        const cuuint32_t estr[2] = {1, 1};
+        return encode_fn()(m, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                           const_cast<void*>(X), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    });
 }
 
 // e4m3 weight tile map: global layout A is [row group][k-octet][16 rows][8 bytes]; a 3-D view (128-byte block,
 // k-octet, row group) with box (128, 8, 8) lands a 128 x 64 tile as [row group][k-octet][16 rows x 8 bytes].
 inline bool make_map_a8(CUtensorMap* map, const void* A, long long m, int k) {
-    const cuuint64_t dims[3] = {128, (cuuint64_t)(k / 8), (cuuint64_t)(m / 16)};
-    const cuuint64_t strides[2] = {128, (cuuint64_t)16 * k};
-    const cuuint32_t box[3] = {128, kBlockK / 8, kTileM / 16};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(A), dims, strides, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return cached_map(map, 2, A, m, k, 0, [&](CUtensorMap* mp) {
+        const cuuint64_t dims[3] = {128, (cuuint64_t)(k / 8), (cuuint64_t)(m / 16)};
+        const cuuint64_t strides[2] = {128, (cuuint64_t)16 * k};
+        const cuuint32_t box[3] = {128, kBlockK / 8, kTileM / 16};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        return encode_fn()(mp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(A), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    });
 }
 
 // Token tile map for activations in layout B [k/32][n/16][4 k-octets][16 tokens][8 k]: viewed as (one 8-token x 8-k
@@ -182,14 +268,35 @@ inline bool make_map_a8(CUtensorMap* map, const void* A, long long m, int k) {
 // of np tokens x 64 k lands as [k-octet (8)][8-token group (np/8)][128 B]: the UMMA no-swizzle K-major layout with a
 // k-octet step of np * 16 bytes and an 8-token step of 128 bytes.  Token blocks beyond n are zero-filled.
 inline bool make_map_xb(CUtensorMap* map, const void* X, int n, int k, int wt, int np) {
-    const cuuint64_t dims[5] = {64, 2, (cuuint64_t)(n / 16), 4, (cuuint64_t)(k / 32)};
-    const cuuint64_t strides[4] = {128, 1024, 256, (cuuint64_t)(n / 16) * 1024};
-    const cuuint32_t box[5] = {64, 2, (cuuint32_t)(np / 16), 4, kBlockK / 32};
-    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-    return encode_fn()(map, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5,
-                       const_cast<void*>(X), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return cached_map(map, 3, X, n, k, wt * 1024 + np, [&](CUtensorMap* m) {
+        const cuuint64_t dims[5] = {64, 2, (cuuint64_t)(n / 16), 4, (cuuint64_t)(k / 32)};
+        const cuuint64_t strides[4] = {128, 1024, 256, (cuuint64_t)(n / 16) * 1024};
+        const cuuint32_t box[5] = {64, 2, (cuuint32_t)(np / 16), 4, kBlockK / 32};
+        const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        return encode_fn()(m, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5,
+                           const_cast<void*>(X), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    });
+}
+
+// 16-bit weight tile map.  Global layout A is [row group][k-octet][half][8 rows][8 k]; the 4-D view (64 elements =
+// one 8-row core matrix, k-octet, row group, half) with box (64, 8, 8, 2) is traversed k-octet first, so each row
+// group's 2 KB run of a k block is fetched as consecutive requests, and lands in shared memory as
+// [half][row group][k-octet][128 B]: core matrix (accumulator 8-row group i = 8*half + row group, k-octet o) sits at
+// i*1024 + o*128, uniform strides for one M = 128 descriptor.  `rows` may span several matrices stored back to back
+// (the experts of a fused-MoE weight tensor).
+inline bool make_map_a16(CUtensorMap* map, const void* A, long long rows, int k, int wt) {
+    return cached_map(map, 4, A, rows, k, wt, [&](CUtensorMap* m) {
+        const cuuint64_t dims[4] = {64, (cuuint64_t)(k / 8), (cuuint64_t)(rows / 16), 2};
+        const cuuint64_t strides[3] = {256, (cuuint64_t)16 * k * 2, 128};
+        const cuuint32_t box[4] = {64, kBlockK / 8, kTileM / 16, 2};
+        const cuuint32_t estr[4] = {1, 1, 1, 1};
+        return encode_fn()(m, wt == kFP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                           const_cast<void*>(A), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    });
 }
 
 }  // namespace umma

@@ -211,8 +211,10 @@ def gemv_layoutA(A, B, alpha: float = 1, beta: float = 0, scale_matrix=None, bia
     the reference kernels.  For e4m3 weights ``scale_matrix=None`` means unit scales."""
     m, k, code = _gemv_checks(A, B, scale_matrix, bias)
     C = torch.empty((1, m), dtype=B.dtype, device=B.device)
+    aux, _keep = _aux(B, m, 1, k)
     check(lib.mlk_gemv_layoutA(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, k, code, alpha, beta,
-                               _scale_ptr(scale_matrix, m, k), _bias_ptr(bias, B, m), int(fp8_repacked), _stream(B)))
+                               _scale_ptr(scale_matrix, m, k), _bias_ptr(bias, B, m), int(fp8_repacked),
+                               ctypes.byref(aux), _stream(B)))
     return C
 
 
@@ -223,9 +225,10 @@ def gemv_layoutA_wapper(A, B, m: int, k: int, alpha: float = 1, beta: float = 0,
     m2, k2, code = _gemv_checks(A, B, scale_matrix, bias)
     _chk(m == m2 and k == k2, "m, k do not match the tensors")
     C = torch.empty((1, m), dtype=B.dtype, device=B.device)
+    aux, _keep = _aux(B, m, 1, k)
     check(lib.mlk_gemv_layoutA_wapper(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, k, code, alpha, beta, blockDimX,
                                       kernelId, kernelParam1, kernelParam2, _scale_ptr(scale_matrix, m, k),
-                                      _bias_ptr(bias, B, m), int(fp8_repacked), _stream(B)))
+                                      _bias_ptr(bias, B, m), int(fp8_repacked), ctypes.byref(aux), _stream(B)))
     return C
 
 
@@ -252,50 +255,73 @@ def _gemm_checks(A, B, b_layout: bool):
 
 _SYNC_BUFFERS = {}   # (device index, stream handle) -> [counters, status, workspace, MlkAux]
 _WS_BYTES = {}       # (device index, m, n-tile, k) -> workspace bytes of the tcgen05 kernel
+_MIN_WS_FLOATS = 1 << 20
+
+
+def _stream_bufs(device: torch.device, stream: int, tiles: int = 0):
+    key = (device.index, stream)
+    bufs = _SYNC_BUFFERS.get(key)
+    if bufs is None or bufs[0].numel() < tiles:
+        bufs = [torch.zeros(max(4096, tiles), dtype=torch.int32, device=device),
+                torch.zeros(1, dtype=torch.int32, device=device) if bufs is None else bufs[1],
+                None if bufs is None else bufs[2], None]
+        _SYNC_BUFFERS[key] = bufs
+    return bufs
+
+
+def _status_ptr(t: torch.Tensor) -> int:
+    """Device address of the sticky status word of the current stream of `t`'s device."""
+    return _stream_bufs(t.device, _stream(t))[1].data_ptr()
 
 
 def _aux(B: torch.Tensor, m: int, n: int, k: int):
-    """Scratch for the tcgen05 kernel's persistent stream-K grid, kept per (device, stream): a block of counters that
-    every kernel leaves zeroed, the sticky status word of the kernels' bounded waits, and an fp32 workspace that only
-    grows.  Successive launches of one stream may share the workspace: a kernel touches it only after the preceding
-    kernel of the stream has completed (griddepcontrol.wait), and kernels of one stream never run concurrently
-    otherwise; another stream gets its own."""
-    if n > 64:
-        return None, None
+    """Scratch lent to the tcgen05 kernels, kept per (device, stream): a block of counters that every kernel leaves
+    zeroed, the sticky status word of the kernels' bounded waits, and an fp32 workspace that only grows (partial tiles
+    of the persistent stream-K grid; per-token scales of the native-FP8 kernels).  Successive launches of one stream
+    may share it: a kernel touches it only after the preceding kernel of the stream has completed
+    (griddepcontrol.wait), and kernels of one stream never run concurrently otherwise; another stream gets its own.
+    A CUDA graph captures these addresses: replay graphs that were captured on the same stream one at a time.
+    Returns (MlkAux, tensor that keeps the workspace alive)."""
     stream = _stream(B)
-    key = (B.device.index, stream)
-    tiles = m // 128
-    bufs = _SYNC_BUFFERS.get(key)
-    if bufs is None or bufs[0].numel() < tiles:
-        bufs = [torch.zeros(max(4096, tiles), dtype=torch.int32, device=B.device),
-                torch.zeros(1, dtype=torch.int32, device=B.device), None, None]
-        _SYNC_BUFFERS[key] = bufs
-    npad = 16 if n <= 16 else (32 if n <= 32 else 64)
-    wkey = (B.device.index, m, npad, k)
-    nbytes = _WS_BYTES.get(wkey)
-    if nbytes is None:
-        with torch.cuda.device(B.device):
-            nbytes = _WS_BYTES[wkey] = int(lib.mlk_gemm_workspace_bytes(m, n, k))
-    if nbytes == 0:
-        return None, None
+    bufs = _stream_bufs(B.device, stream, m // 128)
+    nbytes = 0
+    if n <= 64 and m % 128 == 0 and k % 64 == 0:
+        npad = 16 if n <= 16 else (32 if n <= 32 else 64)
+        wkey = (B.device.index, m, npad, k)
+        nbytes = _WS_BYTES.get(wkey)
+        if nbytes is None:
+            with torch.cuda.device(B.device):
+                nbytes = _WS_BYTES[wkey] = int(lib.mlk_gemm_workspace_bytes(m, n, k))
     ws = bufs[2]
     if ws is None or ws.numel() * 4 < nbytes:
         # the old buffer may still be in use by kernels already queued on this stream: torch's allocator keeps a freed
-        # block stream-ordered, so dropping the reference here is safe
-        ws = bufs[2] = torch.empty(max(nbytes // 4, 1 << 20), dtype=torch.float32, device=B.device)
+        # block stream-ordered, so dropping the reference here is safe (never while the stream is being captured:
+        # graphs hold the address)
+        if ws is not None and torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("the tcgen05 workspace would have to grow during stream capture: run the shape once "
+                               "eagerly on this stream before capturing")
+        ws = bufs[2] = torch.empty(max(nbytes // 4, _MIN_WS_FLOATS), dtype=torch.float32, device=B.device)
         bufs[3] = None
     if bufs[3] is None:
         bufs[3] = MlkAux(ws.data_ptr(), ws.numel() * 4, bufs[0].data_ptr(), bufs[0].numel(), bufs[1].data_ptr())
     return bufs[3], ws
 
 
-def kernel_status(device=None) -> int:
+def kernel_status(device=None, reset: bool = False) -> int:
     """Sticky status word of the bounded waits inside the tcgen05 kernels for the current stream of `device`
-    (0 = no wait ever expired).  Synchronises the stream."""
+    (0 = no wait ever expired).  Synchronises the stream.  A kernel that gave up leaves its output unwritten and, in
+    the persistent stream-K mode, may leave tile counters behind; ``reset=True`` clears the word and the counters so
+    that the stream can be used again."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     key = (dev.index if dev.index is not None else torch.cuda.current_device(), torch.cuda.current_stream(dev).cuda_stream)
     bufs = _SYNC_BUFFERS.get(key)
-    return 0 if bufs is None else int(bufs[1].item())
+    if bufs is None:
+        return 0
+    value = int(bufs[1].item())
+    if reset and value != 0:
+        bufs[0].zero_()
+        bufs[1].zero_()
+    return value
 
 
 def _alloc_c(B, m, n, c_layout: bool):
@@ -312,7 +338,7 @@ def gemm_layoutA(A, B, alpha: float = 1, beta: float = 0, bias=None):
     C = _alloc_c(B, m, n, False)
     aux, _keep = _aux(B, m, n, k)
     check(lib.mlk_gemm_layoutA(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, code, alpha, beta,
-                               _bias_ptr(bias, B, m), None if aux is None else ctypes.byref(aux), _stream(B)))
+                               _bias_ptr(bias, B, m), ctypes.byref(aux), _stream(B)))
     return C
 
 
@@ -324,10 +350,10 @@ def gemm_layoutA_wapper(A, B, m: int, n: int, k: int, alpha: float = 1, beta: fl
     code = _dense_code(A, B)
     _chk(code != 2, "Unsupported data type")
     C = _alloc_c(B, m, n, False)
-    aux, _keep = _aux(B, m, n, k) if kernelId == 2 else (None, None)
+    aux, _keep = _aux(B, m, n, k)
     check(lib.mlk_gemm_layoutA_wapper(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, code, alpha, beta,
                                       kernelParam1, kernelParam2, kernelParam3, kernelId, _bias_ptr(bias, B, m),
-                                      None if aux is None else ctypes.byref(aux), _stream(B)))
+                                      ctypes.byref(aux), _stream(B)))
     return C
 
 
@@ -337,8 +363,10 @@ def gemm_layoutA_soft_fp8(A, A_Scale, B, alpha: float = 1, beta: float = 0, bias
     m, n, k = _gemm_checks(A, B, False)
     _chk(_dense_code(A, B) == 2, "Unsupported data type")
     C = _alloc_c(B, m, n, False)
+    aux, _keep = _aux(B, m, n, k)
     check(lib.mlk_gemm_layoutA_soft_fp8(A.data_ptr(), _scale_ptr(A_Scale, m, k), B.data_ptr(), C.data_ptr(), m, n, k,
-                                        alpha, beta, _bias_ptr(bias, B, m), int(fp8_repacked), _stream(B)))
+                                        alpha, beta, _bias_ptr(bias, B, m), int(fp8_repacked), ctypes.byref(aux),
+                                        _stream(B)))
     return C
 
 
@@ -350,9 +378,11 @@ def gemm_layoutA_soft_fp8_wapper(A, A_Scale, B, m: int, n: int, k: int, alpha: f
     _chk((m, n, k) == (m2, n2, k2), "m, n, k do not match the tensors")
     _chk(_dense_code(A, B) == 2, "Unsupported data type")
     C = _alloc_c(B, m, n, False)
+    aux, _keep = _aux(B, m, n, k)
     check(lib.mlk_gemm_layoutA_soft_fp8_wapper(A.data_ptr(), _scale_ptr(A_Scale, m, k), B.data_ptr(), C.data_ptr(),
                                                m, n, k, alpha, beta, kernelParam1, kernelParam2, kernelParam3,
-                                               kernelId, _bias_ptr(bias, B, m), int(fp8_repacked), _stream(B)))
+                                               kernelId, _bias_ptr(bias, B, m), int(fp8_repacked), ctypes.byref(aux),
+                                               _stream(B)))
     return C
 
 
@@ -369,8 +399,9 @@ def gemm_layoutAB_ContinuousC(A, B, alpha: float = 1, beta: float = 0, bias=None
     code = _dense_code(A, B)
     _chk(code != 2, "Unsupported data type")
     C = _alloc_c(B, m, n, False)
+    aux, _keep = _aux(B, m, n, k)
     check(lib.mlk_gemm_layoutAB_ContinuousC(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, code, alpha, beta,
-                                            _bias_ptr(bias, B, m), _stream(B)))
+                                            _bias_ptr(bias, B, m), ctypes.byref(aux), _stream(B)))
     return C
 
 
@@ -383,9 +414,10 @@ def gemm_layoutAB_ContinuousC_wapper(A, B, m: int, n: int, k: int, alpha: float 
     code = _dense_code(A, B)
     _chk(code != 2, "Unsupported data type")
     C = _alloc_c(B, m, n, False)
+    aux, _keep = _aux(B, m, n, k)
     check(lib.mlk_gemm_layoutAB_ContinuousC_wapper(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, code, alpha,
                                                    beta, kernelParam1, kernelParam2, kernelParam3, kernelId,
-                                                   _bias_ptr(bias, B, m), _stream(B)))
+                                                   _bias_ptr(bias, B, m), ctypes.byref(aux), _stream(B)))
     return C
 
 
@@ -395,8 +427,9 @@ def gemm_layoutABC(A, B, alpha: float = 1, beta: float = 0, bias=None):
     code = _dense_code(A, B)
     _chk(code != 2, "Unsupported data type")
     C = _alloc_c(B, m, n, True)
+    aux, _keep = _aux(B, m, n, k)
     check(lib.mlk_gemm_layoutABC(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, code, alpha, beta,
-                                 _bias_ptr(bias, B, m), _stream(B)))
+                                 _bias_ptr(bias, B, m), ctypes.byref(aux), _stream(B)))
     return C
 
 
@@ -408,9 +441,10 @@ def gemm_layoutABC_wapper(A, B, m: int, n: int, k: int, alpha: float = 1, beta: 
     code = _dense_code(A, B)
     _chk(code != 2, "Unsupported data type")
     C = _alloc_c(B, m, n, True)
+    aux, _keep = _aux(B, m, n, k)
     check(lib.mlk_gemm_layoutABC_wapper(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, n, k, code, alpha, beta,
                                         kernelParam1, kernelParam2, kernelParam3, kernelId, _bias_ptr(bias, B, m),
-                                        _stream(B)))
+                                        ctypes.byref(aux), _stream(B)))
     return C
 
 
@@ -582,7 +616,8 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
             _cuda_contig(w1s, "w1_scale")
             _cuda_contig(w2s, "w2_scale")
             _chk(w1s.dtype == torch.float32 and w2s.dtype == torch.float32, "w1_scale and w2_scale must be float32.")
-            _chk(w1s.numel() == E * (m1 // 128) * (k1 // 128) and w2s.numel() == E * (m2 // 128) * (k2 // 128),
+            _chk(w1s.numel() == E * ((m1 + 127) // 128) * ((k1 + 127) // 128) and
+                 w2s.numel() == E * ((m2 + 127) // 128) * ((k2 + 127) // 128),
                  "scales must be [E, rows/128, cols/128]")
         code, rg = 2, 0
     else:
@@ -605,7 +640,8 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
                                         padded_num_experts.data_ptr(), experts_ids.data_ptr(), C.data_ptr(),
                                         y.data_ptr(), _ptr(w1s), _ptr(w2s), code, int(fp8_repacked),
                                         int(vals["microBatchSize"]), mp, ml, _ptr(scratch),
-                                        0 if scratch is None else scratch.numel() * 4, tune_arr, _stream(x)))
+                                        0 if scratch is None else scratch.numel() * 4, tune_arr, _status_ptr(x),
+                                        _stream(x)))
 
 
 # ---------------------------------------------------------------------------------------------------

@@ -28,6 +28,8 @@ import torch
 import muxi_native_layout_kernels_b200 as mlk
 from muxi_native_layout_kernels_b200._lib import MlkError, PKG_DIR
 
+SMS = torch.cuda.get_device_properties(0).multi_processor_count if torch.cuda.is_available() else 148
+
 L2_BYTES = 126 << 20
 POOL_BYTES = 3 * L2_BYTES
 
@@ -111,7 +113,7 @@ def candidates(kind, m, n, k):
         if fp8 and m % 128 == 0 and k % 64 == 0:
             # KernelId 3: tcgen05 pipeline for e4m3 weights, (raw ring stages, cluster size)
             cands += [(256, 3, st, ck) for st in (2, 3, 4, 6, 8) for ck in range(1, 9)
-                      if (m // 128) * ck <= 148 * min(4, max(1, (227 * 1024) // (max(st * 8192, 8192) + 4096 + 2048)))]
+                      if (m // 128) * ck <= SMS * min(4, max(1, (227 * 1024) // (max(st * 8192, 8192) + 4096 + 2048)))]
         return cands
     # kernelId 1 / 3 / 4: the warp-level kernel with 8 / 4 / 2 warps per CTA
     cands = [(kid, rg, wm, sk) for kid, rg, wm, sk in itertools.product([1, 3, 4], [1, 2], [1, 2, 4, 8], [1, 2, 4])
@@ -120,7 +122,7 @@ def candidates(kind, m, n, k):
         # tcgen05 pipeline for e4m3 weights: (unused, raw ring stages, cluster size)
         np_ = 16 if n <= 16 else (32 if n <= 32 else 64)
         cands += [(2, 1, st, ck) for st in (2, 3, 4, 6, 8) for ck in range(1, 9)
-                  if (m // 128) * ck <= 148 * min(4, max(1, (227 * 1024) // (max(st * 8192, np_ * 512) + 2 * np_ * 128 + 2048)))]
+                  if (m // 128) * ck <= SMS * min(4, max(1, (227 * 1024) // (max(st * 8192, np_ * 512) + 2 * np_ * 128 + 2048)))]
     if kind == "a" and n <= 4:
         cands += [(kid, rg, 0, sk) for kid, rg, sk in itertools.product([5, 6, 7], [1, 2], [1, 2, 4]) if m % (16 * rg) == 0]
     if kind in ("a", "conc", "abc") and n <= 64 and (kind == "a" or n % 16 == 0):
@@ -132,15 +134,8 @@ def candidates(kind, m, n, k):
             for st in (2, 3, 4, 5, 6, 8):
                 np_ = 16 if n <= 16 else (32 if n <= 32 else 64)
                 smem = st * (16384 + np_ * 128) + 2048
-                if ck <= k // 64 and (m // 128) * ck <= 148 * max(1, (227 * 1024) // smem):
+                if ck <= k // 64 and (m // 128) * ck <= SMS * max(1, (227 * 1024) // smem):
                     cands.append((2, 1, st, ck))
-    if kind == "a" and 16 < n <= 64 and m % 256 == 0:
-        # kernelId 8: the cluster kernel with 256 rows per CTA (two accumulators share the token tile)
-        np_ = 32 if n <= 32 else 64
-        for ck in range(1, 9):
-            for st in (2, 3, 4):
-                if ck <= k // 64 and st * (32768 + np_ * 128) >= np_ * 1024:
-                    cands.append((8, 1, st, ck))
     return cands
 
 

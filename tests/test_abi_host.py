@@ -22,8 +22,13 @@ def test_library_exports_every_declared_symbol():
     raw = ctypes.CDLL(str(_lib.LIB_PATH))
     for n in names:
         assert hasattr(raw, n), f"{n} is declared in include/mlk_b200.h but not exported"
-    # and the ctypes prototypes cover the header exactly
+    # and the ctypes prototypes cover the header exactly, argument count included
     assert sorted(_lib.PROTOTYPES) == names
+    text = re.sub(r"/\*.*?\*/", "", (ROOT / "include" / "mlk_b200.h").read_text(), flags=re.S)
+    for name, params in re.findall(r"\b(mlk_[A-Za-z0-9_]+)\s*\(([^;{]*)\)\s*;", text):
+        params = params.strip()
+        count = 0 if params in ("", "void") else params.count(",") + 1
+        assert count == len(_lib.PROTOTYPES[name][1]), f"{name}: header has {count} parameters, ctypes {len(_lib.PROTOTYPES[name][1])}"
 
 
 def test_status_strings_and_build_info():
@@ -163,8 +168,8 @@ def test_c_abi_rejects_bad_shapes_before_touching_the_device():
     one = ctypes.c_void_p(16)   # never dereferenced: the shape check comes first
     assert lib.mlk_gemm_layoutA(one, one, one, 100, 16, 128, 0, 1.0, 0.0, None, None, None) == 1
     assert b"multiple of 128" in lib.mlk_last_error()
-    assert lib.mlk_gemv_layoutA_wapper(one, one, one, 40, 64, 0, 1.0, 0.0, 256, 1, 1, 1, None, None, 0, None) == 1
-    assert lib.mlk_gemv_layoutA_wapper(one, one, one, 64, 64, 0, 1.0, 0.0, 256, 7, 1, 1, None, None, 0, None) == 2
+    assert lib.mlk_gemv_layoutA_wapper(one, one, one, 40, 64, 0, 1.0, 0.0, 256, 1, 1, 1, None, None, 0, None, None) == 1
+    assert lib.mlk_gemv_layoutA_wapper(one, one, one, 64, 64, 0, 1.0, 0.0, 256, 7, 1, 1, None, None, 0, None, None) == 2
     assert lib.mlk_gemm_layoutA_wapper(one, one, one, 128, 16, 128, 0, 1.0, 0.0, 3, 1, 1, 1, None, None, None) == 1
     assert lib.mlk_layoutB(one, one, 10, 32, None) == 1
     assert lib.mlk_fp8_weight_repack(one, one, 6, None) == 1

@@ -310,36 +310,6 @@ def test_soft_fp8_tcgen05_block_scales(repacked, full_scales):
             _close_rel(y, odense.gemm_ref(x, Wd), f"gemv fp8 tcgen05 scaled[{name}] m={m} k={k}", tol)
 
 
-@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
-def test_gemm_tcgen05_two_tiles_per_cta(dt):
-    """kernelId 8: 256 weight rows per CTA, two accumulators fed by one token tile, cluster split-K."""
-    dev = require_gpu()
-    for (m, k) in [(256, 128), (512, 1024), (1024, 4096), (2304, 768)]:
-        W, A = _weights(m, k, 190 + m, dt, dev)
-        bias = randn((1, m), 191, 1.0, dt)
-        for n in [1, 9, 16, 17, 32, 33, 64]:
-            X = randn((n, k), 192 + n, 1.0, dt)
-            want = odense.gemm_ref(X, W)
-            for stages, ck in [(2, 1), (3, 2), (4, 3), (2, 8), (4, 5)]:
-                if ck > k // 64:
-                    continue
-                C = mlk.gemm_layoutA_wapper(A, X.to(dev), m, n, k, kernelParam2=stages, kernelParam3=ck, kernelId=8)
-                assert_close(C, want, f"pair m={m} k={k} n={n} stages={stages} cluster={ck} {dt}")
-            C = mlk.gemm_layoutA_wapper(A, X.to(dev), m, n, k, alpha=0.5, kernelParam2=3, kernelParam3=2, kernelId=8,
-                                        bias=bias.to(dev))
-            assert_close(C, odense.gemm_ref(X, W, alpha=0.5, bias=bias), f"pair bias m={m} n={n}")
-    # bit-identical from run to run, and a clean status word
-    X = randn((48, 4096), 193, 1.0, dt).to(dev)
-    A2 = _weights(1024, 4096, 194, dt, dev)[1]
-    ref = mlk.gemm_layoutA_wapper(A2, X, 1024, 48, 4096, kernelParam2=3, kernelParam3=4, kernelId=8)
-    for _ in range(3):
-        assert torch.equal(ref, mlk.gemm_layoutA_wapper(A2, X, 1024, 48, 4096, kernelParam2=3, kernelParam3=4, kernelId=8))
-    with pytest.raises(RuntimeError, match="256"):
-        A3 = _weights(384, 256, 195, dt, dev)[1]
-        mlk.gemm_layoutA_wapper(A3, randn((8, 256), 196, 1.0, dt).to(dev), 384, 8, 256, kernelParam2=2, kernelParam3=1, kernelId=8)
-    assert mlk.kernel_status() == 0
-
-
 def test_gemm_errors_and_determinism():
     dev = require_gpu()
     W, A = _weights(256, 256, 80, torch.bfloat16, dev)
