@@ -111,6 +111,10 @@ typedef struct mlk_aux {
 /* Workspace size (bytes) that covers every kernelId-2 launch of this shape on the current device; 0 if the shape
  * cannot use that kernel. */
 int64_t mlk_gemm_workspace_bytes(int m, int n, int k);
+/* Workspace size (bytes, 128-byte aligned) the native-e4m3 kernels (GEMM kernelId 9, GeMV KernelId 4) need for n tokens
+ * of k elements: 1 KB of token scales plus 2 k bytes per token for the activations rewritten as two e4m3 terms; 0 if
+ * those kernels cannot run (n > 64, k % 64 != 0). */
+int64_t mlk_soft_fp8_workspace_bytes(int n, int k);
 
 /* ---- GeMV: y[1,m] = alpha * A x (+ bias) ------------------------------------------------------- */
 
@@ -120,6 +124,10 @@ int64_t mlk_gemm_workspace_bytes(int m, int n, int k);
  *   kernelId 3: e4m3 only, m % 128 == 0, k % 64 == 0: the TMA -> convert -> tcgen05 pipeline of the
  *               soft-FP8 GEMM (see kernelId 2 there); kernelParam1 = raw ring stages (2,3,4,6,8), kernelParam2 =
  *               cluster size (1..8), blockDimX ignored
+ *   kernelId 4: e4m3 only, no scale_matrix, m % 128 == 0: the weights go to the 8-bit tensor-core MMA undecoded (see
+ *               kernelId 9 of the narrow GEMM); blockDimX = k per stage (64; 128 or 256 = 128, k a multiple of it),
+ *               kernelParam1 = ring stages (2,3,4,6,8), kernelParam2 = cluster size (1..8); needs aux->workspace of
+ *               mlk_soft_fp8_workspace_bytes(1, k) bytes
  *   scale_matrix: e4m3 only, fp32 [ceil(m/128)][ceil(k/128)], may be NULL (= all ones)
  *   fp8_order: 0 natural bytes, 1 bytes as written by mlk_fp8_weight_repack
  *   beta is accepted and ignored, as in the reference kernels. */
@@ -149,6 +157,17 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
  *   Block scales are applied in the decode as rne_bf16(w * s), the weight the reference's torch recipe
  *   (muxi_layout_kernels/utils.py:14-25) dequantises to; kernelId 1, 3, 4 apply s to the fp32 sums of each 128-wide
  *   k block instead, and the reference's kernels truncate fp32(w) * s to bf16: all within one bf16 ulp per weight.
+ * kernelId 9 (soft_fp8 entry points, no block scales, row-major B, n <= 64): the e4m3 weight bytes are fed to
+ *   tcgen05.mma.kind::f8f6f4 as they are (moved from the TMA-landed tile into tensor memory, no arithmetic), and a small
+ *   kernel in front rewrites the bf16 activations as two e4m3 terms each (hi + lo, exact under a power-of-two scale per
+ *   token chosen from the token's largest magnitude), so every product is exact and is accumulated in fp32.
+ *   kernelParam1 = k per stage (64 or 128; 0 / 1 = 64), kernelParam2 = ring stages (2,3,4,6,8), kernelParam3 = cluster
+ *   size (1..8).  Needs aux->workspace of mlk_soft_fp8_workspace_bytes(n, k) bytes, 128-byte aligned.  Differences a
+ *   caller can see: an e4m3 NaN byte (0x7F, 0xFF) in the weights is a NaN (the decode kernels, like the reference's,
+ *   read it as +-480); activations more than 2^11 below the largest magnitude of their token lose low bits (absolute
+ *   error <= 2^-17 of that maximum per element); a token that holds an Inf or NaN yields NaN outputs.  The table-driven
+ *   entry point uses it by default and falls back to kernelId 2 (same kernelParam2 / 3) when a scale tensor is
+ *   passed or the scratch is missing.
  * kernelId 5, 6, 7 (CUDA-core FMA + shuffle kernel with 256, 128, 64 threads; 16-bit weights, row-major B and C,
  *   n <= 4): kernelParam1 = row groups per warp (1,2), kernelParam2 unused, kernelParam3 = cluster split-K. */
 

@@ -22,6 +22,7 @@ PROTOTYPES = {
     "mlk_set_option": (c_int, [c_int, c_int]),
     "mlk_get_option": (c_int, [c_int]),
     "mlk_gemm_workspace_bytes": (c_i64, [c_int, c_int, c_int]),
+    "mlk_soft_fp8_workspace_bytes": (c_i64, [c_int, c_int]),
     "mlk_table_load": (c_int, [c_int, c_cp]),
     "mlk_table_lookup": (c_int, [c_int, c_int, c_int, c_int, C.POINTER(c_int), C.POINTER(c_int)]),
     "mlk_table_file_name": (c_cp, [c_int]),

@@ -27,11 +27,13 @@ SOURCES = [
     "dense.cu",
     "dense_umma.cu",
     "dense_umma_f8.cu",
+    "dense_umma_f8n.cu",
     "prepack.cu",
     "moe_router.cu",
     "moe_align.cu",
     "moe_experts.cu",
     "moe_umma.cu",
+    "moe_umma_f8n.cu",
     "moe_exchange.cu",
     "selector.cpp",
 ]

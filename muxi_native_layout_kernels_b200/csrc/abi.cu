@@ -82,6 +82,14 @@ int gemm_common(int variant_x, int variant_c, const void* A, const float* scale,
     p.A = A; p.X = B; p.C = C; p.bias = bias; p.scale = scale;
     p.m = m; p.n = n; p.k = k; p.alpha = alpha;
     p.x_layout = variant_x; p.c_layout = variant_c; p.fp8_order = fp8_order;
+    if (kernelId == 9) {
+        // e4m3 weights undecoded into tcgen05.mma.kind::f8f6f4: kernelParam1 = k per stage (64, or 128; 0 / 1 = 64),
+        // kernelParam2 = ring stages, kernelParam3 = cluster size
+        if (wt != kE4M3) return fail(kUnsupported, "gemm: kernelId 9 takes e4m3 weights");
+        if (variant_c != 0 && n % 16 != 0) return fail(kInvalidArg, "gemm: layout C needs n %% 16 == 0");
+        return launch_dense_umma_f8n(p, p1 <= 1 ? 64 : p1, p2, p3 < 1 ? 1 : p3, aux ? aux->workspace : nullptr,
+                                     aux ? (long long)aux->workspace_bytes : 0, aux ? aux->status : nullptr, s);
+    }
     if (kernelId == 2 && wt == kE4M3) {
         // TMA -> convert -> tcgen05 pipeline for e4m3 weights: kernelParam2 = raw ring stages, kernelParam3 = cluster
         // size; block scales ride on the decode (rounded to bf16 first, as the reference's torch check does)
@@ -123,12 +131,21 @@ int gemm_table(int table, int variant_x, int variant_c, const void* A, const flo
                      (dtype != MLK_E4M3
                           ? (t.b >= 1 && t.b <= 4 && ((t.c >= 2 && t.c <= 6) || t.c == 8) && t.d >= 0 && t.d <= 16)
                           : ((t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 && t.d <= 8));
+    const bool have_f8n = dtype == MLK_E4M3 && scale == nullptr && variant_x == 0 && n <= 64 && k <= f8n_max_k() && aux != nullptr &&
+                          aux->workspace != nullptr && ((uintptr_t)aux->workspace & 127) == 0 &&
+                          aux->workspace_bytes >= f8n_scratch_bytes(n, k);
+    const bool ok9 = t.a == 9 && have_f8n && (t.b <= 1 || t.b == 64 || t.b == 128) &&
+                     (t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 && t.d <= 8 &&
+                     t.d <= k / (t.b == 128 ? 128 : 64);
     const bool ok5 = t.a >= 5 && t.a <= 7 && n <= 4 && variant_x == 0 && variant_c == 0 && dtype != MLK_E4M3 &&
                      (t.b == 1 || t.b == 2) && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b) == 0;
-    if (!ok1 && !ok2 && !ok5) t = default_args(table, m, n, k);
+    if (!ok1 && !ok2 && !ok5 && !ok9) t = default_args(table, m, n, k);
+    // the native-e4m3 kernel needs the caller's scratch and has no block scales; otherwise the decode pipeline runs
+    // (kernelParam2 = raw ring stages and kernelParam3 = cluster size mean the same there)
+    if (t.a == 9 && !have_f8n) t.a = 2;
     // the tcgen05 kernel reads through tensor maps, which want 16-byte aligned bases; e4m3 activations in layout B
     // have no tcgen05 variant
-    if (t.a == 2 && ((((uintptr_t)A | (uintptr_t)B) & 15) != 0 || (variant_x != 0 && dtype == MLK_E4M3)))
+    if ((t.a == 2 || t.a == 9) && ((((uintptr_t)A | (uintptr_t)B) & 15) != 0 || (variant_x != 0 && dtype == MLK_E4M3)))
         t = warp_level_default_args(table, m, n, k);
     return gemm_common(variant_x, variant_c, A, scale, B, C, m, n, k, dtype, alpha, t.b, t.c, t.d, t.a, bias,
                        fp8_order, s, aux);
@@ -163,6 +180,11 @@ int mlk_set_option(int option_id, int value) {
     return kOk;
 }
 int mlk_get_option(int option_id) { return option(option_id); }
+
+int64_t mlk_soft_fp8_workspace_bytes(int n, int k) {
+    if (n <= 0 || n > 64 || k <= 0 || k % 64 != 0 || k > f8n_max_k()) return 0;
+    return f8n_scratch_bytes(n, k);
+}
 
 int64_t mlk_gemm_workspace_bytes(int m, int n, int k) {
     if (m <= 0 || n <= 0 || k <= 0 || m % 128 != 0 || k % 64 != 0 || n > 64) return 0;
@@ -236,7 +258,13 @@ int mlk_gemv_layoutA_wapper(const void* A, const void* x, void* y, int m, int k,
         // TMA -> convert -> tcgen05 pipeline: kernelParam1 = raw ring stages, kernelParam2 = cluster size
         return launch_dense_umma_f8(p, kernelParam1, kernelParam2, aux ? aux->status : nullptr, (cudaStream_t)s);
     }
-    return fail(kUnsupported, "gemv: kernelId %d is not built (1 = tensor-core, 2 = CUDA-core, 3 = tcgen05 for e4m3)", kernelId);
+    if (kernelId == 4 && wt == kE4M3) {
+        // e4m3 weights undecoded into tcgen05.mma.kind::f8f6f4: blockDimX = k per stage (64, or 128 for 128 and 256),
+        // kernelParam1 = ring stages, kernelParam2 = cluster size
+        return launch_dense_umma_f8n(p, blockDimX == 64 ? 64 : 128, kernelParam1, kernelParam2, aux ? aux->workspace : nullptr,
+                                     aux ? (long long)aux->workspace_bytes : 0, aux ? aux->status : nullptr, (cudaStream_t)s);
+    }
+    return fail(kUnsupported, "gemv: kernelId %d is not built (1 = tensor-core, 2 = CUDA-core, 3 / 4 = tcgen05 for e4m3)", kernelId);
 }
 
 int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dtype, float alpha, float beta,
@@ -252,7 +280,19 @@ int mlk_gemv_layoutA(const void* A, const void* x, void* y, int m, int k, int dt
                     (t.c == 1 || t.c == 2) && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.c) == 0;
     const bool ok3 = dtype == MLK_E4M3 && t.b == 3 && m % 128 == 0 && k % 64 == 0 &&
                      (t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 && t.d <= 8;
-    if (!ok && !ok3) t = default_args(table, m, 1, k);
+    const bool have_scratch = aux != nullptr && aux->workspace != nullptr && ((uintptr_t)aux->workspace & 127) == 0 &&
+                              aux->workspace_bytes >= f8n_scratch_bytes(1, k) && scale_matrix == nullptr && k <= f8n_max_k();
+    const bool ok4 = dtype == MLK_E4M3 && t.b == 4 && m % 128 == 0 && k % 64 == 0 && have_scratch && ((uintptr_t)A & 15) == 0 &&
+                     ((uintptr_t)x & 15) == 0 && (t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6 || t.c == 8) && t.d >= 1 &&
+                     t.d <= 8 && t.d <= k / (t.a == 64 ? 64 : 128) && k % (t.a == 64 ? 64 : 128) == 0;
+    if (!ok && !ok3 && !ok4) t = default_args(table, m, 1, k);
+    if (t.b == 4 && !(dtype == MLK_E4M3 && m % 128 == 0 && k % (t.a == 64 ? 64 : 128) == 0 && have_scratch &&
+                      ((uintptr_t)A & 15) == 0 && ((uintptr_t)x & 15) == 0)) {
+        // no scratch, block scales or unaligned operands: the warp-level kernel
+        int sk = 1;
+        while (sk < 8 && (m / 16) * sk < 2 * sm_count() && (k / 32) / (8 * sk * 2) >= 4) sk *= 2;
+        t = TuneArgs{256, 1, 1, sk};
+    }
     return mlk_gemv_layoutA_wapper(A, x, y, m, k, dtype, alpha, beta, t.a, t.b, t.c, t.d, scale_matrix, bias,
                                    fp8_order, aux, s);
 }

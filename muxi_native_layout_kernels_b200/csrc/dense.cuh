@@ -40,6 +40,12 @@ int launch_dense_umma(int wt, const DenseParams& p, int ctas_per_sm, int stages,
 long long umma_workspace_bytes(int m, int n, int k, int sms, int ctas_per_sm);
 // e4m3 weights through the TMA -> convert -> tcgen05 pipeline (block scales applied in the decode); status may be null
 int launch_dense_umma_f8(const DenseParams& p, int stages, int cluster_k, int* status, cudaStream_t stream);
+// e4m3 weights handed to tcgen05.mma.kind::f8f6f4 undecoded, activations rewritten as two e4m3 terms by a kernel in
+// front (dense_umma_f8n.cu); scratch: f8n_scratch_bytes(n, k) bytes, 128-byte aligned, owned by the call until it completes
+long long f8n_scratch_bytes(int n, int k);
+int f8n_max_k();   // longest row the activation split handles
+int launch_dense_umma_f8n(const DenseParams& p, int bk, int stages, int cluster_k, void* scratch, long long scratch_bytes,
+                          int* status, cudaStream_t stream);
 int launch_gemv_simt(int wt, const DenseParams& p, int rows_per_warp_log2, cudaStream_t stream);
 
 }  // namespace mlk

@@ -20,10 +20,10 @@ int launch_router_gemm(const void* x, const void* gate_weight, int score_fun, in
 int launch_moe_align(int T, int E, int topk, int mbs, const int32_t* topk_ids, int32_t* sorted_token_ids,
                      int32_t* cumsum, int32_t* padded_num_experts, int32_t* experts_ids_out,
                      const int32_t* experts_map, int experts_map_len, cudaStream_t s, void* worklist = nullptr,
-                     int block_slots = 0);
+                     int block_slots = 0, int32_t* cpos_slot = nullptr);
 
 // Work list written by the alignment kernel into the spare half of the caller's workspace C:
-//   int32 header[4] = {n_items, 0, 0, 0}; then n_items x int4 {expert, first position in sorted_token_ids, slots,
+//   int32 header[4] = {n_items, routed slots on this rank, 0, 0}; then n_items x int4 {expert, first position in sorted_token_ids, slots,
 //   first compact position}: compact positions number the routed slots expert by expert without the padding
 struct MoeWorkHeader {
     int n_items, pad0, pad1, pad2;
@@ -51,8 +51,9 @@ struct MoeParams {
     long long scratch_bytes;
     int* status;                  // sticky error word of the bounded waits inside the tcgen05 kernels (0 = ok), or null
     int nt, wm1, sk1, rg, wm2, sk2;   // tuning (0 = choose by shape): token tiles, GEMM1 row warps / split-K, GEMM2 row groups / row warps / split-K;
-                                      // wm1 = 100 + s1 and wm2 = 100 + s2 select the tcgen05 kernels (16-bit weights, combine scratch given)
-                                      // with s1 / s2 ring stages and sk1 / sk2 CTAs per cluster
+                                      // wm1 = 100 + s1 and wm2 = 100 + s2 select the tcgen05 kernels (combine scratch given)
+                                      // with s1 / s2 ring stages and sk1 / sk2 CTAs per cluster; 200 + s1 / 200 + s2 the
+                                      // native-e4m3 tcgen05 kernels (e4m3 weights without block scales)
 };
 
 int launch_fused_experts(const MoeParams& p, cudaStream_t s);
@@ -64,6 +65,16 @@ int launch_moe_gather_positions(const void* x, const int32_t* sorted, const int4
 int launch_moe_umma(int mode, int wt, const void* W, int E, int rows, int k, const void* X, long long x_rows, void* out,
                     const int4* worklist, const int32_t* sorted, const void* topk_weights, int n_slots, int np, int stages,
                     int cluster_k, int max_items, int fp8_order, const float* scale, int* status, cudaStream_t s);
+// the same two GEMMs with e4m3 weights undecoded into the 8-bit MMA (moe_umma_f8n.cu): activation rows as split planes
+bool moe_f8n_supported(int H, int I);
+int launch_moe_split_gather(const void* x, const int32_t* cpos_slot, const int4* worklist, int topk, int H, int repacked,
+                            void* planes, float* inv_scale, int n_slots, cudaStream_t s);
+int launch_moe_split_inplace(void* act, const int4* worklist, int I, int repacked, float* inv_scale, int n_slots,
+                             cudaStream_t s);
+int launch_moe_umma_f8n(int mode, const void* W, int E, int rows, int k, const void* planes, const float* inv_scale,
+                        long long plane_rows, void* out, const int4* worklist, const int32_t* sorted,
+                        const void* topk_weights, int n_slots, int np, int stages, int cluster_k, int max_items, int* status,
+                        cudaStream_t s);
 int launch_fused_experts_static(const MoeParams& p, cudaStream_t s);   // combine scratch in a built-in device array
 
 // Expert-parallel exchange helpers (moe_exchange.cu).

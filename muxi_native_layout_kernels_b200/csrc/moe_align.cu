@@ -10,7 +10,8 @@
 //   cumsum_buffer: [e] = start_e + count_e for e < E, [E] = padded total -- the state the reference leaves
 //     behind after its second kernel has used the buffer as per-expert cursors
 //   experts_map: global id -> local id, -1 = not on this rank (slot is skipped)
-// Optionally the kernel also emits the expert-compute work list (see MoeWorkHeader in moe.cuh).
+// Optionally the kernel also emits the expert-compute work list (see MoeWorkHeader in moe.cuh) and, with it, the slot of
+// every compact position (cpos_slot: the routed slots numbered expert by expert without the padding).
 #include "moe.cuh"
 #include "status.h"
 
@@ -25,9 +26,11 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
                                                         int32_t* __restrict__ cumsum, int32_t* __restrict__ nblocks,
                                                         int32_t* __restrict__ block_expert,
                                                         const int32_t* __restrict__ experts_map, int n_global,
-                                                        int4* __restrict__ worklist, int block_slots) {
+                                                        int4* __restrict__ worklist, int block_slots,
+                                                        int32_t* __restrict__ cpos_slot) {
     __shared__ int cnt[kMaxExperts];
     __shared__ int cursor[kMaxExperts];
+    __shared__ int pad_before[kMaxExperts];     // padding in front of expert e: position minus compact position
     __shared__ int warp_tot[32], warp_tot2[32], warp_tot3[32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
@@ -80,6 +83,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
     const int excl3 = ((warp > 0) ? warp_tot3[warp - 1] : 0) + incl3 - c;
     if (tid < E) {
         cursor[tid] = excl;
+        pad_before[tid] = excl - excl3;
         cumsum[tid] = excl + c;
         for (int b = excl / mbs; b < (excl + padded) / mbs; ++b) block_expert[b] = tid;
         if (worklist != nullptr)
@@ -90,14 +94,18 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
     if (tid == E - 1) {
         cumsum[E] = excl + padded;
         nblocks[0] = (excl + padded) / mbs;
-        if (worklist != nullptr) worklist[0] = make_int4(excl2 + items, 0, 0, 0);
+        if (worklist != nullptr) worklist[0] = make_int4(excl2 + items, excl3 + c, 0, 0);
     }
     __syncthreads();
 
     for (int i = tid; i < numel; i += blockDim.x) {
         int e = topk_ids[i];
         if (experts_map != nullptr) e = (e >= 0 && e < n_global) ? experts_map[e] : -1;
-        if (e >= 0 && e < E) sorted[atomicAdd(&cursor[e], 1)] = i;
+        if (e >= 0 && e < E) {
+            const int pos = atomicAdd(&cursor[e], 1);
+            sorted[pos] = i;
+            if (cpos_slot != nullptr) cpos_slot[pos - pad_before[e]] = i;
+        }
     }
 }
 
@@ -106,7 +114,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
 int launch_moe_align(int T, int E, int topk, int mbs, const int32_t* topk_ids, int32_t* sorted_token_ids,
                      int32_t* cumsum, int32_t* padded_num_experts, int32_t* experts_ids_out,
                      const int32_t* experts_map, int experts_map_len, cudaStream_t s, void* worklist,
-                     int block_slots) {
+                     int block_slots, int32_t* cpos_slot) {
     if (!topk_ids || !sorted_token_ids || !cumsum || !padded_num_experts || !experts_ids_out)
         return fail(kInvalidArg, "moe_align: null pointer");
     if (T < 0 || topk <= 0) return fail(kInvalidArg, "moe_align: bad batch size / topK");
@@ -120,7 +128,7 @@ int launch_moe_align(int T, int E, int topk, int mbs, const int32_t* topk_ids, i
     const int n_global = experts_map_len;
     moe_align_kernel<<<1, 1024, 0, s>>>(topk_ids, (int)numel, E, mbs, max_blocks, max_padded, sorted_token_ids, cumsum,
                                         padded_num_experts, experts_ids_out, experts_map, n_global,
-                                        reinterpret_cast<int4*>(worklist), block_slots);
+                                        reinterpret_cast<int4*>(worklist), block_slots, cpos_slot);
     return check_launch("moe_align");
 }
 

@@ -315,14 +315,15 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
             while (sk > 1 && kblocks / sk < 4) --sk;
             return sk;
         };
-        m.wm1 = 103; m.sk1 = cluster(m.I / 128, m.H / 64);
-        m.wm2 = 103; m.sk2 = cluster(m.H / 128, m.I / 64);
+        const int fam = (wt == kE4M3 && !scale && moe_f8n_supported(m.H, m.I)) ? 200 : 100;
+        m.wm1 = fam + 3; m.sk1 = cluster(m.I / 128, m.H / 64);
+        m.wm2 = fam + 3; m.sk2 = cluster(m.H / 128, m.I / 64);
         if (wt != kE4M3 && want > 64) m.nt = 16;
     }
     int nt_tiles = want <= 8 ? 1 : (want <= 16 ? 2 : (want <= 32 ? 4 : 8));
     if (m.nt == 1 || m.nt == 2 || m.nt == 4 || m.nt == 8) nt_tiles = m.nt;
     // 16 tiles (128 slots per work item) exist for the tcgen05 kernels with 16-bit weights only
-    if (m.nt == 16) nt_tiles = (wt != kE4M3 && m.wm1 >= 100 && m.wm2 >= 100 && m.scratch != nullptr) ? 16 : 8;
+    if (m.nt == 16) nt_tiles = (wt != kE4M3 && m.wm1 >= 100 && m.wm1 < 200 && m.wm2 >= 100 && m.wm2 < 200 && m.scratch != nullptr) ? 16 : 8;
     const int block_slots = nt_tiles * 8;
     const int max_items = (int)std::min<long long>(slots, (long long)std::min<long long>(m.E, slots) + slots / block_slots);
 
@@ -333,11 +334,18 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
     // combine scratch until the second GEMM overwrites it.
     const size_t c_bytes = (size_t)slots * 2 * m.I * 2;
     const size_t wl_bytes = 16 * (size_t)(max_items + 1);
-    const bool umma = m.wm1 >= 100 && m.wm2 >= 100 && m.scratch != nullptr && m.I % 128 == 0 &&
+    // native-e4m3 tcgen05 kernels (moe_umma_f8n.cu): tuning values 200 + stages; e4m3 weights without block scales
+    // only, otherwise the same arguments run the decode kernels (100 + stages)
+    if (m.wm1 >= 200 && m.wm2 >= 200 && !(wt == kE4M3 && !scale && moe_f8n_supported(m.H, m.I))) {
+        m.wm1 -= 100;
+        m.wm2 -= 100;
+    }
+    const bool f8n = m.wm1 >= 200 && m.wm2 >= 200 && m.scratch != nullptr && (long long)slots * m.H * 4 <= m.scratch_bytes;
+    const bool umma = !f8n && m.wm1 >= 100 && m.wm1 < 200 && m.wm2 >= 100 && m.wm2 < 200 && m.scratch != nullptr && m.I % 128 == 0 &&
                       m.H % 128 == 0 && (long long)slots * m.H * 4 <= m.scratch_bytes;
     if (nt_tiles == 16 && !umma) return fail(kInvalidArg, "fused_experts_compute: 128-slot work items need the tcgen05 kernels (sizes multiples of 128, combine scratch)");
 
-    if (!umma && (m.wm1 >= 100 || m.wm2 >= 100)) {
+    if (!umma && !f8n && (m.wm1 >= 100 || m.wm2 >= 100)) {
         // tuned for the tcgen05 kernels but this call cannot use them: the warp-level kernels choose for themselves
         m.wm1 = m.sk1 = m.rg = m.wm2 = m.sk2 = 0;
     }
@@ -349,10 +357,38 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
         return fail(kInvalidArg, "fused_experts_compute: workspace C too small for the work list");
     void* worklist = cbytes + wl_off;
 
+    // native-e4m3 path: the slot of every compact position and the two arrays of inverse row scales follow the work list
+    const size_t aux_off = (wl_off + wl_bytes + 15) & ~(size_t)15;
+    if (f8n && aux_off + 12 * (size_t)slots > c_bytes)
+        return fail(kInvalidArg, "fused_experts_compute: workspace C too small for the native-e4m3 bookkeeping");
+    int32_t* const cpos_slot = f8n ? reinterpret_cast<int32_t*>(cbytes + aux_off) : nullptr;
+    float* const inv1 = reinterpret_cast<float*>(cbytes + aux_off + 4 * (size_t)slots);
+    float* const inv2 = inv1 + slots;
+
     if (int st = launch_moe_align(m.T, m.E, m.topk, mbs, m.topk_ids, m.sorted_token_ids, m.cumsum,
                                   m.padded_num_experts, m.experts_ids, m.experts_map, m.experts_map_len, s, worklist,
-                                  block_slots))
+                                  block_slots, cpos_slot))
         return st;
+
+    if (f8n) {
+        // split planes of the routed token rows borrow the combine scratch (2 H bytes per row of its 4 H) until the
+        // second GEMM overwrites it; the [position, I] activation in the front of C is split in place
+        const int np = block_slots < 16 ? 16 : block_slots;
+        const int4* wl = reinterpret_cast<const int4*>(worklist);
+        if (int st = launch_moe_split_gather(m.x, cpos_slot, wl, m.topk, m.H, m.fp8_order, m.scratch, inv1, (int)slots, s)) return st;
+        if (int st = launch_moe_umma_f8n(1, m.w1, m.E, m.I, m.H, m.scratch, inv1, slots, m.C, wl, m.sorted_token_ids, m.topk_weights,
+                                         (int)slots, np, m.wm1 - 200, m.sk1 > 0 ? m.sk1 : 1, max_items, m.status, s))
+            return st;
+        if (int st = launch_moe_split_inplace(m.C, wl, m.I, m.fp8_order, inv2, (int)slots, s)) return st;
+        if (int st = launch_moe_umma_f8n(2, m.w2, m.E, m.H, m.I, m.C, inv2, slots, m.scratch, wl, m.sorted_token_ids, m.topk_weights,
+                                         (int)slots, np, m.wm2 - 200, m.sk2 > 0 ? m.sk2 : 1, max_items, m.status, s))
+            return st;
+        const long long total = (long long)m.T * (m.H / 8);
+        const int grid = (int)std::min<long long>((total + 255) / 256, 8LL * sm_count());
+        moe_combine_kernel<kBF16><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
+                                                      m.topk, m.H, m.y);
+        return check_launch("moe_combine");
+    }
 
     if (umma) {
         const int np = block_slots < 16 ? 16 : block_slots;

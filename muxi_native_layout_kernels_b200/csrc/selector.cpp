@@ -48,12 +48,37 @@ const char* table_file_name(int table) {
 TuneArgs default_args(int table, int m, int n, int k) {
     // Target: at least ~2 CTAs of 8 warps per SM so that enough 16-byte loads are in flight.
     const int target_ctas = 2 * sm_count();
+    if (table == kTableGemvSoftFp8 && m % 128 == 0 && k % 128 == 0) {
+        // the same kernel for one token (KernelId 4): BLOCK_DIM_X = k per stage, KernelParam1 = ring stages,
+        // KernelParam2 = CTAs per cluster; the entry point falls back to KernelId 1 when it cannot run
+        const TuneArgs g = default_args(kTableGemmLayoutASoftFp8, m, 1, k);
+        return TuneArgs{g.b, 4, g.c, g.d};
+    }
     if (is_gemv(table)) {
         int rg = 1;
         int ctas = m / 16;
         int sk = 1;
         while (sk < 8 && ctas * sk < target_ctas && (k / 32) / (8 * sk * 2) >= 4) sk *= 2;
         return TuneArgs{256, 1, rg, sk};
+    }
+    if (table == kTableGemmLayoutASoftFp8 && m % 128 == 0 && k % 128 == 0 && n >= 1 && n <= 64) {
+        // e4m3 weights straight into the 8-bit tensor-core MMA (kernelId 9; the entry point falls back to the decode
+        // pipeline, kernelId 2 with the same kernelParam2 / 3, for calls with block scales or without scratch):
+        // kernelParam1 = k per stage, kernelParam2 = ring stages, kernelParam3 = CTAs per cluster, chosen so that all
+        // CTAs are resident at once (one wave) and fill most of it
+        const int tiles = m / 128;
+        const int np = n <= 16 ? 16 : (n <= 32 ? 32 : 64);
+        const int bk = (np == 16 && tiles >= 150) ? 64 : 128;
+        const int stages = 3;
+        const int smem = stages * (128 * bk + (bk / 64) * np * 128) + 2048;
+        int resident = (200 * 1024) / smem;
+        if (resident > 5) resident = 5;
+        if (resident < 1) resident = 1;
+        int ck = (sm_count() * resident) / tiles;
+        if (ck > 8) ck = 8;
+        while (ck > 1 && (k / bk) / ck < 2) --ck;
+        if (ck < 1) ck = 1;
+        return TuneArgs{9, bk, stages, ck};
     }
     if (m % 128 == 0 && k % 64 == 0 && n >= 2 && n <= 64) {
         // tcgen05 tile kernel, one cluster per 128-row tile: enough CTAs for three to four per SM (they are small, and

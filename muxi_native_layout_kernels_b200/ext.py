@@ -211,7 +211,7 @@ def gemv_layoutA(A, B, alpha: float = 1, beta: float = 0, scale_matrix=None, bia
     the reference kernels.  For e4m3 weights ``scale_matrix=None`` means unit scales."""
     m, k, code = _gemv_checks(A, B, scale_matrix, bias)
     C = torch.empty((1, m), dtype=B.dtype, device=B.device)
-    aux, _keep = _aux(B, m, 1, k)
+    aux, _keep = _aux(B, m, 1, k, stream_k=False)
     check(lib.mlk_gemv_layoutA(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, k, code, alpha, beta,
                                _scale_ptr(scale_matrix, m, k), _bias_ptr(bias, B, m), int(fp8_repacked),
                                ctypes.byref(aux), _stream(B)))
@@ -225,7 +225,7 @@ def gemv_layoutA_wapper(A, B, m: int, k: int, alpha: float = 1, beta: float = 0,
     m2, k2, code = _gemv_checks(A, B, scale_matrix, bias)
     _chk(m == m2 and k == k2, "m, k do not match the tensors")
     C = torch.empty((1, m), dtype=B.dtype, device=B.device)
-    aux, _keep = _aux(B, m, 1, k)
+    aux, _keep = _aux(B, m, 1, k, stream_k=False)
     check(lib.mlk_gemv_layoutA_wapper(A.data_ptr(), B.data_ptr(), C.data_ptr(), m, k, code, alpha, beta, blockDimX,
                                       kernelId, kernelParam1, kernelParam2, _scale_ptr(scale_matrix, m, k),
                                       _bias_ptr(bias, B, m), int(fp8_repacked), ctypes.byref(aux), _stream(B)))
@@ -256,6 +256,7 @@ def _gemm_checks(A, B, b_layout: bool):
 _SYNC_BUFFERS = {}   # (device index, stream handle) -> [counters, status, workspace, MlkAux]
 _WS_BYTES = {}       # (device index, m, n-tile, k) -> workspace bytes of the tcgen05 kernel
 _MIN_WS_FLOATS = 1 << 20
+_RETIRED = []        # workspaces replaced during a stream capture: CUDA graphs may still reference them
 
 
 def _stream_bufs(device: torch.device, stream: int, tiles: int = 0):
@@ -274,18 +275,21 @@ def _status_ptr(t: torch.Tensor) -> int:
     return _stream_bufs(t.device, _stream(t))[1].data_ptr()
 
 
-def _aux(B: torch.Tensor, m: int, n: int, k: int):
+def _aux(B: torch.Tensor, m: int, n: int, k: int, stream_k: bool = True):
     """Scratch lent to the tcgen05 kernels, kept per (device, stream): a block of counters that every kernel leaves
     zeroed, the sticky status word of the kernels' bounded waits, and an fp32 workspace that only grows (partial tiles
     of the persistent stream-K grid; per-token scales of the native-FP8 kernels).  Successive launches of one stream
     may share it: a kernel touches it only after the preceding kernel of the stream has completed
     (griddepcontrol.wait), and kernels of one stream never run concurrently otherwise; another stream gets its own.
     A CUDA graph captures these addresses: replay graphs that were captured on the same stream one at a time.
-    Returns (MlkAux, tensor that keeps the workspace alive)."""
+    stream_k=False: the call cannot use the persistent stream-K grid (e4m3 weights, GeMV) and needs no more than the
+    minimum workspace.  Returns (MlkAux, tensor that keeps the workspace alive)."""
     stream = _stream(B)
     bufs = _stream_bufs(B.device, stream, m // 128)
     nbytes = 0
-    if n <= 64 and m % 128 == 0 and k % 64 == 0:
+    if not stream_k:
+        nbytes = 1024 + 2 * k * min(n, 64)       # what mlk_soft_fp8_workspace_bytes(n, k) reports
+    elif n <= 64 and m % 128 == 0 and k % 64 == 0:
         npad = 16 if n <= 16 else (32 if n <= 32 else 64)
         wkey = (B.device.index, m, npad, k)
         nbytes = _WS_BYTES.get(wkey)
@@ -295,11 +299,10 @@ def _aux(B: torch.Tensor, m: int, n: int, k: int):
     ws = bufs[2]
     if ws is None or ws.numel() * 4 < nbytes:
         # the old buffer may still be in use by kernels already queued on this stream: torch's allocator keeps a freed
-        # block stream-ordered, so dropping the reference here is safe (never while the stream is being captured:
-        # graphs hold the address)
+        # block stream-ordered, so dropping the reference here is safe -- except while the stream is being captured:
+        # graphs captured earlier hold the old address, so the old buffer is then kept alive for good
         if ws is not None and torch.cuda.is_current_stream_capturing():
-            raise RuntimeError("the tcgen05 workspace would have to grow during stream capture: run the shape once "
-                               "eagerly on this stream before capturing")
+            _RETIRED.append(ws)
         ws = bufs[2] = torch.empty(max(nbytes // 4, _MIN_WS_FLOATS), dtype=torch.float32, device=B.device)
         bufs[3] = None
     if bufs[3] is None:
@@ -363,7 +366,7 @@ def gemm_layoutA_soft_fp8(A, A_Scale, B, alpha: float = 1, beta: float = 0, bias
     m, n, k = _gemm_checks(A, B, False)
     _chk(_dense_code(A, B) == 2, "Unsupported data type")
     C = _alloc_c(B, m, n, False)
-    aux, _keep = _aux(B, m, n, k)
+    aux, _keep = _aux(B, m, n, k, stream_k=False)
     check(lib.mlk_gemm_layoutA_soft_fp8(A.data_ptr(), _scale_ptr(A_Scale, m, k), B.data_ptr(), C.data_ptr(), m, n, k,
                                         alpha, beta, _bias_ptr(bias, B, m), int(fp8_repacked), ctypes.byref(aux),
                                         _stream(B)))
@@ -378,7 +381,7 @@ def gemm_layoutA_soft_fp8_wapper(A, A_Scale, B, m: int, n: int, k: int, alpha: f
     _chk((m, n, k) == (m2, n2, k2), "m, n, k do not match the tensors")
     _chk(_dense_code(A, B) == 2, "Unsupported data type")
     C = _alloc_c(B, m, n, False)
-    aux, _keep = _aux(B, m, n, k)
+    aux, _keep = _aux(B, m, n, k, stream_k=False)
     check(lib.mlk_gemm_layoutA_soft_fp8_wapper(A.data_ptr(), _scale_ptr(A_Scale, m, k), B.data_ptr(), C.data_ptr(),
                                                m, n, k, alpha, beta, kernelParam1, kernelParam2, kernelParam3,
                                                kernelId, _bias_ptr(bias, B, m), int(fp8_repacked), ctypes.byref(aux),

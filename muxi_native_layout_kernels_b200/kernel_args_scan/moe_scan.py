@@ -63,6 +63,7 @@ def scan_case(cfg, T, w1, w2, wg, g, dev):
         return time_layer(lambda i: fused_moe(xs[i], w1, w2, logits[i], topk, True, tune=args, **kw))
 
     best_args, best_us = (0, 0, 0, 0, 0, 0), try_args((0, 0, 0, 0, 0, 0))
+    print(f"  T={T}: library default {best_us:.1f} us", flush=True)
     nts = [n for n in (1, 2, 4, 8) if n * 8 <= max(8, 2 * T)]
     # few routed slots leave few work items: deeper split-K is then the only source of CTAs
     few = T * topk <= 64
@@ -91,6 +92,21 @@ def scan_case(cfg, T, w1, w2, wg, g, dev):
                 continue
             for st2, ck2 in itertools.product([2, 3, 4, 6], [1, 2, 4, 8]):
                 args = (nt, g1_best[0], g1_best[1], 0, 100 + st2, ck2)
+                us = try_args(args)
+                if us is not None and us < best_us:
+                    best_args, best_us = args, us
+    if fp8 and H % 128 == 0 and I % 128 == 0:
+        # native-e4m3 tcgen05 expert GEMMs (weights undecoded into the 8-bit MMA): wm = 200 + ring stages
+        for nt in [n for n in (2, 4, 8) if n * 8 <= max(16, 2 * T)]:
+            g1_best, g1_us = None, float("inf")
+            for st1, ck1 in itertools.product([2, 3, 4, 6], [1, 2, 4, 8] if few else [1, 2, 4]):
+                us = try_args((nt, 200 + st1, ck1, 0, 203, 2))
+                if us is not None and us < g1_us:
+                    g1_best, g1_us = (200 + st1, ck1), us
+            if g1_best is None:
+                continue
+            for st2, ck2 in itertools.product([2, 3, 4, 6], [1, 2, 3, 4, 6]):
+                args = (nt, g1_best[0], g1_best[1], 0, 200 + st2, ck2)
                 us = try_args(args)
                 if us is not None and us < best_us:
                     best_args, best_us = args, us

@@ -119,10 +119,11 @@ def test_packaged_table_rows_name_launches_the_library_accepts():
                 assert p3 < 2 or p3 <= k // 64, what
             elif kid == 2 and fp8:
                 assert n <= 64 and p2 in (2, 3, 4, 6, 8) and 1 <= p3 <= min(8, k // 64), what
-            elif kid == 8:
-                assert layout_a and not fp8 and n <= 64 and m % 256 == 0 and p2 in (2, 3, 4) and 1 <= p3 <= min(8, k // 64), what
+            elif kid == 9:       # e4m3 weights undecoded into the 8-bit MMA: k per stage, ring stages, cluster size
+                assert fp8 and n <= 64 and p1 in (64, 128) and k % p1 == 0 and p2 in (2, 3, 4, 6, 8), what
+                assert 1 <= p3 <= min(8, k // p1), what
                 np_ = 16 if n <= 16 else (32 if n <= 32 else 64)
-                assert p2 * (32768 + np_ * 128) >= np_ * 1024, what     # the ring holds the fp32 partial tiles
+                assert p2 * (128 * p1 + (p1 // 64) * np_ * 128) + 1024 <= 227 * 1024, what
             elif kid in (5, 6, 7):
                 assert layout_a and not fp8 and n <= 4 and p1 in (1, 2) and p3 in (1, 2, 4, 8) and m % (16 * p1) == 0, what
             else:
@@ -135,6 +136,10 @@ def test_packaged_table_rows_name_launches_the_library_accepts():
             what = (name, m, k, block, kid, p1, p2)
             if kid == 3:
                 assert fp8 and m % 128 == 0 and k % 64 == 0 and p1 in (2, 3, 4, 6, 8) and 1 <= p2 <= 8, what
+            elif kid == 4:
+                bk = 64 if block == 64 else 128
+                assert fp8 and block in (64, 128, 256) and m % 128 == 0 and k % bk == 0 and p1 in (2, 3, 4, 6, 8), what
+                assert 1 <= p2 <= min(8, k // bk), what
             else:
                 assert block in (64, 128, 256) and (kid == 1 or (kid == 2 and not fp8)), what
                 assert p1 in (1, 2) and p2 in (1, 2, 4, 8) and m % (16 * p1) == 0, what
@@ -142,9 +147,10 @@ def test_packaged_table_rows_name_launches_the_library_accepts():
         what = (E, topk, H, I, fp8, T, nt, wm1, sk1, rg2, wm2, sk2)
         assert nt in (1, 2, 4, 8) or (nt == 16 and wm1 >= 100 and not fp8), what
         assert (wm1 >= 100) == (wm2 >= 100), what
-        if wm1 >= 100:       # tcgen05 expert GEMMs: 100 + ring stages, CTAs per cluster
-            assert H % 128 == 0 and I % 128 == 0, what
-            assert wm1 - 100 in (2, 3, 4, 6) and wm2 - 100 in (2, 3, 4, 6) and 1 <= sk1 <= min(8, H // 64) and 1 <= sk2 <= min(8, I // 64), what
+        if wm1 >= 100:       # tcgen05 expert GEMMs: 100 (decode) or 200 (native e4m3) + ring stages, CTAs per cluster
+            fam = 200 if wm1 >= 200 else 100
+            assert H % 128 == 0 and I % 128 == 0 and (fam == 100 or fp8) and (wm2 >= 200) == (wm1 >= 200), what
+            assert wm1 - fam in (2, 3, 4, 6) and wm2 - fam in (2, 3, 4, 6) and 1 <= sk1 <= min(8, H // 64) and 1 <= sk2 <= min(8, I // 64), what
         else:
             assert wm1 in (1, 2, 4, 8) and wm2 in (1, 2, 4, 8) and sk1 in (1, 2, 4, 8) and sk2 in (1, 2, 4, 8) and rg2 in (1, 2), what
 

@@ -246,6 +246,90 @@ def test_soft_fp8_tcgen05_pipeline(repacked):
                                                              kernelId=2, fp8_repacked=repacked))
 
 
+@pytest.mark.parametrize("repacked", [False, True])
+def test_soft_fp8_native_tensor_core_kernel(repacked):
+    """kernelId 9 (GEMM) / 4 (GeMV): e4m3 weights undecoded into tcgen05.mma.kind::f8f6f4, activations split into two
+    e4m3 terms under a per-token power-of-two scale.  Same oracle and tolerance as the decode kernels."""
+    dev = require_gpu()
+    for (m, k) in [(128, 128), (256, 384), (512, 1024), (1024, 4096)]:
+        W8 = rand_e4m3((m, k), 270 + m)
+        A = mlk.layoutA(W8.to(dev))
+        if repacked:
+            A = mlk.fp8_weight_repack(A)
+        bias = randn((1, m), 271, 1.0, torch.bfloat16)
+        for n in [1, 7, 16, 17, 32, 48, 64]:
+            X = randn((n, k), 272 + n, 1.0, torch.bfloat16)
+            want = odense.gemm_ref(X, W8.to(torch.bfloat16))
+            for bk, stages, ck in [(64, 2, 1), (64, 3, 2), (128, 4, 4), (64, 6, 3), (64, 8, 8), (128, 6, 8), (128, 2, 1)]:
+                if ck > k // bk or k % bk:
+                    continue
+                C = mlk.gemm_layoutA_soft_fp8_wapper(A, None, X.to(dev), m, n, k, kernelParam1=bk, kernelParam2=stages,
+                                                     kernelParam3=ck, kernelId=9, fp8_repacked=repacked)
+                assert_close(C, want, f"fp8 native m={m} k={k} n={n} bk={bk} stages={stages} cluster={ck}")
+            C = mlk.gemm_layoutA_soft_fp8_wapper(A, None, X.to(dev), m, n, k, alpha=0.5, kernelParam1=64, kernelParam2=4,
+                                                 kernelParam3=2, kernelId=9, bias=bias.to(dev), fp8_repacked=repacked)
+            assert_close(C, odense.gemm_ref(X, W8.to(torch.bfloat16), alpha=0.5, bias=bias), f"fp8 native bias m={m} n={n}")
+        x = randn((1, k), 273, 1.0, torch.bfloat16)
+        for bk, stages, ck in [(64, 2, 2), (128, 4, 1), (256, 3, 2)]:
+            if k % min(bk, 128) or ck > k // min(bk, 128):
+                continue
+            y = mlk.gemv_layoutA_wapper(A, x.to(dev), m, k, blockDimX=bk, kernelId=4, kernelParam1=stages, kernelParam2=ck,
+                                        fp8_repacked=repacked)
+            assert_close(y, odense.gemm_ref(x, W8.to(torch.bfloat16)), f"gemv fp8 native m={m} k={k} {bk},{stages},{ck}")
+    # bit-identical from run to run
+    X = randn((40, 4096), 274, 1.0, torch.bfloat16).to(dev)
+    call = lambda: mlk.gemm_layoutA_soft_fp8_wapper(A, None, X, 1024, 40, 4096, kernelParam1=64, kernelParam2=4,
+                                                    kernelParam3=4, kernelId=9, fp8_repacked=repacked)
+    ref = call()
+    for _ in range(3):
+        assert torch.equal(ref, call())
+    assert mlk.kernel_status() == 0
+    # block scales are not this kernel's business
+    with pytest.raises(RuntimeError, match="block scales"):
+        mlk.gemm_layoutA_soft_fp8_wapper(A, torch.ones(8, 32, device=dev), X, 1024, 40, 4096, kernelParam1=64,
+                                         kernelParam2=4, kernelParam3=4, kernelId=9, fp8_repacked=repacked)
+
+
+def test_soft_fp8_native_kernel_exactness_and_ranges():
+    """Properties of the two-term activation split: every finite e4m3 byte is multiplied exactly; rows of very
+    different magnitude in one call keep their precision (per-token scale); tiny and huge activations; zero rows."""
+    dev = require_gpu()
+    table = torch.from_numpy(olay.e4m3_decode_table())
+    raw = (torch.arange(128 * 128, dtype=torch.int64) * 37 % 256).to(torch.uint8).reshape(128, 128)
+    raw = torch.where((raw & 0x7F) == 0x7F, torch.zeros_like(raw), raw)          # the two NaN encodings -> 0
+    A = mlk.layoutA(raw.view(torch.float8_e4m3fn).to(dev))
+    want = table[raw.long()]
+    for half in range(2):                         # 64 one-hot tokens per call: C[j, row] = W[row, half * 64 + j]
+        X = torch.zeros(64, 128, dtype=torch.bfloat16)
+        X[torch.arange(64), half * 64 + torch.arange(64)] = 1.0
+        C = mlk.gemm_layoutA_soft_fp8_wapper(A, None, X.to(dev), 128, 64, 128, kernelParam1=64, kernelParam2=2,
+                                             kernelParam3=1, kernelId=9)
+        assert torch.equal(C.float().cpu(), want[:, half * 64:(half + 1) * 64].t().contiguous())
+    # tokens of magnitudes 1e-30 ... 1e30 in one batch, plus an all-zero token
+    m, k = 256, 1024
+    W8 = rand_e4m3((m, k), 280)
+    A = mlk.layoutA(W8.to(dev))
+    X = randn((16, k), 281, 1.0, torch.float32)
+    mags = torch.tensor([1e-30, 1e-20, 1e-10, 1e-5, 1e-3, 0.1, 1.0, 10.0, 1e3, 1e5, 1e10, 1e20, 1e30, 3.0, 0.0, 1.0])
+    X = (X * mags[:, None]).to(torch.bfloat16)
+    C = mlk.gemm_layoutA_soft_fp8_wapper(A, None, X.to(dev), m, 16, k, kernelParam1=128, kernelParam2=3, kernelParam3=2,
+                                         kernelId=9).float().cpu()
+    ref = X.double() @ W8.to(torch.bfloat16).double().t()
+    for t in range(16):
+        scale = float(ref[t].abs().max()) or 1.0
+        err = float((C[t].double() - ref[t]).abs().max()) / scale
+        assert err < 6e-3, f"token {t} (magnitude {float(mags[t])}): error {err} of the row's largest output"
+    assert bool((C[14] == 0).all())
+    # an element 2^-14 of its token's maximum: still resolved to 2^-17 of the maximum
+    X = torch.zeros(1, k, dtype=torch.bfloat16)
+    X[0, 0] = 1024.0
+    X[0, 1] = 1024.0 * 2.0 ** -14 * 1.4375
+    y = mlk.gemv_layoutA_wapper(A, X.to(dev), m, k, blockDimX=64, kernelId=4, kernelParam1=2, kernelParam2=1).double().cpu()
+    ref = X.double() @ W8.to(torch.bfloat16).double().t()
+    bound = 2.0 ** -17 * 1024.0 * float(W8.float()[:, 1].abs().max()) + 2.0 ** -8 * ref.abs()
+    assert bool(((y - ref).abs() <= bound + 1e-6).all())
+
+
 def _close_rel(got, want, what, tol=1e-2):
     """|got - want| <= tol * (rms(want) + |want|): the absolute part follows the output scale, which block scales
     move by orders of magnitude."""

@@ -299,6 +299,31 @@ def test_moe_soft_fp8_tcgen05_expert_gemms(T, repack):
         assert_close(y, y0.cpu(), f"fp8 tcgen05 vs warp-level T={T} tune={tune}", scale_atol=True)
 
 
+@pytest.mark.parametrize("T", [1, 8, 32, 130, 520])
+@pytest.mark.parametrize("repack", [False, True])
+def test_moe_soft_fp8_native_tensor_core_expert_gemms(T, repack):
+    """e4m3 experts on the native-e4m3 tcgen05 kernels (tuning values 200 + stages: weight bytes undecoded into the
+    8-bit MMA, activation rows as two e4m3 terms, the activation of the first GEMM split in place), against the same
+    oracle and against the warp-level kernels; with an expert map; and with block scales, where the same tuning
+    arguments must run the decode kernels instead."""
+    E, topk, H, I = 32, 8, 256, 128
+    x = randn((T, H), 900 + T, 1.0)
+    w1 = rand_e4m3((E, 2 * I, H), 901, 0.25)
+    w2 = rand_e4m3((E, H, I), 902, 0.25)
+    logits = randn((T, E), 903 + T, 1.0)
+    for tune in [(1, 202, 1, 0, 202, 1), (2, 203, 2, 0, 204, 2), (4, 204, 4, 0, 206, 1), (8, 202, 2, 0, 203, 2)]:
+        y = _moe_compare(x, w1, w2, logits, topk, f"moe fp8 native T={T} repack={repack} tune={tune}", fp8=True,
+                         repack=repack, tune=tune)
+        y0 = _moe_compare(x, w1, w2, logits, topk, f"moe fp8 warp-level T={T}", fp8=True, repack=repack,
+                          tune=(tune[0], 2, 1, 1, 2, 1))
+        assert_close(y, y0.cpu(), f"fp8 native vs warp-level T={T} tune={tune}", scale_atol=True)
+    g = torch.Generator().manual_seed(904)
+    scales = (torch.rand(E, 2 * I // 128, H // 128, generator=g) * 0.5 + 0.01,
+              torch.rand(E, H // 128, I // 128, generator=g) * 0.5 + 0.01)
+    _moe_compare(x, w1, w2, logits, topk, f"moe fp8 native tuning with scales T={T}", fp8=True, scales=scales, repack=repack,
+                 tune=(2, 203, 2, 0, 203, 2))
+
+
 @pytest.mark.parametrize("T", [1, 32, 130])
 @pytest.mark.parametrize("repack", [False, True])
 def test_moe_soft_fp8_tcgen05_block_scales(T, repack):
