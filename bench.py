@@ -155,6 +155,33 @@ def time_cpu(passes: int, warm: int = 1):
     return total / dt / 1e9, dt
 
 
+def time_cpu_moe():
+    """The oracle's fused MoE (the reference's torch formulation, muxi_layout_kernels/utils.py:131-244) on the host
+    cores, one run each of the two MoE configurations at their largest token count; weights seeded as in
+    kernel_args_scan/moe_bench.py but generated on the host."""
+    from oracle import moe as omoe
+    torch.set_num_threads(os.cpu_count() or 1)
+    out = []
+    for name, (E, topk, H, I, fp8, seed, T) in {"C4 mixtral bf16": (8, 2, 4096, 14336, False, 3, 256),
+                                              "C5 fine-grained e4m3": (128, 8, 2048, 768, True, 4, 512)}.items():
+        g = torch.Generator().manual_seed(seed)
+        # timing only: one seeded expert, repeated for every expert (generating 1.4 G random weights on the host would
+        # take longer than the layer itself)
+        wdt, std = (torch.float8_e4m3fn, 0.5) if fp8 else (torch.bfloat16, 0.02)
+        w1 = (torch.randn(2 * I, H, generator=g) * std).to(wdt).unsqueeze(0).repeat(E, 1, 1)
+        w2 = (torch.randn(H, I, generator=g) * std).to(wdt).unsqueeze(0).repeat(E, 1, 1)
+        wg = (torch.randn(E, H, generator=g) * 0.02).to(torch.bfloat16)
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+        logits = (x.float() @ wg.float().t()).to(torch.bfloat16)
+        t0 = time.perf_counter()
+        omoe.fused_moe_ref(x, w1, w2, logits, topk, True)
+        dt = time.perf_counter() - t0
+        out.append({"config": name, "T": T, "us": round(dt * 1e6, 1), "cores": os.cpu_count(), "kind": "port",
+                    "sample": "one run of the whole layer (router + experts), torch on all host threads; one seeded expert's weights repeated for all experts"})
+        del w1, w2
+    return out
+
+
 def run_reference(args):
     rank, world, _ = dist_env()
     if rank != 0:
@@ -350,6 +377,27 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e, ms_e2e_eager = float(t[0]), float(t[1]), float(t[2])
 
+    peak, peak_kind = measured_peak()
+    # every BASELINE configuration that is not the headline step, one row per (operator, dtype, shape, tokens): each
+    # rank times its own row shards, the row's time is the max over ranks
+    per_config = None
+    if not args.no_per_config:
+        from muxi_native_layout_kernels_b200.kernel_args_scan import dense_bench
+        try:
+            per_config = dense_bench.run(dev, peak, rank, world)
+            if world > 1:
+                t = torch.tensor([r["us"] for r in per_config], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                for r, us in zip(per_config, t.tolist()):
+                    # whole-job figures: all ranks' bytes over the slowest rank's time; fractions per GPU
+                    wb = 1 if r["dtype"] == "e4m3" else 2
+                    nbytes = r["N"] * world * r["K"] * wb + 2 * r["tokens"] * (r["K"] + r["N"] * world)
+                    r.update(N=r["N"] * world, us=round(us, 2), gbs=round(nbytes / us / 1e3, 1),
+                             frac_measured=round(nbytes / us / 1e3 / world / peak, 3),
+                             frac_nominal_8TBs=round(nbytes / us / 1e3 / world / NOMINAL_HBM_GBS, 3))
+        except Exception as exc:       # the headline line must still be printed
+            per_config = {"error": repr(exc)[:300]}
+
     moe_ep = None
     if world > 1 and not args.no_moe:
         # every rank takes part (collectives inside); rank 0 reports
@@ -363,8 +411,12 @@ def run_ours(args):
         ms_step = ms / args.steps
         value = step_bytes_total / (ms_step * 1e-3) / 1e9
         e2e_value = step_bytes_total / (ms_e2e / args.steps * 1e-3) / 1e9
-        peak, peak_kind = measured_peak()
         per_rank_bytes = sum(algorithmic_bytes(n, N // world, K) for (n, N, K) in order)
+        per_rank_weights = sum(N // world * K * 2 for (N, K) in SHAPES)
+        between = per_rank_weights - max(N // world * K * 2 for (N, K) in SHAPES)
+        l2_note = (f"consecutive launches use different weight matrices; {between / 1e6:.0f} MB of other weights stream between "
+                   f"two uses of one matrix (L2 is 126 MB)" + ("" if between > 126e6 else
+                   ": at this shard size the weights are partly L2-resident, so the value is not a pure HBM figure"))
         achieved = per_rank_bytes / (ms_step * 1e-3) / 1e9
         line = {
             "metric": "narrow_gemm_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -373,7 +425,7 @@ def run_ours(args):
             "config": {"workload": "narrow_gemm_bf16_llama8b", "tokens": TOKENS, "shapes": SHAPES, "variant": "gemm_layoutA",
                        "launches_per_step": len(order), "sharding": f"rows/{world}",
                        "static_weights": True,
-                       "l2": "consecutive launches use different weight matrices; >= 235 MB stream between two uses of one matrix (L2 is 126 MB)",
+                       "l2": l2_note,
                        "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "GB/s", "mode": "CUDA graph of one step, a three-stage pipeline: the activations host -> device in two copies on a copy stream, the 21 public API calls on the compute stream as their inputs arrive (token counts in the order 1, 2, 4, 64, 32, 16, 8), every result device -> host on a second copy stream; the step ends when the last result is in host memory",
@@ -387,19 +439,26 @@ def run_ours(args):
                          "peak_source": f"of {peak_kind}",
                          "kernel": "dense_umma_kernel (17 launches) / gemv_simt_kernel (3) / dense_mma_kernel (1-2), averaged"},
         }
+        if per_config is not None:
+            line["per_config"] = per_config
         if world == 1 and not args.no_moe:
             # second half of the metric: fused-MoE layer time (router + alignment + experts + combine), CUDA-graph
             # replay over 8 different activation batches, see kernel_args_scan/moe_bench.py
             from muxi_native_layout_kernels_b200.kernel_args_scan import moe_bench
-            line["moe_layer_us"] = moe_bench.run("both", None, 24, dev)
+            line["moe_layer_us"] = moe_bench.run("both", None, 24, dev, peak=peak)
         if world > 1 and not args.no_moe:
             line["moe_layer_us"] = moe_ep
-            line["moe_layer_mode"] = (f"expert parallel over {world} GPUs: E/{world} experts per rank, tokens replicated, "
-                                      "NCCL all-reduce of the fp32 shares; us_eager = eager calls (host launch overhead included), us_graph = CUDA-graph replays; max over ranks")
+            line["moe_layer_mode"] = (f"expert parallel over {world} GPUs, E/{world} experts per rank, both modes of parallel.py on identical "
+                                      "seeded weights: replicated (tokens on every rank, experts_map, NCCL all-reduce of the shares) and "
+                                      "all_to_all (tokens sharded, NCCL all-to-all dispatch and combine); parity_ok = every rank's output "
+                                      "of one batch equals the single-GPU layer within |d| <= 1e-2 max(1, rms) + 1e-2 |want|; "
+                                      "us_eager = eager calls (host launch overhead included), us_graph = CUDA-graph replays; max over ranks")
         if world == 1 and not args.no_cpu:
             gbs, dt = time_cpu(passes=args.cpu_passes)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
                                     "sample": f"{args.cpu_passes} full passes over the 21-case grid, torch fp32 matmul, all host threads"}
+            if not args.no_moe:
+                line["cpu_baseline"]["moe_layer_us"] = time_cpu_moe()
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -414,6 +473,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--cpu-passes", type=int, default=5)
     ap.add_argument("--no-moe", action="store_true", help="skip the fused-MoE layer timings")
+    ap.add_argument("--no-per-config", action="store_true", help="skip the per-configuration table (C1, C2 variants, C3)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -255,6 +255,8 @@ int mlk_moe_align(int batchSize, int expertCount, int topK, int microBatchSize, 
  * cluster split-K of GEMM1 (1,2,4,8), row groups per warp of GEMM2 (1,2), row warps of GEMM2 (1,2,4), cluster split-K of
  * GEMM2}; a 0 lets the library choose that value from the shape.
  * status: one device int, sticky error word of the bounded waits inside the tcgen05 expert kernels (0 = ok), or NULL.
+ * out_fp32 != 0 (needs combine_scratch): y is [T, H] fp32 and receives the un-rounded sums over this rank's experts,
+ *   so that an expert-parallel caller can add the ranks' shares before the one rounding.
  * combine_scratch: optional T*topK*H floats.  With it the weighted expert outputs are kept in fp32 and summed per
  * token in a fixed order with one final rounding (bit-reproducible).  With NULL they are accumulated into y with
  * 16-bit atomics, as the reference does (csrc/moe_kernels/group_gemm_second.h:333-346): one rounding per addend
@@ -266,7 +268,7 @@ int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int
                               int32_t* experts_ids, void* C, void* y, const float* w1_scale, const float* w2_scale,
                               int dtype, int fp8_order, int microBatchSize, const int32_t* experts_map,
                               int experts_map_len, float* combine_scratch, int64_t combine_scratch_bytes,
-                              const int32_t* tune, int32_t* status, mlk_stream_t s);
+                              const int32_t* tune, int32_t* status, int out_fp32, mlk_stream_t s);
 
 /* Expert compute for callers that must not allocate device memory (a plugin running under another runtime's memory
  * pool, a serving loop whose allocator is off limits on the request path).  It has no
@@ -281,7 +283,7 @@ int mlk_fused_experts_compute_static(const void* w1, const void* w2, const void*
                                      int32_t* experts_ids, void* C, void* y, const float* w1_scale,
                                      const float* w2_scale, int dtype, int fp8_order, int microBatchSize,
                                      const int32_t* experts_map, int experts_map_len, const int32_t* tune,
-                                     int32_t* status, mlk_stream_t s);
+                                     int32_t* status, int out_fp32, mlk_stream_t s);
 
 /* ---- expert-parallel token exchange (no counterpart in the reference, which is single-GPU) ------------------ */
 
@@ -290,7 +292,8 @@ int mlk_fused_experts_compute_static(const void* w1, const void* w2, const void*
 int mlk_moe_gather_rows(const void* x, const int32_t* idx, void* out, int64_t n_rows, int hidden, int64_t x_rows,
                         mlk_stream_t s);
 /* y[t,:] = round( sum_j float(rows[pos[t*topK + j],:]) ), j ascending, entries with pos outside [0, n_rows) skipped.
- * Combine step: `rows` are the weighted expert outputs as they come back from the combine all-to-all. */
+ * Combine step: `rows` are the weighted expert outputs as they come back from the combine all-to-all.
+ * dtype: 0 / 1 = rows and y in bf16 / fp16; 2 / 3 = rows in fp32 (un-rounded weighted outputs), y in bf16 / fp16. */
 int mlk_moe_unpermute_sum(const void* rows, const int32_t* pos, void* y, int64_t T, int topK, int hidden,
                           int64_t n_rows, int dtype, mlk_stream_t s);
 

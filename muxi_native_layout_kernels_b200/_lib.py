@@ -56,12 +56,12 @@ PROTOTYPES = {
     "mlk_moe_align": (c_int, [c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_vp]),
     "mlk_fused_experts_compute_static": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp,
                                                  c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp,
-                                                 c_int, C.POINTER(C.c_int32), c_vp, c_vp]),
+                                                 c_int, C.POINTER(C.c_int32), c_vp, c_int, c_vp]),
     "mlk_moe_gather_rows": (c_int, [c_vp, c_vp, c_vp, c_i64, c_int, c_i64, c_vp]),
     "mlk_moe_unpermute_sum": (c_int, [c_vp, c_vp, c_vp, c_i64, c_int, c_int, c_i64, c_int, c_vp]),
     "mlk_fused_experts_compute": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp,
                                           c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp,
-                                          c_int, c_vp, c_i64, C.POINTER(C.c_int32), c_vp, c_vp]),
+                                          c_int, c_vp, c_i64, C.POINTER(C.c_int32), c_vp, c_int, c_vp]),
 }
 
 

@@ -392,7 +392,7 @@ MoeParams moe_params(const void* w1, const void* w2, const void* x, int batch_si
                      int inter, const int32_t* topk_ids, const void* topk_weights, int32_t* sorted_token_ids,
                      int32_t* cumsum_buffer, int32_t* padded_num_experts, int32_t* experts_ids, void* C, void* y,
                      const float* w1_scale, const float* w2_scale, int dtype, int fp8_order, int microBatchSize,
-                     const int32_t* experts_map, int experts_map_len, const int32_t* tune, int32_t* status) {
+                     const int32_t* experts_map, int experts_map_len, const int32_t* tune, int32_t* status, int out_fp32) {
     MoeParams p{};
     p.w1 = w1; p.w2 = w2; p.x = x; p.T = batch_size; p.E = expert_count; p.topk = topK; p.H = hidden; p.I = inter;
     p.topk_ids = topk_ids; p.topk_weights = topk_weights; p.sorted_token_ids = sorted_token_ids;
@@ -400,6 +400,7 @@ MoeParams moe_params(const void* w1, const void* w2, const void* x, int batch_si
     p.C = C; p.y = y; p.w1_scale = w1_scale; p.w2_scale = w2_scale; p.dtype = dtype; p.fp8_order = fp8_order;
     p.mbs = microBatchSize; p.experts_map = experts_map; p.experts_map_len = experts_map_len;
     p.status = status;
+    p.y_fp32 = out_fp32;
     if (tune) { p.nt = tune[0]; p.wm1 = tune[1]; p.sk1 = tune[2]; p.rg = tune[3]; p.wm2 = tune[4]; p.sk2 = tune[5]; }
     return p;
 }
@@ -411,11 +412,11 @@ int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int
                               int32_t* experts_ids, void* C, void* y, const float* w1_scale, const float* w2_scale,
                               int dtype, int fp8_order, int microBatchSize, const int32_t* experts_map,
                               int experts_map_len, float* combine_scratch, int64_t combine_scratch_bytes,
-                              const int32_t* tune, int32_t* status, mlk_stream_t s) {
+                              const int32_t* tune, int32_t* status, int out_fp32, mlk_stream_t s) {
     clear_error();
     MoeParams p = moe_params(w1, w2, x, batch_size, expert_count, topK, hidden, inter, topk_ids, topk_weights,
                              sorted_token_ids, cumsum_buffer, padded_num_experts, experts_ids, C, y, w1_scale, w2_scale,
-                             dtype, fp8_order, microBatchSize, experts_map, experts_map_len, tune, status);
+                             dtype, fp8_order, microBatchSize, experts_map, experts_map_len, tune, status, out_fp32);
     p.scratch = combine_scratch; p.scratch_bytes = combine_scratch_bytes;
     return launch_fused_experts(p, (cudaStream_t)s);
 }
@@ -426,11 +427,12 @@ int mlk_fused_experts_compute_static(const void* w1, const void* w2, const void*
                                      int32_t* experts_ids, void* C, void* y, const float* w1_scale,
                                      const float* w2_scale, int dtype, int fp8_order, int microBatchSize,
                                      const int32_t* experts_map, int experts_map_len, const int32_t* tune,
-                                     int32_t* status, mlk_stream_t s) {
+                                     int32_t* status, int out_fp32, mlk_stream_t s) {
     clear_error();
     const MoeParams p = moe_params(w1, w2, x, batch_size, expert_count, topK, hidden, inter, topk_ids, topk_weights,
                                    sorted_token_ids, cumsum_buffer, padded_num_experts, experts_ids, C, y, w1_scale,
-                                   w2_scale, dtype, fp8_order, microBatchSize, experts_map, experts_map_len, tune, status);
+                                   w2_scale, dtype, fp8_order, microBatchSize, experts_map, experts_map_len, tune, status,
+                                   out_fp32);
     return launch_fused_experts_static(p, (cudaStream_t)s);
 }
 

@@ -49,6 +49,7 @@ struct MoeParams {
     int experts_map_len;
     float* scratch;               // optional [T*topk, H] fp32 for the deterministic combine
     long long scratch_bytes;
+    int y_fp32;                   // y is [T, H] fp32: the token sums un-rounded (needs the combine scratch)
     int* status;                  // sticky error word of the bounded waits inside the tcgen05 kernels (0 = ok), or null
     int nt, wm1, sk1, rg, wm2, sk2;   // tuning (0 = choose by shape): token tiles, GEMM1 row warps / split-K, GEMM2 row groups / row warps / split-K;
                                       // wm1 = 100 + s1 and wm2 = 100 + s2 select the tcgen05 kernels (combine scratch given)

@@ -28,8 +28,8 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restric
     }
 }
 
-template <int WT>
-__global__ void __launch_bounds__(256) unpermute_sum_kernel(const uint4* __restrict__ rows,
+template <int WT, bool ROWS32>
+__global__ void __launch_bounds__(256) unpermute_sum_kernel(const void* __restrict__ rows_,
                                                            const int32_t* __restrict__ pos, uint4* __restrict__ y,
                                                            long long T, int topk, int octs, long long n_rows) {
     const long long total = T * octs;
@@ -41,10 +41,17 @@ __global__ void __launch_bounds__(256) unpermute_sum_kernel(const uint4* __restr
         for (int j = 0; j < topk; ++j) {
             const long long p = pos[t * topk + j];
             if (p < 0 || p >= n_rows) continue;
-            const uint4 v = rows[p * octs + o];
-            const float2 v0 = unpack2<WT>(v.x), v1 = unpack2<WT>(v.y), v2 = unpack2<WT>(v.z), v3 = unpack2<WT>(v.w);
-            a[0] += v0.x; a[1] += v0.y; a[2] += v1.x; a[3] += v1.y;
-            a[4] += v2.x; a[5] += v2.y; a[6] += v3.x; a[7] += v3.y;
+            if constexpr (ROWS32) {
+                const float4* src = reinterpret_cast<const float4*>(rows_) + (p * octs + o) * 2;
+                const float4 u = src[0], w = src[1];
+                a[0] += u.x; a[1] += u.y; a[2] += u.z; a[3] += u.w;
+                a[4] += w.x; a[5] += w.y; a[6] += w.z; a[7] += w.w;
+            } else {
+                const uint4 v = reinterpret_cast<const uint4*>(rows_)[p * octs + o];
+                const float2 v0 = unpack2<WT>(v.x), v1 = unpack2<WT>(v.y), v2 = unpack2<WT>(v.z), v3 = unpack2<WT>(v.w);
+                a[0] += v0.x; a[1] += v0.y; a[2] += v1.x; a[3] += v1.y;
+                a[4] += v2.x; a[5] += v2.y; a[6] += v3.x; a[7] += v3.y;
+            }
         }
         uint4 out;
         out.x = pack2<WT>(a[0], a[1]);
@@ -77,14 +84,17 @@ int launch_gather_rows(const void* x, const int32_t* idx, void* out, long long n
 int launch_unpermute_sum(const void* rows, const int32_t* pos, void* y, long long T, int topk, int H, long long n_rows,
                          int dtype, cudaStream_t s) {
     if (T < 0 || topk <= 0 || H <= 0 || H % 8 != 0) return fail(kInvalidArg, "moe_unpermute_sum: bad sizes");
-    if (dtype != kBF16 && dtype != kFP16) return fail(kInvalidArg, "moe_unpermute_sum: rows must be bf16 or fp16");
+    if (dtype < 0 || dtype > 3) return fail(kInvalidArg, "moe_unpermute_sum: dtype code must be 0..3");
     if (T == 0) return kOk;
     if (!pos || !y || (n_rows > 0 && !rows)) return fail(kInvalidArg, "moe_unpermute_sum: null pointer");
     const int octs = H / 8;
-    if (dtype == kFP16)
-        unpermute_sum_kernel<kFP16><<<grid_for(T * octs), 256, 0, s>>>((const uint4*)rows, pos, (uint4*)y, T, topk, octs, n_rows);
-    else
-        unpermute_sum_kernel<kBF16><<<grid_for(T * octs), 256, 0, s>>>((const uint4*)rows, pos, (uint4*)y, T, topk, octs, n_rows);
+    const int g = grid_for(T * octs);
+    switch (dtype) {
+        case 0: unpermute_sum_kernel<kBF16, false><<<g, 256, 0, s>>>(rows, pos, (uint4*)y, T, topk, octs, n_rows); break;
+        case 1: unpermute_sum_kernel<kFP16, false><<<g, 256, 0, s>>>(rows, pos, (uint4*)y, T, topk, octs, n_rows); break;
+        case 2: unpermute_sum_kernel<kBF16, true><<<g, 256, 0, s>>>(rows, pos, (uint4*)y, T, topk, octs, n_rows); break;
+        default: unpermute_sum_kernel<kFP16, true><<<g, 256, 0, s>>>(rows, pos, (uint4*)y, T, topk, octs, n_rows); break;
+    }
     return check_launch("moe_unpermute_sum");
 }
 

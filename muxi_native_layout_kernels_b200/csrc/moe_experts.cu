@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const MoeGemmParams p) {
 
 // Un-permute + sum: y[t, :] = round16( sum_j scratch[t*topk + j, :] ) over the slots whose expert lives on this
 // rank, in ascending j.  One thread per (token, 8 columns).
-template <int WT>
+template <int WT, bool F32>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ scratch,
                                                          const int32_t* __restrict__ topk_ids,
                                                          const int32_t* __restrict__ experts_map, int map_len, int E,
@@ -194,13 +194,36 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
             a[0] += u.x; a[1] += u.y; a[2] += u.z; a[3] += u.w;
             a[4] += w.x; a[5] += w.y; a[6] += w.z; a[7] += w.w;
         }
-        uint4 out;
-        out.x = pack2<WT>(a[0], a[1]);
-        out.y = pack2<WT>(a[2], a[3]);
-        out.z = pack2<WT>(a[4], a[5]);
-        out.w = pack2<WT>(a[6], a[7]);
-        reinterpret_cast<uint4*>(y)[i] = out;
+        if constexpr (F32) {
+            // the un-rounded sums (expert-parallel callers add the shares of the ranks before the one rounding)
+            float4* const dst = reinterpret_cast<float4*>(y) + 2 * i;
+            dst[0] = make_float4(a[0], a[1], a[2], a[3]);
+            dst[1] = make_float4(a[4], a[5], a[6], a[7]);
+        } else {
+            uint4 out;
+            out.x = pack2<WT>(a[0], a[1]);
+            out.y = pack2<WT>(a[2], a[3]);
+            out.z = pack2<WT>(a[4], a[5]);
+            out.w = pack2<WT>(a[6], a[7]);
+            reinterpret_cast<uint4*>(y)[i] = out;
+        }
     }
+}
+
+// y[t, :] = sum of the token's rows in the combine scratch, in the activation type or (y_fp32) un-rounded
+int launch_combine(const MoeParams& m, int wt, cudaStream_t s) {
+    const long long total = (long long)m.T * (m.H / 8);
+    const int grid = (int)std::min<long long>((total + 255) / 256, 8LL * sm_count());
+    if (m.y_fp32)
+        moe_combine_kernel<kBF16, true><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
+                                                             m.topk, m.H, m.y);
+    else if (wt == kFP16)
+        moe_combine_kernel<kFP16, false><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
+                                                              m.topk, m.H, m.y);
+    else
+        moe_combine_kernel<kBF16, false><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
+                                                              m.topk, m.H, m.y);
+    return check_launch("moe_combine");
 }
 
 template <int WT, int NT, int RG, bool SCALE, int MODE>
@@ -383,11 +406,7 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
         if (int st = launch_moe_umma_f8n(2, m.w2, m.E, m.H, m.I, m.C, inv2, slots, m.scratch, wl, m.sorted_token_ids, m.topk_weights,
                                          (int)slots, np, m.wm2 - 200, m.sk2 > 0 ? m.sk2 : 1, max_items, m.status, s))
             return st;
-        const long long total = (long long)m.T * (m.H / 8);
-        const int grid = (int)std::min<long long>((total + 255) / 256, 8LL * sm_count());
-        moe_combine_kernel<kBF16><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
-                                                      m.topk, m.H, m.y);
-        return check_launch("moe_combine");
+        return launch_combine(m, wt, s);
     }
 
     if (umma) {
@@ -403,15 +422,7 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
                                      m.sorted_token_ids, m.topk_weights, (int)slots, np, m.wm2 - 100, m.sk2 > 0 ? m.sk2 : 1,
                                      max_items, m.fp8_order, scale ? m.w2_scale : nullptr, m.status, s))
             return st;
-        const long long total = (long long)m.T * (m.H / 8);
-        const int grid = (int)std::min<long long>((total + 255) / 256, 8LL * sm_count());
-        if (wt == kFP16)
-            moe_combine_kernel<kFP16><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
-                                                          m.topk, m.H, m.y);
-        else
-            moe_combine_kernel<kBF16><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
-                                                          m.topk, m.H, m.y);
-        return check_launch("moe_combine");
+        return launch_combine(m, wt, s);
     }
 
     // ---- GEMM1: act[slot, 0..I) = silu(x W1_gate^T) * (x W1_up^T)
@@ -468,6 +479,7 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
     int sk2 = m.sk2 > 0 ? m.sk2 : pick_sk(tiles2 * std::min(m.E, (int)slots), m.I / 32, 8 / wm2);
     if (sk2 != 1 && sk2 != 2 && sk2 != 4 && sk2 != 8) return fail(kInvalidArg, "fused_experts_compute: split-K must be 1, 2, 4 or 8");
     const bool det = m.scratch != nullptr;
+    if (m.y_fp32 && !det) return fail(kInvalidArg, "fused_experts_compute: fp32 output needs the combine scratch");
     if (det && m.scratch_bytes < (long long)slots * m.H * 4)
         return fail(kInvalidArg, "fused_experts_compute: combine scratch holds %lld bytes, needs %lld", m.scratch_bytes,
                     (long long)slots * m.H * 4);
@@ -475,15 +487,7 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
     g2.scratch = det ? m.scratch : nullptr;
     if (int st = launch_moe_gemm<2>(wt, scale, g2, nt_tiles, rg2, tiles2, sk2, max_items, s)) return st;
     if (!det) return kOk;
-    const long long total = (long long)m.T * (m.H / 8);
-    const int grid = (int)std::min<long long>((total + 255) / 256, 8LL * sm_count());
-    if (wt == kFP16)
-        moe_combine_kernel<kFP16><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
-                                                      m.topk, m.H, m.y);
-    else
-        moe_combine_kernel<kBF16><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
-                                                      m.topk, m.H, m.y);
-    return check_launch("moe_combine");
+    return launch_combine(m, wt, s);
 }
 
 // ---------------------------------------------------------------------------------------------------------

@@ -561,7 +561,8 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
     per warp of the second GEMM: 1 or 2, other values = automatic) is used, split-K is chosen from the shape.
     Extra keywords: ``fp8_repacked`` marks e4m3 weights that went through ``fp8_weight_repack``;
     ``deterministic`` (default True) sums each token's expert outputs in fp32 in a fixed order with one rounding,
-    False uses 16-bit atomic adds into ``y`` as the reference does; ``tune`` = six launch integers (token tiles per
+    False uses 16-bit atomic adds into ``y`` as the reference does; a float32 ``y`` (deterministic only) receives the
+    un-rounded sums; ``tune`` = six launch integers (token tiles per
     work item, GEMM1 row warps, GEMM1 split-K, GEMM2 row groups per warp, GEMM2 row warps, GEMM2 split-K; 0 = automatic).
     """
     w1, w2, x = experts_weights_matrix1, experts_weights_matrix2, activations
@@ -569,6 +570,7 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
         k_ in kwargs for k_ in ("w1_scale", "w2_scale", "block_shape", "soft_fp8"))
     fp8_repacked = bool(kwargs.pop("fp8_repacked", False))
     deterministic = bool(kwargs.pop("deterministic", True))
+    out_fp32 = y.dtype == torch.float32 and activations.dtype != torch.float32
     tune = kwargs.pop("tune", None)
     if fp8_form:
         names = ["w1_scale", "w2_scale", "block_shape", "soft_fp8", "microBatchSize", "experts_map"]
@@ -604,7 +606,8 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
     topK = dynamic_experts_per_act
     _chk(topk_ids.numel() == batch_size * topK, "topk_ids must be [batch_size, topK]")
     _chk(C.numel() >= topK * m1 * batch_size and C.dtype == x.dtype, "C must hold topK * 2I * batch_size elements")
-    _chk(y.shape == x.shape and y.dtype == x.dtype, "y must look like activations")
+    _chk(y.shape == x.shape and (y.dtype == x.dtype or (out_fp32 and deterministic)),
+         "y must look like activations (or be their float32 twin, with deterministic=True)")
     w1s = w2s = None
     if fp8_form:
         _chk(w1.element_size() == 1, "experts_weights_matrix1 must be a 1-byte (float8_e4m3fn) tensor.")
@@ -644,7 +647,7 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
                                         y.data_ptr(), _ptr(w1s), _ptr(w2s), code, int(fp8_repacked),
                                         int(vals["microBatchSize"]), mp, ml, _ptr(scratch),
                                         0 if scratch is None else scratch.numel() * 4, tune_arr, _status_ptr(x),
-                                        _stream(x)))
+                                        int(out_fp32), _stream(x)))
 
 
 # ---------------------------------------------------------------------------------------------------

@@ -42,7 +42,7 @@ def build(cfg, dev):
     return w1, w2, wg, g
 
 
-def run_case(cfg, T, w1, w2, wg, g, dev, iters, scales=False):
+def run_case(cfg, T, w1, w2, wg, g, dev, iters, scales=False, peak=6450.0):
     E, H, I, topk, fp8 = cfg["E"], cfg["H"], cfg["I"], cfg["topk"], cfg["fp8"]
     xs = [torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16) for _ in range(NBATCH)]
     logits = [(x.float() @ wg.float().t()).to(torch.bfloat16) for x in xs]
@@ -86,33 +86,87 @@ def run_case(cfg, T, w1, w2, wg, g, dev, iters, scales=False):
     e1.record()
     torch.cuda.synchronize()
     us_graph = e0.elapsed_time(e1) * 1e3 / (reps * NBATCH)
+    gbs = nbytes / us_graph / 1e3
     return {"T": T, "experts_hit": distinct, "us_graph": round(us_graph, 2), "us_eager": round(us_eager, 2),
-            "algorithmic_mb": round(nbytes / 1e6, 1), "gbs": round(nbytes / us_graph / 1e3, 1)}
+            "algorithmic_mb": round(nbytes / 1e6, 1), "gbs": round(gbs, 1), "frac_measured": round(gbs / peak, 3),
+            "frac_nominal_8TBs": round(gbs / 8000.0, 3)}
 
 
-def run(config="both", tokens=None, iters=24, dev=None, scales=False):
+def run(config="both", tokens=None, iters=24, dev=None, scales=False, peak=6450.0):
     dev = dev or torch.device("cuda")
     mlk.set_static_weights(True)
     out = {}
     for name in (["mixtral", "fine"] if config == "both" else [config]):
         cfg = CONFIGS[name]
         w1, w2, wg, g = build(cfg, dev)
-        out[name] = [run_case(cfg, T, w1, w2, wg, g, dev, iters, scales) for T in (tokens or cfg["tokens"])]
+        out[name] = [run_case(cfg, T, w1, w2, wg, g, dev, iters, scales, peak) for T in (tokens or cfg["tokens"])]
         del w1, w2
         torch.cuda.empty_cache()
     return out
 
 
+def _close(got, want):
+    want = want.float()
+    scale = max(1.0, float(want.pow(2).mean().sqrt()))
+    return bool(((got.float() - want).abs() <= 1e-2 * scale + 1e-2 * want.abs()).all())
+
+
+def _time_ep(call, iters, graphs, dev):
+    """us per call: eager (host launch overhead included) and, if asked for and possible, as CUDA-graph replays of
+    NBATCH calls; max over ranks."""
+    import torch.distributed as dist
+    for i in range(NBATCH):
+        call(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for it in range(iters):
+        call(it % NBATCH)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    out = {"us_eager": round(float(t[0]), 2)}
+    if graphs:
+        graph = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            call(0)
+            with torch.cuda.graph(graph, stream=s):
+                for i in range(NBATCH):
+                    call(i)
+        torch.cuda.current_stream().wait_stream(s)
+        graph.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        reps = max(1, iters // NBATCH)
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (reps * NBATCH)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out["us_graph"] = round(float(t[0]), 2)
+        del graph
+    return out
+
+
 def run_ep(config, rank, world, tokens=None, iters=24, dev=None, graphs=False):
-    """Expert-parallel layer time on `world` ranks (one process per GPU, torch.distributed initialised): every rank
-    holds E / world experts, tokens and router logits are replicated, each rank adds its experts' share
-    (parallel.fused_moe_ep_replicated: experts_map + NCCL all-reduce of the fp32 sums).  Timed with CUDA events
-    around `iters` eager layer calls over 8 activation batches after a barrier (us_eager, host launch overhead included)
-    and, with graphs=True, around replays of a CUDA graph holding the 8 calls and their all-reduces (us_graph); max over ranks.
-    Weights are random per rank (timing only; parity of this mode is covered by tests/test_gpu_multi.py)."""
+    """Expert-parallel layer on `world` ranks (one process per GPU, torch.distributed initialised), both modes of
+    parallel.py, on identical seeded weights: every rank generates the full expert weights from the same seed, keeps
+    its E / world experts and checks its output of one batch against the single-GPU layer it computes from the full
+    weights (parity_ok).
+      replicated   tokens and router logits on every rank, each rank adds its experts' share (experts_map), NCCL
+                   all-reduce of the shares; us_eager and us_graph
+      all_to_all   tokens sharded T / world per rank, NCCL all-to-all dispatch of the routed rows, local experts,
+                   all-to-all combine; as CUDA-graph replays as well (fixed-capacity exchange)
+    Times are CUDA events around the calls after a barrier, max over ranks."""
     import torch.distributed as dist
 
-    from muxi_native_layout_kernels_b200.parallel import fused_moe_ep_replicated
+    from muxi_native_layout_kernels_b200.parallel import fused_moe_ep, fused_moe_ep_replicated
     dev = dev or torch.device("cuda")
     mlk.set_static_weights(True)
     out = {}
@@ -121,54 +175,38 @@ def run_ep(config, rank, world, tokens=None, iters=24, dev=None, graphs=False):
         E, H, I, topk, fp8 = cfg["E"], cfg["H"], cfg["I"], cfg["topk"], cfg["fp8"]
         if E % world != 0:
             continue
-        local = dict(cfg, E=E // world, seed=cfg["seed"] * 100 + rank)
-        w1, w2, _, _ = build(local, dev)
-        g = torch.Generator(device=dev).manual_seed(cfg["seed"])          # same on every rank
-        wg = (torch.randn(E, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        w1, w2, wg, g = build(cfg, dev)                     # same seed, same bytes on every rank
+        el = E // world
+        w1l, w2l = w1[rank * el:(rank + 1) * el].contiguous(), w2[rank * el:(rank + 1) * el].contiguous()
         kw = dict(block_shape=[128, 128], soft_fp8=True, fp8_repacked=True) if fp8 else {}
+        kw_ep = dict(soft_fp8=True, fp8_repacked=True) if fp8 else {}
         rows = []
         for T in (tokens or cfg["tokens"]):
             xs = [torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16) for _ in range(NBATCH)]
             logits = [(x.float() @ wg.float().t()).to(torch.bfloat16) for x in xs]
-            for i in range(NBATCH):
-                fused_moe_ep_replicated(xs[i], w1, w2, logits[i], topk, True, **kw)
-            torch.cuda.synchronize()
-            dist.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for it in range(iters):
-                fused_moe_ep_replicated(xs[it % NBATCH], w1, w2, logits[it % NBATCH], topk, True, **kw)
-            e1.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            row = {"T": T, "us_eager": round(float(t[0]), 2), "experts_per_rank": E // world}
-            if graphs:
-                # the same 8 layer calls (all-reduce included) captured in one CUDA graph: no host launch overhead
-                graph = torch.cuda.CUDAGraph()
-                s = torch.cuda.Stream()
-                s.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(s):
-                    with torch.cuda.graph(graph, stream=s):
-                        for i in range(NBATCH):
-                            fused_moe_ep_replicated(xs[i], w1, w2, logits[i], topk, True, **kw)
-                torch.cuda.current_stream().wait_stream(s)
-                graph.replay()
-                torch.cuda.synchronize()
-                dist.barrier()
-                reps = max(1, iters // NBATCH)
-                e0.record()
-                for _ in range(reps):
-                    graph.replay()
-                e1.record()
-                torch.cuda.synchronize()
-                t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (reps * NBATCH)], device=dev, dtype=torch.float64)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                row["us_graph"] = round(float(t[0]), 2)
-                del graph
+            want = fused_moe(xs[0], w1, w2, logits[0], topk, True, **kw)
+            row = {"T": T, "experts_per_rank": el}
+            got = fused_moe_ep_replicated(xs[0], w1l, w2l, logits[0], topk, True, **kw)
+            rep = _time_ep(lambda i: fused_moe_ep_replicated(xs[i], w1l, w2l, logits[i], topk, True, **kw), iters, graphs, dev)
+            rep["parity_ok"] = _close(got, want)
+            row["replicated"] = rep
+            if T % world == 0:
+                tl = T // world
+                xl = [x[rank * tl:(rank + 1) * tl].contiguous() for x in xs]
+                ll = [l[rank * tl:(rank + 1) * tl].contiguous() for l in logits]
+                got = fused_moe_ep(xl[0], w1l, w2l, ll[0], topk, True, **kw_ep)
+                a2a = _time_ep(lambda i: fused_moe_ep(xl[i], w1l, w2l, ll[i], topk, True, **kw_ep), iters, graphs, dev)
+                a2a["parity_ok"] = _close(got, want[rank * tl:(rank + 1) * tl])
+                a2a["tokens_per_rank"] = tl
+                row["all_to_all"] = a2a
+            flags = torch.tensor([int(row["replicated"]["parity_ok"]), int(row.get("all_to_all", {}).get("parity_ok", True))], device=dev)
+            dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+            row["replicated"]["parity_ok"] = bool(flags[0])
+            if "all_to_all" in row:
+                row["all_to_all"]["parity_ok"] = bool(flags[1])
             rows.append(row)
         out[name] = rows
-        del w1, w2
+        del w1, w2, w1l, w2l
         torch.cuda.empty_cache()
     return out
 

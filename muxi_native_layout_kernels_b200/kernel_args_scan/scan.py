@@ -114,6 +114,9 @@ def candidates(kind, m, n, k):
             # KernelId 3: tcgen05 pipeline for e4m3 weights, (raw ring stages, cluster size)
             cands += [(256, 3, st, ck) for st in (2, 3, 4, 6, 8) for ck in range(1, 9)
                       if (m // 128) * ck <= SMS * min(4, max(1, (227 * 1024) // (max(st * 8192, 8192) + 4096 + 2048)))]
+            # KernelId 4: e4m3 weights undecoded into the 8-bit MMA, (k per stage as BLOCK_DIM_X, ring stages, cluster size)
+            cands += [(bk, 4, st, ck) for bk in (64, 128) for st in (2, 3, 4, 6) for ck in range(1, 9)
+                      if k % bk == 0 and ck <= k // bk and (m // 128) * ck <= SMS * min(5, (200 * 1024) // (st * (128 * bk + bk * 32) + 2048))]
         return cands
     # kernelId 1 / 3 / 4: the warp-level kernel with 8 / 4 / 2 warps per CTA
     cands = [(kid, rg, wm, sk) for kid, rg, wm, sk in itertools.product([1, 3, 4], [1, 2], [1, 2, 4, 8], [1, 2, 4])
@@ -123,6 +126,12 @@ def candidates(kind, m, n, k):
         np_ = 16 if n <= 16 else (32 if n <= 32 else 64)
         cands += [(2, 1, st, ck) for st in (2, 3, 4, 6, 8) for ck in range(1, 9)
                   if (m // 128) * ck <= SMS * min(4, max(1, (227 * 1024) // (max(st * 8192, np_ * 512) + 2 * np_ * 128 + 2048)))]
+    if kind == "a_fp8" and n <= 64:
+        # kernelId 9: e4m3 weights undecoded into the 8-bit MMA: (k per stage, ring stages, cluster size), one wave of CTAs
+        np_ = 16 if n <= 16 else (32 if n <= 32 else 64)
+        cands += [(9, bk, st, ck) for bk in (64, 128) for st in (2, 3, 4, 6) for ck in range(1, 9)
+                  if k % bk == 0 and ck <= k // bk and st * (128 * bk + (bk // 64) * np_ * 128) <= 200 * 1024 and
+                  (m // 128) * ck <= SMS * min(5, (200 * 1024) // (st * (128 * bk + (bk // 64) * np_ * 128) + 2048))]
     if kind == "a" and n <= 4:
         cands += [(kid, rg, 0, sk) for kid, rg, sk in itertools.product([5, 6, 7], [1, 2], [1, 2, 4]) if m % (16 * rg) == 0]
     if kind in ("a", "conc", "abc") and n <= 64 and (kind == "a" or n % 16 == 0):

@@ -85,6 +85,7 @@ def fused_moe(
     deterministic: bool = True,
     tune=None,
     gate_weight: Optional[torch.Tensor] = None,
+    out_dtype: Optional[torch.dtype] = None,
 ) -> torch.Tensor:
     # gate_weight [E, H] (extension): the router GEMM runs fused with the routing kernel and `gating_output` is not
     # read (pass None)
@@ -137,7 +138,14 @@ def fused_moe(
     # holds the expert work list.  Nothing in it has to be zero.
     C = torch.empty(topk * m1 * B, dtype=hidden_states.dtype, device=dev)
     # the fixed-order combine writes every element of y; the atomic variant accumulates into zeros
-    y = torch.empty_like(hidden_states) if deterministic else torch.zeros_like(hidden_states)
+    # out_dtype=torch.float32 (extension, deterministic only): the sums over this rank's experts un-rounded, for callers
+    # that add the shares of several ranks before the one rounding
+    if out_dtype is not None and out_dtype != hidden_states.dtype:
+        if out_dtype != torch.float32 or not deterministic:
+            raise ValueError("out_dtype must be the activation dtype or torch.float32 (with deterministic=True)")
+        y = torch.empty(hidden_states.shape, dtype=torch.float32, device=dev)
+    else:
+        y = torch.empty_like(hidden_states) if deterministic else torch.zeros_like(hidden_states)
 
     if tune is None:
         # with an experts_map (expert parallelism) the work per local expert is that of the full layer: the row of

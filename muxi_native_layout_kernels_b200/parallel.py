@@ -60,12 +60,13 @@ class DispatchPlan:
     send_slot: torch.Tensor      # int32 [n_send]: flat slot (token*topk + j) of every row sent, grouped by destination
     send_token: torch.Tensor     # int32 [n_send]: source token of every row sent
     send_expert: torch.Tensor    # int32 [n_send]: expert id local to the destination rank
-    send_counts: List[int]       # rows sent to each rank
+    send_counts: torch.Tensor    # int64 [world]: rows sent to each rank (same device as the routing)
     slot_to_row: torch.Tensor    # int32 [T*topk]: position of slot in the send order (= in the returned rows)
 
 
 def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int) -> DispatchPlan:
-    """Groups the routed slots of this rank by destination rank (stable: ascending slot inside a destination)."""
+    """Groups the routed slots of this rank by destination rank (stable: ascending slot inside a destination).
+    Pure tensor arithmetic on the device of ``topk_ids``: nothing is copied to the host here."""
     T, topk = topk_ids.shape
     flat = topk_ids.reshape(-1).to(torch.int64)
     dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
@@ -77,23 +78,50 @@ def plan_dispatch(topk_ids: torch.Tensor, experts_per_rank: int, world: int) -> 
         send_slot=order.to(torch.int32),
         send_token=torch.div(order, topk, rounding_mode="floor").to(torch.int32),
         send_expert=(flat[order] - dest[order] * experts_per_rank).to(torch.int32),
-        send_counts=[int(c) for c in counts.tolist()],      # host copy: all_to_all_single needs split sizes on the host
+        send_counts=counts,
         slot_to_row=slot_to_row.to(torch.int32),
     )
 
 
-def exchange_counts(send_counts: List[int], device, group=None) -> List[int]:
+def exchange_counts(send_counts: torch.Tensor, group=None):
+    """All-to-all of the per-destination row counts, then ONE device -> host copy of both count vectors (the split
+    sizes of the row exchange have to be host integers).  Returns (send_counts, recv_counts) as lists."""
     world = dist.get_world_size(group)
-    s = torch.tensor(send_counts, dtype=torch.int64, device=device)
-    r = torch.empty(world, dtype=torch.int64, device=device)
+    s = send_counts.to(torch.int64)
+    r = torch.empty(world, dtype=torch.int64, device=s.device)
     dist.all_to_all_single(r, s, group=group)
-    return [int(v) for v in r.tolist()]
+    both = torch.cat([s, r]).tolist()
+    return [int(v) for v in both[:world]], [int(v) for v in both[world:]]
 
 
 def _a2a(send: torch.Tensor, send_counts: List[int], recv_counts: List[int], group=None) -> torch.Tensor:
     recv = torch.empty((sum(recv_counts),) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
     dist.all_to_all_single(recv, send.contiguous(), output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
     return recv
+
+
+# every routed row travels with its routing: [H activations | local expert id (int32) | routing weight (fp32)], padded
+# to a multiple of 16 bytes, so that the dispatch is one all-to-all
+_HEADER_BYTES = 16
+
+
+def pack_rows(rows: torch.Tensor, expert: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """[R, H] 16-bit rows + int32 expert ids + weights -> uint8 [R, 2 H + 16]."""
+    R, H = rows.shape
+    buf = torch.empty(R, 2 * H + _HEADER_BYTES, dtype=torch.uint8, device=rows.device)
+    buf[:, :2 * H] = rows.contiguous().view(torch.uint8).view(R, 2 * H)
+    head = torch.zeros(R, 4, dtype=torch.int32, device=rows.device)
+    head[:, 0] = expert
+    head[:, 1] = weight.float().view(torch.int32)
+    buf[:, 2 * H:] = head.view(torch.uint8).view(R, _HEADER_BYTES)
+    return buf
+
+
+def unpack_rows(buf: torch.Tensor, H: int, dtype: torch.dtype):
+    R = buf.shape[0]
+    rows = buf[:, :2 * H].contiguous().view(dtype).view(R, H)
+    head = buf[:, 2 * H:].contiguous().view(torch.int32).view(R, 4)
+    return rows, head[:, 0].contiguous(), head[:, 1].contiguous().view(torch.float32)
 
 
 def moe_exchange(
@@ -103,23 +131,24 @@ def moe_exchange(
     combine_fn: Callable[[torch.Tensor, torch.Tensor, int, int], torch.Tensor],
     group=None,
 ) -> torch.Tensor:
-    """Dispatch -> local expert compute -> combine for this rank's tokens.
+    """Dispatch -> local expert compute -> combine for this rank's tokens: two all-to-alls of rows (one packed buffer
+    each way) after one small all-to-all of the counts and one device -> host copy.
 
-    experts_fn(rows [R,H], local_expert [R] int32, weight [R]) -> weighted outputs [R,H] (same dtype as rows)
+    experts_fn(rows [R,H], local_expert [R] int32, weight [R] fp32) -> weighted outputs [R,H] in fp32
     gather_fn(x [T,H], token_index [R] int32) -> rows [R,H]
-    combine_fn(rows [R,H], slot_to_row [T*topk] int32, T, topk) -> y [T,H]
+    combine_fn(rows [R,H] fp32, slot_to_row [T*topk] int32, T, topk) -> y [T,H] in x.dtype
     """
     world = dist.get_world_size(group)
     T, topk = topk_ids.shape
+    H = x.shape[1]
     plan = plan_dispatch(topk_ids, experts_per_rank, world)
-    recv_counts = exchange_counts(plan.send_counts, x.device, group)
+    send_counts, recv_counts = exchange_counts(plan.send_counts, group)
     rows = gather_fn(x, plan.send_token)
-    w_send = topk_weights.reshape(-1)[plan.send_slot.long()].contiguous()
-    rows_in = _a2a(rows, plan.send_counts, recv_counts, group)
-    e_in = _a2a(plan.send_expert, plan.send_counts, recv_counts, group)
-    w_in = _a2a(w_send, plan.send_counts, recv_counts, group)
+    w_send = topk_weights.reshape(-1)[plan.send_slot.long()]
+    packed_in = _a2a(pack_rows(rows, plan.send_expert, w_send), send_counts, recv_counts, group)
+    rows_in, e_in, w_in = unpack_rows(packed_in, H, x.dtype)
     out_rows = experts_fn(rows_in, e_in, w_in)
-    back = _a2a(out_rows, recv_counts, plan.send_counts, group)
+    back = _a2a(out_rows, recv_counts, send_counts, group)
     return combine_fn(back, plan.slot_to_row, T, topk)
 
 
@@ -135,14 +164,32 @@ def _gpu_gather(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def _gpu_combine(rows: torch.Tensor, slot_to_row: torch.Tensor, T: int, topk: int) -> torch.Tensor:
+def _gpu_combine(rows: torch.Tensor, slot_to_row: torch.Tensor, T: int, topk: int, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """y[t] = round(sum_j rows[slot_to_row[t * topk + j]]), j ascending, fp32 rows: the single-GPU combine."""
     from ._lib import check, lib
     H = rows.shape[1]
-    y = torch.empty((T, H), dtype=rows.dtype, device=rows.device)
-    code = 1 if rows.dtype == torch.float16 else 0
+    y = torch.empty((T, H), dtype=out_dtype, device=rows.device)
+    code = (1 if out_dtype == torch.float16 else 0) + (2 if rows.dtype == torch.float32 else 0)
     check(lib.mlk_moe_unpermute_sum(rows.data_ptr() if rows.numel() else None, slot_to_row.data_ptr(), y.data_ptr(), T,
                                     topk, H, rows.shape[0], code, torch.cuda.current_stream(rows.device).cuda_stream))
     return y
+
+
+def _expert_map(E: int, e_local: int, rank: int, device) -> torch.Tensor:
+    emap = torch.full((E,), -1, dtype=torch.int32, device=device)
+    emap[rank * e_local:(rank + 1) * e_local] = torch.arange(e_local, dtype=torch.int32, device=device)
+    return emap
+
+
+_MAPS = {}
+
+
+def _cached_expert_map(E: int, e_local: int, rank: int, device) -> torch.Tensor:
+    key = (E, e_local, rank, str(device))
+    m = _MAPS.get(key)
+    if m is None:
+        m = _MAPS[key] = _expert_map(E, e_local, rank, device)
+    return m
 
 
 def fused_moe_ep(
@@ -150,17 +197,45 @@ def fused_moe_ep(
     topk: int, renormalize: bool, group=None, score_func: str = "softmax", num_expert_group: int = 1,
     topk_group: int = 1, gating_bias: Optional[torch.Tensor] = None, w1_scale: Optional[torch.Tensor] = None,
     w2_scale: Optional[torch.Tensor] = None, soft_fp8: bool = False, fp8_repacked: bool = False,
+    exchange: str = "all_to_all",
 ) -> torch.Tensor:
     """Expert-parallel fused MoE for this rank's tokens ``hidden_states [T_local, H]``; ``w1_local [E/G, 2I, H]`` and
-    ``w2_local [E/G, H, I]`` hold this rank's experts in layout A; ``gating_output [T_local, E]`` covers all experts."""
+    ``w2_local [E/G, H, I]`` hold this rank's experts in layout A; ``gating_output [T_local, E]`` covers all experts.
+
+    exchange="all_to_all": the router runs locally, every routed (token, slot) row travels to the rank that owns its
+      expert with exactly the rows that are routed there (NCCL all-to-all with split sizes, which costs one
+      device -> host copy of the counts per call: not capturable in a CUDA graph), is weighted there and comes back
+      in fp32; the source rank adds each token's top-k rows in slot order and rounds once -- the arithmetic of the
+      single-GPU layer.
+    exchange="gather": static shapes, capturable.  Tokens and logits are all-gathered (every rank needs T_local equal),
+      every rank computes the fp32 share of its experts for all tokens (``experts_map``) and a reduce-scatter hands
+      each rank the sum for its own tokens.  With top-k of the order of the rank count nearly every token visits
+      every rank anyway, and a fixed-capacity all-to-all would move the same bytes."""
     from . import ext
     T, H = hidden_states.shape
     E = gating_output.shape[1]
     world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
     e_local = w1_local.shape[0]
     if e_local * world != E:
         raise ValueError(f"{E} experts over {world} ranks need {E // max(world, 1)} local experts, got {e_local}")
     dev = hidden_states.device
+    if exchange == "gather":
+        from .muxi_moe_planC import fused_moe
+        x_all = torch.empty((world * T, H), dtype=hidden_states.dtype, device=dev)
+        l_all = torch.empty((world * T, E), dtype=gating_output.dtype, device=dev)
+        dist.all_gather_into_tensor(x_all, hidden_states.contiguous(), group=group)
+        dist.all_gather_into_tensor(l_all, gating_output.contiguous(), group=group)
+        kw = dict(w1_scale=w1_scale, w2_scale=w2_scale, block_shape=[128, 128], soft_fp8=True, fp8_repacked=fp8_repacked) if soft_fp8 else {}
+        share = fused_moe(x_all, w1_local, w2_local, l_all, topk, renormalize, use_grouped_topk=num_expert_group != 1,
+                          num_expert_group=num_expert_group, topk_group=topk_group, gating_bias=gating_bias,
+                          score_func=score_func, experts_map=_cached_expert_map(E, e_local, rank, dev),
+                          out_dtype=torch.float32, **kw)
+        mine = torch.empty((T, H), dtype=torch.float32, device=dev)
+        dist.reduce_scatter_tensor(mine, share, group=group)
+        return mine.to(hidden_states.dtype)
+    if exchange != "all_to_all":
+        raise ValueError("exchange must be 'all_to_all' or 'gather'")
     ids = torch.empty(T, topk, dtype=torch.int32, device=dev)
     wts = torch.empty(T, topk, dtype=hidden_states.dtype, device=dev)
     ext.fused_routing_gate(gating_output, 0 if score_func == "softmax" else 1, T, H, num_expert_group, topk_group, ids,
@@ -168,40 +243,48 @@ def fused_moe_ep(
 
     def experts_fn(rows, local_expert, weight):
         R = rows.shape[0]
-        y = torch.zeros_like(rows)
+        y = torch.zeros((R, H), dtype=torch.float32, device=dev)
         if R == 0:
             return y
         m1 = w1_local.shape[1]
         n_pad = R + e_local * 15
-        sorted_ids = torch.full((n_pad,), R, dtype=torch.int32, device=dev)
+        sorted_ids = torch.empty((n_pad,), dtype=torch.int32, device=dev)
         cumsum = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
         nblk = torch.empty(1, dtype=torch.int32, device=dev)
         blk = torch.empty((n_pad + 15) // 16, dtype=torch.int32, device=dev)
         C = torch.empty(m1 * R, dtype=rows.dtype, device=dev)
         args = (w1_local, w2_local, rows, R, e_local, 1, local_expert.view(R, 1).contiguous(),
-                weight.view(R, 1).contiguous(), sorted_ids, cumsum, nblk, blk, C, y)
+                weight.to(rows.dtype).view(R, 1).contiguous(), sorted_ids, cumsum, nblk, blk, C, y)
         if soft_fp8:
             ext.fused_experts_compute(*args, w1_scale, w2_scale, [128, 128], True, fp8_repacked=fp8_repacked)
         else:
             ext.fused_experts_compute(*args)
         return y
 
-    return moe_exchange(hidden_states, ids, wts, e_local, experts_fn, _gpu_gather, _gpu_combine, group)
+    return moe_exchange(hidden_states, ids, wts, e_local, experts_fn, _gpu_gather,
+                        lambda rows, s2r, T_, k_: _gpu_combine(rows, s2r, T_, k_, hidden_states.dtype), group)
 
 
-def fused_moe_ep_replicated(hidden_states, w1_local, w2_local, gating_output, topk, renormalize, group=None, **kw):
+def fused_moe_ep_replicated(hidden_states, w1_local, w2_local, gating_output, topk, renormalize, group=None,
+                            reduce_dtype: torch.dtype = torch.float32, **kw):
     """Tokens replicated on every rank; each rank adds its experts' share (``experts_map``) and the shares are summed
-    with an all-reduce.  This is the expert-parallel mode the reference's ``experts_map`` hook was made for."""
+    with an all-reduce.  This is the expert-parallel mode the reference's ``experts_map`` hook was made for
+    (csrc/moe_kernels/moe_align_tokens.h:44-49).  The shares leave the layer as un-rounded fp32 sums and are reduced in
+    fp32 (one rounding at the end, as on one GPU); ``reduce_dtype=torch.bfloat16`` halves the all-reduce traffic at
+    the price of one rounding per rank."""
     from .muxi_moe_planC import fused_moe
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     E = gating_output.shape[1]
     e_local = w1_local.shape[0]
-    emap = torch.full((E,), -1, dtype=torch.int32, device=hidden_states.device)
-    emap[rank * e_local:(rank + 1) * e_local] = torch.arange(e_local, dtype=torch.int32, device=hidden_states.device)
-    y = fused_moe(hidden_states, w1_local, w2_local, gating_output, topk, renormalize, experts_map=emap, **kw)
-    if world > 1:
-        y32 = y.float()
-        dist.all_reduce(y32, group=group)
-        y = y32.to(hidden_states.dtype)
-    return y
+    emap = _cached_expert_map(E, e_local, rank, hidden_states.device)
+    if world == 1:
+        return fused_moe(hidden_states, w1_local, w2_local, gating_output, topk, renormalize, experts_map=emap, **kw)
+    if reduce_dtype == torch.float32:
+        share = fused_moe(hidden_states, w1_local, w2_local, gating_output, topk, renormalize, experts_map=emap,
+                          out_dtype=torch.float32, **kw)
+        dist.all_reduce(share, group=group)
+        return share.to(hidden_states.dtype)
+    share = fused_moe(hidden_states, w1_local, w2_local, gating_output, topk, renormalize, experts_map=emap, **kw)
+    dist.all_reduce(share, group=group)
+    return share

@@ -47,11 +47,11 @@ def _call(static, x, w1, w2, ids, wts, E, topk, H, I, emap=None, tune=None):
               None, None, 0, 0, 16, None if emap is None else emap.data_ptr(), 0 if emap is None else emap.numel())
     tune_arr = None if tune is None else (ctypes.c_int32 * 6)(*tune)
     if static:
-        status = lib.mlk_fused_experts_compute_static(*common, tune_arr, status_word.data_ptr(), stream)
+        status = lib.mlk_fused_experts_compute_static(*common, tune_arr, status_word.data_ptr(), 0, stream)
     else:
         scratch = torch.empty(T * topk * H, dtype=torch.float32, device=dev)
         status = lib.mlk_fused_experts_compute(*common, scratch.data_ptr(), scratch.numel() * 4, tune_arr,
-                                               status_word.data_ptr(), stream)
+                                               status_word.data_ptr(), 0, stream)
     torch.cuda.synchronize()
     assert int(status_word.item()) == 0
     return status, y
@@ -110,6 +110,6 @@ def test_static_scratch_entry_point_rejects_oversized_problem():
     one = ctypes.c_void_p(256)    # never dereferenced: the size check comes before any launch
     # 4096 tokens x top-8 x 2048 hidden = 64 Mi floats > 2 Mi
     st = lib.mlk_fused_experts_compute_static(one, one, one, 4096, 128, 8, 2048, 768, one, one, one, one, one, one, one,
-                                              one, None, None, 0, 0, 16, None, 0, None, None, None)
+                                              one, None, None, 0, 0, 16, None, 0, None, None, 0, None)
     assert st == 1
     assert b"exceeds the built-in scratch" in lib.mlk_last_error()
