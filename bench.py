@@ -68,6 +68,16 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
+def measured_tensor_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"])
+        except Exception:
+            pass
+    return 1590.0
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
 
@@ -384,11 +394,16 @@ def run_ours(args):
     if not args.no_per_config:
         from muxi_native_layout_kernels_b200.kernel_args_scan import dense_bench
         try:
-            per_config = dense_bench.run(dev, peak, rank, world)
+            per_config = dense_bench.run(dev, peak, rank, world, tensor_peak=measured_tensor_peak())
             if world > 1:
                 t = torch.tensor([r["us"] for r in per_config], device=dev, dtype=torch.float64)
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 for r, us in zip(per_config, t.tolist()):
+                    if r["config"] == "F3":
+                        tf = 2.0 * r["N"] * world * r["tokens"] * r["K"] / us / 1e6
+                        r.update(N=r["N"] * world, us=round(us, 2), tflops=round(tf, 1),
+                                 frac_measured_tensor=round(tf / world / measured_tensor_peak(), 3))
+                        continue
                     # whole-job figures: all ranks' bytes over the slowest rank's time; fractions per GPU
                     wb = 1 if r["dtype"] == "e4m3" else 2
                     nbytes = r["N"] * world * r["K"] * wb + 2 * r["tokens"] * (r["K"] + r["N"] * world)
@@ -448,9 +463,10 @@ def run_ours(args):
             line["moe_layer_us"] = moe_bench.run("both", None, 24, dev, peak=peak)
         if world > 1 and not args.no_moe:
             line["moe_layer_us"] = moe_ep
-            line["moe_layer_mode"] = (f"expert parallel over {world} GPUs, E/{world} experts per rank, both modes of parallel.py on identical "
-                                      "seeded weights: replicated (tokens on every rank, experts_map, NCCL all-reduce of the shares) and "
-                                      "all_to_all (tokens sharded, NCCL all-to-all dispatch and combine); parity_ok = every rank's output "
+            line["moe_layer_mode"] = (f"expert parallel over {world} GPUs, E/{world} experts per rank, the modes of parallel.py on identical "
+                                      "seeded weights: replicated (tokens on every rank, experts_map, NCCL all-reduce of the fp32 shares), "
+                                      "all_to_all (tokens sharded, NCCL all-to-all dispatch of the routed rows and combine of fp32 rows) and "
+                                      "gather_reduce_scatter (tokens sharded, all-gather + local share + reduce-scatter, static shapes); parity_ok = every rank's output "
                                       "of one batch equals the single-GPU layer within |d| <= 1e-2 max(1, rms) + 1e-2 |want|; "
                                       "us_eager = eager calls (host launch overhead included), us_graph = CUDA-graph replays; max over ranks")
         if world == 1 and not args.no_cpu:

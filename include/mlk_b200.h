@@ -187,6 +187,14 @@ int mlk_gemm_layoutA_soft_fp8_wapper(const void* A, const float* A_scale, const 
 int mlk_gemm_layoutA_soft_fp8(const void* A, const float* A_scale, const void* B, void* C, int m, int n, int k,
                               float alpha, float beta, const void* bias, int fp8_order, const mlk_aux* aux,
                               mlk_stream_t s);
+/* Many-token GEMM on the same prepacked weights (any n; the prefill-side consumer of layout A): 16-bit weights with more
+ * than 64 tokens run on a tcgen05 tile kernel with 128 x 128 or 128 x 256 (weight rows x tokens) tiles and the whole k
+ * range per CTA (kernelId 10 of mlk_gemm_layoutA_wapper: kernelParam1 = tokens per tile, kernelParam2 = ring stages);
+ * e4m3 weights (scale_matrix NULL = unit scales) and calls with few tokens run the narrow kernels 64 tokens at a time.
+ * Reference: muxi_hgemm_layoutA, csrc/muxi_hgemm_layoutA.cu:12-217 (beta accepted and ignored; the reference adds
+ * beta * C of its own freshly allocated C). */
+int mlk_muxi_hgemm_layoutA(const void* A, const float* scale_matrix, const void* B, void* C, int m, int n, int k, int dtype,
+                           float alpha, float beta, const void* bias, int fp8_order, const mlk_aux* aux, mlk_stream_t s);
 /* A layout A, B layout B, C row-major.  Reference: gemm_layoutAB_ContinuousC_wapper,
  * csrc/gemm_layout_ab_continuous_c.cu:982; table-driven form :1051. */
 int mlk_gemm_layoutAB_ContinuousC_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype,

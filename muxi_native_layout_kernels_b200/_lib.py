@@ -40,6 +40,8 @@ PROTOTYPES = {
                                                  c_int, c_int, c_int, c_vp, c_int, c_vp, c_vp]),
     "mlk_gemm_layoutA_soft_fp8": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_int,
                                           c_vp, c_vp]),
+    "mlk_muxi_hgemm_layoutA": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_vp, c_int, c_vp,
+                                       c_vp]),
     "mlk_gemm_layoutAB_ContinuousC_wapper": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32,
                                                      c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp]),
     "mlk_gemm_layoutAB_ContinuousC": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_f32, c_f32, c_vp,

@@ -28,6 +28,7 @@ SOURCES = [
     "dense_umma.cu",
     "dense_umma_f8.cu",
     "dense_umma_f8n.cu",
+    "hgemm_umma.cu",
     "prepack.cu",
     "moe_router.cu",
     "moe_align.cu",

@@ -71,6 +71,26 @@ int check_gemm_shape(int m, int n, int k) {
     return kOk;
 }
 
+int gemm_table(int table, int variant_x, int variant_c, const void* A, const float* scale, const void* B, void* C,
+               int m, int n, int k, int dtype, float alpha, const void* bias, int fp8_order, cudaStream_t s,
+               const mlk_aux* aux);
+
+// The many-token tile kernel gives every CTA the whole k range, so it wants about as many (128-row, 128-token) tiles as
+// there are SMs.  With fewer tiles and at most 256 tokens the narrow kernels (k split over clusters), 64 tokens per
+// launch, finish sooner although they stream the weights once per launch.
+bool few_tiles_for_hgemm(int m, int n) { return n <= 256 && (long long)(m / 128) * ((n + 127) / 128) * 10 < 7LL * sm_count(); }
+
+int gemm_in_token_chunks(int table, const void* A, const float* scale, const void* B, void* C, int m, int n, int k, int dtype,
+                         float alpha, const void* bias, int fp8_order, cudaStream_t s, const mlk_aux* aux) {
+    for (int n0 = 0; n0 < n; n0 += 64) {
+        const int nn = n - n0 < 64 ? n - n0 : 64;
+        const void* Bc = reinterpret_cast<const uint8_t*>(B) + (size_t)n0 * k * 2;
+        void* Cc = reinterpret_cast<uint8_t*>(C) + (size_t)n0 * m * 2;
+        if (int st = gemm_table(table, 0, 0, A, scale, Bc, Cc, m, nn, k, dtype, alpha, bias, fp8_order, s, aux)) return st;
+    }
+    return kOk;
+}
+
 int gemm_common(int variant_x, int variant_c, const void* A, const float* scale, const void* B, void* C, int m, int n,
                 int k, int dtype, float alpha, int p1, int p2, int p3, int kernelId, const void* bias, int fp8_order,
                 cudaStream_t s, const mlk_aux* aux = nullptr) {
@@ -82,6 +102,14 @@ int gemm_common(int variant_x, int variant_c, const void* A, const float* scale,
     p.A = A; p.X = B; p.C = C; p.bias = bias; p.scale = scale;
     p.m = m; p.n = n; p.k = k; p.alpha = alpha;
     p.x_layout = variant_x; p.c_layout = variant_c; p.fp8_order = fp8_order;
+    if (kernelId == 10) {
+        // many-token tile kernel (hgemm_umma.cu): kernelParam1 = tokens per tile (128, 256; 0 = automatic), kernelParam2 =
+        // ring stages (2, 3, 4, 6; 0 = automatic)
+        if (wt == kE4M3) return fail(kUnsupported, "gemm: kernelId 10 takes 16-bit weights");
+        if (variant_x != 0 || variant_c != 0) return fail(kUnsupported, "gemm: kernelId 10 needs row-major B and C");
+        if (p1 <= 1 && few_tiles_for_hgemm(m, n)) return gemm_in_token_chunks(kTableGemmLayoutA, A, nullptr, B, C, m, n, k, dtype, alpha, bias, 0, s, aux);
+        return launch_hgemm_umma(wt, p, p1 == 1 ? 0 : p1, p2 == 1 ? 0 : p2, aux ? aux->status : nullptr, s);
+    }
     if (kernelId == 9) {
         // e4m3 weights undecoded into tcgen05.mma.kind::f8f6f4: kernelParam1 = k per stage (64, or 128; 0 / 1 = 64),
         // kernelParam2 = ring stages, kernelParam3 = cluster size
@@ -119,7 +147,7 @@ int gemm_common(int variant_x, int variant_c, const void* A, const float* scale,
 
 int gemm_table(int table, int variant_x, int variant_c, const void* A, const float* scale, const void* B, void* C,
                int m, int n, int k, int dtype, float alpha, const void* bias, int fp8_order, cudaStream_t s,
-               const mlk_aux* aux = nullptr) {
+               const mlk_aux* aux) {
     clear_error();
     if (int st = check_gemm_shape(m, n, k)) return st;
     TuneArgs t = global_table(table).get(m, n, k, nullptr);
@@ -139,13 +167,16 @@ int gemm_table(int table, int variant_x, int variant_c, const void* A, const flo
                      t.d <= k / (t.b == 128 ? 128 : 64);
     const bool ok5 = t.a >= 5 && t.a <= 7 && n <= 4 && variant_x == 0 && variant_c == 0 && dtype != MLK_E4M3 &&
                      (t.b == 1 || t.b == 2) && (t.d == 1 || t.d == 2 || t.d == 4 || t.d == 8) && m % (16 * t.b) == 0;
-    if (!ok1 && !ok2 && !ok5 && !ok9) t = default_args(table, m, n, k);
+    const bool ok10 = t.a == 10 && variant_x == 0 && variant_c == 0 && dtype != MLK_E4M3 && (t.b == 0 || t.b == 128 || t.b == 256) &&
+                      (t.c == 0 || t.c == 2 || t.c == 3 || t.c == 4 || t.c == 6) &&
+                      (t.c == 0 || (size_t)t.c * (16384 + (t.b == 128 ? 128 : 256) * 128) + 1024 <= 227 * 1024);
+    if (!ok1 && !ok2 && !ok5 && !ok9 && !ok10) t = default_args(table, m, n, k);
     // the native-e4m3 kernel needs the caller's scratch and has no block scales; otherwise the decode pipeline runs
     // (kernelParam2 = raw ring stages and kernelParam3 = cluster size mean the same there)
     if (t.a == 9 && !have_f8n) t.a = 2;
     // the tcgen05 kernel reads through tensor maps, which want 16-byte aligned bases; e4m3 activations in layout B
     // have no tcgen05 variant
-    if ((t.a == 2 || t.a == 9) && ((((uintptr_t)A | (uintptr_t)B) & 15) != 0 || (variant_x != 0 && dtype == MLK_E4M3)))
+    if ((t.a == 2 || t.a == 9 || t.a == 10) && ((((uintptr_t)A | (uintptr_t)C | (uintptr_t)B) & 15) != 0 || (variant_x != 0 && dtype == MLK_E4M3)))
         t = warp_level_default_args(table, m, n, k);
     return gemm_common(variant_x, variant_c, A, scale, B, C, m, n, k, dtype, alpha, t.b, t.c, t.d, t.a, bias,
                        fp8_order, s, aux);
@@ -318,6 +349,25 @@ int mlk_gemm_layoutA_soft_fp8(const void* A, const float* A_scale, const void* B
     return gemm_table(kTableGemmLayoutASoftFp8, 0, 0, A, A_scale, B, C, m, n, k, MLK_E4M3, alpha, bias, fp8_order,
                       (cudaStream_t)s, aux);
 }
+int mlk_muxi_hgemm_layoutA(const void* A, const float* scale_matrix, const void* B, void* C, int m, int n, int k, int dtype,
+                           float alpha, float, const void* bias, int fp8_order, const mlk_aux* aux, mlk_stream_t s) {
+    clear_error();
+    const int wt = wt_of(dtype);
+    if (wt < 0) return fail(kInvalidArg, "Unsupported data type code %d", dtype);
+    if (m <= 0 || n <= 0 || k <= 0) return fail(kInvalidArg, "muxi_hgemm_layoutA: m, n, k must be positive");
+    if (m % 128 != 0) return fail(kInvalidArg, "m must be a multiple of 128 (m=%d)", m);
+    if (k % 128 != 0) return fail(kInvalidArg, "k must be a multiple of 128 (k=%d)", k);
+    if (wt != kE4M3 && scale_matrix != nullptr) return fail(kInvalidArg, "muxi_hgemm_layoutA: scale_matrix needs 1-byte weights");
+    if (wt != kE4M3 && n > 64 && !few_tiles_for_hgemm(m, n)) {
+        DenseParams p{};
+        p.A = A; p.X = B; p.C = C; p.bias = bias; p.m = m; p.n = n; p.k = k; p.alpha = alpha;
+        return launch_hgemm_umma(wt, p, 0, 0, aux ? aux->status : nullptr, (cudaStream_t)s);
+    }
+    // e4m3 weights, and 16-bit calls with few tokens or few tiles: the narrow kernels, 64 tokens per launch
+    return gemm_in_token_chunks(wt == kE4M3 ? kTableGemmLayoutASoftFp8 : kTableGemmLayoutA, A, wt == kE4M3 ? scale_matrix : nullptr, B,
+                                C, m, n, k, dtype, alpha, bias, wt == kE4M3 ? fp8_order : 0, (cudaStream_t)s, aux);
+}
+
 int mlk_gemm_layoutAB_ContinuousC_wapper(const void* A, const void* B, void* C, int m, int n, int k, int dtype,
                                          float alpha, float, int p1, int p2, int p3, int kernelId, const void* bias,
                                          const mlk_aux* aux, mlk_stream_t s) {

@@ -46,6 +46,8 @@ long long f8n_scratch_bytes(int n, int k);
 int f8n_max_k();   // longest row the activation split handles
 int launch_dense_umma_f8n(const DenseParams& p, int bk, int stages, int cluster_k, void* scratch, long long scratch_bytes,
                           int* status, cudaStream_t stream);
+// many-token GEMM on the tcgen05 tile kernel (hgemm_umma.cu): nt = tokens per tile (128, 256; 0 = automatic), 16-bit weights
+int launch_hgemm_umma(int wt, const DenseParams& p, int nt, int stages, int* status, cudaStream_t stream);
 int launch_gemv_simt(int wt, const DenseParams& p, int rows_per_warp_log2, cudaStream_t stream);
 
 }  // namespace mlk

@@ -61,6 +61,11 @@ TuneArgs default_args(int table, int m, int n, int k) {
         while (sk < 8 && ctas * sk < target_ctas && (k / 32) / (8 * sk * 2) >= 4) sk *= 2;
         return TuneArgs{256, 1, rg, sk};
     }
+    if (table == kTableGemmLayoutA && m % 128 == 0 && k % 64 == 0 && n > 64) {
+        // more tokens than the narrow tcgen05 tile holds: the many-token tile kernel (kernelId 10), tile and ring chosen
+        // by the launcher
+        return TuneArgs{10, 0, 0, 0};
+    }
     if (table == kTableGemmLayoutASoftFp8 && m % 128 == 0 && k % 128 == 0 && n >= 1 && n <= 64) {
         // e4m3 weights straight into the 8-bit tensor-core MMA (kernelId 9; the entry point falls back to the decode
         // pipeline, kernelId 2 with the same kernelParam2 / 3, for calls with block scales or without scratch):

@@ -396,6 +396,30 @@ def gemm_layoutA_linear(A, B, alpha: float = 1, beta: float = 0, scale_matrix=No
     return gemm_layoutA(A, B, alpha, beta, bias)
 
 
+def muxi_hgemm_layoutA(A, B, alpha: float = 1, beta: float = 0, scale_matrix=None, bias=None, *, fp8_repacked: bool = False):
+    """``C[n,m] = alpha * B A^T (+ bias)`` for any token count n, A in layout A (16-bit, or e4m3 with optional 128x128
+    block scales), B and C row-major (csrc/muxi_hgemm_layoutA.cu:12-217): the prefill-side consumer of the weights the
+    GeMV / narrow-GEMM operators stream.  ``beta`` is ignored (the reference applies it to its own uninitialised C)."""
+    _chk(A.is_cuda, "A must be a CUDA tensor")
+    _chk(B.is_cuda, "B must be a CUDA tensor")
+    _chk(A.is_contiguous(), "A must be contiguous")
+    _chk(B.is_contiguous(), "B must be contiguous")
+    m, A_k = _layoutA_dims(A)
+    _chk(B.dim() == 2, "B must be a 2D tensor")
+    n, B_k = B.shape
+    _chk(A_k == B_k, "A and B must have the same k")
+    _chk(m % 128 == 0, "m must be a multiple of 128")
+    _chk(A_k % 128 == 0, "k must be a multiple of 128")
+    code = _dense_code(A, B)
+    _chk(code == 2 or scale_matrix is None, "scale_matrix needs 1-byte weights")
+    C = torch.empty((n, m), dtype=B.dtype, device=B.device)
+    aux, _keep = _aux(B, m, min(n, 64), A_k, stream_k=(code != 2))
+    check(lib.mlk_muxi_hgemm_layoutA(A.data_ptr(), _scale_ptr(scale_matrix, m, A_k), B.data_ptr(), C.data_ptr(), m, n, A_k,
+                                     code, alpha, beta, _bias_ptr(bias, B, m), int(fp8_repacked), ctypes.byref(aux),
+                                     _stream(B)))
+    return C
+
+
 def gemm_layoutAB_ContinuousC(A, B, alpha: float = 1, beta: float = 0, bias=None):
     """A layout A, B layout B (from ``layoutB``), C row-major (csrc/gemm_layout_ab_continuous_c.cu:1051)."""
     m, n, k = _gemm_checks(A, B, True)
@@ -665,7 +689,6 @@ def _out_of_scope(name: str, why: str):
 gemmEx = _out_of_scope("gemmEx", "it wraps the vendor GEMM of the reference platform (csrc/gemm_ex.cu); use torch.matmul")
 muxi_hgemm = _out_of_scope("muxi_hgemm", "large-n prefill GEMM family (csrc/muxi_hgemm.cu)")
 muxi_hgemm_layout = _out_of_scope("muxi_hgemm_layout", "large-n prefill GEMM family (csrc/muxi_hgemm_layout.cu)")
-muxi_hgemm_layoutA = _out_of_scope("muxi_hgemm_layoutA", "large-n prefill GEMM family (csrc/muxi_hgemm_layoutA.cu)")
 muxi_hgemm_layoutC = _out_of_scope("muxi_hgemm_layoutC", "large-n prefill GEMM family (csrc/muxi_hgemm_layoutC.cu)")
 routing_gate = _out_of_scope("routing_gate", "legacy split MoE, superseded by fused_routing_gate (csrc/moe_kernels/routing_gate.cu)")
 experts_compute = _out_of_scope("experts_compute", "legacy host-synchronous MoE, superseded by fused_experts_compute (csrc/moe_kernels/experts_compute.cu)")

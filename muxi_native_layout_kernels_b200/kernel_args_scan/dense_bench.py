@@ -7,6 +7,7 @@ C2  narrow GEMM, tokens {1,2,4,8,16,32,64} x {(4096,4096), (14336,4096), (4096,1
     through gemm_layoutAB_ContinuousC and gemm_layoutABC (activations prepared with layoutB; token counts below 16 are
     zero-padded to 16 rows as that operator requires, bytes are counted with the true token count).  The bf16
     gemm_layoutA grid is the headline step of bench.py and is not repeated here.
+F3  many-token GEMM muxi_hgemm_layoutA, bf16, 128 and 1024 tokens (TFLOP/s against the dense bf16 peak).
 C3  soft-FP8: gemv_layoutA and gemm_layoutA_soft_fp8 with e4m3 weights, tokens {1, 8, 32} x {(28672,8192),
     (8192,28672), (8192,8192)}.
 Role of the reference's benchmark_and_test/gemv_benchmark.py and gemm_benchmark.py (same traffic formula, :111).
@@ -70,7 +71,7 @@ def _row(config, op, dtype, N, K, n, us, wbytes, peak):
             "gbs": round(gbs, 1), "frac_measured": round(gbs / peak, 3), "frac_nominal_8TBs": round(gbs / NOMINAL_HBM_GBS, 3)}
 
 
-def run(dev=None, peak=6450.0, rank=0, world=1, configs=("C1", "C2", "C3")):
+def run(dev=None, peak=6450.0, rank=0, world=1, configs=("C1", "C2", "C3", "F3"), tensor_peak=1633.9):
     """Rows for this rank's row shard of every weight matrix (rank g owns rows [g N / world, (g + 1) N / world))."""
     dev = dev or torch.device("cuda")
     mlk.set_static_weights(True)
@@ -120,13 +121,28 @@ def run(dev=None, peak=6450.0, rank=0, world=1, configs=("C1", "C2", "C3")):
                                  _time(lambda A: mlk.gemm_layoutA_soft_fp8(A, None, X), pool), 1, peak))
             del pool
             torch.cuda.empty_cache()
+    if "F3" in configs:
+        # many-token GEMM on the same prepacked weights (muxi_hgemm_layoutA): tensor-core bound, TFLOP/s against the
+        # measured dense bf16 peak
+        g = torch.Generator().manual_seed(5)
+        for (N, K) in [(4096, 4096), (14336, 4096), (8192, 8192)]:
+            W = shard((torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)).to(dev)
+            pool = _pool(W)
+            for n in (128, 1024):
+                X = torch.randn(n, K, generator=g).to(torch.bfloat16).to(dev)
+                us = _time(lambda A: mlk.muxi_hgemm_layoutA(A, X), pool)
+                tf = 2.0 * W.shape[0] * n * K / us / 1e6
+                rows.append({"config": "F3", "op": "muxi_hgemm_layoutA", "dtype": "bf16", "N": W.shape[0], "K": K, "tokens": n,
+                             "us": round(us, 2), "tflops": round(tf, 1), "frac_measured_tensor": round(tf / tensor_peak, 3)})
+            del pool
+            torch.cuda.empty_cache()
     return rows
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", action="store_true")
-    ap.add_argument("--configs", default="C1,C2,C3")
+    ap.add_argument("--configs", default="C1,C2,C3,F3")
     a = ap.parse_args()
     out = run(configs=tuple(a.configs.split(",")))
     if a.json:

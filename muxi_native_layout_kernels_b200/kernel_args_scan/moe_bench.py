@@ -161,8 +161,10 @@ def run_ep(config, rank, world, tokens=None, iters=24, dev=None, graphs=False):
     weights (parity_ok).
       replicated   tokens and router logits on every rank, each rank adds its experts' share (experts_map), NCCL
                    all-reduce of the shares; us_eager and us_graph
-      all_to_all   tokens sharded T / world per rank, NCCL all-to-all dispatch of the routed rows, local experts,
-                   all-to-all combine; as CUDA-graph replays as well (fixed-capacity exchange)
+      all_to_all   tokens sharded T / world per rank, NCCL all-to-all dispatch of exactly the routed rows, local
+                   experts, all-to-all combine of the fp32 rows; us_eager only (the split sizes cost a host copy)
+      gather_reduce_scatter  tokens sharded, static shapes: all-gather of tokens and logits, local share, reduce-scatter
+                   of the fp32 shares; us_eager and us_graph
     Times are CUDA events around the calls after a barrier, max over ranks."""
     import torch.distributed as dist
 
@@ -195,15 +197,21 @@ def run_ep(config, rank, world, tokens=None, iters=24, dev=None, graphs=False):
                 xl = [x[rank * tl:(rank + 1) * tl].contiguous() for x in xs]
                 ll = [l[rank * tl:(rank + 1) * tl].contiguous() for l in logits]
                 got = fused_moe_ep(xl[0], w1l, w2l, ll[0], topk, True, **kw_ep)
-                a2a = _time_ep(lambda i: fused_moe_ep(xl[i], w1l, w2l, ll[i], topk, True, **kw_ep), iters, graphs, dev)
+                # exact split sizes need one device -> host copy per call: eager only
+                a2a = _time_ep(lambda i: fused_moe_ep(xl[i], w1l, w2l, ll[i], topk, True, **kw_ep), iters, False, dev)
                 a2a["parity_ok"] = _close(got, want[rank * tl:(rank + 1) * tl])
                 a2a["tokens_per_rank"] = tl
                 row["all_to_all"] = a2a
-            flags = torch.tensor([int(row["replicated"]["parity_ok"]), int(row.get("all_to_all", {}).get("parity_ok", True))], device=dev)
+                got = fused_moe_ep(xl[0], w1l, w2l, ll[0], topk, True, exchange="gather", **kw_ep)
+                gat = _time_ep(lambda i: fused_moe_ep(xl[i], w1l, w2l, ll[i], topk, True, exchange="gather", **kw_ep), iters, graphs, dev)
+                gat["parity_ok"] = _close(got, want[rank * tl:(rank + 1) * tl])
+                gat["tokens_per_rank"] = tl
+                row["gather_reduce_scatter"] = gat
+            modes = [m for m in ("replicated", "all_to_all", "gather_reduce_scatter") if m in row]
+            flags = torch.tensor([int(row[m]["parity_ok"]) for m in modes], device=dev)
             dist.all_reduce(flags, op=dist.ReduceOp.MIN)
-            row["replicated"]["parity_ok"] = bool(flags[0])
-            if "all_to_all" in row:
-                row["all_to_all"]["parity_ok"] = bool(flags[1])
+            for m, f in zip(modes, flags.tolist()):
+                row[m]["parity_ok"] = bool(f)
             rows.append(row)
         out[name] = rows
         del w1, w2, w1l, w2l

@@ -37,16 +37,36 @@ def main():
         el = E // world
         w1l, w2l = w1a[rank * el:(rank + 1) * el].contiguous(), w2a[rank * el:(rank + 1) * el].contiguous()
         xs, ls = x[rank * T:(rank + 1) * T].contiguous(), logits[rank * T:(rank + 1) * T].contiguous()
-        y_ep = parallel.fused_moe_ep(xs, w1l, w2l, ls, topk, True, soft_fp8=fp8).float()
         want = full[rank * T:(rank + 1) * T]
-        scale = max(1.0, float(want.pow(2).mean().sqrt()))
-        d1 = (y_ep - want).abs()
-        ok1 = bool((d1 <= 1e-2 * scale + 1e-2 * want.abs()).all())
-        y_rep = parallel.fused_moe_ep_replicated(x, w1l, w2l, logits, topk, True, **kw).float()
-        d2 = (y_rep - full).abs()
-        ok2 = bool((d2 <= 1e-2 * scale + 1e-2 * full.abs()).all())
-        print(f"rank {rank} E={E} fp8={fp8}: ep max {float(d1.max()):.4g} ok={ok1}; replicated max {float(d2.max()):.4g} ok={ok2}", flush=True)
-        ok = ok and ok1 and ok2
+        scale = max(1.0, float(full.pow(2).mean().sqrt()))
+
+        def close(got, ref):
+            d = (got.float() - ref).abs()
+            return bool((d <= 1e-2 * scale + 1e-2 * ref.abs()).all()), float(d.max())
+
+        res = {}
+        res["all_to_all"] = close(parallel.fused_moe_ep(xs, w1l, w2l, ls, topk, True, soft_fp8=fp8), want)
+        res["gather"] = close(parallel.fused_moe_ep(xs, w1l, w2l, ls, topk, True, soft_fp8=fp8, exchange="gather"), want)
+        res["replicated fp32"] = close(parallel.fused_moe_ep_replicated(x, w1l, w2l, logits, topk, True, **kw), full)
+        res["replicated bf16"] = close(parallel.fused_moe_ep_replicated(x, w1l, w2l, logits, topk, True,
+                                                                        reduce_dtype=torch.bfloat16, **kw), full)
+        # the static-shape modes inside a CUDA graph (collectives included), replayed on new inputs
+        xg, lg = xs.clone(), ls.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            parallel.fused_moe_ep(xg, w1l, w2l, lg, topk, True, soft_fp8=fp8, exchange="gather")
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                yg = parallel.fused_moe_ep(xg, w1l, w2l, lg, topk, True, soft_fp8=fp8, exchange="gather")
+        torch.cuda.current_stream().wait_stream(side)
+        graph.replay()
+        torch.cuda.synchronize()
+        res["gather graph"] = close(yg, want)
+        del graph
+        for name, (good, dmax) in res.items():
+            print(f"rank {rank} E={E} fp8={fp8} {name}: max diff {dmax:.4g} ok={good}", flush=True)
+            ok = ok and good
     # dense: row shard, then all-gather of the output columns
     W = (torch.randn(1024, 512, generator=g) * 0.05).to(torch.bfloat16).to(dev)
     X = torch.randn(8, 512, generator=g).to(torch.bfloat16).to(dev)

@@ -62,7 +62,9 @@ def test_table_load_lookup_and_miss_default(tmp_path, capfd):
     assert lib.mlk_table_lookup(2, 8192 + 16, 8, 1024, out, ctypes.byref(hit)) == 0
     w = list(out)
     assert hit.value == 0 and w[0] == 1 and w[1] in (1, 2) and w[2] in (1, 2, 4, 8) and w[3] in (1, 2, 4, 8)
-    assert lib.mlk_table_lookup(2, 8192, 128, 1024, out, ctypes.byref(hit)) == 0 and list(out)[0] == 1
+    # more than 64 tokens on 128-row tiles: the many-token tcgen05 tile kernel; layout-B variants stay warp-level
+    assert lib.mlk_table_lookup(2, 8192, 128, 1024, out, ctypes.byref(hit)) == 0 and list(out)[0] == 10
+    assert lib.mlk_table_lookup(1, 8192, 128, 1024, out, ctypes.byref(hit)) == 0 and list(out)[0] == 1
     capfd.readouterr()
     assert lib.mlk_table_lookup(2, 8192, 8, 1024, out, ctypes.byref(hit)) == 0
     assert list(out) == first and hit.value == 1

@@ -394,6 +394,45 @@ def test_soft_fp8_tcgen05_block_scales(repacked, full_scales):
             _close_rel(y, odense.gemm_ref(x, Wd), f"gemv fp8 tcgen05 scaled[{name}] m={m} k={k}", tol)
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_many_token_gemm_tile_kernel(dt):
+    """muxi_hgemm_layoutA / kernelId 10: 128 x 128 and 128 x 256 (weight rows x tokens) tcgen05 tiles, whole k per CTA,
+    any token count; also gemm_layoutA above 64 tokens, which runs on it by default."""
+    dev = require_gpu()
+    for (m, k) in [(128, 128), (384, 512), (1024, 4096)]:
+        W, A = _weights(m, k, 300 + m, dt, dev)
+        bias = randn((1, m), 301, 1.0, dt)
+        for n in [65, 128, 200, 256, 257, 700, 1024]:
+            X = randn((n, k), 302 + n, 1.0, dt)
+            want = odense.gemm_ref(X, W)
+            assert_close(mlk.muxi_hgemm_layoutA(A, X.to(dev)), want, f"hgemm m={m} k={k} n={n} {dt}")
+            for nt, stages in [(128, 2), (128, 6), (256, 3), (256, 4)]:
+                C = mlk.gemm_layoutA_wapper(A, X.to(dev), m, n, k, kernelParam1=nt, kernelParam2=stages, kernelId=10)
+                assert_close(C, want, f"hgemm tile m={m} k={k} n={n} nt={nt} stages={stages} {dt}")
+            if n <= 256:
+                assert_close(mlk.gemm_layoutA(A, X.to(dev)), want, f"gemm_layoutA above 64 tokens m={m} n={n}")
+        X = randn((300, k), 303, 1.0, dt)
+        C = mlk.muxi_hgemm_layoutA(A, X.to(dev), alpha=0.5, bias=bias.to(dev))
+        assert_close(C, odense.gemm_ref(X, W, alpha=0.5, bias=bias), f"hgemm alpha bias m={m}")
+        # few tokens: the narrow kernels
+        X = randn((40, k), 304, 1.0, dt)
+        assert_close(mlk.muxi_hgemm_layoutA(A, X.to(dev)), odense.gemm_ref(X, W), f"hgemm 40 tokens m={m}")
+    assert mlk.kernel_status() == 0
+
+
+def test_many_token_gemm_e4m3_weights():
+    """muxi_hgemm_layoutA with e4m3 weights (with and without block scales): the narrow kernels, 64 tokens at a time."""
+    dev = require_gpu()
+    m, k, n = 512, 1024, 200
+    W8 = rand_e4m3((m, k), 310)
+    A = mlk.layoutA(W8.to(dev))
+    X = randn((n, k), 311, 1.0, torch.bfloat16)
+    assert_close(mlk.muxi_hgemm_layoutA(A, X.to(dev)), odense.gemm_ref(X, W8.to(torch.bfloat16)), "hgemm e4m3")
+    scale = (torch.rand(m // 128, k // 128, generator=torch.Generator().manual_seed(312)) * 2).float()
+    want_s = (X.float() @ odense.dequant_exact_scale(W8, scale).t()).to(torch.bfloat16)
+    _close_rel(mlk.muxi_hgemm_layoutA(A, X.to(dev), scale_matrix=scale.to(dev)), want_s, "hgemm e4m3 scaled")
+
+
 def test_gemm_errors_and_determinism():
     dev = require_gpu()
     W, A = _weights(256, 256, 80, torch.bfloat16, dev)

@@ -51,12 +51,13 @@ def _worker(rank, port, out):
                 h = w1l[e].float() @ rows[r].float()
                 a = (F.silu(h[:I]) * h[I:]).to(x.dtype).float()        # the kernels round the activation once
                 y[r] = float(weight[r]) * (w2l[e].float() @ a)
-            return y.to(rows.dtype)
+            return y                                                   # fp32 rows travel back
 
         gather_fn = lambda t, idx: t[idx.long()]
 
         def combine_fn(rows, slot_to_row, T_, topk_):
-            return rows.float()[slot_to_row.long()].view(T_, topk_, -1).sum(1).to(rows.dtype)
+            assert rows.dtype == torch.float32
+            return rows[slot_to_row.long()].view(T_, topk_, -1).sum(1).to(x.dtype)
 
         y = parallel.moe_exchange(xs, ids.to(torch.int32), wts, e_local, experts_fn, gather_fn, combine_fn)
         y32 = omoe.experts_ref(xs, w1, w2, ids, wts, compute_dtype=torch.float32)
@@ -68,7 +69,7 @@ def _worker(rank, port, out):
         y_all = parallel.all_gather_columns(y_loc)
         dense_ok = torch.equal(y_all, odense.gemm_ref(Xd, W))
         plan = parallel.plan_dispatch(ids.to(torch.int32), e_local, WORLD)
-        plan_ok = (sum(plan.send_counts) == T * topk and
+        plan_ok = (int(plan.send_counts.sum()) == T * topk and
                    bool((plan.send_slot.long()[plan.slot_to_row.long()] == torch.arange(T * topk)).all()) and
                    bool((plan.send_expert >= 0).all()) and bool((plan.send_expert < e_local).all()))
         out.put((rank, rep, dense_ok, plan_ok))
@@ -95,11 +96,22 @@ def test_expert_parallel_exchange_and_row_sharding_world2():
 def test_plan_dispatch_single_process():
     ids = torch.tensor([[0, 5], [7, 1], [2, 3]], dtype=torch.int32)
     plan = parallel.plan_dispatch(ids, experts_per_rank=4, world=2)
-    assert plan.send_counts == [4, 2]
+    assert plan.send_counts.tolist() == [4, 2]
     assert plan.send_slot.tolist() == [0, 3, 4, 5, 1, 2]          # stable inside a destination
     assert plan.send_token.tolist() == [0, 1, 2, 2, 0, 1]
     assert plan.send_expert.tolist() == [0, 1, 2, 3, 1, 3]
     assert plan.slot_to_row.tolist() == [0, 4, 5, 1, 2, 3]
+
+
+def test_packed_dispatch_rows_round_trip():
+    g = torch.Generator().manual_seed(5)
+    rows = torch.randn(7, 64, generator=g).to(torch.bfloat16)
+    expert = torch.arange(7, dtype=torch.int32) * 3 - 2
+    weight = torch.rand(7, generator=g).to(torch.bfloat16)
+    buf = parallel.pack_rows(rows, expert, weight)
+    assert buf.shape == (7, 2 * 64 + 16) and buf.dtype == torch.uint8
+    r2, e2, w2 = parallel.unpack_rows(buf, 64, torch.bfloat16)
+    assert torch.equal(r2, rows) and torch.equal(e2, expert) and torch.equal(w2, weight.float())
 
 
 def test_shard_rows_rejects_uneven_split():
