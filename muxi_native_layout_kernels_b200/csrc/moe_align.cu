@@ -12,6 +12,7 @@
 //   experts_map: global id -> local id, -1 = not on this rank (slot is skipped)
 // Optionally the kernel also emits the expert-compute work list (see MoeWorkHeader in moe.cuh) and, with it, the slot of
 // every compact position (cpos_slot: the routed slots numbered expert by expert without the padding).
+#include "common.cuh"
 #include "moe.cuh"
 #include "status.h"
 
@@ -34,6 +35,10 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int32_t* __restri
     __shared__ int warp_tot[32], warp_tot2[32], warp_tot3[32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
+    // the routing comes from the preceding kernel of the stream (and the buffers written here may still be read by it
+    // or its predecessors); the kernels behind this one may become resident meanwhile
+    pdl_wait();
+    pdl_launch_dependents();
     for (int e = tid; e < E; e += blockDim.x) cnt[e] = 0;
     for (int b = tid; b < max_blocks; b += blockDim.x) block_expert[b] = 0;
     for (int i = tid; i < max_padded; i += blockDim.x) sorted[i] = numel;   // sentinel everywhere; slots overwrite it below
@@ -126,10 +131,18 @@ int launch_moe_align(int T, int E, int topk, int mbs, const int32_t* topk_ids, i
     const int max_blocks = (max_padded + mbs - 1) / mbs;
     if (experts_map != nullptr && experts_map_len <= 0) return fail(kInvalidArg, "moe_align: experts_map needs its length");
     const int n_global = experts_map_len;
-    moe_align_kernel<<<1, 1024, 0, s>>>(topk_ids, (int)numel, E, mbs, max_blocks, max_padded, sorted_token_ids, cumsum,
-                                        padded_num_experts, experts_ids_out, experts_map, n_global,
-                                        reinterpret_cast<int4*>(worklist), block_slots, cpos_slot);
-    return check_launch("moe_align");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    cfg.attrs = attr;
+    cfg.numAttrs = launch_attrs(attr, 1);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, moe_align_kernel, topk_ids, (int)numel, E, mbs, max_blocks, max_padded,
+                                             sorted_token_ids, cumsum, padded_num_experts, experts_ids_out, experts_map, n_global,
+                                             reinterpret_cast<int4*>(worklist), block_slots, cpos_slot);
+    if (e != cudaSuccess) return fail(kCudaError, "moe_align launch: %s", cudaGetErrorString(e));
+    return kOk;
 }
 
 }  // namespace mlk

@@ -179,6 +179,9 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
                                                          const int32_t* __restrict__ topk_ids,
                                                          const int32_t* __restrict__ experts_map, int map_len, int E,
                                                          int T, int topk, int H, void* __restrict__ y) {
+    // the rows come from the second GEMM, the preceding kernel of the stream
+    pdl_wait();
+    pdl_launch_dependents();
     const int octs = H >> 3;
     const long long total = (long long)T * octs;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -214,16 +217,18 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
 int launch_combine(const MoeParams& m, int wt, cudaStream_t s) {
     const long long total = (long long)m.T * (m.H / 8);
     const int grid = (int)std::min<long long>((total + 255) / 256, 8LL * sm_count());
-    if (m.y_fp32)
-        moe_combine_kernel<kBF16, true><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
-                                                             m.topk, m.H, m.y);
-    else if (wt == kFP16)
-        moe_combine_kernel<kFP16, false><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
-                                                              m.topk, m.H, m.y);
-    else
-        moe_combine_kernel<kBF16, false><<<grid, 256, 0, s>>>(m.scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T,
-                                                              m.topk, m.H, m.y);
-    return check_launch("moe_combine");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    cfg.attrs = attr;
+    cfg.numAttrs = launch_attrs(attr, 1);
+    auto kern = m.y_fp32 ? moe_combine_kernel<kBF16, true> : (wt == kFP16 ? moe_combine_kernel<kFP16, false> : moe_combine_kernel<kBF16, false>);
+    const float* scratch = m.scratch;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, scratch, m.topk_ids, m.experts_map, m.experts_map_len, m.E, m.T, m.topk, m.H, m.y);
+    if (e != cudaSuccess) return fail(kCudaError, "moe_combine launch: %s", cudaGetErrorString(e));
+    return kOk;
 }
 
 template <int WT, int NT, int RG, bool SCALE, int MODE>

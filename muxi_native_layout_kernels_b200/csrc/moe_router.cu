@@ -159,6 +159,9 @@ __global__ void __launch_bounds__(128) router_kernel(const void* __restrict__ lo
                                                      int G, int KG, int32_t* __restrict__ ids, void* __restrict__ wts,
                                                      int topk, const void* __restrict__ bias, int renormalize) {
     extern __shared__ float sm[];
+    // the logits come from the preceding kernel of the stream; the kernels behind this one may become resident
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row = blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= T) return;
@@ -324,13 +327,20 @@ int launch_router(const void* gating_output, int score_fun, int T, int E, int n_
     const int warps = 4;
     const int grid = (T + warps - 1) / warps;
     const size_t smem = (size_t)warps * (E + 2 * n_groups) * sizeof(float);
-    if (dtype == 1)
-        router_kernel<kFP16><<<grid, warps * 32, smem, s>>>(gating_output, score_fun, T, E, n_groups, topk_groups,
-                                                            experts_ids, weights, topk, bias, renormalize);
-    else
-        router_kernel<kBF16><<<grid, warps * 32, smem, s>>>(gating_output, score_fun, T, E, n_groups, topk_groups,
-                                                            experts_ids, weights, topk, bias, renormalize);
-    return check_launch("fused_routing_gate");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(warps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    cfg.attrs = attr;
+    cfg.numAttrs = launch_attrs(attr, 1);
+    const cudaError_t e = dtype == 1 ? cudaLaunchKernelEx(&cfg, router_kernel<kFP16>, gating_output, score_fun, T, E, n_groups, topk_groups,
+                                                          experts_ids, weights, topk, bias, renormalize)
+                                     : cudaLaunchKernelEx(&cfg, router_kernel<kBF16>, gating_output, score_fun, T, E, n_groups, topk_groups,
+                                                          experts_ids, weights, topk, bias, renormalize);
+    if (e != cudaSuccess) return fail(kCudaError, "fused_routing_gate launch: %s", cudaGetErrorString(e));
+    return kOk;
 }
 
 }  // namespace mlk

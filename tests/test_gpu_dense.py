@@ -4,6 +4,7 @@ Tolerance: |got - want| <= 1e-2 + 1e-2 * |want| on the 16-bit outputs (fp32 accu
 combined form of the "max-abs / max-rel <= 1e-2" bar: a bf16 value of magnitude 4..8 has a unit in the last place
 of 0.031, so a pure absolute bound cannot hold for correct results, and a pure relative one blows up near zero.
 """
+import ctypes
 import itertools
 
 import pytest
@@ -589,3 +590,32 @@ def test_config_soft_fp8_llama70b(N, K):
         want = (X.float() @ Wf.t()).to(torch.bfloat16)
         assert_close(mlk.gemm_layoutA_soft_fp8(A, None, X.to(dev)), want, f"C3 gemm {(N, K)} n={n}")
         assert_close(mlk.gemm_layoutA_soft_fp8(A_rep, None, X.to(dev), fp8_repacked=True), want, f"C3 repacked n={n}")
+
+
+def test_offline_tuner_writes_rows_the_library_uses(tmp_path):
+    """The offline tuner on two tiny keys (role of the reference's kernel_args_scan/gemv_kernel_args_scan.py:135-157):
+    it must write a row per key into a table file of the reference's format, the library must load that file and
+    return exactly those rows, and the table-driven entry point must give the oracle's result with them."""
+    import csv
+    from muxi_native_layout_kernels_b200._lib import lib, load_tables
+    from muxi_native_layout_kernels_b200.kernel_args_scan import scan
+    dev = require_gpu()
+    try:
+        scan.main(["--table", "layoutA_gemm", "--shapes", "256x256", "--tokens", "16", "--out", str(tmp_path)])
+        scan.main(["--table", "layout_gemv_bf16", "--shapes", "256x256", "--out", str(tmp_path)])
+        for t, name, key in ((2, "layoutA_gemm_dispatch_arg.csv", (256, 16, 256)), (5, "layout_gemv_bf16_dispatch_arg.csv", (256, 256))):
+            rows = list(csv.reader(open(tmp_path / name)))
+            assert rows[0] == (scan.GEMM_HEADER if t == 2 else scan.GEMV_HEADER)
+            assert len(rows) == 2 and tuple(int(v) for v in rows[1][:len(key)]) == key
+            assert lib.mlk_table_load(t, str(tmp_path / name).encode()) == 0
+            out, hit = (ctypes.c_int * 4)(), ctypes.c_int(0)
+            assert lib.mlk_table_lookup(t, key[0], key[1] if t == 2 else 1, key[-1], out, ctypes.byref(hit)) == 0
+            assert hit.value == 1 and list(out) == [int(v) for v in rows[1][len(key):]]
+        W, A = _weights(256, 256, 400, torch.bfloat16, dev)
+        X = randn((16, 256), 401, 1.0, torch.bfloat16)
+        assert_close(mlk.gemm_layoutA(A, X.to(dev)), odense.gemm_ref(X, W), "gemm with the tuner's row")
+        assert_close(mlk.gemv_layoutA(A, X[:1].to(dev)), odense.gemm_ref(X[:1], W), "gemv with the tuner's row")
+        log = list(csv.reader(open(tmp_path / "layoutA_gemm_scan_result.csv")))
+        assert len(log) > 10 and all(r[-1] != "WRONG" for r in log)
+    finally:
+        load_tables()     # the packaged tables again
