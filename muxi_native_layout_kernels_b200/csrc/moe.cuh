@@ -54,7 +54,8 @@ struct MoeParams {
     int nt, wm1, sk1, rg, wm2, sk2;   // tuning (0 = choose by shape): token tiles, GEMM1 row warps / split-K, GEMM2 row groups / row warps / split-K;
                                       // wm1 = 100 + s1 and wm2 = 100 + s2 select the tcgen05 kernels (combine scratch given)
                                       // with s1 / s2 ring stages and sk1 / sk2 CTAs per cluster; 200 + s1 / 200 + s2 the
-                                      // native-e4m3 tcgen05 kernels (e4m3 weights without block scales)
+                                      // native-e4m3 tcgen05 kernels (e4m3 weights without block scales); there sk2 = 10 + r
+                                      // (11..18) runs the second GEMM without clusters, r 128-row tiles per CTA
 };
 
 int launch_fused_experts(const MoeParams& p, cudaStream_t s);

@@ -367,6 +367,7 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
     if (m.wm1 >= 200 && m.wm2 >= 200 && !(wt == kE4M3 && !scale && moe_f8n_supported(m.H, m.I))) {
         m.wm1 -= 100;
         m.wm2 -= 100;
+        if (m.sk2 > 8) m.sk2 = 1;      // "row tiles per CTA" exists for the native kernels only
     }
     const bool f8n = m.wm1 >= 200 && m.wm2 >= 200 && m.scratch != nullptr && (long long)slots * m.H * 4 <= m.scratch_bytes;
     const bool umma = !f8n && m.wm1 >= 100 && m.wm1 < 200 && m.wm2 >= 100 && m.wm2 < 200 && m.scratch != nullptr && m.I % 128 == 0 &&

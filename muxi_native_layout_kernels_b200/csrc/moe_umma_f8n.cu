@@ -188,7 +188,32 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
             abort_flag = 1;
         }
         __syncwarp();
-        if (!abort_flag) {
+        if (MODE == 1 && SK == 1) {
+            // no cluster: straight from tensor memory to the activation.  This thread holds gate row lrow (first
+            // accumulator) and up row lrow (second) of the tile; a warp writes 32 consecutive elements of a slot's row.
+            if (!abort_flag) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint16_t* const out = reinterpret_cast<uint16_t*>(p.out) + (size_t)cpos0 * p.rows + (size_t)tile * kTileM + lrow;
+#pragma unroll
+                for (int c0 = 0; c0 < NP; c0 += 16) {
+                    if (c0 < nslots) {
+                        uint32_t g[16], u[16];
+                        tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + c0, g);
+                        tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + NP + c0, u);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            if (c0 + i < nslots) {
+                                const float inv = __ldg(p.inv_scale + cpos0 + c0 + i);
+                                const float gate = __uint_as_float(g[i]) * inv, up = __uint_as_float(u[i]) * inv;
+                                out[(size_t)(c0 + i) * p.rows] = __bfloat16_as_ushort(__float2bfloat16_rn(gate / (1.f + __expf(-gate)) * up));
+                            }
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+        } else if (!abort_flag) {
             // accumulators x inverse row scale -> fp32 partial tiles [which][slot][tile row] in the idle ring
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float* const red = reinterpret_cast<float*>(base_ptr);
@@ -209,7 +234,217 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
     }
     __syncwarp();
 
-    moe_cluster_epilogue<kBF16, NP, MODE, true>(p, base, tile, rank, SK, nslots, pos0, cpos0, tid);
+    if (!(MODE == 1 && SK == 1)) moe_cluster_epilogue<kBF16, NP, MODE, true>(p, base, tile, rank, SK, nslots, pos0, cpos0, tid);
+
+    if (warp == 0 && lane == 0 && abort_flag) {
+        for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(full(i % STAGES), (i / STAGES) & 1);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// Second GEMM with several 128-row weight tiles per CTA.  With a short k (the intermediate size of a fine-grained
+// expert: 768 = 12 stages) a CTA that handles one tile spends as long on its start-up and its epilogue as on streaming.
+// Here a CTA walks R consecutive row tiles of its work item: barriers, tensor memory and the TMA ring are set up once
+// and the ring keeps streaming across tile boundaries; the accumulator is double-buffered (up to 32 slots per item), so
+// the MMAs of the next tile run while the mover warps write the previous tile's rows; no cluster, so the epilogue goes
+// straight from tensor memory to the fp32 rows of the combine scratch (128 consecutive floats per slot and warp pass).
+template <int NP, int STAGES>
+__global__ void __launch_bounds__(192, 2) moe_umma_f8n_rows_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                   const __grid_constant__ CUtensorMap map_x,
+                                                                   const MoeUmmaParams p, const int tiles_per_cta) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr int AB = NP <= 32 ? 2 : 1;               // accumulator buffers
+    constexpr int S2 = NP == 16 ? 2 : (NP == 32 ? 2 : 4);
+    constexpr int kXTile = NP * 128;
+    constexpr int kStageBytes = kRaw + kXTile;
+    constexpr uint32_t kTmemCols = (AB * NP + S2 * kACols) <= 64 ? 64 : 128;
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 2 * S2 + 2 * AB];
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile int abort_flag;
+    __shared__ int slot_s[NP];
+    __shared__ float factor_s[NP];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    pdl_wait();
+    pdl_launch_dependents();
+    const int n_items = p.worklist[0].x;
+    if ((int)blockIdx.z >= n_items) return;
+    const int4 item = p.worklist[1 + blockIdx.z];
+    const int expert = item.x, pos0 = item.y, nslots = item.z, cpos0 = item.w;
+    const int tiles_total = p.tiles_per_expert;
+    const int tile0 = blockIdx.x * tiles_per_cta;
+    const int ntiles = min(tiles_per_cta, tiles_total - tile0);
+    const int KB = p.kblocks;
+    const int total = ntiles * KB;
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* const base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bar0 = smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto a_full = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };
+    auto a_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + S2 + s); };
+    auto acc_full = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 * S2 + b); };
+    auto acc_empty = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 * S2 + AB + b); };
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full(s), 1);
+            mbar_init(empty(s), 1);
+        }
+        for (int s = 0; s < S2; ++s) {
+            mbar_init(a_full(s), 4);
+            mbar_init(a_empty(s), 1);
+        }
+        for (int b = 0; b < AB; ++b) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), 4);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid >= 64 && tid - 64 < NP) {
+        // slot and factor (inverse row scale x routing weight) of every column of the accumulator
+        const int c = tid - 64;
+        int slot = -1;
+        float f = 0.f;
+        if (c < nslots) {
+            slot = p.sorted[pos0 + c];
+            if (slot < p.n_slots) f = __ldg(p.inv_scale + cpos0 + c) * load_scalar16<kBF16>(p.topk_weights, slot);
+            else slot = -1;
+        }
+        slot_s[c] = slot;
+        factor_s[c] = f;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+
+    int issued = 0;
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer: units (tile, k block), tile-major ----
+        int tl = 0, kb = 0;
+        for (int u = 0; u < total; ++u) {
+            const int s = u % STAGES;
+            if (u >= STAGES && !mbar_wait(empty(s), ((u / STAGES) - 1) & 1)) {
+                abort_flag = 1;
+                if (p.status) atomicExch(p.status, 1);
+            }
+            if (abort_flag) break;
+            mbar_expect_tx(full(s), kStageBytes);
+            tma_load_3d(base + s * kStageBytes, &map_a, full(s), 0, kb * (kBK / 8),
+                        (expert * tiles_total + tile0 + tl) * (kTileM / 16));
+            tma_load_2d(base + s * kStageBytes + kRaw, &map_x, full(s), kb * 128, cpos0);
+            ++issued;
+            if (++kb == KB) { kb = 0; ++tl; }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        constexpr uint32_t idesc = instr_desc_f8<NP>();
+        int tl = 0, kb = 0;
+        for (int u = 0; u < total; ++u) {
+            const int s = u % STAGES, s2 = u % S2, b = tl % AB;
+            bool ok = !abort_flag;
+            if (ok && kb == 0 && tl >= AB) ok = mbar_wait(acc_empty(b), ((tl / AB) - 1) & 1);   // the epilogue has read it
+            if (ok) ok = mbar_wait(a_full(s2), (u / S2) & 1);
+            if (!ok) {
+                if (!abort_flag && p.status) atomicExch(p.status, 2);
+                abort_flag = 1;
+                break;
+            }
+            mbar_wait(full(s), (u / STAGES) & 1);       // already complete (the movers waited for it)
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t xt = base + s * kStageBytes + kRaw;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int term = 0; term < 2; ++term) {
+                    const uint64_t db = smem_desc(xt + term * 64 + j * 32, 16, 1024, 2);
+                    umma_f8_ts(tmem + b * NP, tmem + AB * NP + s2 * kACols + j * 8, db, idesc, (kb > 0 || j > 0 || term > 0) ? 1u : 0u);
+                }
+            }
+            umma_commit(empty(s));
+            umma_commit(a_empty(s2));
+            if (++kb == KB) {
+                umma_commit(acc_full(b));
+                kb = 0;
+                ++tl;
+            }
+        }
+    } else if (warp >= 2) {
+        // ---- mover warps (thread = tile row = tensor-memory lane); after a tile's last k block, its epilogue ----
+        const int quad = warp & 3, lrow = quad * 32 + lane;
+        int u = 0;
+        for (int tl = 0; tl < ntiles && !abort_flag; ++tl) {
+            bool ok = true;
+            for (int kb = 0; kb < KB; ++kb, ++u) {
+                const int s = u % STAGES, s2 = u % S2;
+                if (lane == 0) {
+                    ok = !abort_flag && mbar_wait(full(s), (u / STAGES) & 1);
+                    if (ok && u >= S2) ok = mbar_wait(a_empty(s2), ((u / S2) - 1) & 1);
+                    if (!ok) {
+                        if (!abort_flag && p.status) atomicExch(p.status, 8);
+                        abort_flag = 1;
+                    }
+                }
+                ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint8_t* raw = base_ptr + s * kStageBytes + (lrow >> 4) * (kBK * 16) + (lrow & 15) * 8;
+                uint32_t v[16];
+#pragma unroll
+                for (int o = 0; o < 8; ++o) {
+                    const uint2 x = *reinterpret_cast<const uint2*>(raw + o * 128);
+                    v[2 * o] = x.x;
+                    v[2 * o + 1] = x.y;
+                }
+                tmem_st16(tmem + ((uint32_t)(quad * 32) << 16) + AB * NP + s2 * kACols, v);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a_full(s2)) : "memory");
+            }
+            if (!ok) break;
+            const int b = tl % AB;
+            if (lane == 0 && (abort_flag || !mbar_wait(acc_full(b), (tl / AB) & 1))) {
+                if (!abort_flag && p.status) atomicExch(p.status, 3);
+                abort_flag = 1;
+            }
+            ok = __shfl_sync(0xFFFFFFFFu, abort_flag ? 0 : 1, 0) != 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float* const out = reinterpret_cast<float*>(p.out) + (size_t)(tile0 + tl) * kTileM + lrow;
+#pragma unroll
+            for (int c0 = 0; c0 < NP; c0 += 16) {
+                if (c0 < nslots) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + b * NP + c0, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int slot = slot_s[c0 + i];
+                        if (slot >= 0) out[(size_t)slot * p.rows] = __uint_as_float(r[i]) * factor_s[c0 + i];
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(b)) : "memory");
+        }
+    }
+    __syncwarp();
 
     if (warp == 0 && lane == 0 && abort_flag) {
         for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(full(i % STAGES), (i / STAGES) & 1);
@@ -266,6 +501,25 @@ const void* kernel_for(int np, int stages) {
     return nullptr;
 }
 
+template <int NP>
+const void* rows_kernel_for_stages(int stages) {
+    switch (stages) {
+        case 2: return reinterpret_cast<const void*>(moe_umma_f8n_rows_kernel<NP, 2>);
+        case 3: return reinterpret_cast<const void*>(moe_umma_f8n_rows_kernel<NP, 3>);
+        case 4: return reinterpret_cast<const void*>(moe_umma_f8n_rows_kernel<NP, 4>);
+        case 6: return reinterpret_cast<const void*>(moe_umma_f8n_rows_kernel<NP, 6>);
+    }
+    return nullptr;
+}
+const void* rows_kernel_for(int np, int stages) {
+    switch (np) {
+        case 16: return rows_kernel_for_stages<16>(stages);
+        case 32: return rows_kernel_for_stages<32>(stages);
+        case 64: return rows_kernel_for_stages<64>(stages);
+    }
+    return nullptr;
+}
+
 int launch_split(const void* kern, void** args, int rows, int k, cudaStream_t s) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)rows);
@@ -302,6 +556,42 @@ int launch_moe_umma_f8n(int mode, const void* W, int E, int rows, int k, const v
                         const void* topk_weights, int n_slots, int np, int stages, int cluster_k, int max_items, int* status,
                         cudaStream_t s) {
     if (rows % kTileM != 0 || k % kBK != 0) return fail(kInvalidArg, "moe (tcgen05, native e4m3): sizes must be multiples of 128 (rows) and 64 (k)");
+    if (mode == 2 && cluster_k >= 11 && cluster_k <= 18) {
+        // second GEMM, no cluster, cluster_k - 10 row tiles per CTA
+        const int tiles_per_cta = cluster_k - 10;
+        if (encode_fn() == nullptr) return fail(kUnsupported, "moe (tcgen05): cuTensorMapEncodeTiled is not available");
+        if (((uintptr_t)planes & 127) != 0) return fail(kInvalidArg, "moe (tcgen05, native e4m3): split planes must be 128-byte aligned");
+        const void* kern = rows_kernel_for(np, stages);
+        if (kern == nullptr) return fail(kInvalidArg, "moe (tcgen05, native e4m3): token tile %d / stages %d not built", np, stages);
+        const size_t want = (size_t)stages * (kRaw + np * 128) + 1024;
+        const int s2 = np == 64 ? 4 : 2, ab = np <= 32 ? 2 : 1;
+        const size_t smem = prepare_kernel(kern, 192, want, (ab * np + s2 * kACols) <= 64 ? 64 : 128);
+        if (smem == 0) return fail(kCudaError, "moe (tcgen05, native e4m3): a CTA with %d stages does not fit on this device", stages);
+        CUtensorMap ma, mx;
+        if (!make_map_a8_bk(&ma, W, (long long)E * rows, k, kBK)) return fail(kUnsupported, "moe (tcgen05): weight tensor map rejected");
+        if (!make_map_planes(&mx, planes, plane_rows, k, np)) return fail(kUnsupported, "moe (tcgen05): activation tensor map rejected");
+        MoeUmmaParams mp{};
+        mp.worklist = worklist; mp.sorted = sorted; mp.topk_weights = topk_weights; mp.out = out;
+        mp.rows = rows;
+        mp.tiles_per_expert = rows / kTileM;
+        mp.kblocks = k / kBK;
+        mp.n_slots = n_slots;
+        mp.status = status;
+        mp.inv_scale = inv_scale;
+        int tpc = tiles_per_cta;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)((rows / kTileM + tiles_per_cta - 1) / tiles_per_cta), 1, (unsigned)max_items);
+        cfg.blockDim = dim3(192);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[2];
+        cfg.attrs = attr;
+        cfg.numAttrs = launch_attrs(attr, 1);
+        void* args[4] = {&ma, &mx, &mp, &tpc};
+        const cudaError_t e = cudaLaunchKernelExC(&cfg, kern, args);
+        if (e != cudaSuccess) return fail(kCudaError, "moe_umma_f8n_rows launch: %s", cudaGetErrorString(e));
+        return kOk;
+    }
     if (cluster_k < 1 || cluster_k > 8 || cluster_k > k / kBK) return fail(kInvalidArg, "moe (tcgen05, native e4m3): cluster size %d out of range", cluster_k);
     if (encode_fn() == nullptr) return fail(kUnsupported, "moe (tcgen05): cuTensorMapEncodeTiled is not available");
     if (((uintptr_t)planes & 127) != 0) return fail(kInvalidArg, "moe (tcgen05, native e4m3): split planes must be 128-byte aligned");

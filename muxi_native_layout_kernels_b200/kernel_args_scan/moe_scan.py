@@ -105,7 +105,8 @@ def scan_case(cfg, T, w1, w2, wg, g, dev):
                     g1_best, g1_us = (200 + st1, ck1), us
             if g1_best is None:
                 continue
-            for st2, ck2 in itertools.product([2, 3, 4, 6], [1, 2, 3, 4, 6]):
+            # second GEMM: CTAs per cluster, or 10 + row tiles per CTA (no cluster)
+            for st2, ck2 in itertools.product([2, 3, 4, 6], [1, 2, 4, 11, 12, 14, 16, 18]):
                 args = (nt, g1_best[0], g1_best[1], 0, 200 + st2, ck2)
                 us = try_args(args)
                 if us is not None and us < best_us:
