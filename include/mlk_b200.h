@@ -261,7 +261,20 @@ int mlk_moe_align(int batchSize, int expertCount, int topK, int microBatchSize, 
  * w2_scale [E,H/128,I/128] (NULL = ones).
  * tune: NULL, or six host ints {token tiles per work item (1,2,4,8 = 8..64 slots), row warps of GEMM1 (1,2,4),
  * cluster split-K of GEMM1 (1,2,4,8), row groups per warp of GEMM2 (1,2), row warps of GEMM2 (1,2,4), cluster split-K of
- * GEMM2}; a 0 lets the library choose that value from the shape.
+ * GEMM2}; a 0 lets the library choose that value from the shape.  Values of the two "row warps" fields select
+ * the kernel family:
+ *     1, 2, 4        warp-level mma.sync kernels (any shape, 16-bit atomics or fp32 combine)
+ *     100 + stages   tcgen05 kernels, 16-bit weights or e4m3 decoded to bf16 on the way into tensor memory (block
+ *                    scales allowed); needs hidden % 128 == 0, inter % 128 == 0 and a combine scratch; token tiles
+ *                    per work item may then also be 16 (128 slots, 16-bit weights only)
+ *     200 + stages   tcgen05 kernels that multiply the e4m3 weight bytes undecoded (kind::f8f6f4): the routed token
+ *                    rows and the activation are rewritten as two e4m3 terms under a per-row power-of-two scale.
+ *                    e4m3 weights without block scales only; with scales or 16-bit weights the same row runs as
+ *                    100 + stages.  For this family "cluster split-K of GEMM2" = 10 + R (R = 1..8) selects the
+ *                    second-GEMM kernel without a cluster in which one CTA walks R consecutive 128-row tiles of
+ *                    the same work item.
+ *   Both fields name the same family; a mixed pair, or a tcgen05 family on a call that cannot use it, runs the
+ *   warp-level kernels with the library's own values.  ring stages: 2..8.
  * status: one device int, sticky error word of the bounded waits inside the tcgen05 expert kernels (0 = ok), or NULL.
  * out_fp32 != 0 (needs combine_scratch): y is [T, H] fp32 and receives the un-rounded sums over this rank's experts,
  *   so that an expert-parallel caller can add the ranks' shares before the one rounding.
