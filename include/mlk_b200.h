@@ -273,6 +273,8 @@ int mlk_moe_align(int batchSize, int expertCount, int topK, int microBatchSize, 
  *                    100 + stages.  For this family "cluster split-K of GEMM2" = 10 + R (R = 1..8) selects the
  *                    second-GEMM kernel without a cluster in which one CTA walks R consecutive 128-row tiles of
  *                    the same work item.
+ *     300            decode batches (batch_size <= 8, batch_size * topK <= 64): the whole expert compute as one
+ *                    cooperative kernel, see mlk_fused_routing_experts_compute; larger batches run the library's choice
  *   Both fields name the same family; a mixed pair, or a tcgen05 family on a call that cannot use it, runs the
  *   warp-level kernels with the library's own values.  ring stages: 2..8.
  * status: one device int, sticky error word of the bounded waits inside the tcgen05 expert kernels (0 = ok), or NULL.
@@ -290,6 +292,27 @@ int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int
                               int dtype, int fp8_order, int microBatchSize, const int32_t* experts_map,
                               int experts_map_len, float* combine_scratch, int64_t combine_scratch_bytes,
                               const int32_t* tune, int32_t* status, int out_fp32, mlk_stream_t s);
+
+/* Routing and expert compute in one call: mlk_fused_routing_gate_renorm on gating_output [batch_size, num_experts]
+ * (arguments as there; topk_ids and topk_weights are OUTPUTS here) followed by mlk_fused_experts_compute (all other
+ * arguments as there).  Same results as the two calls.  For decode batches -- at most 8 tokens and 64 routed slots,
+ * num_experts <= 256, both "row warps" fields of tune >= 300 -- the whole layer is one cooperative kernel, one CTA per
+ * SM: every CTA routes the tokens for itself, a producer warp streams the CTA's share of both weight matrices through a
+ * 192 KB shared-memory ring with bulk copies, sixteen consumer warps multiply the segments as they land, one bounded
+ * grid barrier separates the two GEMMs, and the per-token sums are formed in the CTA that owns the output rows (no
+ * combine scratch needed on that path).  Every other call runs the router kernel and then the expert compute.
+ * (The same tuning values on mlk_fused_experts_compute run the decode kernel without the routing.)
+ * Reference: the sequence issued by muxi_layout_kernels/muxi_moe_planC.py:56-149. */
+int mlk_fused_routing_experts_compute(const void* gating_output, int num_experts, int score_fun, int n_groups,
+                                      int topK_groups, const void* gating_bias, int renormalize, const void* w1,
+                                      const void* w2, const void* x, int batch_size, int expert_count, int topK,
+                                      int hidden, int inter, int32_t* topk_ids, void* topk_weights,
+                                      int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
+                                      int32_t* experts_ids, void* C, void* y, const float* w1_scale,
+                                      const float* w2_scale, int dtype, int fp8_order, int microBatchSize,
+                                      const int32_t* experts_map, int experts_map_len, float* combine_scratch,
+                                      int64_t combine_scratch_bytes, const int32_t* tune, int32_t* status, int out_fp32,
+                                      mlk_stream_t s);
 
 /* Expert compute for callers that must not allocate device memory (a plugin running under another runtime's memory
  * pool, a serving loop whose allocator is off limits on the request path).  It has no

@@ -35,6 +35,7 @@ SOURCES = [
     "moe_experts.cu",
     "moe_umma.cu",
     "moe_umma_f8n.cu",
+    "moe_decode.cu",
     "moe_exchange.cu",
     "selector.cpp",
 ]

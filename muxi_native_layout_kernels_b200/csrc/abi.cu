@@ -471,6 +471,27 @@ int mlk_fused_experts_compute(const void* w1, const void* w2, const void* x, int
     return launch_fused_experts(p, (cudaStream_t)s);
 }
 
+int mlk_fused_routing_experts_compute(const void* gating_output, int num_experts, int score_fun, int n_groups,
+                                      int topK_groups, const void* gating_bias, int renormalize, const void* w1,
+                                      const void* w2, const void* x, int batch_size, int expert_count, int topK,
+                                      int hidden, int inter, int32_t* topk_ids, void* topk_weights,
+                                      int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,
+                                      int32_t* experts_ids, void* C, void* y, const float* w1_scale,
+                                      const float* w2_scale, int dtype, int fp8_order, int microBatchSize,
+                                      const int32_t* experts_map, int experts_map_len, float* combine_scratch,
+                                      int64_t combine_scratch_bytes, const int32_t* tune, int32_t* status, int out_fp32,
+                                      mlk_stream_t s) {
+    clear_error();
+    if (!gating_output) return fail(kInvalidArg, "fused_routing_experts_compute: gating_output is null");
+    MoeParams p = moe_params(w1, w2, x, batch_size, expert_count, topK, hidden, inter, topk_ids, topk_weights,
+                             sorted_token_ids, cumsum_buffer, padded_num_experts, experts_ids, C, y, w1_scale, w2_scale,
+                             dtype, fp8_order, microBatchSize, experts_map, experts_map_len, tune, status, out_fp32);
+    p.scratch = combine_scratch; p.scratch_bytes = combine_scratch_bytes;
+    p.gating = gating_output; p.gating_bias = gating_bias; p.n_global = num_experts; p.score_fun = score_fun;
+    p.n_groups = n_groups; p.topk_groups = topK_groups; p.renormalize = renormalize;
+    return launch_fused_experts(p, (cudaStream_t)s);
+}
+
 int mlk_fused_experts_compute_static(const void* w1, const void* w2, const void* x, int batch_size, int expert_count,
                                      int topK, int hidden, int inter, const int32_t* topk_ids, const void* topk_weights,
                                      int32_t* sorted_token_ids, int32_t* cumsum_buffer, int32_t* padded_num_experts,

@@ -50,6 +50,10 @@ struct MoeParams {
     float* scratch;               // optional [T*topk, H] fp32 for the deterministic combine
     long long scratch_bytes;
     int y_fp32;                   // y is [T, H] fp32: the token sums un-rounded (needs the combine scratch)
+    // routing fused in front (mlk_fused_routing_experts_compute): gating != nullptr makes topk_ids / topk_weights outputs
+    const void* gating;           // [T, n_global_experts] router logits, activation dtype
+    const void* gating_bias;
+    int n_global, score_fun, n_groups, topk_groups, renormalize;
     int* status;                  // sticky error word of the bounded waits inside the tcgen05 kernels (0 = ok), or null
     int nt, wm1, sk1, rg, wm2, sk2;   // tuning (0 = choose by shape): token tiles, GEMM1 row warps / split-K, GEMM2 row groups / row warps / split-K;
                                       // wm1 = 100 + s1 and wm2 = 100 + s2 select the tcgen05 kernels (combine scratch given)
@@ -77,6 +81,10 @@ int launch_moe_umma_f8n(int mode, const void* W, int E, int rows, int k, const v
                         long long plane_rows, void* out, const int4* worklist, const int32_t* sorted,
                         const void* topk_weights, int n_slots, int np, int stages, int cluster_k, int max_items, int* status,
                         cudaStream_t s);
+// decode batches (at most 8 tokens, 64 routed slots) as one cooperative kernel (moe_decode.cu); tuning values of 300 or
+// more in both "row warps" fields select it
+bool moe_decode_supported(const MoeParams& m);
+int launch_moe_decode(const MoeParams& m, cudaStream_t s);
 int launch_fused_experts_static(const MoeParams& p, cudaStream_t s);   // combine scratch in a built-in device array
 
 // Expert-parallel exchange helpers (moe_exchange.cu).

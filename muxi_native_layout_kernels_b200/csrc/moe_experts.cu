@@ -330,6 +330,20 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
     const long long slots = (long long)m.T * m.topk;
     const long long mean2 = (2 * slots + m.E - 1) / m.E;
     const long long want = std::min<long long>(m.T, mean2);
+    // decode batches as one cooperative kernel (moe_decode.cu): tuning values of 300 or more for both GEMMs; a routing
+    // fused in front runs inside that kernel too
+    if (m.wm1 >= 300 && m.wm2 >= 300) {
+        if (moe_decode_supported(m)) return launch_moe_decode(m, s);
+        m.nt = m.wm1 = m.sk1 = m.rg = m.wm2 = m.sk2 = 0;     // too many tokens for it: the library's own choice
+    }
+    if (m.gating != nullptr) {
+        // every other path: the router kernel first
+        if (int st = launch_router(m.gating, m.score_fun, m.T, m.n_global, m.n_groups, m.topk_groups,
+                                   const_cast<int32_t*>(m.topk_ids), const_cast<void*>(m.topk_weights), m.topk, m.gating_bias,
+                                   m.dtype == kFP16 ? 1 : 0, s, m.renormalize))
+            return st;
+        m.gating = nullptr;
+    }
     // No tuning arguments at all (a geometry without a row in the table): the tcgen05 kernels where they apply.
     // 16-bit weights always; e4m3 from about 16 slots per expert on (below that the warp-level kernels, which
     // decode in the registers of many small CTAs, measured faster).  One cluster per (work item, 128-row tile):

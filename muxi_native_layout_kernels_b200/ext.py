@@ -587,7 +587,10 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
     ``deterministic`` (default True) sums each token's expert outputs in fp32 in a fixed order with one rounding,
     False uses 16-bit atomic adds into ``y`` as the reference does; a float32 ``y`` (deterministic only) receives the
     un-rounded sums; ``tune`` = six launch integers (token tiles per
-    work item, GEMM1 row warps, GEMM1 split-K, GEMM2 row groups per warp, GEMM2 row warps, GEMM2 split-K; 0 = automatic).
+    work item, GEMM1 row warps, GEMM1 split-K, GEMM2 row groups per warp, GEMM2 row warps, GEMM2 split-K; 0 = automatic);
+    ``routing`` = (gating_output, score_fun, n_groups, topK_groups, gating_bias, renormalize) runs ``fused_routing_gate``
+    in front inside the same library call (``topk_ids`` and ``actived_experts_weights`` become outputs): for decode
+    batches with the single-kernel tuning (300) the whole layer is then one launch.
     """
     w1, w2, x = experts_weights_matrix1, experts_weights_matrix2, activations
     fp8_form = (len(args) > 0 and not isinstance(args[0], int)) or any(
@@ -596,6 +599,7 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
     deterministic = bool(kwargs.pop("deterministic", True))
     out_fp32 = y.dtype == torch.float32 and activations.dtype != torch.float32
     tune = kwargs.pop("tune", None)
+    routing = kwargs.pop("routing", None)
     if fp8_form:
         names = ["w1_scale", "w2_scale", "block_shape", "soft_fp8", "microBatchSize", "experts_map"]
         vals = {"soft_fp8": False, "microBatchSize": 16, "experts_map": None}
@@ -664,14 +668,25 @@ def fused_experts_compute(experts_weights_matrix1, experts_weights_matrix2, acti
     tune_arr = (ctypes.c_int32 * 6)(*t6)
     # fp32 [slots, H] buffer for the fixed-order combine (torch's caching allocator makes this a pointer bump)
     scratch = torch.empty((batch_size * topK, k1), dtype=torch.float32, device=x.device) if deterministic else None
-    check(lib.mlk_fused_experts_compute(w1.data_ptr(), w2.data_ptr(), x.data_ptr(), batch_size, E, topK, k1, k2,
-                                        topk_ids.data_ptr(), actived_experts_weights.data_ptr(),
-                                        sorted_token_ids.data_ptr(), cumsum_buffer.data_ptr(),
-                                        padded_num_experts.data_ptr(), experts_ids.data_ptr(), C.data_ptr(),
-                                        y.data_ptr(), _ptr(w1s), _ptr(w2s), code, int(fp8_repacked),
-                                        int(vals["microBatchSize"]), mp, ml, _ptr(scratch),
-                                        0 if scratch is None else scratch.numel() * 4, tune_arr, _status_ptr(x),
-                                        int(out_fp32), _stream(x)))
+    tail = (w1.data_ptr(), w2.data_ptr(), x.data_ptr(), batch_size, E, topK, k1, k2, topk_ids.data_ptr(),
+            actived_experts_weights.data_ptr(), sorted_token_ids.data_ptr(), cumsum_buffer.data_ptr(),
+            padded_num_experts.data_ptr(), experts_ids.data_ptr(), C.data_ptr(), y.data_ptr(), _ptr(w1s), _ptr(w2s), code,
+            int(fp8_repacked), int(vals["microBatchSize"]), mp, ml, _ptr(scratch),
+            0 if scratch is None else scratch.numel() * 4, tune_arr, _status_ptr(x), int(out_fp32), _stream(x))
+    if routing is None:
+        check(lib.mlk_fused_experts_compute(*tail))
+        return
+    # routing fused in front: (gating_output, score_fun, n_groups, topK_groups, gating_bias, renormalize); topk_ids and
+    # actived_experts_weights are then outputs
+    gating, score_fun, n_groups, topk_groups, gbias, renorm = routing
+    _cuda_contig(gating, "gating_output")
+    _chk(gating.dtype == x.dtype and gating.dim() == 2 and gating.size(0) == batch_size,
+         "gating_output must be [batch_size, num_experts] in the activation dtype")
+    if gbias is not None:
+        _cuda_contig(gbias, "gating_bias")
+        _chk(gbias.dtype == gating.dtype and gbias.numel() == gating.size(1), "gating_bias must be [num_experts] in the logits' dtype")
+    check(lib.mlk_fused_routing_experts_compute(gating.data_ptr(), gating.size(1), int(score_fun), int(n_groups),
+                                                int(topk_groups), _ptr(gbias), int(bool(renorm)), *tail))
 
 
 # ---------------------------------------------------------------------------------------------------

@@ -112,9 +112,21 @@ def fused_moe(
     # 1. router
     topk_ids = torch.empty(B, topk, dtype=torch.int32, device=dev)
     topk_weights = torch.empty(B, topk, dtype=hidden_states.dtype, device=dev)
+    e1, m1, k1 = w1.shape
+    e2, m2, k2 = w2.shape
+    if tune is None:
+        # with an experts_map (expert parallelism) the work per local expert is that of the full layer: the row of
+        # the global expert count applies
+        tune = lookup_moe_args(num_experts if experts_map is not None else e1, topk, H, k2, soft_fp8, B)
+    # decode batches tuned for the single-kernel path: the routing runs inside the expert-compute call (one launch
+    # for the whole layer); otherwise the router kernel comes first
+    routing = None
+    if gate_weight is None and tune is not None and len(tune) == 6 and tune[1] >= 300 and tune[4] >= 300 and B <= 8 and B * topk <= 64 \
+            and num_experts <= 256:
+        routing = (gating_output, score_fun, num_expert_group, topk_group, gating_bias, bool(renormalize))
     # renormalisation (reference: two torch ops, muxi_moe_planC.py:69-70) happens inside the router kernel, with the
     # same roundings
-    if gate_weight is not None:
+    elif gate_weight is not None:
         ext.fused_router_gemm_gate(hidden_states, gate_weight, score_fun, num_expert_group, topk_group, topk_ids,
                                    topk_weights, topk, gating_bias, renormalize=bool(renormalize))
     else:
@@ -122,8 +134,6 @@ def fused_moe(
                                topk, gating_bias, renormalize=bool(renormalize))
 
     # 2. experts
-    e1, m1, k1 = w1.shape
-    e2, m2, k2 = w2.shape
     assert e1 == e2
     assert k1 == m2
     micro_batchsize = 16
@@ -147,10 +157,6 @@ def fused_moe(
     else:
         y = torch.empty_like(hidden_states) if deterministic else torch.zeros_like(hidden_states)
 
-    if tune is None:
-        # with an experts_map (expert parallelism) the work per local expert is that of the full layer: the row of
-        # the global expert count applies
-        tune = lookup_moe_args(num_experts if experts_map is not None else e1, topk, H, k2, soft_fp8, B)
     if experts_map is not None and experts_map.dtype != torch.int:
         experts_map = experts_map.to(torch.int)
     if soft_fp8:
@@ -158,13 +164,13 @@ def fused_moe(
                                   cumsum_buffer, padded_num_experts, experts_ids, C, y, w1_scale, w2_scale,
                                   block_shape if block_shape is not None else [128, 128], soft_fp8,
                                   experts_map=experts_map, fp8_repacked=fp8_repacked, deterministic=deterministic,
-                                  tune=tune)
+                                  tune=tune, routing=routing)
     else:
         ext.fused_experts_compute(w1, w2, hidden_states, B, e1, topk, topk_ids, topk_weights, sorted_token_ids,
                                   cumsum_buffer, padded_num_experts, experts_ids, C, y, APerWarp=APerWarp,
                                   splitK=splitK, tile_m_2=tile_m_2, tile_n_2=tile_n_2, tile_k_2=tile_k_2,
                                   block_dim_x_gemm=block_dim_x_gemm, experts_map=experts_map,
-                                  deterministic=deterministic, tune=tune)
+                                  deterministic=deterministic, tune=tune, routing=routing)
     return y.view(shape)
 
 

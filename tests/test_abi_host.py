@@ -149,7 +149,9 @@ def test_packaged_table_rows_name_launches_the_library_accepts():
         what = (E, topk, H, I, fp8, T, nt, wm1, sk1, rg2, wm2, sk2)
         assert nt in (1, 2, 4, 8) or (nt == 16 and wm1 >= 100 and not fp8), what
         assert (wm1 >= 100) == (wm2 >= 100), what
-        if wm1 >= 100:       # tcgen05 expert GEMMs: 100 (decode) or 200 (native e4m3) + ring stages, CTAs per cluster
+        if wm1 >= 300:       # decode batches as one cooperative kernel
+            assert wm2 >= 300 and T <= 8 and T * topk <= 64 and H % 32 == 0 and I % 32 == 0, what
+        elif wm1 >= 100:     # tcgen05 expert GEMMs: 100 (decode) or 200 (native e4m3) + ring stages, CTAs per cluster
             fam = 200 if wm1 >= 200 else 100
             assert H % 128 == 0 and I % 128 == 0 and (fam == 100 or fp8) and (wm2 >= 200) == (wm1 >= 200), what
             assert wm1 - fam in (2, 3, 4, 6) and wm2 - fam in (2, 3, 4, 6) and 1 <= sk1 <= min(8, H // 64), what

@@ -325,6 +325,193 @@ def test_moe_soft_fp8_native_tensor_core_expert_gemms(T, repack):
                  tune=(2, 203, 2, 0, 203, 2))
 
 
+@pytest.mark.parametrize("T", [1, 2, 5, 8])
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "fp8", "fp8_repacked", "fp8_scaled"])
+def test_moe_decode_single_kernel(kind, T):
+    """Tuning values of 300 in both row-warp fields: the whole expert compute of a decode batch (at most 8 tokens, 64
+    routed slots) as one cooperative kernel with the weights streamed through a shared-memory ring by bulk copies.
+    Against the oracle and the warp-level three-launch path; replays must agree bit for bit (fixed summation orders,
+    and the kernel's counters must come back to zero between launches)."""
+    dev = require_gpu()
+    E, topk, H, I = 32, 8, 256, 128
+    fp8 = kind.startswith("fp8")
+    dt = torch.float16 if kind == "fp16" else torch.bfloat16
+    x = randn((T, H), 1000 + T, 1.0, dt)
+    logits = randn((T, E), 1003 + T, 1.0, dt)
+    scales = None
+    if fp8:
+        w1 = rand_e4m3((E, 2 * I, H), 1001, 0.25)
+        w2 = rand_e4m3((E, H, I), 1002, 0.25)
+        if kind == "fp8_scaled":
+            g = torch.Generator().manual_seed(1004)
+            scales = (torch.rand(E, 2 * I // 128, H // 128, generator=g) * 0.5 + 0.01,
+                      torch.rand(E, H // 128, I // 128, generator=g) * 0.5 + 0.01)
+    else:
+        w1 = randn((E, 2 * I, H), 1001, 0.05, dt)
+        w2 = randn((E, H, I), 1002, 0.05, dt)
+    repack = kind == "fp8_repacked"
+    y0 = _moe_compare(x, w1, w2, logits, topk, f"moe warp-level {kind} T={T}", fp8=fp8, scales=scales, repack=repack,
+                      tune=(1, 2, 1, 1, 2, 1))
+    tune = (1, 300, 1, 0, 300, 1)
+    first = None
+    for rep in range(4):
+        y = _moe_compare(x, w1, w2, logits, topk, f"moe decode {kind} T={T}", fp8=fp8, scales=scales, repack=repack, tune=tune)
+        assert_close(y, y0.float().cpu(), f"decode kernel vs warp-level {kind} T={T}", scale_atol=True)
+        first = y if first is None else first
+        assert torch.equal(y, first), (kind, T, rep)
+    assert mlk.kernel_status() == 0
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8", "fp8_scaled"])
+@pytest.mark.parametrize("T,E,topk,H,I", [(1, 8, 2, 1024, 3584), (3, 16, 4, 2048, 768), (8, 64, 8, 512, 1536), (2, 8, 8, 96, 160)])
+def test_moe_decode_single_kernel_shapes(kind, T, E, topk, H, I):
+    """Shapes that exercise the ring: more segments per unit than consumer warps (K = 3584 in 16-bit = 14 segments),
+    segment counts that do not divide the warps (3, 5, 6), several laps of the ring, K not a multiple of 128."""
+    if kind == "fp8_scaled" and (H % 128 or I % 128):
+        pytest.skip("block scales need multiples of 128")
+    fp8 = kind.startswith("fp8")
+    x = randn((T, H), 1300 + T, 1.0)
+    logits = randn((T, E), 1303 + T, 1.0)
+    scales = None
+    if fp8:
+        w1 = rand_e4m3((E, 2 * I, H), 1301, 0.25)
+        w2 = rand_e4m3((E, H, I), 1302, 0.25)
+        if kind == "fp8_scaled":
+            g = torch.Generator().manual_seed(1304)
+            scales = (torch.rand(E, 2 * I // 128, H // 128, generator=g) * 0.5 + 0.01,
+                      torch.rand(E, H // 128, I // 128, generator=g) * 0.5 + 0.01)
+    else:
+        w1 = randn((E, 2 * I, H), 1301, 0.03)
+        w2 = randn((E, H, I), 1302, 0.03)
+    _moe_compare(x, w1, w2, logits, topk, f"moe decode {kind} {(T, E, topk, H, I)}", fp8=fp8, scales=scales,
+                 tune=(1, 300, 1, 0, 300, 1))
+    assert mlk.kernel_status() == 0
+
+
+def test_moe_decode_single_kernel_expert_map_and_fallback():
+    dev = require_gpu()
+    E, topk, H, I, T = 16, 4, 128, 128, 6
+    x = randn((T, H), 1100).to(dev)
+    w1 = mlk.layoutA(randn((E, 2 * I, H), 1101, 0.05).to(dev))
+    w2 = mlk.layoutA(randn((E, H, I), 1102, 0.05).to(dev))
+    logits = randn((T, E), 1103).to(dev)
+    tune = (1, 300, 1, 0, 300, 1)
+    full = planC_moe(x, w1, w2, logits, topk, True, tune=tune)
+    assert_close(full, planC_moe(x, w1, w2, logits, topk, True, tune=(1, 2, 1, 1, 2, 1)).float().cpu(), 'decode vs warp-level')
+    assert torch.equal(planC_moe(x[:1], w1, w2, logits[:1], topk, True, tune=tune), full[:1])
+    acc = torch.zeros(T, H, dtype=torch.float32, device=dev)
+    for rank in range(4):
+        lo = rank * 4
+        emap = torch.full((E,), -1, dtype=torch.int32)
+        emap[lo:lo + 4] = torch.arange(4, dtype=torch.int32)
+        part = planC_moe(x, w1[lo:lo + 4].contiguous(), w2[lo:lo + 4].contiguous(), logits, topk, True,
+                         experts_map=emap.to(dev), tune=tune, out_dtype=torch.float32)
+        assert part.dtype == torch.float32
+        acc += part
+    assert_close(acc.to(torch.bfloat16), full.float().cpu(), "decode kernel, EP shares", atol=2e-2, rtol=2e-2)
+    # 40 tokens are more than the kernel takes: the same tuning row runs the library's own choice
+    T2 = 40
+    x2, l2 = randn((T2, H), 1104).to(dev), randn((T2, E), 1105).to(dev)
+    assert_close(planC_moe(x2, w1, w2, l2, topk, True, tune=tune), planC_moe(x2, w1, w2, l2, topk, True).float().cpu(),
+                 "decode tuning on a large batch", atol=2e-2, rtol=2e-2)
+    assert mlk.kernel_status() == 0
+
+
+@pytest.mark.parametrize("case", ROUTER_CASES)
+@pytest.mark.parametrize("T", [1, 4, 8])
+def test_moe_decode_single_kernel_routes_like_the_router_kernel(case, T):
+    """With the routing fused in front (one launch for the whole layer) topk_ids / topk_weights must equal the router
+    kernel's bit for bit, and the layer must equal the two-call form bit for bit, for every routing configuration."""
+    dev = require_gpu()
+    E, topk, G, KG, use_bias, score = case
+    if T * topk > 64:
+        pytest.skip("more routed slots than the single-kernel path takes")
+    H, I = 128, 64
+    x = randn((T, H), 1400 + T).to(dev)
+    logits = randn((T, E), 1401 + T + E).to(dev)
+    bias = randn((E,), 1402, 0.1).to(dev) if use_bias else None
+    w1 = mlk.layoutA(randn((E, 2 * I, H), 1403, 0.05).to(dev))
+    w2 = mlk.layoutA(randn((E, H, I), 1404, 0.05).to(dev))
+    sf = 0 if score == "softmax" else 1
+    ids0 = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    wts0 = torch.empty(T, topk, dtype=torch.bfloat16, device=dev)
+    mlk.fused_routing_gate(logits, sf, T, H, G, KG, ids0, wts0, topk, bias, renormalize=True)
+    mbs = 16
+    n = T * topk + E * (mbs - 1)
+
+    def run(routing, ids, wts):
+        bufs = [torch.empty(n, dtype=torch.int32, device=dev), torch.empty(E + 1, dtype=torch.int32, device=dev),
+                torch.empty(1, dtype=torch.int32, device=dev), torch.empty((n + mbs - 1) // mbs, dtype=torch.int32, device=dev)]
+        C = torch.empty(T * topk * 2 * I, dtype=torch.bfloat16, device=dev)
+        y = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+        mlk.fused_experts_compute(w1, w2, x, T, E, topk, ids, wts, *bufs, C, y, microBatchSize=mbs,
+                                  tune=(1, 300, 1, 0, 300, 1), routing=routing)
+        return y
+
+    y0 = run(None, ids0, wts0)
+    ids1 = torch.full_like(ids0, -5)
+    wts1 = torch.zeros_like(wts0)
+    y1 = run((logits, sf, G, KG, bias, True), ids1, wts1)
+    torch.cuda.synchronize()
+    assert torch.equal(ids1, ids0) and torch.equal(wts1, wts0), case
+    assert torch.equal(y1, y0), case
+    # the same call with a tuning row of another family: router kernel + expert kernels inside the one library call
+    ids2 = torch.full_like(ids0, -5)
+    wts2 = torch.zeros_like(wts0)
+    bufs = [torch.empty(n, dtype=torch.int32, device=dev), torch.empty(E + 1, dtype=torch.int32, device=dev),
+            torch.empty(1, dtype=torch.int32, device=dev), torch.empty((n + mbs - 1) // mbs, dtype=torch.int32, device=dev)]
+    y2 = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+    mlk.fused_experts_compute(w1, w2, x, T, E, topk, ids2, wts2, *bufs, torch.empty(T * topk * 2 * I, dtype=torch.bfloat16, device=dev),
+                              y2, microBatchSize=mbs, tune=(1, 2, 1, 1, 2, 1), routing=(logits, sf, G, KG, bias, True))
+    torch.cuda.synchronize()
+    assert torch.equal(ids2, ids0) and torch.equal(wts2, wts0), case
+    assert_close(y2, y0.float().cpu(), f"routed call, warp-level kernels {case}")
+    assert mlk.kernel_status() == 0
+
+
+@pytest.mark.parametrize("T,E,topk,mapped", [(1, 8, 2, False), (8, 128, 8, False), (5, 16, 4, True)])
+def test_moe_decode_single_kernel_leaves_the_alignment_outputs(T, E, topk, mapped):
+    """The single-kernel path fills sorted_token_ids / cumsum_buffer / padded_num_experts / experts_ids as the
+    stand-alone alignment op does (slot order inside an expert is unspecified in the contract)."""
+    dev = require_gpu()
+    H, I, mbs = 128, 64, 16
+    g = torch.Generator().manual_seed(1200 + T)
+    ids = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(T)]).to(torch.int32)
+    emap = None
+    n_local = E
+    if mapped:
+        n_local = E // 2
+        emap = torch.full((E,), -1, dtype=torch.int32)
+        emap[::2] = torch.arange(n_local, dtype=torch.int32)
+    want_sorted, want_cumsum, want_nblk, want_blk = _run_align(ids, n_local, mbs, emap, dev)
+    x = randn((T, H), 1201).to(dev)
+    w1 = mlk.layoutA(randn((n_local, 2 * I, H), 1202, 0.05).to(dev))
+    w2 = mlk.layoutA(randn((n_local, H, I), 1203, 0.05).to(dev))
+    wts = torch.full((T, topk), 1.0 / topk, dtype=torch.bfloat16, device=dev)
+    n = T * topk + n_local * (mbs - 1)
+    sorted_ids = torch.full((n,), -3, dtype=torch.int32, device=dev)
+    cumsum = torch.full((n_local + 1,), -3, dtype=torch.int32, device=dev)
+    nblk = torch.full((1,), -3, dtype=torch.int32, device=dev)
+    blk = torch.full(((n + mbs - 1) // mbs,), -3, dtype=torch.int32, device=dev)
+    C = torch.empty(T * topk * 2 * I, dtype=torch.bfloat16, device=dev)
+    y = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+    mlk.fused_experts_compute(w1, w2, x, T, n_local, topk, ids.to(dev), wts, sorted_ids, cumsum, nblk, blk, C, y,
+                              microBatchSize=mbs, experts_map=None if emap is None else emap.to(dev),
+                              tune=(1, 300, 1, 0, 300, 1))
+    torch.cuda.synchronize()
+    assert torch.equal(cumsum.cpu(), want_cumsum) and int(nblk.item()) == want_nblk
+    assert torch.equal(blk.cpu(), want_blk)
+    got_sorted = sorted_ids.cpu()
+    start = 0
+    for e in range(n_local):
+        end = int(want_cumsum[e])
+        padded_end = start + ((end - start + mbs - 1) // mbs) * mbs
+        assert sorted(got_sorted[start:end].tolist()) == sorted(want_sorted[start:end].tolist())
+        assert bool((got_sorted[end:padded_end] == T * topk).all())
+        start = padded_end
+    assert bool((got_sorted[start:] == T * topk).all())
+
+
 @pytest.mark.parametrize("T", [1, 32, 130])
 @pytest.mark.parametrize("repack", [False, True])
 def test_moe_soft_fp8_tcgen05_block_scales(T, repack):
