@@ -145,6 +145,47 @@ __device__ __forceinline__ void split_row_cta(const uint4* xr, bool zero_row, in
     }
 }
 
+// The same for one row per WARP (k <= 32 * 8 * kSplitChunks = 2048): no CTA barrier, all of the row's loads in flight
+// at once, one warp-wide maximum.  Every lane of the warp must call it.
+constexpr int kSplitWarpMaxK = 32 * 8 * kSplitChunks;
+
+__device__ __forceinline__ void split_row_warp(const uint4* xr, int k, int repacked, uint8_t* out, float* inv_scale) {
+    const int chunks = k >> 3;
+    const int lane = threadIdx.x & 31;
+    uint4 v[kSplitChunks];
+    uint32_t m = 0;
+#pragma unroll
+    for (int r = 0; r < kSplitChunks; ++r) {
+        const int c = lane + r * 32;
+        v[r] = make_uint4(0u, 0u, 0u, 0u);
+        if (c < chunks)
+            asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[r].x), "=r"(v[r].y), "=r"(v[r].z), "=r"(v[r].w) : "l"(xr + c));
+    }
+#pragma unroll
+    for (int r = 0; r < kSplitChunks; ++r) {
+        const uint32_t w[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            m = max(m, w[i] & 0x7FFFu);
+            m = max(m, (w[i] >> 16) & 0x7FFFu);
+        }
+    }
+    m = __reduce_max_sync(0xFFFFFFFFu, m);      // also: every lane's loads of the row have completed (in-place use)
+    const float sc = row_scale_from_bits(m);
+    if (lane == 0) *inv_scale = 1.f / sc;       // exact: a power of two
+#pragma unroll
+    for (int r = 0; r < kSplitChunks; ++r) {
+        const int c = lane + r * 32;
+        if (c < chunks) {
+            uint2 hi8, lo8;
+            split_chunk(v[r], sc, repacked, hi8, lo8);
+            uint8_t* const dst = out + (c >> 3) * 128 + (c & 7) * 8;
+            *reinterpret_cast<uint2*>(dst) = hi8;
+            *reinterpret_cast<uint2*>(dst + 64) = lo8;
+        }
+    }
+}
+
 // CTA size for rows of k elements: a multiple of 32 with kSplitChunks chunks per thread at most
 inline int split_threads(int k) {
     const int chunks = k / 8;

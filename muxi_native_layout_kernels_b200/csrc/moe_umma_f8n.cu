@@ -481,6 +481,29 @@ __global__ void __launch_bounds__(512) moe_split_inplace_kernel(uint4* __restric
     split_row_cta(r, false, k, repacked, reinterpret_cast<uint8_t*>(r), inv_scale + row);
 }
 
+// The two kernels above with one row per warp (rows of at most 2048 elements): eight rows per CTA, no CTA barrier.
+__global__ void __launch_bounds__(256) moe_split_gather_warp_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ cpos_slot,
+                                                                   const int4* __restrict__ worklist, int topk, int k,
+                                                                   int repacked, uint8_t* __restrict__ planes,
+                                                                   float* __restrict__ inv_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= worklist[0].y) return;
+    const int token = cpos_slot[row] / topk;
+    split_row_warp(x + (size_t)token * (k >> 3), k, repacked, planes + (size_t)row * 2 * k, inv_scale + row);
+}
+
+__global__ void __launch_bounds__(256) moe_split_inplace_warp_kernel(uint4* __restrict__ act, const int4* __restrict__ worklist,
+                                                                    int k, int repacked, float* __restrict__ inv_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= worklist[0].y) return;
+    uint4* const r = act + (size_t)row * (k >> 3);
+    split_row_warp(r, k, repacked, reinterpret_cast<uint8_t*>(r), inv_scale + row);
+}
+
 template <int NP, int MODE>
 const void* kernel_for_stages(int stages) {
     switch (stages) {
@@ -520,10 +543,12 @@ const void* rows_kernel_for(int np, int stages) {
     return nullptr;
 }
 
-int launch_split(const void* kern, void** args, int rows, int k, cudaStream_t s) {
+int launch_split(const void* kern, const void* warp_kern, void** args, int rows, int k, cudaStream_t s) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)rows);
-    cfg.blockDim = dim3(split_threads(k));
+    const bool by_warp = k <= kSplitWarpMaxK;
+    if (by_warp) kern = warp_kern;
+    cfg.gridDim = dim3((unsigned)(by_warp ? (rows + 7) / 8 : rows));
+    cfg.blockDim = dim3(by_warp ? 256 : split_threads(k));
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
     cfg.attrs = attr;
@@ -540,13 +565,15 @@ bool moe_f8n_supported(int H, int I) { return H % 128 == 0 && I % 128 == 0 && H 
 int launch_moe_split_gather(const void* x, const int32_t* cpos_slot, const int4* worklist, int topk, int H, int repacked,
                             void* planes, float* inv_scale, int n_slots, cudaStream_t s) {
     void* args[8] = {&x, &cpos_slot, &worklist, &topk, &H, &repacked, &planes, &inv_scale};
-    return launch_split(reinterpret_cast<const void*>(moe_split_gather_kernel), args, n_slots, H, s);
+    return launch_split(reinterpret_cast<const void*>(moe_split_gather_kernel), reinterpret_cast<const void*>(moe_split_gather_warp_kernel),
+                        args, n_slots, H, s);
 }
 
 int launch_moe_split_inplace(void* act, const int4* worklist, int I, int repacked, float* inv_scale, int n_slots,
                              cudaStream_t s) {
     void* args[5] = {&act, &worklist, &I, &repacked, &inv_scale};
-    return launch_split(reinterpret_cast<const void*>(moe_split_inplace_kernel), args, n_slots, I, s);
+    return launch_split(reinterpret_cast<const void*>(moe_split_inplace_kernel), reinterpret_cast<const void*>(moe_split_inplace_warp_kernel),
+                        args, n_slots, I, s);
 }
 
 // One grouped GEMM on split planes.  mode 1: W = w1 [E, 2I, k=H], planes of the gathered tokens, out = act [n_slots, I]
