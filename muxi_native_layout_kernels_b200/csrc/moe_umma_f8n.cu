@@ -77,6 +77,7 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
     auto a_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + S2 + s); };
     const uint32_t acc_full = bar0 + 8u * (2 * STAGES + 2 * S2);
 
+    int early = 0;
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full(s), 1);
@@ -89,6 +90,16 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
         mbar_init(acc_full, 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the first ring's worth of weights and planes is on its way while tensor memory is being allocated: the
+        // barriers are this thread's own, nobody else touches the ring yet
+        for (; early < STAGES && early < nunits; ++early) {
+            mbar_expect_tx(full(early), kStageBytes);
+            tma_load_3d(base + early * kStageBytes, &map_a, full(early), 0, (kb0 + early) * (kBK / 8), a_tile * (kTileM / 16));
+            if constexpr (MODE == 1)
+                tma_load_3d(base + early * kStageBytes + kRaw, &map_a, full(early), 0, (kb0 + early) * (kBK / 8),
+                            (a_tile + p.up_tile_offset) * (kTileM / 16));
+            tma_load_2d(base + early * kStageBytes + NA * kRaw, &map_x, full(early), (kb0 + early) * 128, cpos0);
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
@@ -101,10 +112,10 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_slot;
 
-    int issued = 0;
+    int issued = early;
     if (warp == 0 && lane == 0) {
         // ---- TMA producer ----
-        for (int i = 0; i < nunits; ++i) {
+        for (int i = early; i < nunits; ++i) {
             const int s = i % STAGES;
             if (i >= STAGES && !mbar_wait(empty(s), ((i / STAGES) - 1) & 1)) {
                 abort_flag = 1;
@@ -292,6 +303,7 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_rows_kernel(const __grid_
     auto acc_full = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 * S2 + b); };
     auto acc_empty = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 * S2 + AB + b); };
 
+    int early = 0;
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full(s), 1);
@@ -307,6 +319,15 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_rows_kernel(const __grid_
         }
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the first ring's worth of weights and planes is on its way while the other warps finish the prologue
+        // (tensor-memory allocation, the slots' factors): the barriers are this thread's own, nobody else touches the ring yet
+        for (; early < STAGES && early < total; ++early) {
+            const int tl = early / KB, kb = early - tl * KB;
+            mbar_expect_tx(full(early), kStageBytes);
+            tma_load_3d(base + early * kStageBytes, &map_a, full(early), 0, kb * (kBK / 8),
+                        (expert * tiles_total + tile0 + tl) * (kTileM / 16));
+            tma_load_2d(base + early * kStageBytes + kRaw, &map_x, full(early), kb * 128, cpos0);
+        }
     }
     if (tid >= 64 && tid - 64 < NP) {
         // slot and factor (inverse row scale x routing weight) of every column of the accumulator
@@ -332,11 +353,11 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_rows_kernel(const __grid_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_slot;
 
-    int issued = 0;
+    int issued = early;
     if (warp == 0 && lane == 0) {
         // ---- TMA producer: units (tile, k block), tile-major ----
-        int tl = 0, kb = 0;
-        for (int u = 0; u < total; ++u) {
+        int tl = early / KB, kb = early - tl * KB;
+        for (int u = early; u < total; ++u) {
             const int s = u % STAGES;
             if (u >= STAGES && !mbar_wait(empty(s), ((u / STAGES) - 1) & 1)) {
                 abort_flag = 1;
