@@ -276,8 +276,8 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_rows_kernel(const __grid_
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 2 * S2 + 2 * AB];
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int abort_flag;
-    __shared__ int slot_s[NP];
-    __shared__ float factor_s[NP];
+    __shared__ int slot_w[4][NP];          // per mover warp: slot and factor of every accumulator column
+    __shared__ float factor_w[4][NP];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -329,18 +329,21 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_rows_kernel(const __grid_
             tma_load_2d(base + early * kStageBytes + kRaw, &map_x, full(early), kb * 128, cpos0);
         }
     }
-    if (tid >= 64 && tid - 64 < NP) {
-        // slot and factor (inverse row scale x routing weight) of every column of the accumulator
-        const int c = tid - 64;
-        int slot = -1;
-        float f = 0.f;
-        if (c < nslots) {
-            slot = p.sorted[pos0 + c];
-            if (slot < p.n_slots) f = __ldg(p.inv_scale + cpos0 + c) * load_scalar16<kBF16>(p.topk_weights, slot);
-            else slot = -1;
+    // slot and factor (inverse row scale x routing weight) of every column of the accumulator: every mover warp loads
+    // them for itself (lane l: columns l and l + 32), so that the loads stay in flight across the prologue and the
+    // weights' first round trip ...
+    constexpr int NCH = (NP + 31) / 32;
+    int my_slot[NCH];
+    float my_factor[NCH];
+#pragma unroll
+    for (int h = 0; h < NCH; ++h) {
+        my_slot[h] = -1;
+        my_factor[h] = 0.f;
+        const int c = lane + 32 * h;
+        if (warp >= 2 && c < NP && c < nslots) {
+            my_slot[h] = p.sorted[pos0 + c];
+            my_factor[h] = __ldg(p.inv_scale + cpos0 + c);
         }
-        slot_s[c] = slot;
-        factor_s[c] = f;
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
@@ -407,6 +410,17 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_rows_kernel(const __grid_
     } else if (warp >= 2) {
         // ---- mover warps (thread = tile row = tensor-memory lane); after a tile's last k block, its epilogue ----
         const int quad = warp & 3, lrow = quad * 32 + lane;
+        // ... and published in this warp's own copy in shared memory (no barrier across the mover warps needed)
+#pragma unroll
+        for (int h = 0; h < NCH; ++h) {
+            if (my_slot[h] >= 0 && my_slot[h] < p.n_slots) my_factor[h] *= load_scalar16<kBF16>(p.topk_weights, my_slot[h]);
+            else my_slot[h] = -1;
+            if (lane + 32 * h < NP) {
+                slot_w[quad][lane + 32 * h] = my_slot[h];
+                factor_w[quad][lane + 32 * h] = my_factor[h];
+            }
+        }
+        __syncwarp();
         int u = 0;
         for (int tl = 0; tl < ntiles && !abort_flag; ++tl) {
             bool ok = true;
@@ -455,8 +469,8 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_rows_kernel(const __grid_
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const int slot = slot_s[c0 + i];
-                        if (slot >= 0) out[(size_t)slot * p.rows] = __uint_as_float(r[i]) * factor_s[c0 + i];
+                        const int slot = slot_w[quad][c0 + i];
+                        if (slot >= 0) out[(size_t)slot * p.rows] = __uint_as_float(r[i]) * factor_w[quad][c0 + i];
                     }
                 }
             }
