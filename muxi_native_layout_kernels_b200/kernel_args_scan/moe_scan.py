@@ -127,6 +127,9 @@ def main(argv=None):
     ap.add_argument("--config", default="both", choices=["mixtral", "fine", "both"])
     ap.add_argument("--tokens", default=None)
     ap.add_argument("--out", default=str(_MOE_TABLE_FILE))
+    ap.add_argument("--experts", type=int, default=None,
+                    help="expert count to scan instead of the configuration's: the rows an expert-parallel rank with that "
+                         "many local experts looks up (with tokens = global tokens x local / global experts)")
     a = ap.parse_args(argv)
     dev = torch.device("cuda")
     mlk.set_static_weights(True)
@@ -141,7 +144,9 @@ def main(argv=None):
     except FileNotFoundError:
         pass
     for name in (["mixtral", "fine"] if a.config == "both" else [a.config]):
-        cfg = CONFIGS[name]
+        cfg = dict(CONFIGS[name])
+        if a.experts is not None:
+            cfg["E"] = a.experts
         w1, w2, wg, g = build(cfg, dev)
         for T in ([int(t) for t in a.tokens.split(",")] if a.tokens else cfg["tokens"]):
             args, us = scan_case(cfg, T, w1, w2, wg, g, dev)

@@ -48,14 +48,19 @@ def _moe_table():
     return _MOE_TABLE
 
 
-def lookup_moe_args(E: int, topk: int, H: int, I: int, fp8: bool, T: int):
+def lookup_moe_args(E: int, topk: int, H: int, I: int, fp8: bool, T: int, allow_decode: bool = True):
+    """Row of the smallest tabulated token count >= T (the last row beyond the table).  allow_decode=False skips rows
+    of the single-kernel decode path (tuning values >= 300), which takes at most 8 tokens and 64 routed slots."""
     rows = _moe_table().get((E, topk, H, I, int(fp8)))
     if not rows:
         return None
-    for t, args in rows:
+    usable = [(t, args) for t, args in rows if allow_decode or args[1] < 300]
+    if not usable:
+        return None
+    for t, args in usable:
         if t >= T:
             return args
-    return rows[-1][1]
+    return usable[-1][1]
 
 
 def fused_moe(
@@ -115,9 +120,14 @@ def fused_moe(
     e1, m1, k1 = w1.shape
     e2, m2, k2 = w2.shape
     if tune is None:
-        # with an experts_map (expert parallelism) the work per local expert is that of the full layer: the row of
-        # the global expert count applies
-        tune = lookup_moe_args(num_experts if experts_map is not None else e1, topk, H, k2, soft_fp8, B)
+        # with an experts_map (expert parallelism) this rank sees e1 of the num_experts experts and, on average, that
+        # share of the routed slots: the expert GEMMs have the work items of a layer with e1 experts and
+        # B * e1 / num_experts tokens, and that row applies
+        t_eff = B if experts_map is None else max(1, -(-B * e1 // num_experts))
+        decode_ok = B <= 8 and B * topk <= 64
+        tune = lookup_moe_args(e1, topk, H, k2, soft_fp8, t_eff, decode_ok)
+        if tune is None and experts_map is not None:
+            tune = lookup_moe_args(num_experts, topk, H, k2, soft_fp8, B, decode_ok)   # no row for the local count: the full layer's
     # decode batches tuned for the single-kernel path: the routing runs inside the expert-compute call (one launch
     # for the whole layer); otherwise the router kernel comes first
     routing = None
