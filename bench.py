@@ -464,7 +464,8 @@ def run_ours(args):
         if world > 1 and not args.no_moe:
             line["moe_layer_us"] = moe_ep
             line["moe_layer_mode"] = (f"expert parallel over {world} GPUs, E/{world} experts per rank, the modes of parallel.py on identical "
-                                      "seeded weights: replicated (tokens on every rank, experts_map, NCCL all-reduce of the fp32 shares), "
+                                      "seeded weights: replicated (tokens on every rank, experts_map, NCCL all-reduce of the fp32 shares), replicated_peer_reduce "
+                                      "(the same, shares added over NVLink peer memory by one kernel per rank, no NCCL call), "
                                       "all_to_all (tokens sharded, NCCL all-to-all dispatch of the routed rows and combine of fp32 rows) and "
                                       "gather_reduce_scatter (tokens sharded, all-gather + local share + reduce-scatter, static shapes); parity_ok = every rank's output "
                                       "of one batch equals the single-GPU layer within |d| <= 1e-2 max(1, rms) + 1e-2 |want|; "

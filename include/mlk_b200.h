@@ -341,6 +341,19 @@ int mlk_moe_gather_rows(const void* x, const int32_t* idx, void* out, int64_t n_
 int mlk_moe_unpermute_sum(const void* rows, const int32_t* pos, void* y, int64_t T, int topK, int hidden,
                           int64_t n_rows, int dtype, mlk_stream_t s);
 
+/* Expert-parallel combine over peer memory (NVLink / NVSwitch), one kernel per rank instead of an all-reduce and a
+ * cast: rank i adds rows [T i / world, T (i + 1) / world) of every rank's fp32 share [T, hidden] in rank order, rounds
+ * once to `dtype` (0 = bf16, 1 = fp16) and stores the finished rows into every rank's output [T, hidden].
+ *   shares_dev / outs_dev / flags_dev: DEVICE arrays of `world` pointers -- every rank's share, output and flag block,
+ *   all peer-accessible (symmetric memory, IPC or cuMemMap'd allocations).  A flag block is
+ *   mlk_ep_reduce_flag_bytes() bytes, zero before the first call and owned by these calls from then on.
+ * All ranks must issue the same sequence of calls (same T, hidden).  The launch is capturable in a CUDA graph.  Waits on
+ * peers are bounded: on expiry *status (may be NULL) receives 0x0E000001 and the output of that call is incomplete.
+ * The kernel uses plain loads and stores on the peer pointers, no TMA, no multicast. */
+int64_t mlk_ep_reduce_flag_bytes(void);
+int mlk_ep_reduce_shares(const void* const* shares_dev, void* const* outs_dev, void* const* flags_dev, int rank, int world,
+                         int64_t T, int hidden, int dtype, int32_t* status, mlk_stream_t s);
+
 #ifdef __cplusplus
 }
 #endif

@@ -36,6 +36,7 @@ SOURCES = [
     "moe_umma.cu",
     "moe_umma_f8n.cu",
     "moe_decode.cu",
+    "ep_reduce.cu",
     "moe_exchange.cu",
     "selector.cpp",
 ]

@@ -437,6 +437,14 @@ int mlk_moe_unpermute_sum(const void* rows, const int32_t* pos, void* y, int64_t
     return launch_unpermute_sum(rows, pos, y, T, topK, hidden, n_rows, dtype, (cudaStream_t)s);
 }
 
+int64_t mlk_ep_reduce_flag_bytes(void) { return ep_reduce_flag_bytes(); }
+
+int mlk_ep_reduce_shares(const void* const* shares_dev, void* const* outs_dev, void* const* flags_dev, int rank, int world,
+                         int64_t T, int hidden, int dtype, int32_t* status, mlk_stream_t s) {
+    clear_error();
+    return launch_ep_reduce(shares_dev, outs_dev, flags_dev, rank, world, T, hidden, dtype, status, (cudaStream_t)s);
+}
+
 namespace {
 MoeParams moe_params(const void* w1, const void* w2, const void* x, int batch_size, int expert_count, int topK, int hidden,
                      int inter, const int32_t* topk_ids, const void* topk_weights, int32_t* sorted_token_ids,

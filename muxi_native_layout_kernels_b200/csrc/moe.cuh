@@ -93,4 +93,10 @@ int launch_gather_rows(const void* x, const int32_t* idx, void* out, long long n
 int launch_unpermute_sum(const void* rows, const int32_t* pos, void* y, long long T, int topk, int H, long long n_rows,
                          int dtype, cudaStream_t s);
 
+// Sum of the ranks' fp32 shares over peer memory, rounded once, finished rows stored into every rank's output
+// (ep_reduce.cu).  The three arguments are DEVICE arrays of `world` pointers (every rank's share / output / flag block).
+long long ep_reduce_flag_bytes();
+int launch_ep_reduce(const void* const* shares_dev, void* const* outs_dev, void* const* flags_dev, int rank, int world,
+                     long long T, int H, int dtype, int* status, cudaStream_t s);
+
 }  // namespace mlk

@@ -161,6 +161,8 @@ def run_ep(config, rank, world, tokens=None, iters=24, dev=None, graphs=False):
     weights (parity_ok).
       replicated   tokens and router logits on every rank, each rank adds its experts' share (experts_map), NCCL
                    all-reduce of the shares; us_eager and us_graph
+      replicated_peer_reduce   the same with the shares added by one kernel per rank over peer memory
+                   (parallel.PeerReducer) instead of the all-reduce and the cast
       all_to_all   tokens sharded T / world per rank, NCCL all-to-all dispatch of exactly the routed rows, local
                    experts, all-to-all combine of the fp32 rows; us_eager only (the split sizes cost a host copy)
       gather_reduce_scatter  tokens sharded, static shapes: all-gather of tokens and logits, local share, reduce-scatter
@@ -168,7 +170,7 @@ def run_ep(config, rank, world, tokens=None, iters=24, dev=None, graphs=False):
     Times are CUDA events around the calls after a barrier, max over ranks."""
     import torch.distributed as dist
 
-    from muxi_native_layout_kernels_b200.parallel import fused_moe_ep, fused_moe_ep_replicated
+    from muxi_native_layout_kernels_b200.parallel import PeerReducer, fused_moe_ep, fused_moe_ep_replicated
     dev = dev or torch.device("cuda")
     mlk.set_static_weights(True)
     out = {}
@@ -192,6 +194,19 @@ def run_ep(config, rank, world, tokens=None, iters=24, dev=None, graphs=False):
             rep = _time_ep(lambda i: fused_moe_ep_replicated(xs[i], w1l, w2l, logits[i], topk, True, **kw), iters, graphs, dev)
             rep["parity_ok"] = _close(got, want)
             row["replicated"] = rep
+            # the same with the shares added over peer memory by one kernel per rank instead of the all-reduce
+            try:
+                red = PeerReducer(T, H, torch.bfloat16)
+            except Exception as e:          # no peer-mappable memory on this machine (every rank fails alike)
+                red = None
+                row["replicated_peer_reduce"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+            if red is not None:
+                got = fused_moe_ep_replicated(xs[0], w1l, w2l, logits[0], topk, True, reducer=red, **kw).clone()
+                pr = _time_ep(lambda i: fused_moe_ep_replicated(xs[i], w1l, w2l, logits[i], topk, True, reducer=red, **kw),
+                              iters, graphs, dev)
+                pr["parity_ok"] = _close(got, want)
+                row["replicated_peer_reduce"] = pr
+                del red
             if T % world == 0:
                 tl = T // world
                 xl = [x[rank * tl:(rank + 1) * tl].contiguous() for x in xs]
@@ -207,7 +222,8 @@ def run_ep(config, rank, world, tokens=None, iters=24, dev=None, graphs=False):
                 gat["parity_ok"] = _close(got, want[rank * tl:(rank + 1) * tl])
                 gat["tokens_per_rank"] = tl
                 row["gather_reduce_scatter"] = gat
-            modes = [m for m in ("replicated", "all_to_all", "gather_reduce_scatter") if m in row]
+            modes = [m for m in ("replicated", "replicated_peer_reduce", "all_to_all", "gather_reduce_scatter")
+                     if m in row and "parity_ok" in row[m]]
             flags = torch.tensor([int(row[m]["parity_ok"]) for m in modes], device=dev)
             dist.all_reduce(flags, op=dist.ReduceOp.MIN)
             for m, f in zip(modes, flags.tolist()):

@@ -91,6 +91,7 @@ def fused_moe(
     tune=None,
     gate_weight: Optional[torch.Tensor] = None,
     out_dtype: Optional[torch.dtype] = None,
+    out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     # gate_weight [E, H] (extension): the router GEMM runs fused with the routing kernel and `gating_output` is not
     # read (pass None)
@@ -160,12 +161,19 @@ def fused_moe(
     # the fixed-order combine writes every element of y; the atomic variant accumulates into zeros
     # out_dtype=torch.float32 (extension, deterministic only): the sums over this rank's experts un-rounded, for callers
     # that add the shares of several ranks before the one rounding
+    # out (extension): the tensor the result is written to (e.g. a buffer other GPUs can read), contiguous, of the
+    # result's shape and dtype
     if out_dtype is not None and out_dtype != hidden_states.dtype:
         if out_dtype != torch.float32 or not deterministic:
             raise ValueError("out_dtype must be the activation dtype or torch.float32 (with deterministic=True)")
-        y = torch.empty(hidden_states.shape, dtype=torch.float32, device=dev)
+        y = torch.empty(hidden_states.shape, dtype=torch.float32, device=dev) if out is None else out
+    elif out is not None:
+        y = out if deterministic else out.zero_()
     else:
         y = torch.empty_like(hidden_states) if deterministic else torch.zeros_like(hidden_states)
+    if out is not None and (out.shape != hidden_states.shape or not out.is_contiguous() or
+                            out.dtype != (out_dtype or hidden_states.dtype)):
+        raise ValueError("out must be contiguous with the result's shape and dtype")
 
     if experts_map is not None and experts_map.dtype != torch.int:
         experts_map = experts_map.to(torch.int)

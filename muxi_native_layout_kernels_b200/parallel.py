@@ -265,13 +265,47 @@ def fused_moe_ep(
                         lambda rows, s2r, T_, k_: _gpu_combine(rows, s2r, T_, k_, hidden_states.dtype), group)
 
 
+class PeerReducer:
+    """Buffers and launch of the expert-parallel combine over peer memory (``mlk_ep_reduce_shares``): every rank's fp32
+    share ``[tokens, hidden]``, every rank's 16-bit output and a flag block, allocated as symmetric memory so that each
+    rank holds pointers to all of them.  One kernel per rank adds the shares of the rows it owns in rank order, rounds
+    once and stores the rows into every rank's output: a reduce-scatter and an all-gather in one pass over NVLink, no
+    NCCL call, capturable in a CUDA graph.  All ranks must construct it collectively and call ``reduce`` in step."""
+
+    def __init__(self, tokens: int, hidden: int, dtype: torch.dtype = torch.bfloat16, group=None, device=None):
+        import torch.distributed._symmetric_memory as symm
+        from ._lib import lib
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.tokens, self.hidden, self.dtype = tokens, hidden, dtype
+        self.share = symm.empty((tokens, hidden), dtype=torch.float32, device=device)
+        self.out = symm.empty((tokens, hidden), dtype=dtype, device=device)
+        self.flags = symm.empty((int(lib.mlk_ep_reduce_flag_bytes()) // 4,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self._handles = [symm.rendezvous(t, group) for t in (self.share, self.out, self.flags)]
+        torch.cuda.synchronize(device)
+        dist.barrier(group)              # every rank's flag block is zero before anybody's first launch
+
+    def reduce(self) -> torch.Tensor:
+        """Adds the ranks' ``share`` buffers; returns ``out`` (the same tensor every call)."""
+        from . import ext
+        from ._lib import check, lib
+        hs, ho, hf = self._handles
+        check(lib.mlk_ep_reduce_shares(hs.buffer_ptrs_dev, ho.buffer_ptrs_dev, hf.buffer_ptrs_dev, self.rank, self.world,
+                                       self.tokens, self.hidden, 1 if self.dtype == torch.float16 else 0,
+                                       ext._status_ptr(self.share), ext._stream(self.share)))
+        return self.out
+
+
 def fused_moe_ep_replicated(hidden_states, w1_local, w2_local, gating_output, topk, renormalize, group=None,
-                            reduce_dtype: torch.dtype = torch.float32, **kw):
+                            reduce_dtype: torch.dtype = torch.float32, reducer: Optional[PeerReducer] = None, **kw):
     """Tokens replicated on every rank; each rank adds its experts' share (``experts_map``) and the shares are summed
     with an all-reduce.  This is the expert-parallel mode the reference's ``experts_map`` hook was made for
     (csrc/moe_kernels/moe_align_tokens.h:44-49).  The shares leave the layer as un-rounded fp32 sums and are reduced in
     fp32 (one rounding at the end, as on one GPU); ``reduce_dtype=torch.bfloat16`` halves the all-reduce traffic at
-    the price of one rounding per rank."""
+    the price of one rounding per rank.  ``reducer`` (a ``PeerReducer`` for this token count) replaces the all-reduce and
+    the cast by one peer-memory kernel per rank."""
     from .muxi_moe_planC import fused_moe
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
@@ -280,6 +314,12 @@ def fused_moe_ep_replicated(hidden_states, w1_local, w2_local, gating_output, to
     emap = _cached_expert_map(E, e_local, rank, hidden_states.device)
     if world == 1:
         return fused_moe(hidden_states, w1_local, w2_local, gating_output, topk, renormalize, experts_map=emap, **kw)
+    if reducer is not None:
+        # shares straight into peer-readable memory, one kernel per rank adds them over NVLink (fp32, rank order, one
+        # rounding); the returned tensor is the reducer's output buffer
+        fused_moe(hidden_states, w1_local, w2_local, gating_output, topk, renormalize, experts_map=emap,
+                  out_dtype=torch.float32, out=reducer.share, **kw)
+        return reducer.reduce()
     if reduce_dtype == torch.float32:
         share = fused_moe(hidden_states, w1_local, w2_local, gating_output, topk, renormalize, experts_map=emap,
                           out_dtype=torch.float32, **kw)

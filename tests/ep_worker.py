@@ -15,6 +15,34 @@ from muxi_native_layout_kernels_b200 import parallel  # noqa: E402
 from muxi_native_layout_kernels_b200.muxi_moe_planC import fused_moe  # noqa: E402
 
 
+def _peer_reduce_cases(parallel, red, x, w1l, w2l, logits, topk, kw, full, close, world):
+    import muxi_native_layout_kernels_b200 as mlk
+    res = {}
+    y1 = parallel.fused_moe_ep_replicated(x, w1l, w2l, logits, topk, True, reducer=red, **kw).clone()
+    y2 = parallel.fused_moe_ep_replicated(x, w1l, w2l, logits, topk, True, reducer=red, **kw).clone()
+    res["replicated peer-memory reduce"] = close(y1, full)
+    gathered = [torch.empty_like(y1) for _ in range(world)]
+    dist.all_gather(gathered, y1)
+    same = torch.equal(y1, y2) and all(torch.equal(gathered[0], t) for t in gathered)
+    res["peer-memory reduce deterministic"] = (same, 0.0)
+    xr, lr = x.clone(), logits.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        parallel.fused_moe_ep_replicated(xr, w1l, w2l, lr, topk, True, reducer=red, **kw)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            yr = parallel.fused_moe_ep_replicated(xr, w1l, w2l, lr, topk, True, reducer=red, **kw)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    res["peer-memory reduce graph"] = (torch.equal(yr, y1), 0.0)
+    del graph
+    assert mlk.kernel_status() == 0
+    return res
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -50,6 +78,15 @@ def main():
         res["replicated fp32"] = close(parallel.fused_moe_ep_replicated(x, w1l, w2l, logits, topk, True, **kw), full)
         res["replicated bf16"] = close(parallel.fused_moe_ep_replicated(x, w1l, w2l, logits, topk, True,
                                                                         reduce_dtype=torch.bfloat16, **kw), full)
+        # the same with the shares added over peer memory (one kernel per rank, no NCCL call); twice in a row (epochs),
+        # bit-equal on all ranks and between the calls, then inside a CUDA graph
+        try:
+            red = parallel.PeerReducer(x.shape[0], H, torch.bfloat16)
+        except Exception as e:      # no peer-mappable memory on this machine: every rank fails alike
+            red = None
+            print(f"rank {rank} peer-memory reduce not run: {type(e).__name__}: {e}", flush=True)
+        if red is not None:
+            res.update(_peer_reduce_cases(parallel, red, x, w1l, w2l, logits, topk, kw, full, close, world))
         # the static-shape modes inside a CUDA graph (collectives included), replayed on new inputs
         xg, lg = xs.clone(), ls.clone()
         side = torch.cuda.Stream()

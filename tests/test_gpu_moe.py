@@ -662,3 +662,42 @@ def test_config_moe_fine_grained_fp8(T, skew):
     y32 = omoe.experts_ref(x.cpu(), w1.cpu(), w2.cpu(), ids, w, compute_dtype=torch.float32)
     rep = assert_close(y, y32, f"C5 T={T} skew={skew}", scale_atol=True)
     print("C5", T, skew, rep, "floor", odense.error_report(y16, y32, scale_atol=True))
+
+
+def test_ep_reduce_shares_single_rank():
+    """mlk_ep_reduce_shares with a world of one (its flags are exchanged with itself): rounding, row ownership, the epoch
+    that lets a CUDA graph replay the launch.  More ranks need more GPUs: tests/ep_worker.py."""
+    dev = require_gpu()
+    from muxi_native_layout_kernels_b200 import ext
+    from muxi_native_layout_kernels_b200._lib import check, lib
+    T, H = 37, 256
+    share = torch.randn(T, H, device=dev) * 100
+    out = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+    flags = torch.zeros(int(lib.mlk_ep_reduce_flag_bytes()) // 4, dtype=torch.int32, device=dev)
+    ptrs = [torch.tensor([t.data_ptr()], dtype=torch.int64, device=dev) for t in (share, out, flags)]
+
+    def launch():
+        check(lib.mlk_ep_reduce_shares(ptrs[0].data_ptr(), ptrs[1].data_ptr(), ptrs[2].data_ptr(), 0, 1, T, H, 0,
+                                       ext._status_ptr(share), ext._stream(share)))
+
+    for rep in range(3):
+        launch()
+        torch.cuda.synchronize()
+        assert torch.equal(out, share.to(torch.bfloat16))
+        assert int(flags[0].item()) == rep + 1 and int(flags[1].item()) == 0
+        share.mul_(-0.5)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            launch()
+    torch.cuda.current_stream().wait_stream(side)
+    for rep in range(3):
+        share.add_(1.0)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, share.to(torch.bfloat16))
+    assert mlk.kernel_status() == 0
+    with pytest.raises(RuntimeError):
+        check(lib.mlk_ep_reduce_shares(ptrs[0].data_ptr(), ptrs[1].data_ptr(), ptrs[2].data_ptr(), 3, 2, T, H, 0, None, None))
