@@ -347,12 +347,17 @@ int mlk_moe_unpermute_sum(const void* rows, const int32_t* pos, void* y, int64_t
  *   shares_dev / outs_dev / flags_dev: DEVICE arrays of `world` pointers -- every rank's share, output and flag block,
  *   all peer-accessible (symmetric memory, IPC or cuMemMap'd allocations).  A flag block is
  *   mlk_ep_reduce_flag_bytes() bytes, zero before the first call and owned by these calls from then on.
+ *   recv_dev: NULL, or the same kind of array for every rank's receive buffer of mlk_ep_reduce_recv_bytes(world, T,
+ *   hidden) bytes (0 = share too large).  With it, shares of at most 64 Ki elements (decode batches) take a one-pass
+ *   form without any barrier: every rank stores its share into every peer's receive buffer as (value, epoch) pairs and
+ *   adds, in rank order, what it receives as the pairs land; every rank computes the whole output itself.
  * All ranks must issue the same sequence of calls (same T, hidden).  The launch is capturable in a CUDA graph.  Waits on
  * peers are bounded: on expiry *status (may be NULL) receives 0x0E000001 and the output of that call is incomplete.
- * The kernel uses plain loads and stores on the peer pointers, no TMA, no multicast. */
+ * The kernels use plain loads and stores on the peer pointers, no TMA, no multicast. */
 int64_t mlk_ep_reduce_flag_bytes(void);
-int mlk_ep_reduce_shares(const void* const* shares_dev, void* const* outs_dev, void* const* flags_dev, int rank, int world,
-                         int64_t T, int hidden, int dtype, int32_t* status, mlk_stream_t s);
+int64_t mlk_ep_reduce_recv_bytes(int world, int64_t T, int hidden);
+int mlk_ep_reduce_shares(const void* const* shares_dev, void* const* outs_dev, void* const* flags_dev, void* const* recv_dev,
+                         int rank, int world, int64_t T, int hidden, int dtype, int32_t* status, mlk_stream_t s);
 
 #ifdef __cplusplus
 }

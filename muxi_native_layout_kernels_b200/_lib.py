@@ -65,7 +65,8 @@ PROTOTYPES = {
                                           c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp,
                                           c_int, c_vp, c_i64, C.POINTER(C.c_int32), c_vp, c_int, c_vp]),
     "mlk_ep_reduce_flag_bytes": (c_i64, []),
-    "mlk_ep_reduce_shares": (c_int, [c_vp, c_vp, c_vp, c_int, c_int, c_i64, c_int, c_int, c_vp, c_vp]),
+    "mlk_ep_reduce_recv_bytes": (c_i64, [c_int, c_i64, c_int]),
+    "mlk_ep_reduce_shares": (c_int, [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_i64, c_int, c_int, c_vp, c_vp]),
     "mlk_fused_routing_experts_compute": (c_int, [c_vp, c_int, c_int, c_int, c_int, c_vp, c_int,
                                                   c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp,
                                                   c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp,

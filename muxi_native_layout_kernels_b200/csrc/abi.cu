@@ -438,11 +438,12 @@ int mlk_moe_unpermute_sum(const void* rows, const int32_t* pos, void* y, int64_t
 }
 
 int64_t mlk_ep_reduce_flag_bytes(void) { return ep_reduce_flag_bytes(); }
+int64_t mlk_ep_reduce_recv_bytes(int world, int64_t T, int hidden) { return ep_reduce_recv_bytes(world, T, hidden); }
 
-int mlk_ep_reduce_shares(const void* const* shares_dev, void* const* outs_dev, void* const* flags_dev, int rank, int world,
-                         int64_t T, int hidden, int dtype, int32_t* status, mlk_stream_t s) {
+int mlk_ep_reduce_shares(const void* const* shares_dev, void* const* outs_dev, void* const* flags_dev, void* const* recv_dev,
+                         int rank, int world, int64_t T, int hidden, int dtype, int32_t* status, mlk_stream_t s) {
     clear_error();
-    return launch_ep_reduce(shares_dev, outs_dev, flags_dev, rank, world, T, hidden, dtype, status, (cudaStream_t)s);
+    return launch_ep_reduce(shares_dev, outs_dev, flags_dev, recv_dev, rank, world, T, hidden, dtype, status, (cudaStream_t)s);
 }
 
 namespace {

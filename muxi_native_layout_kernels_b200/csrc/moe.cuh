@@ -96,7 +96,8 @@ int launch_unpermute_sum(const void* rows, const int32_t* pos, void* y, long lon
 // Sum of the ranks' fp32 shares over peer memory, rounded once, finished rows stored into every rank's output
 // (ep_reduce.cu).  The three arguments are DEVICE arrays of `world` pointers (every rank's share / output / flag block).
 long long ep_reduce_flag_bytes();
-int launch_ep_reduce(const void* const* shares_dev, void* const* outs_dev, void* const* flags_dev, int rank, int world,
-                     long long T, int H, int dtype, int* status, cudaStream_t s);
+long long ep_reduce_recv_bytes(int world, long long T, int H);      // receive buffer of the one-pass form, 0 = share too large for it
+int launch_ep_reduce(const void* const* shares_dev, void* const* outs_dev, void* const* flags_dev, void* const* recv_dev,
+                     int rank, int world, long long T, int H, int dtype, int* status, cudaStream_t s);
 
 }  // namespace mlk

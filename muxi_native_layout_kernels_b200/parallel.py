@@ -283,7 +283,13 @@ class PeerReducer:
         self.out = symm.empty((tokens, hidden), dtype=dtype, device=device)
         self.flags = symm.empty((int(lib.mlk_ep_reduce_flag_bytes()) // 4,), dtype=torch.int32, device=device)
         self.flags.zero_()
+        # decode batches: receive buffer of the one-pass form (every rank's share arrives here as (value, epoch) pairs)
+        recv_bytes = int(lib.mlk_ep_reduce_recv_bytes(self.world, tokens, hidden))
+        self.recv = symm.empty((max(recv_bytes, 16) // 4,), dtype=torch.int32, device=device) if recv_bytes else None
+        if self.recv is not None:
+            self.recv.zero_()
         self._handles = [symm.rendezvous(t, group) for t in (self.share, self.out, self.flags)]
+        self._recv_handle = symm.rendezvous(self.recv, group) if self.recv is not None else None
         torch.cuda.synchronize(device)
         dist.barrier(group)              # every rank's flag block is zero before anybody's first launch
 
@@ -292,7 +298,9 @@ class PeerReducer:
         from . import ext
         from ._lib import check, lib
         hs, ho, hf = self._handles
-        check(lib.mlk_ep_reduce_shares(hs.buffer_ptrs_dev, ho.buffer_ptrs_dev, hf.buffer_ptrs_dev, self.rank, self.world,
+        check(lib.mlk_ep_reduce_shares(hs.buffer_ptrs_dev, ho.buffer_ptrs_dev, hf.buffer_ptrs_dev,
+                                       self._recv_handle.buffer_ptrs_dev if self._recv_handle is not None else None,
+                                       self.rank, self.world,
                                        self.tokens, self.hidden, 1 if self.dtype == torch.float16 else 0,
                                        ext._status_ptr(self.share), ext._stream(self.share)))
         return self.out

@@ -39,6 +39,24 @@ def _peer_reduce_cases(parallel, red, x, w1l, w2l, logits, topk, kw, full, close
     torch.cuda.synchronize()
     res["peer-memory reduce graph"] = (torch.equal(yr, y1), 0.0)
     del graph
+    # both forms of the kernel on their own (one pass with (value, epoch) pairs for small shares, reduce-scatter +
+    # all-gather for large ones) against the shares gathered with NCCL and added in rank order: bit-equal, three calls
+    rank = dist.get_rank()
+    for tokens, hidden in ((5, 256), (300, 512)):
+        r2 = parallel.PeerReducer(tokens, hidden, torch.bfloat16)
+        good = True
+        for call in range(3):
+            gen = torch.Generator(device=x.device).manual_seed(1000 * call + rank)
+            r2.share.copy_(torch.randn(tokens, hidden, generator=gen, device=x.device) * 50)
+            got = r2.reduce().clone()
+            parts = [torch.empty_like(r2.share) for _ in range(world)]
+            dist.all_gather(parts, r2.share)
+            want = parts[0].clone()
+            for pt in parts[1:]:
+                want += pt
+            good = good and torch.equal(got, want.to(torch.bfloat16))
+        res[f"peer-memory reduce alone [{tokens}, {hidden}]"] = (good, 0.0)
+        del r2
     assert mlk.kernel_status() == 0
     return res
 

@@ -677,7 +677,7 @@ def test_ep_reduce_shares_single_rank():
     ptrs = [torch.tensor([t.data_ptr()], dtype=torch.int64, device=dev) for t in (share, out, flags)]
 
     def launch():
-        check(lib.mlk_ep_reduce_shares(ptrs[0].data_ptr(), ptrs[1].data_ptr(), ptrs[2].data_ptr(), 0, 1, T, H, 0,
+        check(lib.mlk_ep_reduce_shares(ptrs[0].data_ptr(), ptrs[1].data_ptr(), ptrs[2].data_ptr(), None, 0, 1, T, H, 0,
                                        ext._status_ptr(share), ext._stream(share)))
 
     for rep in range(3):
@@ -700,4 +700,4 @@ def test_ep_reduce_shares_single_rank():
         assert torch.equal(out, share.to(torch.bfloat16))
     assert mlk.kernel_status() == 0
     with pytest.raises(RuntimeError):
-        check(lib.mlk_ep_reduce_shares(ptrs[0].data_ptr(), ptrs[1].data_ptr(), ptrs[2].data_ptr(), 3, 2, T, H, 0, None, None))
+        check(lib.mlk_ep_reduce_shares(ptrs[0].data_ptr(), ptrs[1].data_ptr(), ptrs[2].data_ptr(), None, 3, 2, T, H, 0, None, None))
