@@ -66,8 +66,10 @@ const char* mlk_build_info(void);
  *        dequantises to (muxi_layout_kernels/utils.py:14-25); the decode is the bottleneck of these kernels, so
  *        this costs throughput (measured: 1.2-1.6x the time).
  *     The reference's kernels truncate fp32(w) * s to bf16; every form stays within one bf16 ulp per weight of the
- *     exact product.  The warp-level kernels (kernelId 1, 3, 4) apply s to the fp32 sums of each 128-wide k block. */
-enum { MLK_OPT_PDL = 0, MLK_OPT_STATIC_WEIGHTS = 1, MLK_OPT_FULL_SCALES = 2 };
+ *     exact product.  The warp-level kernels (kernelId 1, 3, 4) apply s to the fp32 sums of each 128-wide k block.
+ *   MLK_OPT_WAIT_LOG2 (default 0 = built-in, 24): log2 of the number of polls mlk_ep_reduce_shares waits for a peer GPU
+ *     before it gives up (4..30).  Smaller values turn a missing peer into an error status sooner. */
+enum { MLK_OPT_PDL = 0, MLK_OPT_STATIC_WEIGHTS = 1, MLK_OPT_FULL_SCALES = 2, MLK_OPT_WAIT_LOG2 = 3 };
 int mlk_set_option(int option_id, int value);
 int mlk_get_option(int option_id);
 

@@ -27,7 +27,7 @@ const char* last_error() { return g_err; }
 void clear_error() { g_err[0] = 0; }
 
 namespace {
-int g_options[kNumOptions] = {1, 0, 0};
+int g_options[kNumOptions] = {1, 0, 0, 0};
 }
 int option(int which) { return (which >= 0 && which < kNumOptions) ? g_options[which] : 0; }
 void set_option(int which, int value) {

@@ -56,7 +56,7 @@ __device__ __forceinline__ int flag_index(int phase, int cta, int src) {
 
 // Signals this CTA's flag to every rank and waits for every rank's flag (threads 0 .. world - 1 take one peer each).
 __device__ __forceinline__ void exchange_flags(unsigned* const* flags, int rank, int world, int phase, unsigned epoch,
-                                               int* status) {
+                                               unsigned spin_limit, int* status) {
     __syncthreads();
     const int t = threadIdx.x;
     if (t < world) {
@@ -65,7 +65,7 @@ __device__ __forceinline__ void exchange_flags(unsigned* const* flags, int rank,
         unsigned polls = 0;
         // epochs only grow; a flag from a later launch also means this one was passed
         while ((int)(ld_acquire_sys(mine) - epoch) < 0) {
-            if (++polls > kEpSpinLimit) {
+            if (++polls > spin_limit) {
                 if (status != nullptr) atomicCAS(status, 0, kEpExpired);
                 break;
             }
@@ -78,7 +78,7 @@ __device__ __forceinline__ void exchange_flags(unsigned* const* flags, int rank,
 template <int WT>
 __global__ void __launch_bounds__(256) ep_reduce_kernel(const float* const* __restrict__ shares, uint8_t* const* __restrict__ outs,
                                                        unsigned* const* __restrict__ flags, int rank, int world, long long T,
-                                                       int H, int* status) {
+                                                       int H, unsigned spin_limit, int* status) {
     // the share comes from the kernels before this one in the stream: only past this wait may the peers be told that it is
     // complete (and the epoch of the previous launch has been written)
     pdl_wait();
@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const float* const* __re
     unsigned* const my_flags = flags[rank];
     const unsigned epoch = *reinterpret_cast<volatile unsigned*>(my_flags) + 1u;    // read by every CTA before the last one of this launch moves it on
 
-    exchange_flags(flags, rank, world, 0, epoch, status);
+    exchange_flags(flags, rank, world, 0, epoch, spin_limit, status);
 
     const long long r0 = T * rank / world, r1 = T * (rank + 1) / world;
     const int quads = H >> 2;
@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const float* const* __re
     }
     __threadfence_system();
 
-    exchange_flags(flags, rank, world, 1, epoch, status);
+    exchange_flags(flags, rank, world, 1, epoch, spin_limit, status);
 
     // the last CTA out moves the epoch on for the next launch
     if (threadIdx.x == 0) {
@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const float* const* __re
 template <int WT>
 __global__ void __launch_bounds__(256) ep_reduce_ll_kernel(const float* const* __restrict__ shares, uint8_t* const* __restrict__ outs,
                                                           unsigned* const* __restrict__ flags, uint2* const* __restrict__ recv,
-                                                          int rank, int world, long long n, int* status) {
+                                                          int rank, int world, long long n, unsigned spin_limit, int* status) {
     pdl_wait();
     pdl_launch_dependents();
     unsigned* const my_flags = flags[rank];
@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(256) ep_reduce_ll_kernel(const float* const* _
             for (;;) {
                 asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(pair.x), "=r"(pair.y) : "l"(src) : "memory");
                 if (pair.y == epoch || expired) break;
-                if (++polls > kEpSpinLimit) {
+                if (++polls > spin_limit) {
                     expired = true;
                     if (status != nullptr) atomicCAS(status, 0, kEpExpired);
                     break;
@@ -223,15 +223,17 @@ int launch_ep_reduce(const void* const* shares_dev, void* const* outs_dev, void*
     cfg.numAttrs = launch_attrs(attr, 1);
     cudaError_t e;
     const long long n = T * H;
+    const int wl = option(kOptWaitLog2);
+    const unsigned spin = (wl >= 4 && wl <= 30) ? (1u << wl) : kEpSpinLimit;      // poll budget of the waits on peers
     if (recv_dev != nullptr && n <= kEpLlMaxElems && world > 1) {
         // small share: the one-pass form
         auto rv = reinterpret_cast<uint2* const*>(recv_dev);
         cfg.gridDim = dim3((unsigned)std::min<long long>(kEpGrid, (n + 255) / 256));
-        e = dtype == kFP16 ? cudaLaunchKernelEx(&cfg, ep_reduce_ll_kernel<kFP16>, sh, ou, fl, rv, rank, world, n, status)
-                           : cudaLaunchKernelEx(&cfg, ep_reduce_ll_kernel<kBF16>, sh, ou, fl, rv, rank, world, n, status);
+        e = dtype == kFP16 ? cudaLaunchKernelEx(&cfg, ep_reduce_ll_kernel<kFP16>, sh, ou, fl, rv, rank, world, n, spin, status)
+                           : cudaLaunchKernelEx(&cfg, ep_reduce_ll_kernel<kBF16>, sh, ou, fl, rv, rank, world, n, spin, status);
     } else {
-        e = dtype == kFP16 ? cudaLaunchKernelEx(&cfg, ep_reduce_kernel<kFP16>, sh, ou, fl, rank, world, T, H, status)
-                           : cudaLaunchKernelEx(&cfg, ep_reduce_kernel<kBF16>, sh, ou, fl, rank, world, T, H, status);
+        e = dtype == kFP16 ? cudaLaunchKernelEx(&cfg, ep_reduce_kernel<kFP16>, sh, ou, fl, rank, world, T, H, spin, status)
+                           : cudaLaunchKernelEx(&cfg, ep_reduce_kernel<kBF16>, sh, ou, fl, rank, world, T, H, spin, status);
     }
     if (e != cudaSuccess) return fail(kCudaError, "ep_reduce_shares launch: %s", cudaGetErrorString(e));
     return kOk;

@@ -28,7 +28,8 @@ enum Option : int {
     kOptPdl = 0,            // launch kernels with programmatic stream serialization (default 1)
     kOptStaticWeights = 1,  // weight tensors are never written by kernels of the calling stream (default 0)
     kOptFullScales = 2,     // tcgen05 e4m3 kernels: block scales with 16 significant bits instead of 8 (default 0)
-    kNumOptions = 3,
+    kOptWaitLog2 = 3,       // log2 of the poll budget of the waits on OTHER GPUs (peer-memory combine); 0 = built-in (24)
+    kNumOptions = 4,
 };
 int option(int which);
 void set_option(int which, int value);

@@ -701,3 +701,47 @@ def test_ep_reduce_shares_single_rank():
     assert mlk.kernel_status() == 0
     with pytest.raises(RuntimeError):
         check(lib.mlk_ep_reduce_shares(ptrs[0].data_ptr(), ptrs[1].data_ptr(), ptrs[2].data_ptr(), None, 3, 2, T, H, 0, None, None))
+
+
+def test_ep_reduce_shares_reports_a_peer_that_never_arrives():
+    """The expiry path of a bounded wait, end to end: a world of two in which the second rank never launches (its
+    buffers are local stand-ins that nothing writes).  With a small poll budget the kernel must give up, record its
+    status code, end by itself and leave the context usable."""
+    dev = require_gpu()
+    from muxi_native_layout_kernels_b200 import ext
+    from muxi_native_layout_kernels_b200._lib import check, lib
+    T, H = 600, 512                      # 307200 elements: the two-exchange form
+    nflags = int(lib.mlk_ep_reduce_flag_bytes()) // 4
+    share = [torch.ones(T, H, device=dev), torch.ones(T, H, device=dev)]
+    out = [torch.zeros(T, H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    flags = [torch.zeros(nflags, dtype=torch.int32, device=dev) for _ in range(2)]
+    ptrs = [torch.tensor([a.data_ptr(), b.data_ptr()], dtype=torch.int64, device=dev) for a, b in (share, out, flags)]
+    mlk.kernel_status(reset=True)
+    check(lib.mlk_set_option(3, 12))     # 4096 polls instead of 2^24
+    try:
+        check(lib.mlk_ep_reduce_shares(ptrs[0].data_ptr(), ptrs[1].data_ptr(), ptrs[2].data_ptr(), None, 0, 2, T, H, 0,
+                                       ext._status_ptr(share[0]), ext._stream(share[0])))
+        torch.cuda.synchronize()
+    finally:
+        check(lib.mlk_set_option(3, 0))
+    assert mlk.kernel_status(reset=True) == 0x0E000001
+    assert mlk.kernel_status() == 0
+    # small shares, the one-pass form: the pairs of the missing rank never land
+    Ts = 4
+    recv_bytes = int(lib.mlk_ep_reduce_recv_bytes(2, Ts, H))
+    assert recv_bytes == 2 * 2 * Ts * H * 8
+    recv = [torch.zeros(recv_bytes // 4, dtype=torch.int32, device=dev) for _ in range(2)]
+    flags2 = [torch.zeros(nflags, dtype=torch.int32, device=dev) for _ in range(2)]
+    p2 = [torch.tensor([a.data_ptr(), b.data_ptr()], dtype=torch.int64, device=dev) for a, b in (share, out, flags2, recv)]
+    check(lib.mlk_set_option(3, 12))
+    try:
+        check(lib.mlk_ep_reduce_shares(p2[0].data_ptr(), p2[1].data_ptr(), p2[2].data_ptr(), p2[3].data_ptr(), 0, 2, Ts, H, 0,
+                                       ext._status_ptr(share[0]), ext._stream(share[0])))
+        torch.cuda.synchronize()
+    finally:
+        check(lib.mlk_set_option(3, 0))
+    assert mlk.kernel_status(reset=True) == 0x0E000001
+    # the context is intact: an ordinary call still works
+    y = mlk.gemv_layoutA(mlk.layoutA(torch.ones(64, 64, dtype=torch.bfloat16, device=dev)), torch.ones(1, 64, dtype=torch.bfloat16, device=dev))
+    torch.cuda.synchronize()
+    assert float(y[0, 0]) == 64.0 and mlk.kernel_status() == 0
