@@ -69,7 +69,7 @@ def dequant_exact_scale(W8: torch.Tensor, scale: Optional[torch.Tensor]) -> torc
 
 def error_report(got: torch.Tensor, want: torch.Tensor, atol: float = 1e-2, rtol: float = 1e-2,
                  scale_atol: bool = False) -> dict:
-    """Combined-tolerance verdict |got - want| <= atol + rtol * |want| plus the raw figures (max abs, max rel over
+    """Combined-tolerance check |got - want| <= atol + rtol * |want| plus the raw figures (max abs, max rel over
     non-tiny entries).  scale_atol=True multiplies atol by max(1, rms(want)): used where outputs are far larger
     than 1 (soft-FP8 MoE outputs reach 1e3, where one bf16 ulp is already 4-8)."""
     g = got.to(torch.float64).flatten()
