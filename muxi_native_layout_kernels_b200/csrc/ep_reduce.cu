@@ -33,7 +33,7 @@ constexpr int kEpMaxWorld = 16;
 constexpr int kEpFlagBase = 64;         // words 0 / 1: epoch, finished-CTA counter
 constexpr unsigned kEpSpinLimit = 1u << 24;
 constexpr int kEpExpired = 0x0E000001;
-constexpr long long kEpLlMaxElems = 64 * 1024;      // shares up to this many elements take the one-pass form
+constexpr long long kEpLlMaxElems = 256 * 1024;     // shares up to this many elements take the one-pass form
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
     unsigned v;
