@@ -42,7 +42,7 @@ def _peer_reduce_cases(parallel, red, x, w1l, w2l, logits, topk, kw, full, close
     # both forms of the kernel on their own (one pass with (value, epoch) pairs for small shares, reduce-scatter +
     # all-gather for large ones) against the shares gathered with NCCL and added in rank order: bit-equal, three calls
     rank = dist.get_rank()
-    for tokens, hidden in ((5, 256), (300, 512)):
+    for tokens, hidden in ((5, 256), (640, 512)):
         r2 = parallel.PeerReducer(tokens, hidden, torch.bfloat16)
         good = True
         for call in range(3):
