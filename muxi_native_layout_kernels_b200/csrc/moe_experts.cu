@@ -344,12 +344,22 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
             return st;
         m.gating = nullptr;
     }
-    // No tuning arguments at all (a geometry without a row in the table): the tcgen05 kernels where they apply.
-    // 16-bit weights always; e4m3 from about 16 slots per expert on (below that the warp-level kernels, which
-    // decode in the registers of many small CTAs, measured faster).  One cluster per (work item, 128-row tile):
-    // enough CTAs for about four per SM, every CTA with at least four k blocks; three ring stages.
-    if (m.nt == 0 && m.wm1 == 0 && m.sk1 == 0 && m.rg == 0 && m.wm2 == 0 && m.sk2 == 0 && m.scratch != nullptr &&
-        m.I % 128 == 0 && m.H % 128 == 0 && slots * m.H * 4 <= m.scratch_bytes && (wt != kE4M3 || want > 16)) {
+    // No tuning arguments at all (a geometry without a row in the table): what the tuner finds on the tabulated
+    // geometries, as rules.
+    //   * decode batches (one or two tokens) of fine-grained experts (at most 16 MB of weights each): the single
+    //     cooperative kernel;
+    //   * otherwise the tcgen05 kernels where they apply: 16-bit weights always; e4m3 without block scales on the
+    //     native 8-bit kernels at any load (token tiles of 16 / 32 / 64 slots); e4m3 with block scales from about 16
+    //     slots per expert on (below that the warp-level kernels, which decode in the registers of many small CTAs,
+    //     measured faster).  One cluster per (work item, 128-row tile): enough CTAs for about four per SM, every CTA
+    //     with at least four k blocks; the native second GEMM without clusters, one row tile per CTA, once that alone
+    //     gives four CTAs per SM.
+    const bool no_tune = m.nt == 0 && m.wm1 == 0 && m.sk1 == 0 && m.rg == 0 && m.wm2 == 0 && m.sk2 == 0;
+    if (no_tune && m.T <= 2 && (long long)3 * m.I * m.H * esz <= (16LL << 20) && moe_decode_supported(m))
+        return launch_moe_decode(m, s);
+    const bool f8n_ok = wt == kE4M3 && !scale && moe_f8n_supported(m.H, m.I);
+    if (no_tune && m.scratch != nullptr && m.I % 128 == 0 && m.H % 128 == 0 && slots * m.H * 4 <= m.scratch_bytes &&
+        (wt != kE4M3 || f8n_ok || want > 16)) {
         const long long items = std::min<long long>(m.E, slots);
         auto cluster = [&](int tiles, int kblocks) {
             const long long ctas = items * tiles;
@@ -357,9 +367,11 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
             while (sk > 1 && kblocks / sk < 4) --sk;
             return sk;
         };
-        const int fam = (wt == kE4M3 && !scale && moe_f8n_supported(m.H, m.I)) ? 200 : 100;
-        m.wm1 = fam + 3; m.sk1 = cluster(m.I / 128, m.H / 64);
+        const int fam = f8n_ok ? 200 : 100;
+        m.wm1 = fam + (f8n_ok ? 4 : 3); m.sk1 = cluster(m.I / 128, m.H / 64);
         m.wm2 = fam + 3; m.sk2 = cluster(m.H / 128, m.I / 64);
+        if (f8n_ok && items * (m.H / 128) >= 4LL * sm_count()) m.sk2 = 11;
+        if (f8n_ok) m.nt = want <= 16 ? 2 : (want <= 32 ? 4 : 8);
         if (wt != kE4M3 && want > 64) m.nt = 16;
     }
     int nt_tiles = want <= 8 ? 1 : (want <= 16 ? 2 : (want <= 32 ? 4 : 8));
