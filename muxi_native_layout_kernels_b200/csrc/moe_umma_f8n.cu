@@ -264,7 +264,7 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
 // the MMAs of the next tile run while the mover warps write the previous tile's rows; no cluster, so the epilogue goes
 // straight from tensor memory to the fp32 rows of the combine scratch (128 consecutive floats per slot and warp pass).
 template <int NP, int STAGES>
-__global__ void __launch_bounds__(192, 2) moe_umma_f8n_rows_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(192, NP <= 16 ? 6 : 2) moe_umma_f8n_rows_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                    const __grid_constant__ CUtensorMap map_x,
                                                                    const MoeUmmaParams p, const int tiles_per_cta) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
