@@ -29,6 +29,30 @@ _MOE_TABLE_FILE = Path(__file__).resolve().parent / "moe_dispatch_arg.csv"
 _MOE_TABLE = None
 
 
+# Opt-in NVTX ranges around the stages of one layer call ("planC.router", "planC.experts"), for timelines taken with a
+# system profiler; off by default (a range costs host time on every call).
+_NVTX = False
+
+
+def set_nvtx(enabled: bool) -> None:
+    global _NVTX
+    _NVTX = bool(enabled)
+
+
+class _Range:
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if _NVTX:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if _NVTX:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 def _moe_table():
     global _MOE_TABLE
     if _MOE_TABLE is None:
@@ -138,11 +162,13 @@ def fused_moe(
     # renormalisation (reference: two torch ops, muxi_moe_planC.py:69-70) happens inside the router kernel, with the
     # same roundings
     elif gate_weight is not None:
-        ext.fused_router_gemm_gate(hidden_states, gate_weight, score_fun, num_expert_group, topk_group, topk_ids,
-                                   topk_weights, topk, gating_bias, renormalize=bool(renormalize))
+        with _Range("planC.router"):
+            ext.fused_router_gemm_gate(hidden_states, gate_weight, score_fun, num_expert_group, topk_group, topk_ids,
+                                       topk_weights, topk, gating_bias, renormalize=bool(renormalize))
     else:
-        ext.fused_routing_gate(gating_output, score_fun, B, H, num_expert_group, topk_group, topk_ids, topk_weights,
-                               topk, gating_bias, renormalize=bool(renormalize))
+        with _Range("planC.router"):
+            ext.fused_routing_gate(gating_output, score_fun, B, H, num_expert_group, topk_group, topk_ids, topk_weights,
+                                   topk, gating_bias, renormalize=bool(renormalize))
 
     # 2. experts
     assert e1 == e2
@@ -177,6 +203,16 @@ def fused_moe(
 
     if experts_map is not None and experts_map.dtype != torch.int:
         experts_map = experts_map.to(torch.int)
+    with _Range("planC.experts" if routing is None else "planC.router+experts"):
+        _experts(soft_fp8, w1, w2, hidden_states, B, e1, topk, topk_ids, topk_weights, sorted_token_ids, cumsum_buffer,
+                 padded_num_experts, experts_ids, C, y, w1_scale, w2_scale, block_shape, experts_map, fp8_repacked,
+                 deterministic, tune, routing, APerWarp, splitK, tile_m_2, tile_n_2, tile_k_2, block_dim_x_gemm)
+    return y.view(shape)
+
+
+def _experts(soft_fp8, w1, w2, hidden_states, B, e1, topk, topk_ids, topk_weights, sorted_token_ids, cumsum_buffer,
+             padded_num_experts, experts_ids, C, y, w1_scale, w2_scale, block_shape, experts_map, fp8_repacked,
+             deterministic, tune, routing, APerWarp, splitK, tile_m_2, tile_n_2, tile_k_2, block_dim_x_gemm):
     if soft_fp8:
         ext.fused_experts_compute(w1, w2, hidden_states, B, e1, topk, topk_ids, topk_weights, sorted_token_ids,
                                   cumsum_buffer, padded_num_experts, experts_ids, C, y, w1_scale, w2_scale,
@@ -189,7 +225,6 @@ def fused_moe(
                                   splitK=splitK, tile_m_2=tile_m_2, tile_n_2=tile_n_2, tile_k_2=tile_k_2,
                                   block_dim_x_gemm=block_dim_x_gemm, experts_map=experts_map,
                                   deterministic=deterministic, tune=tune, routing=routing)
-    return y.view(shape)
 
 
 class GraphedFusedMoE:

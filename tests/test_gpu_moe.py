@@ -556,6 +556,8 @@ def test_graphed_fused_moe_replays_bit_exactly():
     w1 = mlk.layoutA(randn((E, 2 * I, H), 901, 0.05).to(dev))
     w2 = mlk.layoutA(randn((E, H, I), 902, 0.05).to(dev))
     layer = GraphedFusedMoE(w1, w2, T, E, topk, True)
+    from muxi_native_layout_kernels_b200 import muxi_moe_planC
+    muxi_moe_planC.set_nvtx(True)        # opt-in NVTX ranges around the stages: same results, only markers
     for seed in (903, 904, 905):
         x = randn((T, H), seed, 1.0).to(dev)
         logits = randn((T, E), seed + 10, 1.0).to(dev)
@@ -563,6 +565,7 @@ def test_graphed_fused_moe_replays_bit_exactly():
         got = layer(x, logits)
         torch.cuda.synchronize()
         assert torch.equal(got, want)
+    muxi_moe_planC.set_nvtx(False)
     with pytest.raises(ValueError, match="captured for"):
         layer(x[:3], logits[:3])
 
