@@ -212,3 +212,21 @@ def test_package_utils_match_reference_helpers(golden_dir):
     y = utils.fused_moe(m["x"], m["w1"], m["w2"], m["logits"], m["topk"], m["groups"], m["topk_group"],
                         global_num_experts=m["logits"].shape[1], renormalize=m["renormalize"])
     assert torch.equal(y, m["y"])
+
+
+def test_moe_table_lookup_rules():
+    """lookup_moe_args: the row of the smallest tabulated token count >= T, the last row beyond the table, decode rows
+    (tuning values >= 300) only where the caller can use them, nothing for an unknown geometry."""
+    from muxi_native_layout_kernels_b200.muxi_moe_planC import lookup_moe_args
+    fine = (128, 8, 2048, 768, True)
+    assert lookup_moe_args(*fine, 1)[1] >= 300 and lookup_moe_args(*fine, 2)[1] >= 300
+    assert lookup_moe_args(*fine, 3) == lookup_moe_args(*fine, 4) and lookup_moe_args(*fine, 4)[1] < 300
+    assert lookup_moe_args(*fine, 100) == lookup_moe_args(*fine, 128)
+    assert lookup_moe_args(*fine, 100000) == lookup_moe_args(*fine, 512)
+    # an expert-parallel rank with 16 local experts looks its row up by (16, tokens x 16 / 128); with 32 global tokens
+    # the decode rows (T_eff = 4) cannot be used (the batch is larger than 8) and the next row applies
+    ep = (16, 8, 2048, 768, True)
+    assert lookup_moe_args(*ep, 4)[1] >= 300
+    assert lookup_moe_args(*ep, 4, allow_decode=False)[1] < 300
+    assert lookup_moe_args(*ep, 4, allow_decode=False) == lookup_moe_args(*ep, 16)
+    assert lookup_moe_args(7, 3, 640, 320, False, 5) is None

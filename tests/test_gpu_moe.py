@@ -748,3 +748,22 @@ def test_ep_reduce_shares_reports_a_peer_that_never_arrives():
     y = mlk.gemv_layoutA(mlk.layoutA(torch.ones(64, 64, dtype=torch.bfloat16, device=dev)), torch.ones(1, 64, dtype=torch.bfloat16, device=dev))
     torch.cuda.synchronize()
     assert float(y[0, 0]) == 64.0 and mlk.kernel_status() == 0
+
+
+def test_fused_moe_writes_into_a_given_output_tensor():
+    """out= (extension): the result lands in the caller's tensor, 16-bit or the un-rounded fp32 sums."""
+    dev = require_gpu()
+    E, topk, H, I, T = 16, 4, 256, 128, 19
+    x = randn((T, H), 1500).to(dev)
+    w1 = mlk.layoutA(randn((E, 2 * I, H), 1501, 0.05).to(dev))
+    w2 = mlk.layoutA(randn((E, H, I), 1502, 0.05).to(dev))
+    logits = randn((T, E), 1503).to(dev)
+    want = planC_moe(x, w1, w2, logits, topk, True)
+    buf = torch.full((T, H), 7.0, dtype=torch.bfloat16, device=dev)
+    got = planC_moe(x, w1, w2, logits, topk, True, out=buf)
+    assert got.data_ptr() == buf.data_ptr() and torch.equal(buf, want)
+    buf32 = torch.full((T, H), 7.0, dtype=torch.float32, device=dev)
+    got32 = planC_moe(x, w1, w2, logits, topk, True, out_dtype=torch.float32, out=buf32)
+    assert got32.data_ptr() == buf32.data_ptr() and torch.equal(buf32.to(torch.bfloat16), want)
+    with pytest.raises(ValueError):
+        planC_moe(x, w1, w2, logits, topk, True, out=buf32)
