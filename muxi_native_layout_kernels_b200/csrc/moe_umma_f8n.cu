@@ -263,16 +263,18 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
 // and the ring keeps streaming across tile boundaries; the accumulator is double-buffered (up to 32 slots per item), so
 // the MMAs of the next tile run while the mover warps write the previous tile's rows; no cluster, so the epilogue goes
 // straight from tensor memory to the fp32 rows of the combine scratch (128 consecutive floats per slot and warp pass).
-template <int NP, int STAGES>
-__global__ void __launch_bounds__(192, NP <= 16 ? 6 : 2) moe_umma_f8n_rows_kernel(const __grid_constant__ CUtensorMap map_a,
+template <int NP, int STAGES, int BK>
+__global__ void __launch_bounds__(192, (NP <= 16 && BK == 64) ? 6 : 2) moe_umma_f8n_rows_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                    const __grid_constant__ CUtensorMap map_x,
                                                                    const MoeUmmaParams p, const int tiles_per_cta) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int AB = NP <= 32 ? 2 : 1;               // accumulator buffers
     constexpr int S2 = NP == 16 ? 2 : (NP == 32 ? 2 : 4);
-    constexpr int kXTile = NP * 128;
-    constexpr int kStageBytes = kRaw + kXTile;
-    constexpr uint32_t kTmemCols = (AB * NP + S2 * kACols) <= 64 ? 64 : 128;
+    constexpr int kXTile = NP * 128;                   // split planes of one 64-wide k block
+    constexpr int kRawB = kTileM * BK;                 // weight bytes of one stage: BK = 64 or 128 k per stage
+    constexpr int kACol = BK / 4;                      // their tensor-memory columns
+    constexpr int kStageBytes = kRawB + (BK / 64) * kXTile;
+    constexpr uint32_t kTmemCols = (AB * NP + S2 * kACol) <= 64 ? 64 : ((AB * NP + S2 * kACol) <= 128 ? 128 : 256);
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 2 * S2 + 2 * AB];
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int abort_flag;
@@ -324,9 +326,11 @@ __global__ void __launch_bounds__(192, NP <= 16 ? 6 : 2) moe_umma_f8n_rows_kerne
         for (; early < STAGES && early < total; ++early) {
             const int tl = early / KB, kb = early - tl * KB;
             mbar_expect_tx(full(early), kStageBytes);
-            tma_load_3d(base + early * kStageBytes, &map_a, full(early), 0, kb * (kBK / 8),
+            tma_load_3d(base + early * kStageBytes, &map_a, full(early), 0, kb * (BK / 8),
                         (expert * tiles_total + tile0 + tl) * (kTileM / 16));
-            tma_load_2d(base + early * kStageBytes + kRaw, &map_x, full(early), kb * 128, cpos0);
+#pragma unroll
+            for (int h = 0; h < BK / 64; ++h)
+                tma_load_2d(base + early * kStageBytes + kRawB + h * kXTile, &map_x, full(early), (kb * (BK / 64) + h) * 128, cpos0);
         }
     }
     // slot and factor (inverse row scale x routing weight) of every column of the accumulator: every mover warp loads
@@ -368,9 +372,11 @@ __global__ void __launch_bounds__(192, NP <= 16 ? 6 : 2) moe_umma_f8n_rows_kerne
             }
             if (abort_flag) break;
             mbar_expect_tx(full(s), kStageBytes);
-            tma_load_3d(base + s * kStageBytes, &map_a, full(s), 0, kb * (kBK / 8),
+            tma_load_3d(base + s * kStageBytes, &map_a, full(s), 0, kb * (BK / 8),
                         (expert * tiles_total + tile0 + tl) * (kTileM / 16));
-            tma_load_2d(base + s * kStageBytes + kRaw, &map_x, full(s), kb * 128, cpos0);
+#pragma unroll
+            for (int h = 0; h < BK / 64; ++h)
+                tma_load_2d(base + s * kStageBytes + kRawB + h * kXTile, &map_x, full(s), (kb * (BK / 64) + h) * 128, cpos0);
             ++issued;
             if (++kb == KB) { kb = 0; ++tl; }
         }
@@ -390,13 +396,17 @@ __global__ void __launch_bounds__(192, NP <= 16 ? 6 : 2) moe_umma_f8n_rows_kerne
             }
             mbar_wait(full(s), (u / STAGES) & 1);       // already complete (the movers waited for it)
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t xt = base + s * kStageBytes + kRaw;
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
+            for (int h = 0; h < BK / 64; ++h) {
+                const uint32_t xt = base + s * kStageBytes + kRawB + h * kXTile;
 #pragma unroll
-                for (int term = 0; term < 2; ++term) {
-                    const uint64_t db = smem_desc(xt + term * 64 + j * 32, 16, 1024, 2);
-                    umma_f8_ts(tmem + b * NP, tmem + AB * NP + s2 * kACols + j * 8, db, idesc, (kb > 0 || j > 0 || term > 0) ? 1u : 0u);
+                for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                    for (int term = 0; term < 2; ++term) {
+                        const uint64_t db = smem_desc(xt + term * 64 + j * 32, 16, 1024, 2);
+                        umma_f8_ts(tmem + b * NP, tmem + AB * NP + s2 * kACol + h * 16 + j * 8, db, idesc,
+                                   (kb > 0 || h > 0 || j > 0 || term > 0) ? 1u : 0u);
+                    }
                 }
             }
             umma_commit(empty(s));
@@ -437,15 +447,18 @@ __global__ void __launch_bounds__(192, NP <= 16 ? 6 : 2) moe_umma_f8n_rows_kerne
                 ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint8_t* raw = base_ptr + s * kStageBytes + (lrow >> 4) * (kBK * 16) + (lrow & 15) * 8;
-                uint32_t v[16];
+                const uint8_t* raw = base_ptr + s * kStageBytes + (lrow >> 4) * (BK * 16) + (lrow & 15) * 8;
 #pragma unroll
-                for (int o = 0; o < 8; ++o) {
-                    const uint2 x = *reinterpret_cast<const uint2*>(raw + o * 128);
-                    v[2 * o] = x.x;
-                    v[2 * o + 1] = x.y;
+                for (int h = 0; h < BK / 64; ++h) {
+                    uint32_t v[16];
+#pragma unroll
+                    for (int o = 0; o < 8; ++o) {
+                        const uint2 x = *reinterpret_cast<const uint2*>(raw + (h * 8 + o) * 128);
+                        v[2 * o] = x.x;
+                        v[2 * o + 1] = x.y;
+                    }
+                    tmem_st16(tmem + ((uint32_t)(quad * 32) << 16) + AB * NP + s2 * kACol + h * 16, v);
                 }
-                tmem_st16(tmem + ((uint32_t)(quad * 32) << 16) + AB * NP + s2 * kACols, v);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
@@ -559,21 +572,29 @@ const void* kernel_for(int np, int stages) {
     return nullptr;
 }
 
-template <int NP>
+template <int NP, int BK>
 const void* rows_kernel_for_stages(int stages) {
     switch (stages) {
-        case 2: return reinterpret_cast<const void*>(moe_umma_f8n_rows_kernel<NP, 2>);
-        case 3: return reinterpret_cast<const void*>(moe_umma_f8n_rows_kernel<NP, 3>);
-        case 4: return reinterpret_cast<const void*>(moe_umma_f8n_rows_kernel<NP, 4>);
-        case 6: return reinterpret_cast<const void*>(moe_umma_f8n_rows_kernel<NP, 6>);
+        case 2: return reinterpret_cast<const void*>(moe_umma_f8n_rows_kernel<NP, 2, BK>);
+        case 3: return reinterpret_cast<const void*>(moe_umma_f8n_rows_kernel<NP, 3, BK>);
+        case 4: return reinterpret_cast<const void*>(moe_umma_f8n_rows_kernel<NP, 4, BK>);
+        case 6: return reinterpret_cast<const void*>(moe_umma_f8n_rows_kernel<NP, 6, BK>);
     }
     return nullptr;
 }
-const void* rows_kernel_for(int np, int stages) {
+const void* rows_kernel_for(int np, int stages, int bk) {
+    if (bk == 128) {
+        switch (np) {
+            case 16: return rows_kernel_for_stages<16, 128>(stages);
+            case 32: return rows_kernel_for_stages<32, 128>(stages);
+            case 64: return rows_kernel_for_stages<64, 128>(stages);
+        }
+        return nullptr;
+    }
     switch (np) {
-        case 16: return rows_kernel_for_stages<16>(stages);
-        case 32: return rows_kernel_for_stages<32>(stages);
-        case 64: return rows_kernel_for_stages<64>(stages);
+        case 16: return rows_kernel_for_stages<16, 64>(stages);
+        case 32: return rows_kernel_for_stages<32, 64>(stages);
+        case 64: return rows_kernel_for_stages<64, 64>(stages);
     }
     return nullptr;
 }
@@ -623,20 +644,27 @@ int launch_moe_umma_f8n(int mode, const void* W, int E, int rows, int k, const v
         const int tiles_per_cta = cluster_k - 10;
         if (encode_fn() == nullptr) return fail(kUnsupported, "moe (tcgen05): cuTensorMapEncodeTiled is not available");
         if (((uintptr_t)planes & 127) != 0) return fail(kInvalidArg, "moe (tcgen05, native e4m3): split planes must be 128-byte aligned");
-        const void* kern = rows_kernel_for(np, stages);
+        // stages >= 40: 128 k per stage (stages - 40 ring stages), half as many steps of the mover / MMA chain per tile
+        int bk = kBK;
+        if (stages >= 40) {
+            stages -= 40;
+            if (k % 128 == 0) bk = 128;
+        }
+        const void* kern = rows_kernel_for(np, stages, bk);
         if (kern == nullptr) return fail(kInvalidArg, "moe (tcgen05, native e4m3): token tile %d / stages %d not built", np, stages);
-        const size_t want = (size_t)stages * (kRaw + np * 128) + 1024;
+        const size_t want = (size_t)stages * (kTileM * bk + (bk / 64) * np * 128) + 1024;
         const int s2 = np == 64 ? 4 : 2, ab = np <= 32 ? 2 : 1;
-        const size_t smem = prepare_kernel(kern, 192, want, (ab * np + s2 * kACols) <= 64 ? 64 : 128);
+        const int cols = ab * np + s2 * (bk / 4);
+        const size_t smem = prepare_kernel(kern, 192, want, cols <= 64 ? 64 : (cols <= 128 ? 128 : 256));
         if (smem == 0) return fail(kCudaError, "moe (tcgen05, native e4m3): a CTA with %d stages does not fit on this device", stages);
         CUtensorMap ma, mx;
-        if (!make_map_a8_bk(&ma, W, (long long)E * rows, k, kBK)) return fail(kUnsupported, "moe (tcgen05): weight tensor map rejected");
+        if (!make_map_a8_bk(&ma, W, (long long)E * rows, k, bk)) return fail(kUnsupported, "moe (tcgen05): weight tensor map rejected");
         if (!make_map_planes(&mx, planes, plane_rows, k, np)) return fail(kUnsupported, "moe (tcgen05): activation tensor map rejected");
         MoeUmmaParams mp{};
         mp.worklist = worklist; mp.sorted = sorted; mp.topk_weights = topk_weights; mp.out = out;
         mp.rows = rows;
         mp.tiles_per_expert = rows / kTileM;
-        mp.kblocks = k / kBK;
+        mp.kblocks = k / bk;
         mp.n_slots = n_slots;
         mp.status = status;
         mp.inv_scale = inv_scale;
@@ -654,6 +682,7 @@ int launch_moe_umma_f8n(int mode, const void* W, int E, int rows, int k, const v
         if (e != cudaSuccess) return fail(kCudaError, "moe_umma_f8n_rows launch: %s", cudaGetErrorString(e));
         return kOk;
     }
+    if (stages >= 40) stages -= 40;       // 128 k per stage exists for the second GEMM without clusters only
     if (cluster_k < 1 || cluster_k > 8 || cluster_k > k / kBK) return fail(kInvalidArg, "moe (tcgen05, native e4m3): cluster size %d out of range", cluster_k);
     if (encode_fn() == nullptr) return fail(kUnsupported, "moe (tcgen05): cuTensorMapEncodeTiled is not available");
     if (((uintptr_t)planes & 127) != 0) return fail(kInvalidArg, "moe (tcgen05, native e4m3): split planes must be 128-byte aligned");

@@ -106,7 +106,9 @@ def scan_case(cfg, T, w1, w2, wg, g, dev):
             if g1_best is None:
                 continue
             # second GEMM: CTAs per cluster, or 10 + row tiles per CTA (no cluster)
-            for st2, ck2 in itertools.product([2, 3, 4, 6], [1, 2, 4, 11, 12, 14, 16, 18]):
+            # (240 + stages: 128 k per stage, for the form without clusters)
+            for st2, ck2 in itertools.chain(itertools.product([2, 3, 4, 6], [1, 2, 4, 11, 12, 14, 16, 18]),
+                                            itertools.product([42, 43, 44], [11, 12, 14, 16, 18] if I % 128 == 0 else [])):
                 args = (nt, g1_best[0], g1_best[1], 0, 200 + st2, ck2)
                 us = try_args(args)
                 if us is not None and us < best_us:
