@@ -370,7 +370,10 @@ int launch_fused_experts(const MoeParams& m0, cudaStream_t s) {
         const int fam = f8n_ok ? 200 : 100;
         m.wm1 = fam + (f8n_ok ? 4 : 3); m.sk1 = cluster(m.I / 128, m.H / 64);
         m.wm2 = fam + 3; m.sk2 = cluster(m.H / 128, m.I / 64);
-        if (f8n_ok && items * (m.H / 128) >= 4LL * sm_count()) m.sk2 = 11;
+        if (f8n_ok && items * (m.H / 128) >= 4LL * sm_count()) {
+            m.sk2 = 11;
+            if (m.I % 128 == 0 && want <= 32) m.wm2 = fam + 42;       // 128 k per stage, two ring stages
+        }
         if (f8n_ok) m.nt = want <= 16 ? 2 : (want <= 32 ? 4 : 8);
         if (wt != kE4M3 && want > 64) m.nt = 16;
     }
