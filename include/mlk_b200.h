@@ -274,8 +274,10 @@ int mlk_moe_align(int batchSize, int expertCount, int topK, int microBatchSize, 
  *                    e4m3 weights without block scales only; with scales or 16-bit weights the same row runs as
  *                    100 + stages.  For this family "cluster split-K of GEMM2" = 10 + R (R = 1..8) selects the
  *                    second-GEMM kernel without a cluster in which one CTA walks R consecutive 128-row tiles of
- *                    the same work item; there 240 + stages (instead of 200 + stages) streams 128 k per ring
- *                    stage (inter % 128 == 0).
+ *                    the same work item.  240 + stages (instead of 200 + stages) streams 128 k per ring stage
+ *                    where that form is built: the second GEMM without a cluster (inter % 128 == 0) and the first
+ *                    GEMM with 64-slot token tiles, 2 or 3 stages, no cluster (hidden % 128 == 0); elsewhere it
+ *                    runs as 200 + stages.
  *     300            decode batches (batch_size <= 8, batch_size * topK <= 64): the whole expert compute as one
  *                    cooperative kernel, see mlk_fused_routing_experts_compute; larger batches run the library's choice
  *   Both fields name the same family; a mixed pair, or a tcgen05 family on a call that cannot use it, runs the

@@ -38,16 +38,19 @@ constexpr uint32_t f8n_tmem_cols(int na, int np) {
     return need <= 64 ? 64 : (need <= 128 ? 128 : 256);
 }
 
-template <int NP, int STAGES, int MODE>
+template <int NP, int STAGES, int MODE, int BK>
 __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_constant__ CUtensorMap map_a,
                                                               const __grid_constant__ CUtensorMap map_x,
                                                               const MoeUmmaParams p, const int static_weights) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int NA = MODE == 1 ? 2 : 1;
-    constexpr int S2 = f8n_slots(NA, NP);
-    constexpr int kXTile = NP * 128;
-    constexpr int kStageBytes = NA * kRaw + kXTile;
-    constexpr uint32_t kTmemCols = f8n_tmem_cols(NA, NP);
+    constexpr int S2 = BK == 64 ? f8n_slots(NA, NP) : 2;
+    constexpr int kXTile = NP * 128;                   // split planes of one 64-wide k block
+    constexpr int kRawB = kTileM * BK;                 // weight bytes of one tile and stage: BK = 64 or 128 k per stage
+    constexpr int kACol = BK / 4;                      // their tensor-memory columns
+    constexpr int kStageBytes = NA * kRawB + (BK / 64) * kXTile;
+    constexpr int kColsNeeded = NA * NP + S2 * NA * kACol;
+    constexpr uint32_t kTmemCols = kColsNeeded <= 64 ? 64 : (kColsNeeded <= 128 ? 128 : (kColsNeeded <= 256 ? 256 : 512));
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 2 * S2 + 1];
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int abort_flag;
@@ -94,11 +97,14 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
         // barriers are this thread's own, nobody else touches the ring yet
         for (; early < STAGES && early < nunits; ++early) {
             mbar_expect_tx(full(early), kStageBytes);
-            tma_load_3d(base + early * kStageBytes, &map_a, full(early), 0, (kb0 + early) * (kBK / 8), a_tile * (kTileM / 16));
+            tma_load_3d(base + early * kStageBytes, &map_a, full(early), 0, (kb0 + early) * (BK / 8), a_tile * (kTileM / 16));
             if constexpr (MODE == 1)
-                tma_load_3d(base + early * kStageBytes + kRaw, &map_a, full(early), 0, (kb0 + early) * (kBK / 8),
+                tma_load_3d(base + early * kStageBytes + kRawB, &map_a, full(early), 0, (kb0 + early) * (BK / 8),
                             (a_tile + p.up_tile_offset) * (kTileM / 16));
-            tma_load_2d(base + early * kStageBytes + NA * kRaw, &map_x, full(early), (kb0 + early) * 128, cpos0);
+#pragma unroll
+            for (int h = 0; h < BK / 64; ++h)
+                tma_load_2d(base + early * kStageBytes + NA * kRawB + h * kXTile, &map_x, full(early),
+                            ((kb0 + early) * (BK / 64) + h) * 128, cpos0);
         }
     }
     if (warp == 1) {
@@ -123,11 +129,13 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
             }
             if (abort_flag) break;
             mbar_expect_tx(full(s), kStageBytes);
-            tma_load_3d(base + s * kStageBytes, &map_a, full(s), 0, (kb0 + i) * (kBK / 8), a_tile * (kTileM / 16));
+            tma_load_3d(base + s * kStageBytes, &map_a, full(s), 0, (kb0 + i) * (BK / 8), a_tile * (kTileM / 16));
             if constexpr (MODE == 1)
-                tma_load_3d(base + s * kStageBytes + kRaw, &map_a, full(s), 0, (kb0 + i) * (kBK / 8),
+                tma_load_3d(base + s * kStageBytes + kRawB, &map_a, full(s), 0, (kb0 + i) * (BK / 8),
                             (a_tile + p.up_tile_offset) * (kTileM / 16));
-            tma_load_2d(base + s * kStageBytes + NA * kRaw, &map_x, full(s), (kb0 + i) * 128, cpos0);
+#pragma unroll
+            for (int h = 0; h < BK / 64; ++h)
+                tma_load_2d(base + s * kStageBytes + NA * kRawB + h * kXTile, &map_x, full(s), ((kb0 + i) * (BK / 64) + h) * 128, cpos0);
             ++issued;
         }
     } else if (warp == 1 && lane == 0) {
@@ -142,17 +150,20 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
             }
             mbar_wait(full(s), (i / STAGES) & 1);       // already complete (the movers waited for it)
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t xt = base + s * kStageBytes + NA * kRaw;
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
+            for (int h = 0; h < BK / 64; ++h) {
+                const uint32_t xt = base + s * kStageBytes + NA * kRawB + h * kXTile;
 #pragma unroll
-                for (int term = 0; term < 2; ++term) {
-                    // token tile [NP][hi 64 | lo 64], 128-byte swizzle: hi operand at byte 32 j of every row, lo 64 further
-                    const uint64_t db = smem_desc(xt + term * 64 + j * 32, 16, 1024, 2);
+                for (int j = 0; j < 2; ++j) {
 #pragma unroll
-                    for (int w = 0; w < NA; ++w) {
-                        const uint32_t ta = tmem + NA * NP + (s2 * NA + w) * kACols + j * 8;
-                        umma_f8_ts(tmem + w * NP, ta, db, idesc, (i > 0 || j > 0 || term > 0) ? 1u : 0u);
+                    for (int term = 0; term < 2; ++term) {
+                        // token tile [NP][hi 64 | lo 64], 128-byte swizzle: hi operand at byte 32 j of every row, lo 64 further
+                        const uint64_t db = smem_desc(xt + term * 64 + j * 32, 16, 1024, 2);
+#pragma unroll
+                        for (int w = 0; w < NA; ++w) {
+                            const uint32_t ta = tmem + NA * NP + (s2 * NA + w) * kACol + h * 16 + j * 8;
+                            umma_f8_ts(tmem + w * NP, ta, db, idesc, (i > 0 || h > 0 || j > 0 || term > 0) ? 1u : 0u);
+                        }
                     }
                 }
             }
@@ -179,15 +190,18 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int w = 0; w < NA; ++w) {
-                const uint8_t* raw = base_ptr + s * kStageBytes + w * kRaw + (lrow >> 4) * (kBK * 16) + (lrow & 15) * 8;
-                uint32_t v[16];
+                const uint8_t* raw = base_ptr + s * kStageBytes + w * kRawB + (lrow >> 4) * (BK * 16) + (lrow & 15) * 8;
 #pragma unroll
-                for (int o = 0; o < 8; ++o) {
-                    const uint2 x = *reinterpret_cast<const uint2*>(raw + o * 128);
-                    v[2 * o] = x.x;
-                    v[2 * o + 1] = x.y;
+                for (int h = 0; h < BK / 64; ++h) {
+                    uint32_t v[16];
+#pragma unroll
+                    for (int o = 0; o < 8; ++o) {
+                        const uint2 x = *reinterpret_cast<const uint2*>(raw + (h * 8 + o) * 128);
+                        v[2 * o] = x.x;
+                        v[2 * o + 1] = x.y;
+                    }
+                    tmem_st16(tmem + ((uint32_t)(quad * 32) << 16) + NA * NP + (s2 * NA + w) * kACol + h * 16, v);
                 }
-                tmem_st16(tmem + ((uint32_t)(quad * 32) << 16) + NA * NP + (s2 * NA + w) * kACols, v);
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -552,22 +566,27 @@ __global__ void __launch_bounds__(256) moe_split_inplace_warp_kernel(uint4* __re
     split_row_warp(r, k, repacked, reinterpret_cast<uint8_t*>(r), inv_scale + row);
 }
 
-template <int NP, int MODE>
+template <int NP, int MODE, int BK>
 const void* kernel_for_stages(int stages) {
     switch (stages) {
-        case 2: return reinterpret_cast<const void*>(moe_umma_f8n_kernel<NP, 2, MODE>);
-        case 3: return reinterpret_cast<const void*>(moe_umma_f8n_kernel<NP, 3, MODE>);
-        case 4: return reinterpret_cast<const void*>(moe_umma_f8n_kernel<NP, 4, MODE>);
-        case 6: return reinterpret_cast<const void*>(moe_umma_f8n_kernel<NP, 6, MODE>);
+        case 2: return reinterpret_cast<const void*>(moe_umma_f8n_kernel<NP, 2, MODE, BK>);
+        case 3: return reinterpret_cast<const void*>(moe_umma_f8n_kernel<NP, 3, MODE, BK>);
+        case 4: return reinterpret_cast<const void*>(moe_umma_f8n_kernel<NP, 4, MODE, BK>);
+        case 6: return reinterpret_cast<const void*>(moe_umma_f8n_kernel<NP, 6, MODE, BK>);
     }
     return nullptr;
 }
 template <int MODE>
-const void* kernel_for(int np, int stages) {
+const void* kernel_for(int np, int stages, int bk) {
+    if (bk == 128) {
+        // 128 k per stage: the first GEMM with 64-slot tiles (where the mover / MMA chain per k block weighs most)
+        if (MODE == 1 && np == 64 && stages <= 3) return kernel_for_stages<64, 1, 128>(stages);
+        return nullptr;
+    }
     switch (np) {
-        case 16: return kernel_for_stages<16, MODE>(stages);
-        case 32: return kernel_for_stages<32, MODE>(stages);
-        case 64: return kernel_for_stages<64, MODE>(stages);
+        case 16: return kernel_for_stages<16, MODE, 64>(stages);
+        case 32: return kernel_for_stages<32, MODE, 64>(stages);
+        case 64: return kernel_for_stages<64, MODE, 64>(stages);
     }
     return nullptr;
 }
@@ -682,27 +701,33 @@ int launch_moe_umma_f8n(int mode, const void* W, int E, int rows, int k, const v
         if (e != cudaSuccess) return fail(kCudaError, "moe_umma_f8n_rows launch: %s", cudaGetErrorString(e));
         return kOk;
     }
-    if (stages >= 40) stages -= 40;       // 128 k per stage exists for the second GEMM without clusters only
-    if (cluster_k < 1 || cluster_k > 8 || cluster_k > k / kBK) return fail(kInvalidArg, "moe (tcgen05, native e4m3): cluster size %d out of range", cluster_k);
+    // stages >= 40: 128 k per stage (stages - 40 ring stages) where that form is built (first GEMM, 64-slot tiles, no cluster)
+    int bk = kBK;
+    if (stages >= 40) {
+        stages -= 40;
+        if (mode == 1 && np == 64 && stages <= 3 && cluster_k == 1 && k % 128 == 0) bk = 128;
+    }
+    if (cluster_k < 1 || cluster_k > 8 || cluster_k > k / bk) return fail(kInvalidArg, "moe (tcgen05, native e4m3): cluster size %d out of range", cluster_k);
     if (encode_fn() == nullptr) return fail(kUnsupported, "moe (tcgen05): cuTensorMapEncodeTiled is not available");
     if (((uintptr_t)planes & 127) != 0) return fail(kInvalidArg, "moe (tcgen05, native e4m3): split planes must be 128-byte aligned");
-    const void* kern = mode == 1 ? kernel_for<1>(np, stages) : kernel_for<2>(np, stages);
+    const void* kern = mode == 1 ? kernel_for<1>(np, stages, bk) : kernel_for<2>(np, stages, bk);
     if (kern == nullptr) return fail(kInvalidArg, "moe (tcgen05, native e4m3): token tile %d / stages %d not built", np, stages);
     const int na = mode == 1 ? 2 : 1;
-    const size_t want = std::max((size_t)stages * (na * kRaw + np * 128), (size_t)na * np * 512) + 1024;
+    const size_t want = std::max((size_t)stages * (na * kTileM * bk + (bk / 64) * np * 128), (size_t)na * np * 512) + 1024;
     if (want > 227 * 1024) return fail(kUnsupported, "moe (tcgen05, native e4m3): %d stages do not fit in shared memory", stages);
-    const size_t smem = prepare_kernel(kern, 192, want, (int)f8n_tmem_cols(na, np));
+    const int cols = bk == 64 ? (int)f8n_tmem_cols(na, np) : na * np + 2 * na * (bk / 4);
+    const size_t smem = prepare_kernel(kern, 192, want, cols <= 64 ? 64 : (cols <= 128 ? 128 : (cols <= 256 ? 256 : 512)));
     if (smem == 0) return fail(kCudaError, "moe (tcgen05, native e4m3): a CTA with %d stages does not fit on this device", stages);
     const long long w_rows = (long long)E * (mode == 1 ? 2 * rows : rows);
     CUtensorMap ma, mx;
-    if (!make_map_a8_bk(&ma, W, w_rows, k, kBK)) return fail(kUnsupported, "moe (tcgen05): weight tensor map rejected");
+    if (!make_map_a8_bk(&ma, W, w_rows, k, bk)) return fail(kUnsupported, "moe (tcgen05): weight tensor map rejected");
     if (!make_map_planes(&mx, planes, plane_rows, k, np)) return fail(kUnsupported, "moe (tcgen05): activation tensor map rejected");
     MoeUmmaParams mp{};
     mp.worklist = worklist; mp.sorted = sorted; mp.topk_weights = topk_weights; mp.out = out;
     mp.rows = rows;
     mp.tiles_per_expert = (mode == 1 ? 2 * rows : rows) / kTileM;
     mp.up_tile_offset = rows / kTileM;
-    mp.kblocks = k / kBK;
+    mp.kblocks = k / bk;
     mp.n_slots = n_slots;
     mp.status = status;
     mp.inv_scale = inv_scale;

@@ -99,7 +99,9 @@ def scan_case(cfg, T, w1, w2, wg, g, dev):
         # native-e4m3 tcgen05 expert GEMMs (weights undecoded into the 8-bit MMA): wm = 200 + ring stages
         for nt in [n for n in (2, 4, 8) if n * 8 <= max(16, 2 * T)]:
             g1_best, g1_us = None, float("inf")
-            for st1, ck1 in itertools.product([2, 3, 4, 6], [1, 2, 4, 8] if few else [1, 2, 4]):
+            # (240 + stages: 128 k per stage, built for 64-slot tiles without a cluster)
+            for st1, ck1 in itertools.chain(itertools.product([2, 3, 4, 6], [1, 2, 4, 8] if few else [1, 2, 4]),
+                                            [(42, 1), (43, 1)] if (nt == 8 and H % 128 == 0) else []):
                 us = try_args((nt, 200 + st1, ck1, 0, 203, 2))
                 if us is not None and us < g1_us:
                     g1_best, g1_us = (200 + st1, ck1), us

@@ -154,7 +154,8 @@ def test_packaged_table_rows_name_launches_the_library_accepts():
         elif wm1 >= 100:     # tcgen05 expert GEMMs: 100 (decode) or 200 (native e4m3) + ring stages, CTAs per cluster
             fam = 200 if wm1 >= 200 else 100
             assert H % 128 == 0 and I % 128 == 0 and (fam == 100 or fp8) and (wm2 >= 200) == (wm1 >= 200), what
-            assert wm1 - fam in (2, 3, 4, 6) and 1 <= sk1 <= min(8, H // 64), what
+            assert (wm1 - fam in (2, 3, 4, 6) and 1 <= sk1 <= min(8, H // 64)) or \
+                   (fam == 200 and wm1 - fam in (42, 43) and nt == 8 and sk1 == 1 and H % 128 == 0), what      # 128 k per stage
             assert wm2 - fam in (2, 3, 4, 6) or (fam == 200 and wm2 - fam in (42, 43, 44, 46) and 11 <= sk2 <= 18), what    # 240 + stages: 128 k per stage
             assert 1 <= sk2 <= min(8, I // 64) or (fam == 200 and 11 <= sk2 <= 18), what      # 10 + row tiles per CTA
         else:

@@ -313,7 +313,8 @@ def test_moe_soft_fp8_native_tensor_core_expert_gemms(T, repack):
     logits = randn((T, E), 903 + T, 1.0)
     for tune in [(1, 202, 1, 0, 202, 1), (2, 203, 2, 0, 204, 2), (4, 204, 4, 0, 206, 1), (8, 202, 2, 0, 203, 2),
                  (2, 203, 1, 0, 203, 12), (4, 203, 2, 0, 202, 11), (8, 204, 1, 0, 204, 18),
-                 (2, 203, 1, 0, 243, 11), (4, 204, 1, 0, 242, 12), (8, 203, 1, 0, 244, 14)]:
+                 (2, 203, 1, 0, 243, 11), (4, 204, 1, 0, 242, 12), (8, 203, 1, 0, 244, 14),
+                 (8, 242, 1, 0, 203, 12), (8, 243, 1, 0, 242, 14)]:
         y = _moe_compare(x, w1, w2, logits, topk, f"moe fp8 native T={T} repack={repack} tune={tune}", fp8=True,
                          repack=repack, tune=tune)
         y0 = _moe_compare(x, w1, w2, logits, topk, f"moe fp8 warp-level T={T}", fp8=True, repack=repack,
