@@ -57,6 +57,7 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile = blockIdx.x, rank = blockIdx.y, SK = gridDim.y;
+    const uint64_t wpol = l2_evict_first_policy();       // weights are read once: first out of L2
 
     // the work list and the split planes come from kernels earlier in the stream: nothing can start before them
     pdl_wait();
@@ -97,10 +98,10 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
         // barriers are this thread's own, nobody else touches the ring yet
         for (; early < STAGES && early < nunits; ++early) {
             mbar_expect_tx(full(early), kStageBytes);
-            tma_load_3d(base + early * kStageBytes, &map_a, full(early), 0, (kb0 + early) * (BK / 8), a_tile * (kTileM / 16));
+            tma_load_3d_hint(base + early * kStageBytes, &map_a, full(early), 0, (kb0 + early) * (BK / 8), a_tile * (kTileM / 16), wpol);
             if constexpr (MODE == 1)
-                tma_load_3d(base + early * kStageBytes + kRawB, &map_a, full(early), 0, (kb0 + early) * (BK / 8),
-                            (a_tile + p.up_tile_offset) * (kTileM / 16));
+                tma_load_3d_hint(base + early * kStageBytes + kRawB, &map_a, full(early), 0, (kb0 + early) * (BK / 8),
+                            (a_tile + p.up_tile_offset) * (kTileM / 16), wpol);
 #pragma unroll
             for (int h = 0; h < BK / 64; ++h)
                 tma_load_2d(base + early * kStageBytes + NA * kRawB + h * kXTile, &map_x, full(early),
@@ -129,10 +130,10 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
             }
             if (abort_flag) break;
             mbar_expect_tx(full(s), kStageBytes);
-            tma_load_3d(base + s * kStageBytes, &map_a, full(s), 0, (kb0 + i) * (BK / 8), a_tile * (kTileM / 16));
+            tma_load_3d_hint(base + s * kStageBytes, &map_a, full(s), 0, (kb0 + i) * (BK / 8), a_tile * (kTileM / 16), wpol);
             if constexpr (MODE == 1)
-                tma_load_3d(base + s * kStageBytes + kRawB, &map_a, full(s), 0, (kb0 + i) * (BK / 8),
-                            (a_tile + p.up_tile_offset) * (kTileM / 16));
+                tma_load_3d_hint(base + s * kStageBytes + kRawB, &map_a, full(s), 0, (kb0 + i) * (BK / 8),
+                            (a_tile + p.up_tile_offset) * (kTileM / 16), wpol);
 #pragma unroll
             for (int h = 0; h < BK / 64; ++h)
                 tma_load_2d(base + s * kStageBytes + NA * kRawB + h * kXTile, &map_x, full(s), ((kb0 + i) * (BK / 64) + h) * 128, cpos0);
@@ -296,6 +297,7 @@ __global__ void __launch_bounds__(192, (NP <= 16 && BK == 64) ? 6 : 2) moe_umma_
     __shared__ float factor_w[4][NP];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint64_t wpol = l2_evict_first_policy();       // weights are read once: first out of L2
 
     pdl_wait();
     pdl_launch_dependents();
@@ -340,8 +342,8 @@ __global__ void __launch_bounds__(192, (NP <= 16 && BK == 64) ? 6 : 2) moe_umma_
         for (; early < STAGES && early < total; ++early) {
             const int tl = early / KB, kb = early - tl * KB;
             mbar_expect_tx(full(early), kStageBytes);
-            tma_load_3d(base + early * kStageBytes, &map_a, full(early), 0, kb * (BK / 8),
-                        (expert * tiles_total + tile0 + tl) * (kTileM / 16));
+            tma_load_3d_hint(base + early * kStageBytes, &map_a, full(early), 0, kb * (BK / 8),
+                        (expert * tiles_total + tile0 + tl) * (kTileM / 16), wpol);
 #pragma unroll
             for (int h = 0; h < BK / 64; ++h)
                 tma_load_2d(base + early * kStageBytes + kRawB + h * kXTile, &map_x, full(early), (kb * (BK / 64) + h) * 128, cpos0);
@@ -386,8 +388,8 @@ __global__ void __launch_bounds__(192, (NP <= 16 && BK == 64) ? 6 : 2) moe_umma_
             }
             if (abort_flag) break;
             mbar_expect_tx(full(s), kStageBytes);
-            tma_load_3d(base + s * kStageBytes, &map_a, full(s), 0, kb * (BK / 8),
-                        (expert * tiles_total + tile0 + tl) * (kTileM / 16));
+            tma_load_3d_hint(base + s * kStageBytes, &map_a, full(s), 0, kb * (BK / 8),
+                        (expert * tiles_total + tile0 + tl) * (kTileM / 16), wpol);
 #pragma unroll
             for (int h = 0; h < BK / 64; ++h)
                 tma_load_2d(base + s * kStageBytes + kRawB + h * kXTile, &map_x, full(s), (kb * (BK / 64) + h) * 128, cpos0);
