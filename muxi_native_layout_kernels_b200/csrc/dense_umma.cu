@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const 
         const int nunits = (int)(u1 - u0);
         int lt = tile0, lk = kb0;     // next unit whose weights are loaded
         auto load_a = [&](int s) {
-            tma_load_4d(a_base + s * kABytes, &map_a, full_bar(s), 0, lk * (kBlockK / 8), lt * (kTileM / 16), 0);
+            tma_load_4d_hint(a_base + s * kABytes, &map_a, full_bar(s), 0, lk * (kBlockK / 8), lt * (kTileM / 16), 0, l2_evict_first_policy());
         };
         int i = 0;
         if (static_weights) {

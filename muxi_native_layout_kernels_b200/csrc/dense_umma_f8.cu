@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8_kernel(const __grid_cons
         auto load_raw = [&](int i) {
             const int s = i % STAGES;
             mbar_expect_tx(raw_full(s), kRawBytes);
-            tma_load_3d(r_base + s * kRawBytes, &map_a, raw_full(s), 0, (kb0 + i) * (kBlockK / 8), tile * (kTileM / 16));
+            tma_load_3d_hint(r_base + s * kRawBytes, &map_a, raw_full(s), 0, (kb0 + i) * (kBlockK / 8), tile * (kTileM / 16), l2_evict_first_policy());
             ++raw_issued;
         };
         int ri = 0;      // next unit whose weights are requested

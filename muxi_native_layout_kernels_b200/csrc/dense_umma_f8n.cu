@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8n_kernel(const __grid_con
         // ---- TMA producer ----
         auto load_a = [&](int i) {
             const int s = i % STAGES;
-            tma_load_3d(base + s * kStageBytes, &map_a, full(s), 0, (kb0 + i) * (BK / 8), tile * (kTileM / 16));
+            tma_load_3d_hint(base + s * kStageBytes, &map_a, full(s), 0, (kb0 + i) * (BK / 8), tile * (kTileM / 16), l2_evict_first_policy());
         };
         auto load_x = [&](int i) {
             const int s = i % STAGES;
