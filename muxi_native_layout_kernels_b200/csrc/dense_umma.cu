@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const 
     __shared__ volatile int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint64_t wpol = l2_evict_first_policy();       // weights are read once: first out of L2
     const int G = gridDim.x, g = blockIdx.x;
     const int KB = p.kblocks;
     const long long U = (long long)(p.m / kTileM) * KB;
@@ -176,7 +177,7 @@ __global__ void __launch_bounds__(192, CLUSTER ? 2 : 1) dense_umma_kernel(const 
         const int nunits = (int)(u1 - u0);
         int lt = tile0, lk = kb0;     // next unit whose weights are loaded
         auto load_a = [&](int s) {
-            tma_load_4d_hint(a_base + s * kABytes, &map_a, full_bar(s), 0, lk * (kBlockK / 8), lt * (kTileM / 16), 0, l2_evict_first_policy());
+            tma_load_4d_hint(a_base + s * kABytes, &map_a, full_bar(s), 0, lk * (kBlockK / 8), lt * (kTileM / 16), 0, wpol);
         };
         int i = 0;
         if (static_weights) {

@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8_kernel(const __grid_cons
     __shared__ volatile int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint64_t wpol = l2_evict_first_policy();       // weights are read once: first out of L2
     const int tile = blockIdx.x, rank = blockIdx.y, SK = gridDim.y;
     const int KB = p.kblocks;
     const int kb0 = (int)((long long)KB * rank / SK), kb1 = (int)((long long)KB * (rank + 1) / SK);
@@ -116,7 +117,7 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8_kernel(const __grid_cons
         auto load_raw = [&](int i) {
             const int s = i % STAGES;
             mbar_expect_tx(raw_full(s), kRawBytes);
-            tma_load_3d_hint(r_base + s * kRawBytes, &map_a, raw_full(s), 0, (kb0 + i) * (kBlockK / 8), tile * (kTileM / 16), l2_evict_first_policy());
+            tma_load_3d_hint(r_base + s * kRawBytes, &map_a, raw_full(s), 0, (kb0 + i) * (kBlockK / 8), tile * (kTileM / 16), wpol);
             ++raw_issued;
         };
         int ri = 0;      // next unit whose weights are requested

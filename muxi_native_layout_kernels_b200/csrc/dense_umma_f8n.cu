@@ -74,6 +74,7 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8n_kernel(const __grid_con
     __shared__ volatile int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint64_t wpol = l2_evict_first_policy();       // weights are read once: first out of L2
     const int tile = blockIdx.x, rank = blockIdx.y, SK = gridDim.y;
     const int KB = p.kblocks;
     const int kb0 = (int)((long long)KB * rank / SK), kb1 = (int)((long long)KB * (rank + 1) / SK);
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(192, 2) dense_umma_f8n_kernel(const __grid_con
         // ---- TMA producer ----
         auto load_a = [&](int i) {
             const int s = i % STAGES;
-            tma_load_3d_hint(base + s * kStageBytes, &map_a, full(s), 0, (kb0 + i) * (BK / 8), tile * (kTileM / 16), l2_evict_first_policy());
+            tma_load_3d_hint(base + s * kStageBytes, &map_a, full(s), 0, (kb0 + i) * (BK / 8), tile * (kTileM / 16), wpol);
         };
         auto load_x = [&](int i) {
             const int s = i % STAGES;

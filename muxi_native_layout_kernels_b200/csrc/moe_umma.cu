@@ -44,6 +44,7 @@ __global__ void __launch_bounds__(192, 2) moe_umma_kernel(const __grid_constant_
     __shared__ volatile int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint64_t wpol = l2_evict_first_policy();       // weights are read once: first out of L2
     const int tile = blockIdx.x, rank = blockIdx.y, SK = gridDim.y;
 
     // the work list comes from the alignment kernel earlier in the stream: nothing can start before it
@@ -99,10 +100,10 @@ __global__ void __launch_bounds__(192, 2) moe_umma_kernel(const __grid_constant_
             }
             if (abort_flag) break;
             mbar_expect_tx(full_bar(s), kStageBytes);
-            tma_load_4d_hint(a_addr(s, 0), &map_a, full_bar(s), 0, (kb0 + i) * (kBlockK / 8), a_tile * (kTileM / 16), 0, l2_evict_first_policy());
+            tma_load_4d_hint(a_addr(s, 0), &map_a, full_bar(s), 0, (kb0 + i) * (kBlockK / 8), a_tile * (kTileM / 16), 0, wpol);
             if constexpr (MODE == 1)
                 tma_load_4d_hint(a_addr(s, 1), &map_a, full_bar(s), 0, (kb0 + i) * (kBlockK / 8),
-                            (a_tile + p.up_tile_offset) * (kTileM / 16), 0, l2_evict_first_policy());
+                            (a_tile + p.up_tile_offset) * (kTileM / 16), 0, wpol);
             tma_load_2d(b_addr(s), &map_x, full_bar(s), (kb0 + i) * kBlockK, cpos0);
             ++issued;
         }
@@ -203,6 +204,7 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8_kernel(const __grid_consta
     __shared__ volatile int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint64_t wpol = l2_evict_first_policy();       // weights are read once: first out of L2
     const int tile = blockIdx.x, rank = blockIdx.y, SK = gridDim.y;
 
     pdl_wait();
@@ -268,10 +270,10 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8_kernel(const __grid_consta
             if (ri < nunits && (ri < STAGES || mbar_test_wait(raw_empty(ri % STAGES), ((ri / STAGES) - 1) & 1))) {
                 const int s = ri % STAGES;
                 mbar_expect_tx(raw_full(s), kStageBytes);
-                tma_load_3d_hint(base + s * kStageBytes, &map_a, raw_full(s), 0, (kb0 + ri) * (kBlockK / 8), a_tile * (kTileM / 16), l2_evict_first_policy());
+                tma_load_3d_hint(base + s * kStageBytes, &map_a, raw_full(s), 0, (kb0 + ri) * (kBlockK / 8), a_tile * (kTileM / 16), wpol);
                 if constexpr (MODE == 1)
                     tma_load_3d_hint(base + s * kStageBytes + kRawBytes, &map_a, raw_full(s), 0, (kb0 + ri) * (kBlockK / 8),
-                                (a_tile + p.up_tile_offset) * (kTileM / 16), l2_evict_first_policy());
+                                (a_tile + p.up_tile_offset) * (kTileM / 16), wpol);
                 ++raw_issued;
                 ++ri;
                 progressed = true;
