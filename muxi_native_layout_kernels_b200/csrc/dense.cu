@@ -233,6 +233,7 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const DenseParams p, con
 #pragma unroll
         for (int q = 0; q < NTOK; ++q) acc[r][q] = 0.f;
 
+    const uint64_t wpol = l2_policy_evict_first();
     uint4 ring[D][RG];
     if (!static_weights) {
         pdl_wait();
@@ -242,7 +243,7 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const DenseParams p, con
     for (int d = 0; d < D; ++d)
 #pragma unroll
         for (int r = 0; r < RG; ++r)
-            ring[d][r] = (d < nunits) ? ldg_stream16(ap[r] + (size_t)d * 512) : make_uint4(0, 0, 0, 0);
+            ring[d][r] = (d < nunits) ? ldg_stream16_pol(ap[r] + (size_t)d * 512, wpol) : make_uint4(0, 0, 0, 0);
     if (static_weights) {   // see dense_mma_kernel
         pdl_launch_dependents();
         pdl_wait();
@@ -274,7 +275,7 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const DenseParams p, con
                     acc[r][q] = s;
                 }
                 const int un = u + D;
-                ring[d][r] = (un < nunits) ? ldg_stream16(ap[r] + (size_t)un * 512) : make_uint4(0, 0, 0, 0);
+                ring[d][r] = (un < nunits) ? ldg_stream16_pol(ap[r] + (size_t)un * 512, wpol) : make_uint4(0, 0, 0, 0);
             }
         }
     }
