@@ -50,9 +50,10 @@ __global__ void __launch_bounds__(192, 2) moe_umma_kernel(const __grid_constant_
     // the work list comes from the alignment kernel earlier in the stream: nothing can start before it
     pdl_wait();
     pdl_launch_dependents();
+    // both loads go out together (the list holds an entry for every z of the grid, live or not)
     const int n_items = p.worklist[0].x;
-    if ((int)blockIdx.z >= n_items) return;             // uniform over the cluster (clusters span y only)
     const int4 item = p.worklist[1 + blockIdx.z];
+    if ((int)blockIdx.z >= n_items) return;             // uniform over the cluster (clusters span y only)
     const int expert = item.x, pos0 = item.y, nslots = item.z, cpos0 = item.w;
 
     const int KB = p.kblocks;
@@ -209,9 +210,10 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8_kernel(const __grid_consta
 
     pdl_wait();
     pdl_launch_dependents();
+    // both loads go out together (the list holds an entry for every z of the grid, live or not)
     const int n_items = p.worklist[0].x;
-    if ((int)blockIdx.z >= n_items) return;
     const int4 item = p.worklist[1 + blockIdx.z];
+    if ((int)blockIdx.z >= n_items) return;
     const int expert = item.x, pos0 = item.y, nslots = item.z, cpos0 = item.w;
 
     const int KB = p.kblocks;

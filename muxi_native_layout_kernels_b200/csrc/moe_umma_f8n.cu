@@ -62,9 +62,10 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
     // the work list and the split planes come from kernels earlier in the stream: nothing can start before them
     pdl_wait();
     pdl_launch_dependents();
+    // both loads go out together (the list holds an entry for every z of the grid, live or not)
     const int n_items = p.worklist[0].x;
-    if ((int)blockIdx.z >= n_items) return;             // uniform over the cluster (clusters span y only)
     const int4 item = p.worklist[1 + blockIdx.z];
+    if ((int)blockIdx.z >= n_items) return;             // uniform over the cluster (clusters span y only)
     const int expert = item.x, pos0 = item.y, nslots = item.z, cpos0 = item.w;
 
     const int KB = p.kblocks;
@@ -107,6 +108,14 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
                 tma_load_2d(base + early * kStageBytes + NA * kRawB + h * kXTile, &map_x, full(early),
                             ((kb0 + early) * (BK / 64) + h) * 128, cpos0);
         }
+    }
+    // inverse row scale of every accumulator column (lane l: columns l and l + 32), in flight across the prologue
+    constexpr int NCH = (NP + 31) / 32;
+    float my_inv[NCH];
+#pragma unroll
+    for (int h = 0; h < NCH; ++h) {
+        const int c = lane + 32 * h;
+        my_inv[h] = (warp >= 2 && c < NP && c < nslots) ? __ldg(p.inv_scale + cpos0 + c) : 0.f;
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
@@ -230,7 +239,7 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
                             if (c0 + i < nslots) {
-                                const float inv = __ldg(p.inv_scale + cpos0 + c0 + i);
+                                const float inv = __shfl_sync(0xFFFFFFFFu, my_inv[(c0 + i) >> 5], (c0 + i) & 31);
                                 const float gate = __uint_as_float(g[i]) * inv, up = __uint_as_float(u[i]) * inv;
                                 out[(size_t)(c0 + i) * p.rows] = __bfloat16_as_ushort(__float2bfloat16_rn(gate / (1.f + __expf(-gate)) * up));
                             }
@@ -251,7 +260,7 @@ __global__ void __launch_bounds__(192, 2) moe_umma_f8n_kernel(const __grid_const
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int c = (c0 + i) % NP;
-                    const float inv = c < nslots ? __ldg(p.inv_scale + cpos0 + c) : 0.f;
+                    const float inv = __shfl_sync(0xFFFFFFFFu, my_inv[c >> 5], c & 31);      // 0 past the item's slots
                     red[(c0 + i) * kTileM + lrow] = __uint_as_float(r[i]) * inv;
                 }
             }
@@ -301,9 +310,10 @@ __global__ void __launch_bounds__(192, (NP <= 16 && BK == 64) ? 6 : 2) moe_umma_
 
     pdl_wait();
     pdl_launch_dependents();
+    // both loads go out together (the list holds an entry for every z of the grid, live or not)
     const int n_items = p.worklist[0].x;
-    if ((int)blockIdx.z >= n_items) return;
     const int4 item = p.worklist[1 + blockIdx.z];
+    if ((int)blockIdx.z >= n_items) return;
     const int expert = item.x, pos0 = item.y, nslots = item.z, cpos0 = item.w;
     const int tiles_total = p.tiles_per_expert;
     const int tile0 = blockIdx.x * tiles_per_cta;
