@@ -353,7 +353,7 @@ int mlk_moe_unpermute_sum(const void* rows, const int32_t* pos, void* y, int64_t
  *   all peer-accessible (symmetric memory, IPC or cuMemMap'd allocations).  A flag block is
  *   mlk_ep_reduce_flag_bytes() bytes, zero before the first call and owned by these calls from then on.
  *   recv_dev: NULL, or the same kind of array for every rank's receive buffer of mlk_ep_reduce_recv_bytes(world, T,
- *   hidden) bytes (0 = share too large).  With it, shares of at most 256 Ki elements (decode batches) take a one-pass
+ *   hidden) bytes (0 = share too large).  With it, shares of at most min(256 Ki, 1 Mi / world) elements take a one-pass
  *   form without any barrier: every rank stores its share into every peer's receive buffer as (value, epoch) pairs and
  *   adds, in rank order, what it receives as the pairs land; every rank computes the whole output itself.
  * All ranks must issue the same sequence of calls (same T, hidden).  The launch is capturable in a CUDA graph.  Waits on

@@ -33,7 +33,13 @@ constexpr int kEpMaxWorld = 16;
 constexpr int kEpFlagBase = 64;         // words 0 / 1: epoch, finished-CTA counter
 constexpr unsigned kEpSpinLimit = 1u << 24;
 constexpr int kEpExpired = 0x0E000001;
-constexpr long long kEpLlMaxElems = 256 * 1024;     // shares up to this many elements take the one-pass form
+// Shares up to this many elements take the one-pass form; it moves world x the data of the two-exchange form, so the
+// bound shrinks with the rank count (256 K elements up to four ranks, 128 K at eight).
+constexpr long long kEpLlMaxElems = 256 * 1024;
+constexpr long long kEpLlMaxWorldElems = 1024 * 1024;
+inline bool ep_one_pass(int world, long long n) {
+    return world > 1 && n > 0 && n <= std::min(kEpLlMaxElems, kEpLlMaxWorldElems / world);
+}
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
     unsigned v;
@@ -202,7 +208,7 @@ long long ep_reduce_flag_bytes() { return (long long)(kEpFlagBase + 2 * kEpGrid 
 
 long long ep_reduce_recv_bytes(int world, long long T, int H) {
     const long long n = T * H;
-    return (n > 0 && n <= kEpLlMaxElems) ? 2LL * world * n * 8 : 0;
+    return ep_one_pass(world, n) ? 2LL * world * n * 8 : 0;
 }
 
 int launch_ep_reduce(const void* const* shares_dev, void* const* outs_dev, void* const* flags_dev, void* const* recv_dev,
@@ -225,7 +231,7 @@ int launch_ep_reduce(const void* const* shares_dev, void* const* outs_dev, void*
     const long long n = T * H;
     const int wl = option(kOptWaitLog2);
     const unsigned spin = (wl >= 4 && wl <= 30) ? (1u << wl) : kEpSpinLimit;      // poll budget of the waits on peers
-    if (recv_dev != nullptr && n <= kEpLlMaxElems && world > 1) {
+    if (recv_dev != nullptr && ep_one_pass(world, n)) {
         // small share: the one-pass form
         auto rv = reinterpret_cast<uint2* const*>(recv_dev);
         cfg.gridDim = dim3((unsigned)std::min<long long>(kEpGrid, (n + 255) / 256));
