@@ -232,3 +232,19 @@ def test_moe_table_lookup_rules():
     assert lookup_moe_args(*ep, 4, allow_decode=False)[1] < 300
     assert lookup_moe_args(*ep, 4, allow_decode=False) == lookup_moe_args(*ep, 16)
     assert lookup_moe_args(7, 3, 640, 320, False, 5) is None
+
+
+def test_ep_reduce_buffer_sizes_follow_the_one_pass_bound():
+    """mlk_ep_reduce_recv_bytes: two sets of (value, epoch) pairs from every rank for shares that take the one-pass
+    form, 0 for shares past its bound -- min(256 Ki, 1 Mi / world) elements, since that form moves world x the data
+    of the two-exchange form -- and for a single rank."""
+    from muxi_native_layout_kernels_b200._lib import lib
+    assert lib.mlk_ep_reduce_flag_bytes() > 0
+    n = 64 * 4096                                   # 256 Ki elements
+    for world in (2, 4):
+        assert lib.mlk_ep_reduce_recv_bytes(world, 64, 4096) == 2 * world * n * 8
+        assert lib.mlk_ep_reduce_recv_bytes(world, 65, 4096) == 0
+    assert lib.mlk_ep_reduce_recv_bytes(8, 64, 4096) == 0
+    assert lib.mlk_ep_reduce_recv_bytes(8, 32, 4096) == 2 * 8 * (n // 2) * 8
+    assert lib.mlk_ep_reduce_recv_bytes(8, 0, 4096) == 0
+    assert lib.mlk_ep_reduce_recv_bytes(1, 8, 4096) == 0
