@@ -192,6 +192,18 @@ def time_cpu_moe():
     return out
 
 
+def step_config(world: int) -> dict:
+    """The workload both arms are timed on (their JSON lines carry the same `config`): the 21-case narrow-GEMM grid,
+    weights sharded over their rows at N > 1, with the note on what sits between two uses of one weight matrix."""
+    per_rank_weights = sum(N // world * K * 2 for (N, K) in SHAPES)
+    between = per_rank_weights - max(N // world * K * 2 for (N, K) in SHAPES)
+    l2_note = (f"consecutive launches use different weight matrices; {between / 1e6:.0f} MB of other weights stream between "
+               f"two uses of one matrix (L2 is 126 MB)" + ("" if between > 126e6 else
+               ": at this shard size the weights are partly L2-resident, so the value is not a pure HBM figure"))
+    return {"workload": "narrow_gemm_bf16_llama8b", "tokens": TOKENS, "shapes": SHAPES, "variant": "gemm_layoutA",
+            "launches_per_step": len(case_order()), "sharding": f"rows/{world}", "static_weights": True, "l2": l2_note}
+
+
 def run_reference(args):
     rank, world, _ = dist_env()
     if rank != 0:
@@ -201,7 +213,9 @@ def run_reference(args):
         "impl": "reference", "metric": "narrow_gemm_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "narrow_gemm_bf16_llama8b", "tokens": TOKENS, "shapes": SHAPES, "variant": "torch fp32 matmul on host"},
+        "config": step_config(world),
+        "implementation": "the reference's math for this path (fp32 matmul of the bf16 operands, rounded once) in torch on all "
+                          "host threads, unsharded, on rank 0",
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
                          "sample": f"{max(1, args.steps)} full passes over the 21-case grid (whole workload, all host threads)"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -427,27 +441,19 @@ def run_ours(args):
         value = step_bytes_total / (ms_step * 1e-3) / 1e9
         e2e_value = step_bytes_total / (ms_e2e / args.steps * 1e-3) / 1e9
         per_rank_bytes = sum(algorithmic_bytes(n, N // world, K) for (n, N, K) in order)
-        per_rank_weights = sum(N // world * K * 2 for (N, K) in SHAPES)
-        between = per_rank_weights - max(N // world * K * 2 for (N, K) in SHAPES)
-        l2_note = (f"consecutive launches use different weight matrices; {between / 1e6:.0f} MB of other weights stream between "
-                   f"two uses of one matrix (L2 is 126 MB)" + ("" if between > 126e6 else
-                   ": at this shard size the weights are partly L2-resident, so the value is not a pure HBM figure"))
         achieved = per_rank_bytes / (ms_step * 1e-3) / 1e9
         line = {
             "metric": "narrow_gemm_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "narrow_gemm_bf16_llama8b", "tokens": TOKENS, "shapes": SHAPES, "variant": "gemm_layoutA",
-                       "launches_per_step": len(order), "sharding": f"rows/{world}",
-                       "static_weights": True,
-                       "l2": l2_note,
-                       "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS},
+            "config": step_config(world),
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "GB/s", "mode": "CUDA graph of one step, a three-stage pipeline: the activations host -> device in two copies on a copy stream, the 21 public API calls on the compute stream as their inputs arrive (token counts in the order 1, 2, 4, 64, 32, 16, 8), every result device -> host on a second copy stream; the step ends when the last result is in host memory",
                     "eager_value": step_bytes_total / (ms_e2e_eager / args.steps * 1e-3) / 1e9,
                     "h2d_bytes_per_step": host_in.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2},
             "gpu_launches": len(order) * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                          "traffic": NCU_TRAFFIC_RATIO * per_rank_bytes / len(order),
                          "traffic_source": "average bytes per launch = algorithmic bytes x 1.03, the dram read+write / "
                                            "algorithmic ratio ncu measured on the dense kernels (profiles/dense_kernels_bf16.md)",

@@ -248,3 +248,26 @@ def test_ep_reduce_buffer_sizes_follow_the_one_pass_bound():
     assert lib.mlk_ep_reduce_recv_bytes(8, 32, 4096) == 2 * 8 * (n // 2) * 8
     assert lib.mlk_ep_reduce_recv_bytes(8, 0, 4096) == 0
     assert lib.mlk_ep_reduce_recv_bytes(1, 8, 4096) == 0
+
+
+def test_bench_arms_share_one_config():
+    """bench.py: the line of the library's arm and the line of the reference arm carry the same `config` (one function
+    builds it from the rank count alone), and the reference arm prints it."""
+    import importlib.util
+    import json
+    import subprocess
+    import sys
+    spec = importlib.util.spec_from_file_location("bench_module", ROOT / "bench.py")
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    c1, c8 = bench.step_config(1), bench.step_config(8)
+    assert c1["launches_per_step"] == 21 and c1["sharding"] == "rows/1" and c8["sharding"] == "rows/8"
+    assert "partly L2-resident" in c8["l2"] and "partly L2-resident" not in c1["l2"]
+    src = (ROOT / "bench.py").read_text()
+    assert src.count('"config": step_config(world)') == 2
+    out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["config"] == json.loads(json.dumps(c1))
+    assert line["cpu_baseline"]["kind"] == "port" and line["e2e"]["h2d_bytes_per_step"] == 0
